@@ -1,0 +1,122 @@
+"""Generate the golden fixtures in this folder by running the UNMODIFIED reference.
+
+Usage (only where the reference checkout exists; the fixtures themselves are committed):
+
+    PYTHONDONTWRITEBYTECODE=1 python tests/golden/make_golden.py --reference <path to BiBo checkout>
+
+The script imports ``src.modeling.ffn.moe.BiBoMoELayer`` from the reference checkout, copies
+seeded weights into it, runs forward (and backward) on CPU and stores outputs and gradients (inputs are
+regenerated from the seed by ``oracle.moe_oracle.make_inputs``).  ``tests/test_oracle.py`` replays the files through ``oracle/moe_oracle.py``; the GPU
+parity tests replay them through the CUDA path.
+"""
+import argparse
+import os
+import pathlib
+import sys
+
+import torch
+
+HERE = pathlib.Path(__file__).resolve().parent
+sys.path.insert(0, str(HERE.parents[1]))
+from oracle import moe_oracle as orc  # noqa: E402  (input generator only)
+
+
+def KEEP_EXPERTS(n_glu):
+    return [0, n_glu // 2, n_glu - 1]
+
+
+def upstream_grad(n_tokens, hidden, seed):
+    """The seeded dOut every backward fixture uses."""
+    return torch.randn(1, n_tokens, hidden, generator=torch.Generator().manual_seed(seed * 1000 + 77))
+
+
+def grad_digest(g, seed):
+    """[E, 2]: per-expert L2 norm and inner product with a seeded N(0,1) probe of g's shape."""
+    probe = torch.randn(g.shape, generator=torch.Generator().manual_seed(seed * 1000 + 99))
+    flat, pf = g.reshape(g.shape[0], -1).double(), probe.reshape(g.shape[0], -1).double()
+    return torch.stack([flat.norm(dim=1), (flat * pf).sum(1)], dim=1)
+
+
+def build_layer(ref_root, hidden, inter, n_experts, top_k, pairs, norm, dtype):
+    if ref_root not in sys.path:
+        sys.path.insert(0, ref_root)
+    from src.configuration_bibo import BiBoConfig
+    from src.modeling.ffn.moe import BiBoMoELayer
+    cfg = BiBoConfig(vocab_size=512, hidden_size=hidden, num_hidden_layers=4, num_attention_heads=4,
+                     num_key_value_heads=2, intermediate_size=inter, moe_intermediate_size=inter,
+                     num_routed_experts=n_experts, special_expert_pairs=pairs,
+                     num_experts_per_tok=top_k, norm_topk_prob=norm, bias_update_factor=0.4)
+    layer = BiBoMoELayer(cfg).eval()
+    return layer.to(dtype)
+
+
+def run_case(ref_root, name, n_tokens, hidden, inter, n_experts, top_k, pairs=0, norm="sum",
+             bias_mode="uniform", theta_std=0.5, seed=1, dtype=torch.float32, backward=True,
+             keep_rows=None):
+    n_glu = n_experts - 2 * pairs
+    inp = orc.make_inputs(n_tokens, hidden, inter, n_experts, seed=seed, bias_mode=bias_mode,
+                          theta_std=theta_std)
+    layer = build_layer(ref_root, hidden, inter, n_experts, top_k, pairs, norm, dtype)
+    with torch.no_grad():
+        layer.gate.gate_proj.weight.copy_(inp["w_router"])
+        layer.gate.bias.copy_(inp["bias"])
+        layer.experts.gate_up_proj.copy_(inp["gate_up_proj"][:n_glu])
+        layer.experts.down_proj.copy_(inp["down_proj"][:n_glu])
+        layer.experts.radial_theta.copy_(inp["radial_theta"][:n_glu])
+    x = inp["x"].to(dtype).reshape(1, n_tokens, hidden).clone().requires_grad_(backward)
+    logits = layer.gate.router_logits(x.detach())
+    idx, w = layer.gate(x)
+    out = layer(x)
+    rec = dict(name=name, n_tokens=n_tokens, hidden=hidden, inter=inter, n_experts=n_experts,
+               n_glu=n_glu, pairs=pairs, top_k=top_k, norm=norm, seed=seed, bias_mode=bias_mode,
+               theta_std=theta_std, dtype=str(dtype).split(".")[-1])
+    order = idx[0].argsort(-1)
+    rec["idx_sorted"] = idx[0].gather(-1, order).to(torch.int16)
+    rec["w_sorted"] = w[0].detach().gather(-1, order)
+    rec["counts"] = torch.bincount(idx.flatten(), minlength=n_experts).to(torch.int32)
+    rows = slice(None) if keep_rows is None else slice(0, n_tokens, n_tokens // keep_rows)
+    rec["rows_step"] = 1 if keep_rows is None else n_tokens // keep_rows
+    rec["logits"] = logits.detach()[rows].clone()
+    rec["out"] = out.detach()[0][rows].clone()
+    if backward:
+        dout = upstream_grad(n_tokens, hidden, seed).to(dtype)
+        (out * dout).sum().backward()
+        rec["dx"] = x.grad[0].clone()
+        rec["d_radial_theta"] = layer.experts.radial_theta.grad.clone()
+        rec["d_w_router"] = layer.gate.gate_proj.weight.grad.clone()
+        # expert-weight gradients are large: keep three experts whole plus, for every expert, the
+        # L2 norm and the inner product with a seeded probe tensor (see grad_digest)
+        for key, g in (("d_gate_up_proj", layer.experts.gate_up_proj.grad),
+                       ("d_down_proj", layer.experts.down_proj.grad)):
+            rec[key + "_digest"] = grad_digest(g.float(), seed)
+            rec[key + "_experts"] = KEEP_EXPERTS(n_glu)
+            rec[key + "_sel"] = g[KEEP_EXPERTS(n_glu)].clone()
+    torch.save(rec, HERE / f"{name}.pt")
+    sz = os.path.getsize(HERE / f"{name}.pt") / 1024
+    print(f"{name}: out abs-mean {out.abs().mean():.4e}  counts min/max "
+          f"{int(rec['counts'].min())}/{int(rec['counts'].max())}  {sz:.0f} KiB")
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--reference", required=True)
+    a = ap.parse_args()
+    torch.set_num_threads(8)
+    r = a.reference
+    # the reference's own test geometry: hidden 64, 8 experts, top-2, intermediate 96
+    run_case(r, "tiny_glu", 16, 64, 96, 8, 2, pairs=0, seed=1)
+    run_case(r, "tiny_specials", 16, 64, 96, 8, 2, pairs=1, seed=2)
+    run_case(r, "tiny_softmax", 16, 64, 96, 8, 2, pairs=0, norm="softmax", seed=3)
+    run_case(r, "tiny_raw", 16, 64, 96, 8, 2, pairs=0, norm=False, seed=4)
+    # 64 experts / top-6 at a size the tensor-core kernels accept (hidden, intermediate % 64 == 0)
+    run_case(r, "e64_k6_fp32", 320, 128, 64, 64, 6, seed=5)
+    run_case(r, "e64_k6_bf16", 320, 128, 64, 64, 6, seed=5, dtype=torch.bfloat16)
+    # benchmark configuration 1 (2048 tokens, hidden 512, intermediate 128, bias 0, theta 0,
+    # seed 0); every 32nd output row is kept.  Inputs of every case are regenerated from the seed
+    # by oracle.moe_oracle.make_inputs and are not stored.
+    run_case(r, "config1", 2048, 512, 128, 64, 6, bias_mode="zero", theta_std=0.0, seed=0,
+             backward=False, keep_rows=64)
+
+
+if __name__ == "__main__":
+    main()
