@@ -1,0 +1,324 @@
+#!/usr/bin/env python
+"""Benchmark of the BiBo sparse-MoE feed-forward block (forward) on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload c4|c2|c3|c3a] [--impl reference]
+
+One "step" is one forward pass of the MoE layer over one batch of synthetic tokens.  Prints ONE JSON
+line (rank 0).  `value` is tokens/s of the whole job with the batch already resident in HBM;
+`e2e` is the same metric through the host-buffer C-ABI call (pinned host input copied to the
+device and the result copied back inside the timed region); `roofline` describes the dominant
+kernel, timed with CUDA events recorded around each kernel of the chain inside the timed steps;
+`cpu_baseline` is the CPU oracle (a restatement of the reference's eager per-expert loop) timed on
+this machine's host cores on a bounded sample of the same workload.
+
+Workloads (synthetic, seeded; shapes and distributions of the benchmark configurations):
+  c4  32768 tokens per GPU, hidden 2048, 64 experts, top-6, intermediate 512, bias 0   (default)
+  c2  16384 tokens, hidden 1024, intermediate 256, bias ~ U(-0.01, 0.01)
+  c3  65536 tokens, hidden 2048, intermediate 512, bias = log Zipf(1.1) profile (literal)
+  c3a same with the bias scaled by 0.07 (per-expert counts span about 20x)
+"""
+import argparse
+import json
+import os
+import pathlib
+import sys
+import threading
+import time
+
+import torch
+
+ROOT = pathlib.Path(__file__).resolve().parent
+if str(ROOT) not in sys.path:
+    sys.path.insert(0, str(ROOT))
+
+WORKLOADS = {
+    "c4": dict(n_tokens=32768, hidden=2048, inter=512, bias="zero", zipf_alpha=0.0),
+    "c2": dict(n_tokens=16384, hidden=1024, inter=256, bias="uniform", zipf_alpha=0.0),
+    "c3": dict(n_tokens=65536, hidden=2048, inter=512, bias="zipf", zipf_alpha=1.0),
+    "c3a": dict(n_tokens=65536, hidden=2048, inter=512, bias="zipf", zipf_alpha=0.07),
+}
+N_EXPERTS, TOP_K = 64, 6
+METRIC, UNIT = "moe_layer_fwd_tokens_per_s", "tokens/s"
+
+
+def peaks():
+    p = ROOT / "MEASURED_PEAKS.json"
+    if p.exists():
+        d = json.loads(p.read_text())
+        return dict(hbm=float(d["hbm_gbs"]), tf=float(d["bf16_tflops"]), tf_sus=float(d.get("bf16_tflops_sustained", 0)),
+                    src="measured")
+    return dict(hbm=6650.0, tf=1590.0, tf_sus=1400.0, src="fallback")
+
+
+def synth(wl, device, seed, dtype=torch.bfloat16):
+    """Seeded synthetic tensors generated on `device`: x ~ N(0,1); weights ~ N(0,0.02); theta ~ N(0,0.5)."""
+    g = torch.Generator(device=device).manual_seed(seed)
+    n, h, i = wl["n_tokens"], wl["hidden"], wl["inter"]
+    rn = lambda *s: torch.randn(*s, generator=g, device=device, dtype=torch.float32)
+    t = dict(x=rn(n, h).to(dtype), gate_up_proj=(rn(N_EXPERTS, 2 * i, h) * 0.02).to(dtype),
+             down_proj=(rn(N_EXPERTS, h, i) * 0.02).to(dtype), w_router=(rn(N_EXPERTS, h) * 0.02).to(dtype),
+             radial_theta=rn(N_EXPERTS) * 0.5)
+    if wl["bias"] == "zero":
+        t["bias"] = torch.zeros(N_EXPERTS, device=device)
+    elif wl["bias"] == "uniform":
+        t["bias"] = (torch.rand(N_EXPERTS, generator=g, device=device) * 2 - 1) * 0.01
+    else:
+        prof = 1.0 / torch.arange(1, N_EXPERTS + 1, dtype=torch.float64) ** 1.1
+        t["bias"] = (wl["zipf_alpha"] * torch.log(prof / prof.sum())).float().to(device)
+    return t
+
+
+class ClockSampler(threading.Thread):
+    """Samples SM clock and throttle reasons through NVML while the timed region runs (read-only)."""
+    BITS = {0x8: "hw_slowdown", 0x40: "hw_thermal_slowdown", 0x20: "sw_thermal_slowdown", 0x4: "sw_power_cap"}
+
+    def __init__(self, index):
+        super().__init__(daemon=True)
+        self.index, self.samples, self.reasons, self.max_mhz, self._stop_evt = index, [], set(), None, threading.Event()
+        try:
+            import pynvml
+            pynvml.nvmlInit()
+            self.nv = pynvml
+            self.h = pynvml.nvmlDeviceGetHandleByIndex(index)
+            self.max_mhz = pynvml.nvmlDeviceGetMaxClockInfo(self.h, pynvml.NVML_CLOCK_SM)
+        except Exception:
+            self.nv = None
+
+    def run(self):
+        while self.nv and not self._stop_evt.is_set():
+            try:
+                self.samples.append(self.nv.nvmlDeviceGetClockInfo(self.h, self.nv.NVML_CLOCK_SM))
+                r = self.nv.nvmlDeviceGetCurrentClocksEventReasons(self.h)
+                self.reasons |= {n for b, n in self.BITS.items() if r & b}
+            except Exception:
+                pass
+            time.sleep(0.02)
+
+    def stop(self):
+        self._stop_evt.set()
+        if self.is_alive():
+            self.join()
+        s = sorted(self.samples)
+        return {"sm_mhz": s[len(s) // 2] if s else None, "sm_max_mhz": self.max_mhz, "reasons": sorted(self.reasons),
+                "samples": len(s)}
+
+
+def cpu_oracle_rate(wl, seconds_cap=20.0, sample_tokens=2048, threads=None):
+    """tokens/s of the CPU oracle (fp32, all host threads) on a bounded sample of the workload."""
+    from oracle import moe_oracle as orc
+    threads = threads or os.cpu_count() or 1
+    torch.set_num_threads(threads)
+    bias_mode = {"zero": "zero", "uniform": "uniform", "zipf": "zipf"}[wl["bias"]]
+    inp = orc.make_inputs(sample_tokens, wl["hidden"], wl["inter"], N_EXPERTS, seed=0, bias_mode=bias_mode,
+                          theta_std=0.5, zipf_alpha=wl["zipf_alpha"] or 1.0)
+    run = lambda: orc.moe_forward(inp["x"], inp["w_router"], inp["bias"], inp["gate_up_proj"], inp["down_proj"],
+                                  inp["radial_theta"], TOP_K)
+    with torch.no_grad():
+        run()
+        t0, reps = time.perf_counter(), 0
+        while True:
+            run()
+            reps += 1
+            dt = time.perf_counter() - t0
+            if dt > seconds_cap or (reps >= 3 and dt > 10.0):
+                break
+    return dict(value=sample_tokens * reps / dt, unit=UNIT, cores=torch.get_num_threads(), kind="port",
+                sample=f"{reps} passes of {sample_tokens} tokens (same hidden/intermediate/experts/top-k, fp32) "
+                       f"in {dt:.1f} s; CPU oracle = restatement of the reference's eager per-expert loop")
+
+
+def run_reference(args, wl, rank, world):
+    """The reference arm: the reference's CPU algorithm (oracle port) on host cores, rank 0 only."""
+    if rank != 0:
+        return
+    from oracle import moe_oracle as orc
+    threads = os.cpu_count() or 1
+    torch.set_num_threads(threads)
+    sample = 2048
+    inp = orc.make_inputs(sample, wl["hidden"], wl["inter"], N_EXPERTS, seed=0, bias_mode=wl["bias"], theta_std=0.5,
+                          zipf_alpha=wl["zipf_alpha"] or 1.0)
+    run = lambda: orc.moe_forward(inp["x"], inp["w_router"], inp["bias"], inp["gate_up_proj"], inp["down_proj"],
+                                  inp["radial_theta"], TOP_K)
+    with torch.no_grad():
+        for _ in range(args.warmup):
+            run()
+        t0 = time.perf_counter()
+        for _ in range(args.steps):
+            run()
+        dt = time.perf_counter() - t0
+    val = sample * args.steps / dt
+    desc = (f"each step = one fp32 forward of {sample} tokens of the workload through the CPU oracle "
+            f"(restatement of the reference's eager per-expert loop; the reference itself is Python and is "
+            f"not present on this machine)")
+    print(json.dumps({
+        "impl": "reference", "metric": METRIC, "value": val, "unit": UNIT, "n_gpus": args.gpus, "steps": args.steps,
+        "warmup": args.warmup, "ms_per_step": dt / args.steps * 1e3, "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": workload_config(args, wl, world),
+        "cpu_baseline": {"value": val, "unit": UNIT, "cores": torch.get_num_threads(), "kind": "port", "sample": desc},
+        "e2e": {"value": val, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0}))
+
+
+def workload_config(args, wl, world):
+    return {"workload": f"{args.workload}: MoE layer forward, {wl['n_tokens']} tokens per GPU, hidden {wl['hidden']}, "
+                        f"{N_EXPERTS} experts, top-{TOP_K}, intermediate {wl['inter']}, router bias {wl['bias']}"
+                        + (f" (alpha {wl['zipf_alpha']})" if wl["bias"] == "zipf" else ""),
+            "tokens_per_gpu": wl["n_tokens"], "global_tokens": wl["n_tokens"] * world,
+            "parallelism": "single GPU" if world == 1 else f"expert-parallel ep{world} (tokens data-parallel)",
+            "l2": "per-step working set (activations + expert weights + intermediates) exceeds the 126 MB L2"}
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--workload", default="c4", choices=sorted(WORKLOADS))
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+    wl = WORKLOADS[args.workload]
+    rank, world = int(os.environ.get("RANK", 0)), int(os.environ.get("WORLD_SIZE", 1))
+    local = int(os.environ.get("LOCAL_RANK", 0))
+    if args.impl == "reference":
+        return run_reference(args, wl, rank, world)
+    if args.warmup < 3:
+        args.warmup = 3
+
+    import torch.distributed as dist
+    from bibo_b200 import functional as Fn
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    t = synth(wl, dev, seed=1234 + rank)
+    n, h, i = wl["n_tokens"], wl["hidden"], wl["inter"]
+    dtype = torch.bfloat16
+
+    if world > 1:
+        from bibo_b200 import ep
+        runner = ep.ExpertParallelMoE(t, TOP_K, dist.group.WORLD)
+        step = lambda: runner.forward(t["x"])
+        ws = None
+    else:
+        geo = Fn.Geometry(n, h, i, N_EXPERTS, N_EXPERTS, 0, TOP_K, dtype)
+        ws = Fn.MoEWorkspace(geo, dev, keep_gate_up=False)
+        out = torch.empty_like(t["x"])
+        step = lambda: Fn.moe_forward(t["x"], t["w_router"], t["bias"], t["gate_up_proj"], t["down_proj"],
+                                      t["radial_theta"], TOP_K, "sum", ws=ws, out=out)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for _ in range(args.warmup):
+        step()
+    barrier()
+    # ---- timed region: K steps, events on the launching stream, per-kernel events inside ------------
+    stage_sets = []
+    if ws is not None:   # events are created (first record) before the timed region
+        stage_sets = [[torch.cuda.Event(enable_timing=True) for _ in range(7)] for _ in range(args.steps)]
+        for evs in stage_sets:
+            for e in evs:
+                e.record()
+    sampler = ClockSampler(local)
+    sampler.start()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    launches0 = Fn.launch_count()
+    barrier()
+    e0.record()
+    for k in range(args.steps):
+        if ws is not None:
+            ws.stage_events = stage_sets[k]
+        step()
+    e1.record()
+    barrier()
+    clocks = sampler.stop()
+    launches = Fn.launch_count() - launches0
+    ms_total = torch.tensor([e0.elapsed_time(e1)], device=dev)
+    if world > 1:
+        dist.all_reduce(ms_total, op=dist.ReduceOp.MAX)
+    ms_step = float(ms_total) / args.steps
+    value = n * world / (ms_step * 1e-3)
+
+    # ---- end-to-end: host buffers through the C-ABI host entry (N=1) / the public forward (N>1) ------
+    x_host = t["x"].cpu().pin_memory()
+    out_host = torch.empty_like(x_host).pin_memory()
+    x_dev, out_dev = torch.empty_like(t["x"]), torch.empty_like(t["x"])
+    if world > 1:
+        def e2e_step():
+            x_dev.copy_(x_host, non_blocking=True)
+            out_host.copy_(runner.forward(x_dev), non_blocking=True)
+            torch.cuda.synchronize()
+    else:
+        if ws is not None:
+            ws.stage_events = None
+        e2e_step = lambda: Fn.moe_forward_host(x_host, out_host, x_dev, out_dev, t["w_router"], t["bias"],
+                                               t["gate_up_proj"], t["down_proj"], t["radial_theta"], TOP_K, "sum", ws=ws)
+    for _ in range(3):
+        e2e_step()
+    barrier()
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        e2e_step()
+    barrier()
+    e2e_s = torch.tensor([time.perf_counter() - t0], device=dev)
+    if world > 1:
+        dist.all_reduce(e2e_s, op=dist.ReduceOp.MAX)
+    e2e_val = n * world * args.steps / float(e2e_s)
+
+    if rank != 0:
+        if world > 1:
+            dist.destroy_process_group()
+        return
+
+    pk = peaks()
+    S = n * TOP_K
+    stages, roof = {}, None
+    if stage_sets:
+        names = Fn.MoEWorkspace.STAGES
+        ms = {nm: sum(ev[k].elapsed_time(ev[k + 1]) for ev in stage_sets) / len(stage_sets) for k, nm in enumerate(names)}
+        eb = 2  # bf16 bytes
+        alg = {  # algorithmic work per launch: (flops, bytes)
+            "router": (2.0 * n * h * N_EXPERTS, n * (eb * h + 8 * TOP_K) + eb * N_EXPERTS * h),
+            "plan": (0.0, 0.0),
+            "permute": (0.0, n * (eb * h + eb * TOP_K * h + 8 * TOP_K)),
+            "gemm1_radial": (4.0 * S * h * i, eb * (S * h + S * i + 2 * N_EXPERTS * h * i)),
+            "gemm2": (2.0 * S * h * i, eb * (S * i + S * h + N_EXPERTS * h * i)),
+            "combine": (0.0, n * (eb * TOP_K * h + eb * h + 8 * TOP_K)),
+        }
+        for nm in names:
+            fl, by = alg[nm]
+            tensor = nm.startswith("gemm")
+            ach = (fl / (ms[nm] * 1e-3) / 1e12) if tensor else (by / (ms[nm] * 1e-3) / 1e9)
+            peak = pk["tf"] if tensor else pk["hbm"]
+            stages[nm] = {"ms": round(ms[nm], 4), "bound": "tensor" if tensor else "hbm", "achieved": round(ach, 2),
+                          "unit": "TFLOP/s" if tensor else "GB/s", "frac": round(ach / peak, 4) if nm != "plan" else None}
+        top = max(names, key=lambda nm: ms[nm])
+        ncu_traffic = {"gemm1_radial": None, "gemm2": None}
+        roof = {"kernel": top, "bound": stages[top]["bound"], "achieved": stages[top]["achieved"],
+                "peak": pk["tf"] if stages[top]["bound"] == "tensor" else pk["hbm"], "unit": stages[top]["unit"],
+                "frac": stages[top]["frac"], "traffic": ncu_traffic.get(top),
+                "peak_source": f"of {pk['src']} (burst figure)", "ms_per_launch": stages[top]["ms"]}
+    layer_flops = 36.0 * n * h * i + 2.0 * n * h * N_EXPERTS
+    line = {
+        "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": ms_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
+        "data": "synthetic", "config": workload_config(args, wl, world),
+        "layer_tflops": round(layer_flops * world / (ms_step * 1e-3) / 1e12, 2),
+        "layer_frac_of_bf16_peak": round(layer_flops / (ms_step * 1e-3) / 1e12 / pk["tf"], 4),
+        "roofline": roof, "stages": stages, "clocks": clocks, "gpu_launches": launches,
+        "e2e": {"value": e2e_val, "unit": UNIT, "h2d_bytes_per_step": x_host.numel() * 2 * world,
+                "d2h_bytes_per_step": out_host.numel() * 2 * world},
+    }
+    if world == 1 and not args.no_cpu_baseline:
+        line["cpu_baseline"] = cpu_oracle_rate(wl)
+    print(json.dumps(line))
+    if world > 1:
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

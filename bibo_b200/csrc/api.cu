@@ -1,0 +1,141 @@
+// extern "C" entry points that dispatch K3/K4 and chain the whole block.
+#include "common.cuh"
+
+namespace bibo {
+// gemm_simt.cu
+int gemm_simt_launch(const void* A, const void* B, void* C, const int32_t* plan, int64_t n_tokens,
+                     int n_experts, int n_glu, int top_k, int k_dim, int n_out, int dtype,
+                     cudaStream_t st);
+int radial_rows_launch(const void* gate_up, const float* theta, const int32_t* plan,
+                       int64_t n_tokens, int n_experts, int n_glu, int top_k, int inter, int dtype,
+                       void* h, float* rnorm_out, cudaStream_t st);
+// gemm_tc.cu
+int gemm1_tc_supported(int hidden, int inter, int dtype);
+int gemm1_tc_launch(const void* xp, const void* gate_up_proj, const float* theta, const int32_t* plan,
+                    int64_t n_tokens, int hidden, int inter, int n_experts, int n_glu, int top_k,
+                    void* h, void* gate_up_out, float* rnorm_out, cudaStream_t st);
+int gemm2_tc_supported(int hidden, int inter, int dtype);
+int gemm2_tc_launch(const void* h, const void* down_proj, const int32_t* plan, int64_t n_tokens,
+                    int hidden, int inter, int n_experts, int n_glu, int top_k, void* y,
+                    cudaStream_t st);
+}  // namespace bibo
+
+using namespace bibo;
+
+extern "C" int bibo_moe_version(void) { return 100; }
+extern "C" const char* bibo_moe_last_error_string(void) { return err_buf(); }
+extern "C" int64_t bibo_moe_launch_count(void) { return launch_counter().load(); }
+
+static int check_common(const char* who, int64_t n_tokens, int hidden, int inter, int n_experts,
+                        int n_glu, int top_k, int dtype) {
+  if (dtype != BIBO_F32 && dtype != BIBO_BF16) return fail(BIBO_ERR_ARG, "%s: dtype=%d", who, dtype);
+  if (n_tokens <= 0 || hidden < 1 || inter < 1)
+    return fail(BIBO_ERR_ARG, "%s: n_tokens=%lld hidden=%d inter=%d", who, (long long)n_tokens, hidden, inter);
+  if (n_experts < 1 || n_experts > BIBO_MAX_EXPERTS || n_glu < 0 || n_glu > n_experts || top_k < 1 ||
+      top_k > BIBO_MAX_TOP_K)
+    return fail(BIBO_ERR_UNSUPPORTED, "%s: n_experts=%d n_glu=%d top_k=%d", who, n_experts, n_glu, top_k);
+  return BIBO_OK;
+}
+
+extern "C" int bibo_moe_gemm1_radial_fwd(const void* xp, const void* gate_up_proj, const float* theta,
+                                         const int32_t* plan, int64_t n_tokens, int hidden, int inter,
+                                         int n_experts, int n_glu, int top_k, int dtype, void* h,
+                                         void* gate_up_out, float* rnorm_out, void* stream) {
+  int rc = check_common("gemm1_radial_fwd", n_tokens, hidden, inter, n_experts, n_glu, top_k, dtype);
+  if (rc) return rc;
+  if (n_glu == 0) return BIBO_OK;
+  if (!xp || !gate_up_proj || !theta || !plan || !h) return fail(BIBO_ERR_ARG, "gemm1_radial_fwd: null pointer");
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (gemm1_tc_supported(hidden, inter, dtype) && aligned16(xp) && aligned16(gate_up_proj) && aligned16(h) &&
+      aligned16(gate_up_out))
+    return gemm1_tc_launch(xp, gate_up_proj, theta, plan, n_tokens, hidden, inter, n_experts, n_glu, top_k,
+                           h, gate_up_out, rnorm_out, st);
+  if (!gate_up_out)
+    return fail(BIBO_ERR_ARG,
+                "gemm1_radial_fwd: this dtype/shape runs the two-kernel path and needs the gate_up buffer");
+  rc = gemm_simt_launch(xp, gate_up_proj, gate_up_out, plan, n_tokens, n_experts, n_glu, top_k, hidden,
+                        2 * inter, dtype, st);
+  if (rc) return rc;
+  return radial_rows_launch(gate_up_out, theta, plan, n_tokens, n_experts, n_glu, top_k, inter, dtype, h,
+                            rnorm_out, st);
+}
+
+extern "C" int bibo_moe_gemm2_fwd(const void* h, const void* down_proj, const int32_t* plan,
+                                  int64_t n_tokens, int hidden, int inter, int n_experts, int n_glu,
+                                  int top_k, int dtype, void* y, void* stream) {
+  int rc = check_common("gemm2_fwd", n_tokens, hidden, inter, n_experts, n_glu, top_k, dtype);
+  if (rc) return rc;
+  if (n_glu == 0) return BIBO_OK;
+  if (!h || !down_proj || !plan || !y) return fail(BIBO_ERR_ARG, "gemm2_fwd: null pointer");
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (gemm2_tc_supported(hidden, inter, dtype) && aligned16(h) && aligned16(down_proj) && aligned16(y))
+    return gemm2_tc_launch(h, down_proj, plan, n_tokens, hidden, inter, n_experts, n_glu, top_k, y, st);
+  return gemm_simt_launch(h, down_proj, y, plan, n_tokens, n_experts, n_glu, top_k, inter, hidden, dtype, st);
+}
+
+extern "C" int bibo_moe_forward(const bibo_moe_shape* s, const void* x, const void* w_router,
+                                const float* bias, const void* gate_up_proj, const void* down_proj,
+                                const float* theta, const bibo_moe_workspace* ws, void* out, void* stream) {
+  if (!s || !ws) return fail(BIBO_ERR_ARG, "forward: null shape / workspace");
+  cudaStream_t st_ = static_cast<cudaStream_t>(stream);
+  void* const* ev = ws->stage_events;
+#define BIBO_STAGE(i)                                                              \
+  do {                                                                             \
+    if (ev) BIBO_CUDA(cudaEventRecord(static_cast<cudaEvent_t>(ev[i]), st_));      \
+  } while (0)
+  BIBO_STAGE(0);
+  int rc = bibo_moe_router_fwd(x, w_router, bias, nullptr, s->n_tokens, s->hidden, s->n_experts, s->top_k,
+                               s->norm_mode, s->scale, s->dtype, ws->logits, ws->topk_idx, ws->topk_w,
+                               ws->slot_rank, ws->block_counts, stream);
+  if (rc) return rc;
+  BIBO_STAGE(1);
+  rc = bibo_moe_plan(ws->block_counts, s->n_tokens, s->top_k, s->n_experts, s->n_glu, ws->plan, stream);
+  if (rc) return rc;
+  BIBO_STAGE(2);
+  rc = bibo_moe_permute_fwd(x, ws->topk_idx, ws->slot_rank, ws->plan, s->n_tokens, s->hidden, s->n_experts,
+                            s->n_glu, s->top_k, s->dtype, s->zero_padding, ws->xp, ws->slot_row,
+                            ws->row_token, stream);
+  if (rc) return rc;
+  BIBO_STAGE(3);
+  rc = bibo_moe_gemm1_radial_fwd(ws->xp, gate_up_proj, theta, ws->plan, s->n_tokens, s->hidden, s->inter,
+                                 s->n_experts, s->n_glu, s->top_k, s->dtype, ws->h, ws->gate_up, ws->rnorm,
+                                 stream);
+  if (rc) return rc;
+  BIBO_STAGE(4);
+  rc = bibo_moe_gemm2_fwd(ws->h, down_proj, ws->plan, s->n_tokens, s->hidden, s->inter, s->n_experts,
+                          s->n_glu, s->top_k, s->dtype, ws->y, stream);
+  if (rc) return rc;
+  BIBO_STAGE(5);
+  rc = bibo_moe_combine_fwd(ws->y, x, ws->slot_row, ws->topk_idx, ws->topk_w, s->n_tokens, s->hidden,
+                            s->top_k, s->n_glu, s->n_pos, s->dtype, out, stream);
+  if (rc) return rc;
+  BIBO_STAGE(6);
+#undef BIBO_STAGE
+  return BIBO_OK;
+}
+
+extern "C" int bibo_moe_forward_host(const bibo_moe_shape* s, const void* x_host, void* x_dev,
+                                     const void* w_router, const float* bias, const void* gate_up_proj,
+                                     const void* down_proj, const float* theta,
+                                     const bibo_moe_workspace* ws, void* out_dev, void* out_host,
+                                     void* stream) {
+  if (!s || !x_host || !x_dev || !out_dev || !out_host) return fail(BIBO_ERR_ARG, "forward_host: null pointer");
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const size_t bytes = (size_t)s->n_tokens * s->hidden * (s->dtype == BIBO_F32 ? 4 : 2);
+  BIBO_CUDA(cudaMemcpyAsync(x_dev, x_host, bytes, cudaMemcpyHostToDevice, st));
+  int rc = bibo_moe_forward(s, x_dev, w_router, bias, gate_up_proj, down_proj, theta, ws, out_dev, stream);
+  if (rc) return rc;
+  BIBO_CUDA(cudaMemcpyAsync(out_host, out_dev, bytes, cudaMemcpyDeviceToHost, st));
+  BIBO_CUDA(cudaStreamSynchronize(st));
+  return BIBO_OK;
+}
+
+extern "C" int bibo_moe_debug_plan_header(const int32_t* plan, int32_t* header4_host, void* stream) {
+  if (!plan || !header4_host) return fail(BIBO_ERR_ARG, "debug_plan_header: null pointer");
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  BIBO_CUDA(cudaMemcpyAsync(header4_host, plan, 4 * sizeof(int32_t), cudaMemcpyDeviceToHost, st));
+  BIBO_CUDA(cudaStreamSynchronize(st));
+  if (header4_host[PLAN_STATUS] != 0)
+    return fail(BIBO_ERR_DEVICE_STATUS, "plan status word = %d", header4_host[PLAN_STATUS]);
+  return BIBO_OK;
+}

@@ -1,0 +1,89 @@
+// Shared helpers of libbibo_moe: error reporting, dtype traits, plan layout.
+#pragma once
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include <atomic>
+#include <cstdarg>
+#include <cstdio>
+
+#include "../../include/bibo_moe.h"
+
+namespace bibo {
+
+// ---- host-side error string (per thread) ------------------------------------------------------
+inline char* err_buf() {
+  static thread_local char buf[512] = "no error";
+  return buf;
+}
+inline int fail(int code, const char* fmt, ...) {
+  va_list ap;
+  va_start(ap, fmt);
+  vsnprintf(err_buf(), 512, fmt, ap);
+  va_end(ap);
+  return code;
+}
+inline std::atomic<long long>& launch_counter() {
+  static std::atomic<long long> c{0};
+  return c;
+}
+#define BIBO_CHECK_LAUNCH(name)                                                       \
+  do {                                                                                \
+    bibo::launch_counter().fetch_add(1, std::memory_order_relaxed);                   \
+    cudaError_t e_ = cudaGetLastError();                                              \
+    if (e_ != cudaSuccess)                                                            \
+      return bibo::fail(BIBO_ERR_CUDA, "%s launch: %s", name, cudaGetErrorString(e_)); \
+  } while (0)
+#define BIBO_CUDA(call)                                                                   \
+  do {                                                                                    \
+    cudaError_t e_ = (call);                                                              \
+    if (e_ != cudaSuccess)                                                                \
+      return bibo::fail(BIBO_ERR_CUDA, "%s: %s", #call, cudaGetErrorString(e_));           \
+  } while (0)
+
+inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+
+// ---- plan layout (int32 words) ------------------------------------------------------------------
+constexpr int PLAN_N_TILES = 0, PLAN_ROWS_USED = 1, PLAN_STATUS = 2, PLAN_HDR = 4;
+__host__ __device__ inline int64_t router_blocks(int64_t n_tokens) {
+  return (n_tokens + BIBO_ROUTER_BLOCK_TOKENS - 1) / BIBO_ROUTER_BLOCK_TOKENS;
+}
+__host__ __device__ inline int64_t rows_cap(int64_t n, int k, int n_glu) {
+  int64_t r = n * k + (int64_t)n_glu * (BIBO_TILE_M - 1);
+  return (r + BIBO_TILE_M - 1) / BIBO_TILE_M * BIBO_TILE_M;
+}
+__host__ __device__ inline int64_t tiles_cap(int64_t n, int k, int n_glu) {
+  return rows_cap(n, k, n_glu) / BIBO_TILE_M;
+}
+__host__ __device__ inline int64_t plan_off_counts() { return PLAN_HDR; }
+__host__ __device__ inline int64_t plan_off_expert_off(int E) { return PLAN_HDR + E; }
+__host__ __device__ inline int64_t plan_off_block_base(int E, int n_glu) {
+  return PLAN_HDR + E + n_glu + 1;
+}
+__host__ __device__ inline int64_t plan_off_tiles(int64_t n, int E, int n_glu) {
+  int64_t o = plan_off_block_base(E, n_glu) + router_blocks(n) * E;
+  return (o + 3) / 4 * 4;  // int4-aligned tile records
+}
+__host__ __device__ inline int64_t plan_words(int64_t n, int k, int E, int n_glu) {
+  return plan_off_tiles(n, E, n_glu) + tiles_cap(n, k, n_glu) * 4;
+}
+
+// ---- dtype helpers ------------------------------------------------------------------------------
+template <typename T> __device__ __forceinline__ float to_f32(T v);
+template <> __device__ __forceinline__ float to_f32<float>(float v) { return v; }
+template <> __device__ __forceinline__ float to_f32<__nv_bfloat16>(__nv_bfloat16 v) {
+  return __bfloat162float(v);
+}
+template <typename T> __device__ __forceinline__ T from_f32(float v);
+template <> __device__ __forceinline__ float from_f32<float>(float v) { return v; }
+template <> __device__ __forceinline__ __nv_bfloat16 from_f32<__nv_bfloat16>(float v) {
+  return __float2bfloat16_rn(v);
+}
+
+// accurate sigmoid: IEEE division and expf (no fast-math), so scores round as torch's do
+__device__ __forceinline__ float sigmoid_accurate(float x) {
+  return __fdiv_rn(1.0f, 1.0f + expf(-x));
+}
+
+}  // namespace bibo

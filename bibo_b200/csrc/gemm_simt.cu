@@ -1,0 +1,126 @@
+// General-dtype grouped GEMMs on CUDA cores (fp32 accumulate) and the stand-alone Radial NormSiLU
+// row kernel.  This is the float32 path of K3/K4 (the 1e-4 parity bar rules out tf32) and the path
+// for shapes the tensor-core kernels do not cover; bf16 at tile-friendly shapes goes to gemm_tc.cu.
+#include "common.cuh"
+
+namespace bibo {
+
+constexpr int GM = BIBO_TILE_M, GN = 64, GK = 16;
+
+// C[row, n] = sum_k A[row, k] * B[e][n, k] over the row tiles of the plan.
+// grid = (tiles_cap, ceil(n_out / GN)); tile t belongs to expert tiles[t].x.
+template <typename T>
+__global__ void __launch_bounds__(256)
+grouped_gemm_simt_kernel(const T* __restrict__ A, const T* __restrict__ B, T* __restrict__ C,
+                         const int32_t* __restrict__ plan, int64_t tiles_off, int k_dim, int n_out) {
+  if ((int)blockIdx.x >= plan[PLAN_N_TILES]) return;
+  const int4 tile = reinterpret_cast<const int4*>(plan + tiles_off)[blockIdx.x];
+  const int e = tile.x, row0 = tile.y;
+  const int n0 = blockIdx.y * GN;
+  __shared__ float As[GK][GM + 1];
+  __shared__ float Bs[GK][GN + 1];
+  const int tid = threadIdx.x, ty = tid / 16, tx = tid % 16;
+  const T* Ab = A + (int64_t)row0 * k_dim;
+  const T* Bb = B + ((int64_t)e * n_out + n0) * k_dim;
+  float acc[8][4];
+#pragma unroll
+  for (int i = 0; i < 8; ++i)
+#pragma unroll
+    for (int j = 0; j < 4; ++j) acc[i][j] = 0.f;
+  for (int k0 = 0; k0 < k_dim; k0 += GK) {
+    for (int i = tid; i < GM * GK; i += 256) {
+      int r = i / GK, c = i % GK;
+      As[c][r] = (k0 + c < k_dim) ? to_f32<T>(Ab[(int64_t)r * k_dim + k0 + c]) : 0.f;
+    }
+    for (int i = tid; i < GN * GK; i += 256) {
+      int r = i / GK, c = i % GK;
+      Bs[c][r] = (n0 + r < n_out && k0 + c < k_dim) ? to_f32<T>(Bb[(int64_t)r * k_dim + k0 + c]) : 0.f;
+    }
+    __syncthreads();
+#pragma unroll
+    for (int kk = 0; kk < GK; ++kk) {
+      float a[8], b[4];
+#pragma unroll
+      for (int i = 0; i < 8; ++i) a[i] = As[kk][ty * 8 + i];
+#pragma unroll
+      for (int j = 0; j < 4; ++j) b[j] = Bs[kk][tx * 4 + j];
+#pragma unroll
+      for (int i = 0; i < 8; ++i)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) acc[i][j] = fmaf(a[i], b[j], acc[i][j]);
+    }
+    __syncthreads();
+  }
+#pragma unroll
+  for (int i = 0; i < 8; ++i)
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      int n = n0 + tx * 4 + j;
+      if (n < n_out) C[(int64_t)(row0 + ty * 8 + i) * n_out + n] = from_f32<T>(acc[i][j]);
+    }
+}
+
+// One warp per row of gate_up [rows, 2I]: r = sqrt(mean g^2 + 1e-6), p = sigmoid(theta_e),
+// a = T(silu(g/r) * r^p), h = T(a * up)   (src/modeling/ffn/moe.py:85-92).
+template <typename T>
+__global__ void __launch_bounds__(256)
+radial_rows_kernel(const T* __restrict__ gate_up, const float* __restrict__ theta,
+                   const int32_t* __restrict__ plan, int64_t tiles_off, int inter,
+                   T* __restrict__ h, float* __restrict__ rnorm_out) {
+  const int lane = threadIdx.x & 31;
+  const int64_t row = (int64_t)blockIdx.x * 8 + (threadIdx.x >> 5);
+  if (row >= plan[PLAN_ROWS_USED]) return;
+  const int e = reinterpret_cast<const int4*>(plan + tiles_off)[row / BIBO_TILE_M].x;
+  const T* g = gate_up + row * 2 * inter;
+  const T* u = g + inter;
+  float ss = 0.f;
+  for (int i = lane; i < inter; i += 32) {
+    float v = to_f32<T>(g[i]);
+    ss = fmaf(v, v, ss);
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+  const float r = sqrtf(ss / (float)inter + 1e-6f);
+  const float p = sigmoid_accurate(theta[e]);
+  const float gain = powf(r, p);
+  if (lane == 0 && rnorm_out) rnorm_out[row] = r;
+  for (int i = lane; i < inter; i += 32) {
+    const float z = __fdiv_rn(to_f32<T>(g[i]), r);
+    const float a = __fdiv_rn(z, 1.0f + expf(-z)) * gain;
+    const T a_t = from_f32<T>(a);
+    h[row * inter + i] = from_f32<T>(to_f32<T>(a_t) * to_f32<T>(u[i]));
+  }
+}
+
+int gemm_simt_launch(const void* A, const void* B, void* C, const int32_t* plan, int64_t n_tokens,
+                     int n_experts, int n_glu, int top_k, int k_dim, int n_out, int dtype,
+                     cudaStream_t st) {
+  dim3 grid((unsigned)tiles_cap(n_tokens, top_k, n_glu), (unsigned)((n_out + GN - 1) / GN));
+  const int64_t toff = plan_off_tiles(n_tokens, n_experts, n_glu);
+  if (dtype == BIBO_F32)
+    grouped_gemm_simt_kernel<float><<<grid, 256, 0, st>>>((const float*)A, (const float*)B, (float*)C,
+                                                          plan, toff, k_dim, n_out);
+  else
+    grouped_gemm_simt_kernel<__nv_bfloat16><<<grid, 256, 0, st>>>(
+        (const __nv_bfloat16*)A, (const __nv_bfloat16*)B, (__nv_bfloat16*)C, plan, toff, k_dim, n_out);
+  BIBO_CHECK_LAUNCH("grouped_gemm_simt_kernel");
+  return BIBO_OK;
+}
+
+int radial_rows_launch(const void* gate_up, const float* theta, const int32_t* plan,
+                       int64_t n_tokens, int n_experts, int n_glu, int top_k, int inter, int dtype,
+                       void* h, float* rnorm_out, cudaStream_t st) {
+  const int64_t rows = rows_cap(n_tokens, top_k, n_glu);
+  dim3 grid((unsigned)((rows + 7) / 8));
+  const int64_t toff = plan_off_tiles(n_tokens, n_experts, n_glu);
+  if (dtype == BIBO_F32)
+    radial_rows_kernel<float><<<grid, 256, 0, st>>>((const float*)gate_up, theta, plan, toff, inter,
+                                                    (float*)h, rnorm_out);
+  else
+    radial_rows_kernel<__nv_bfloat16><<<grid, 256, 0, st>>>((const __nv_bfloat16*)gate_up, theta, plan,
+                                                            toff, inter, (__nv_bfloat16*)h, rnorm_out);
+  BIBO_CHECK_LAUNCH("radial_rows_kernel");
+  return BIBO_OK;
+}
+
+}  // namespace bibo

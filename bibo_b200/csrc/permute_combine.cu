@@ -1,0 +1,196 @@
+// K2 permute (token rows -> expert-contiguous rows) and K5 combine (weighted sum of a token's k
+// expert rows).  Both are pure HBM-bandwidth kernels: one warp per token, 16-byte accesses.
+#include "common.cuh"
+
+namespace bibo {
+
+constexpr int PW = 8;  // warps per block
+
+// ---- K2 -------------------------------------------------------------------------------------------
+// Warps [0, n_tokens): lane j < k computes the destination row of slot j; the rows are broadcast by
+// shuffle and every lane copies its 16-byte chunks of x[t] to all k rows (x is read once).
+// Warps [n_tokens, n_tokens + n_glu*(TILE_M-1)): mark (and optionally zero) one padding row each.
+template <int VEC_BYTES>
+__global__ void __launch_bounds__(PW * 32)
+permute_kernel(const uint8_t* __restrict__ x, const int32_t* __restrict__ topk_idx,
+               const int32_t* __restrict__ slot_rank, const int32_t* __restrict__ plan,
+               int64_t n_tokens, int row_bytes, int n_experts, int n_glu, int top_k,
+               int zero_padding, uint8_t* __restrict__ xp, int32_t* __restrict__ slot_row,
+               int32_t* __restrict__ row_token) {
+  const int lane = threadIdx.x & 31;
+  const int64_t w = (int64_t)blockIdx.x * PW + (threadIdx.x >> 5);
+  const int32_t* counts = plan + plan_off_counts();
+  const int32_t* expert_off = plan + plan_off_expert_off(n_experts);
+  const int32_t* block_base = plan + plan_off_block_base(n_experts, n_glu);
+  const int chunks = row_bytes / 16;
+
+  if (w < n_tokens) {
+    int my_row = -1;
+    if (lane < top_k) {
+      const int e = topk_idx[w * top_k + lane];
+      if (e < n_glu) {
+        const int64_t b = w / BIBO_ROUTER_BLOCK_TOKENS;
+        my_row = expert_off[e] + block_base[b * n_experts + e] + slot_rank[w * top_k + lane];
+        row_token[my_row] = (int32_t)w;
+      }
+      slot_row[w * top_k + lane] = my_row;
+    }
+    int rows[BIBO_MAX_TOP_K];
+#pragma unroll
+    for (int j = 0; j < BIBO_MAX_TOP_K; ++j) rows[j] = __shfl_sync(0xffffffffu, my_row, j);
+    const uint4* src = reinterpret_cast<const uint4*>(x + w * row_bytes);
+    for (int c = lane; c < chunks; c += 32) {
+      const uint4 v = __ldg(src + c);
+#pragma unroll
+      for (int j = 0; j < BIBO_MAX_TOP_K; ++j)
+        if (j < top_k && rows[j] >= 0)
+          reinterpret_cast<uint4*>(xp + (int64_t)rows[j] * row_bytes)[c] = v;
+    }
+  } else {
+    const int64_t p = w - n_tokens;
+    const int e = (int)(p / (BIBO_TILE_M - 1));
+    if (e >= n_glu) return;
+    const int row = expert_off[e] + counts[e] + (int)(p % (BIBO_TILE_M - 1));
+    if (row >= expert_off[e + 1]) return;
+    if (lane == 0) row_token[row] = -1;
+    if (zero_padding) {
+      uint4* dst = reinterpret_cast<uint4*>(xp + (int64_t)row * row_bytes);
+      for (int c = lane; c < chunks; c += 32) dst[c] = make_uint4(0, 0, 0, 0);
+    }
+  }
+}
+
+// ---- K5 -------------------------------------------------------------------------------------------
+template <typename T> struct Vec16;
+template <> struct Vec16<float> {
+  static constexpr int N = 4;
+  static __device__ __forceinline__ void load(const void* p, float* f) {
+    float4 v = *reinterpret_cast<const float4*>(p);
+    f[0] = v.x; f[1] = v.y; f[2] = v.z; f[3] = v.w;
+  }
+  static __device__ __forceinline__ void store(void* p, const float* f) {
+    *reinterpret_cast<float4*>(p) = make_float4(f[0], f[1], f[2], f[3]);
+  }
+};
+template <> struct Vec16<__nv_bfloat16> {
+  static constexpr int N = 8;
+  static __device__ __forceinline__ void load(const void* p, float* f) {
+    uint4 v = *reinterpret_cast<const uint4*>(p);
+    const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&v);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      float2 t = __bfloat1622float2(h[i]);
+      f[2 * i] = t.x; f[2 * i + 1] = t.y;
+    }
+  }
+  static __device__ __forceinline__ void store(void* p, const float* f) {
+    uint4 v;
+    __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&v);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) h[i] = __floats2bfloat162_rn(f[2 * i], f[2 * i + 1]);
+    *reinterpret_cast<uint4*>(p) = v;
+  }
+};
+
+// One warp per token; the k rows are summed in slot order (= ascending expert index), fp32.
+template <typename T>
+__global__ void __launch_bounds__(PW * 32)
+combine_kernel(const T* __restrict__ y, const T* __restrict__ x, const int32_t* __restrict__ slot_row,
+               const int32_t* __restrict__ topk_idx, const float* __restrict__ topk_w,
+               int64_t n_tokens, int hidden, int top_k, int n_glu, int n_pos, T* __restrict__ out) {
+  constexpr int VN = Vec16<T>::N;
+  const int lane = threadIdx.x & 31;
+  const int64_t t = (int64_t)blockIdx.x * PW + (threadIdx.x >> 5);
+  if (t >= n_tokens) return;
+  int my_row = -1;
+  float my_w = 0.f;
+  if (lane < top_k) {
+    my_row = slot_row[t * top_k + lane];
+    my_w = topk_w[t * top_k + lane];
+    if (my_row < 0) {  // +Identity / -Identity expert: contributes +w*x or -w*x
+      const int e = topk_idx[t * top_k + lane];
+      if (e >= n_glu + n_pos) my_w = -my_w;
+    }
+  }
+  int rows[BIBO_MAX_TOP_K];
+  float ws[BIBO_MAX_TOP_K];
+#pragma unroll
+  for (int j = 0; j < BIBO_MAX_TOP_K; ++j) {
+    rows[j] = __shfl_sync(0xffffffffu, my_row, j);
+    ws[j] = __shfl_sync(0xffffffffu, my_w, j);
+  }
+  const int chunks = hidden / VN;
+  for (int c = lane; c < chunks; c += 32) {
+    float v[BIBO_MAX_TOP_K][VN];
+#pragma unroll
+    for (int j = 0; j < BIBO_MAX_TOP_K; ++j) {
+      if (j < top_k) {
+        const T* src = rows[j] >= 0 ? y + (int64_t)rows[j] * hidden : x + t * hidden;
+        Vec16<T>::load(src + c * VN, v[j]);
+      }
+    }
+    float acc[VN];
+#pragma unroll
+    for (int i = 0; i < VN; ++i) acc[i] = 0.f;
+#pragma unroll
+    for (int j = 0; j < BIBO_MAX_TOP_K; ++j)
+      if (j < top_k)
+#pragma unroll
+        for (int i = 0; i < VN; ++i) acc[i] += v[j][i] * ws[j];
+    Vec16<T>::store(out + t * hidden + c * VN, acc);
+  }
+}
+
+}  // namespace bibo
+
+using namespace bibo;
+
+extern "C" int bibo_moe_permute_fwd(const void* x, const int32_t* topk_idx, const int32_t* slot_rank,
+                                    const int32_t* plan, int64_t n_tokens, int hidden, int n_experts,
+                                    int n_glu, int top_k, int dtype, int zero_padding, void* xp,
+                                    int32_t* slot_row, int32_t* row_token, void* stream) {
+  if (n_tokens <= 0) return BIBO_OK;
+  if (!x || !topk_idx || !slot_rank || !plan || !xp || !slot_row || !row_token)
+    return fail(BIBO_ERR_ARG, "permute_fwd: null pointer");
+  if (dtype != BIBO_F32 && dtype != BIBO_BF16) return fail(BIBO_ERR_ARG, "permute_fwd: dtype=%d", dtype);
+  if (top_k < 1 || top_k > BIBO_MAX_TOP_K) return fail(BIBO_ERR_UNSUPPORTED, "permute_fwd: top_k=%d", top_k);
+  const int row_bytes = hidden * (dtype == BIBO_F32 ? 4 : 2);
+  if (row_bytes % 16 != 0)
+    return fail(BIBO_ERR_UNSUPPORTED, "permute_fwd: row of %d bytes is not a multiple of 16", row_bytes);
+  if (!aligned16(x) || !aligned16(xp)) return fail(BIBO_ERR_ALIGN, "permute_fwd: x / xp not 16-byte aligned");
+  const int64_t warps = n_tokens + (int64_t)n_glu * (BIBO_TILE_M - 1);
+  dim3 grid((unsigned)((warps + PW - 1) / PW));
+  permute_kernel<16><<<grid, PW * 32, 0, static_cast<cudaStream_t>(stream)>>>(
+      (const uint8_t*)x, topk_idx, slot_rank, plan, n_tokens, row_bytes, n_experts, n_glu, top_k,
+      zero_padding, (uint8_t*)xp, slot_row, row_token);
+  BIBO_CHECK_LAUNCH("permute_kernel");
+  return BIBO_OK;
+}
+
+extern "C" int bibo_moe_combine_fwd(const void* y, const void* x, const int32_t* slot_row,
+                                    const int32_t* topk_idx, const float* topk_w, int64_t n_tokens,
+                                    int hidden, int top_k, int n_glu, int n_pos, int dtype, void* out,
+                                    void* stream) {
+  if (n_tokens <= 0) return BIBO_OK;
+  if (!y || !x || !slot_row || !topk_idx || !topk_w || !out)
+    return fail(BIBO_ERR_ARG, "combine_fwd: null pointer");
+  if (dtype != BIBO_F32 && dtype != BIBO_BF16) return fail(BIBO_ERR_ARG, "combine_fwd: dtype=%d", dtype);
+  if (top_k < 1 || top_k > BIBO_MAX_TOP_K) return fail(BIBO_ERR_UNSUPPORTED, "combine_fwd: top_k=%d", top_k);
+  const int row_bytes = hidden * (dtype == BIBO_F32 ? 4 : 2);
+  if (row_bytes % 16 != 0)
+    return fail(BIBO_ERR_UNSUPPORTED, "combine_fwd: row of %d bytes is not a multiple of 16", row_bytes);
+  if (!aligned16(y) || !aligned16(x) || !aligned16(out))
+    return fail(BIBO_ERR_ALIGN, "combine_fwd: y / x / out not 16-byte aligned");
+  dim3 grid((unsigned)((n_tokens + PW - 1) / PW));
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (dtype == BIBO_F32)
+    combine_kernel<float><<<grid, PW * 32, 0, st>>>((const float*)y, (const float*)x, slot_row, topk_idx,
+                                                    topk_w, n_tokens, hidden, top_k, n_glu, n_pos,
+                                                    (float*)out);
+  else
+    combine_kernel<__nv_bfloat16><<<grid, PW * 32, 0, st>>>(
+        (const __nv_bfloat16*)y, (const __nv_bfloat16*)x, slot_row, topk_idx, topk_w, n_tokens,
+        hidden, top_k, n_glu, n_pos, (__nv_bfloat16*)out);
+  BIBO_CHECK_LAUNCH("combine_kernel");
+  return BIBO_OK;
+}

@@ -1,0 +1,293 @@
+// K1 (general path): router logits + sigmoid + biased top-k + normalised weights + per-block
+// histogram and in-block ranks, and the plan kernel that turns the histograms into row offsets.
+//
+// This file holds the CUDA-core version that accepts any dtype / hidden size / expert count; the
+// bf16 tensor-core version (router_tc.cu) shares select_and_rank() below through router_select.cuh.
+#include "common.cuh"
+#include "router_select.cuh"
+
+namespace bibo {
+
+constexpr int RB = BIBO_ROUTER_BLOCK_TOKENS;  // tokens per block
+constexpr int RK = 32;                        // k-chunk of the logits product
+constexpr int RE = 64;                        // experts per accumulation pass
+
+// One block: RB tokens.  256 threads; thread (ty,tx) owns 8 tokens x 4 experts of the pass.
+template <typename T>
+__global__ void __launch_bounds__(256)
+router_simt_kernel(const T* __restrict__ x, const T* __restrict__ w_router,
+                   const float* __restrict__ bias, const float* __restrict__ logits_in,
+                   int64_t n_tokens, int hidden, int n_experts, int top_k, int norm_mode,
+                   float scale, float* __restrict__ logits_out, int32_t* __restrict__ topk_idx,
+                   float* __restrict__ topk_w, int32_t* __restrict__ slot_rank,
+                   int32_t* __restrict__ block_counts) {
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  const int ld = n_experts | 1;  // odd leading dimension -> conflict-free column walks
+  float* lg = reinterpret_cast<float*>(smem_raw);                 // [RB][ld]
+  float* As = lg + RB * ld;                                        // [RK][RB+1]
+  float* Bs = As + RK * (RB + 1);                                  // [RK][RE+1]
+  uint32_t* mask = reinterpret_cast<uint32_t*>(Bs + RK * (RE + 1));  // select_and_rank scratch
+
+  const int tid = threadIdx.x;
+  const int64_t t0 = (int64_t)blockIdx.x * RB;
+  const int rows = (int)min((int64_t)RB, n_tokens - t0);
+
+  if (logits_in != nullptr) {
+    for (int i = tid; i < RB * n_experts; i += 256) {
+      int r = i / n_experts, c = i % n_experts;
+      lg[r * ld + c] = r < rows ? logits_in[(t0 + r) * n_experts + c] : 0.f;
+    }
+  } else {
+    const int ty = tid / 16, tx = tid % 16;
+    for (int e0 = 0; e0 < n_experts; e0 += RE) {
+      float acc[8][4];
+#pragma unroll
+      for (int i = 0; i < 8; ++i)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) acc[i][j] = 0.f;
+      for (int k0 = 0; k0 < hidden; k0 += RK) {
+        for (int i = tid; i < RB * RK; i += 256) {
+          int r = i / RK, c = i % RK;
+          float v = 0.f;
+          if (r < rows && k0 + c < hidden) v = to_f32<T>(x[(t0 + r) * hidden + k0 + c]);
+          As[c * (RB + 1) + r] = v;
+        }
+        for (int i = tid; i < RE * RK; i += 256) {
+          int r = i / RK, c = i % RK;
+          float v = 0.f;
+          if (e0 + r < n_experts && k0 + c < hidden)
+            v = to_f32<T>(w_router[(int64_t)(e0 + r) * hidden + k0 + c]);
+          Bs[c * (RE + 1) + r] = v;
+        }
+        __syncthreads();
+#pragma unroll 8
+        for (int kk = 0; kk < RK; ++kk) {
+          float a[8], b[4];
+#pragma unroll
+          for (int i = 0; i < 8; ++i) a[i] = As[kk * (RB + 1) + ty * 8 + i];
+#pragma unroll
+          for (int j = 0; j < 4; ++j) b[j] = Bs[kk * (RE + 1) + tx * 4 + j];
+#pragma unroll
+          for (int i = 0; i < 8; ++i)
+#pragma unroll
+            for (int j = 0; j < 4; ++j) acc[i][j] = fmaf(a[i], b[j], acc[i][j]);
+        }
+        __syncthreads();
+      }
+#pragma unroll
+      for (int i = 0; i < 8; ++i)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          int e = e0 + tx * 4 + j;
+          if (e < n_experts) lg[(ty * 8 + i) * ld + e] = acc[i][j];
+        }
+    }
+  }
+  __syncthreads();
+  if (logits_out != nullptr) {
+    for (int i = tid; i < rows * n_experts; i += 256) {
+      int r = i / n_experts, c = i % n_experts;
+      logits_out[(t0 + r) * n_experts + c] = lg[r * ld + c];
+    }
+    __syncthreads();
+  }
+  select_and_rank(lg, ld, mask, bias, t0, rows, n_experts, top_k, norm_mode, scale, topk_idx,
+                  topk_w, slot_rank, block_counts + (int64_t)blockIdx.x * n_experts);
+}
+
+// ---- ranks for routing decided elsewhere ------------------------------------------------------------
+// Same histogram / rank outputs as the router kernel, for callers that bring their own top-k
+// indices (the BiBoFusedExperts.forward(x, idx, w) seam, src/modeling/ffn/moe.py:47-52).
+__global__ void __launch_bounds__(RB)
+rank_kernel(const int32_t* __restrict__ topk_idx, int64_t n_tokens, int n_experts, int top_k,
+            int32_t* __restrict__ slot_rank, int32_t* __restrict__ block_counts,
+            int32_t* __restrict__ status) {
+  constexpr int WORDS = RB / 32;
+  extern __shared__ uint32_t rmask[];  // [n_experts][WORDS]
+  const int tid = threadIdx.x;
+  const int64_t t = (int64_t)blockIdx.x * RB + tid;
+  for (int i = tid; i < n_experts * WORDS; i += RB) rmask[i] = 0u;
+  __syncthreads();
+  int sel[BIBO_MAX_TOP_K];
+  if (t < n_tokens) {
+#pragma unroll
+    for (int j = 0; j < BIBO_MAX_TOP_K; ++j) {
+      if (j < top_k) {
+        int e = topk_idx[t * top_k + j];
+        if (e < 0 || e >= n_experts) { if (status) atomicExch(status, 2); e = 0; }
+        sel[j] = e;
+        uint32_t old = atomicOr(&rmask[e * WORDS + (tid >> 5)], 1u << (tid & 31));
+        if ((old & (1u << (tid & 31))) && status) atomicExch(status, 3);  // one expert twice in a token
+      }
+    }
+  }
+  __syncthreads();
+  if (t < n_tokens) {
+    const int wq = tid >> 5;
+    const uint32_t lt = (1u << (tid & 31)) - 1u;
+#pragma unroll
+    for (int j = 0; j < BIBO_MAX_TOP_K; ++j) {
+      if (j < top_k) {
+        const uint32_t* m = rmask + sel[j] * WORDS;
+        int r = __popc(m[wq] & lt);
+        for (int q = 0; q < wq; ++q) r += __popc(m[q]);
+        slot_rank[t * top_k + j] = r;
+      }
+    }
+  }
+  for (int e = tid; e < n_experts; e += RB) {
+    int c = 0;
+#pragma unroll
+    for (int q = 0; q < WORDS; ++q) c += __popc(rmask[e * WORDS + q]);
+    block_counts[(int64_t)blockIdx.x * n_experts + e] = c;
+  }
+}
+
+// ---- plan -----------------------------------------------------------------------------------------
+// One block of BIBO_MAX_EXPERTS threads; thread e scans its expert's column of block_counts.
+__global__ void __launch_bounds__(BIBO_MAX_EXPERTS)
+plan_kernel(const int32_t* __restrict__ block_counts, int64_t n_tokens, int top_k, int n_experts,
+            int n_glu, int32_t* __restrict__ plan) {
+  __shared__ int s_padded[BIBO_MAX_EXPERTS + 1];
+  __shared__ int s_total;
+  const int e = threadIdx.x;
+  const int nb = (int)router_blocks(n_tokens);
+  int32_t* counts = plan + plan_off_counts();
+  int32_t* expert_off = plan + plan_off_expert_off(n_experts);
+  int32_t* block_base = plan + plan_off_block_base(n_experts, n_glu);
+  int4* tiles = reinterpret_cast<int4*>(plan + plan_off_tiles(n_tokens, n_experts, n_glu));
+
+  if (e == 0) s_total = 0;
+  __syncthreads();
+  int run = 0;
+  if (e < n_experts) {
+#pragma unroll 8
+    for (int b = 0; b < nb; ++b) {
+      int c = block_counts[(int64_t)b * n_experts + e];
+      block_base[(int64_t)b * n_experts + e] = run;
+      run += c;
+    }
+    counts[e] = run;
+    atomicAdd(&s_total, run);
+  }
+  s_padded[e] = (e < n_glu) ? (run + BIBO_TILE_M - 1) / BIBO_TILE_M * BIBO_TILE_M : 0;
+  __syncthreads();
+  if (e == 0) {  // exclusive scan over <= 256 entries
+    int acc = 0;
+    for (int i = 0; i < n_glu; ++i) {
+      int v = s_padded[i];
+      s_padded[i] = acc;
+      acc += v;
+    }
+    s_padded[n_glu] = acc;
+    plan[PLAN_N_TILES] = acc / BIBO_TILE_M;
+    plan[PLAN_ROWS_USED] = acc;
+    plan[PLAN_STATUS] = (s_total == (long long)n_tokens * top_k) ? 0 : 1;
+    plan[3] = 0;
+  }
+  __syncthreads();
+  if (e <= n_glu) expert_off[e] = s_padded[e];
+  if (e < n_glu) {
+    int row0 = s_padded[e];
+    int t = row0 / BIBO_TILE_M;
+    for (int r = 0; r < run; r += BIBO_TILE_M, ++t)
+      tiles[t] = make_int4(e, row0 + r, min(BIBO_TILE_M, run - r), 0);
+  }
+}
+
+}  // namespace bibo
+
+using namespace bibo;
+
+extern "C" int bibo_moe_router_fwd(const void* x, const void* w_router, const float* bias,
+                                   const float* logits_in, int64_t n_tokens, int hidden,
+                                   int n_experts, int top_k, int norm_mode, float scale, int dtype,
+                                   float* logits_out, int32_t* topk_idx, float* topk_w,
+                                   int32_t* slot_rank, int32_t* block_counts, void* stream);
+
+namespace bibo {
+int router_tc_supported(int hidden, int n_experts, int dtype);
+int router_tc_launch(const void* x, const void* w_router, const float* bias, int64_t n_tokens,
+                     int hidden, int n_experts, int top_k, int norm_mode, float scale,
+                     float* logits_out, int32_t* topk_idx, float* topk_w, int32_t* slot_rank,
+                     int32_t* block_counts, cudaStream_t st);
+}
+
+int bibo_moe_router_fwd(const void* x, const void* w_router, const float* bias,
+                        const float* logits_in, int64_t n_tokens, int hidden, int n_experts,
+                        int top_k, int norm_mode, float scale, int dtype, float* logits_out,
+                        int32_t* topk_idx, float* topk_w, int32_t* slot_rank,
+                        int32_t* block_counts, void* stream) {
+  if (n_tokens <= 0) return BIBO_OK;
+  if (!bias || !topk_idx || !topk_w || !slot_rank || !block_counts)
+    return fail(BIBO_ERR_ARG, "router_fwd: null output or bias pointer");
+  if (!logits_in && (!x || !w_router)) return fail(BIBO_ERR_ARG, "router_fwd: null x / w_router");
+  if (n_experts < 1 || n_experts > BIBO_MAX_EXPERTS || top_k < 1 || top_k > BIBO_MAX_TOP_K ||
+      top_k > n_experts)
+    return fail(BIBO_ERR_UNSUPPORTED, "router_fwd: n_experts=%d (max %d) top_k=%d (max %d)",
+                n_experts, BIBO_MAX_EXPERTS, top_k, BIBO_MAX_TOP_K);
+  if (norm_mode < BIBO_NORM_RAW || norm_mode > BIBO_NORM_SOFTMAX)
+    return fail(BIBO_ERR_ARG, "router_fwd: norm_mode=%d", norm_mode);
+  if (dtype != BIBO_F32 && dtype != BIBO_BF16) return fail(BIBO_ERR_ARG, "router_fwd: dtype=%d", dtype);
+  if (!logits_in && hidden < 1) return fail(BIBO_ERR_ARG, "router_fwd: hidden=%d", hidden);
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+
+  if (!logits_in && router_tc_supported(hidden, n_experts, dtype) && aligned16(x) && aligned16(w_router))
+    return router_tc_launch(x, w_router, bias, n_tokens, hidden, n_experts, top_k, norm_mode,
+                            scale, logits_out, topk_idx, topk_w, slot_rank, block_counts, st);
+
+  const int ld = n_experts | 1;
+  size_t smem = sizeof(float) * ((size_t)RB * ld + RK * (RB + 1) + RK * (RE + 1)) +
+                select_smem_bytes(n_experts);
+  dim3 grid((unsigned)router_blocks(n_tokens));
+  if (dtype == BIBO_F32) {
+    auto kern = router_simt_kernel<float>;
+    BIBO_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    kern<<<grid, 256, smem, st>>>((const float*)x, (const float*)w_router, bias, logits_in,
+                                  n_tokens, hidden, n_experts, top_k, norm_mode, scale, logits_out,
+                                  topk_idx, topk_w, slot_rank, block_counts);
+  } else {
+    auto kern = router_simt_kernel<__nv_bfloat16>;
+    BIBO_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    kern<<<grid, 256, smem, st>>>((const __nv_bfloat16*)x, (const __nv_bfloat16*)w_router, bias,
+                                  logits_in, n_tokens, hidden, n_experts, top_k, norm_mode, scale,
+                                  logits_out, topk_idx, topk_w, slot_rank, block_counts);
+  }
+  BIBO_CHECK_LAUNCH("router_simt_kernel");
+  return BIBO_OK;
+}
+
+extern "C" int bibo_moe_route_from_indices(const int32_t* topk_idx, int64_t n_tokens, int n_experts,
+                                           int top_k, int32_t* slot_rank, int32_t* block_counts,
+                                           int32_t* status, void* stream) {
+  if (n_tokens <= 0) return BIBO_OK;
+  if (!topk_idx || !slot_rank || !block_counts) return fail(BIBO_ERR_ARG, "route_from_indices: null pointer");
+  if (n_experts < 1 || n_experts > BIBO_MAX_EXPERTS || top_k < 1 || top_k > BIBO_MAX_TOP_K)
+    return fail(BIBO_ERR_UNSUPPORTED, "route_from_indices: n_experts=%d top_k=%d", n_experts, top_k);
+  rank_kernel<<<(unsigned)router_blocks(n_tokens), RB, sizeof(uint32_t) * n_experts * (RB / 32),
+                static_cast<cudaStream_t>(stream)>>>(topk_idx, n_tokens, n_experts, top_k, slot_rank,
+                                                     block_counts, status);
+  BIBO_CHECK_LAUNCH("rank_kernel");
+  return BIBO_OK;
+}
+
+extern "C" int bibo_moe_plan(const int32_t* block_counts, int64_t n_tokens, int top_k,
+                             int n_experts, int n_glu, int32_t* plan, void* stream) {
+  if (!block_counts || !plan) return fail(BIBO_ERR_ARG, "plan: null pointer");
+  if (n_experts < 1 || n_experts > BIBO_MAX_EXPERTS || n_glu < 0 || n_glu > n_experts)
+    return fail(BIBO_ERR_UNSUPPORTED, "plan: n_experts=%d n_glu=%d", n_experts, n_glu);
+  if (n_tokens <= 0) return fail(BIBO_ERR_ARG, "plan: n_tokens=%lld", (long long)n_tokens);
+  plan_kernel<<<1, BIBO_MAX_EXPERTS, 0, static_cast<cudaStream_t>(stream)>>>(
+      block_counts, n_tokens, top_k, n_experts, n_glu, plan);
+  BIBO_CHECK_LAUNCH("plan_kernel");
+  return BIBO_OK;
+}
+
+extern "C" int64_t bibo_moe_rows_cap(int64_t n, int k, int g) { return rows_cap(n, k, g); }
+extern "C" int64_t bibo_moe_tiles_cap(int64_t n, int k, int g) { return tiles_cap(n, k, g); }
+extern "C" int64_t bibo_moe_router_blocks(int64_t n) { return router_blocks(n); }
+extern "C" int64_t bibo_moe_plan_words(int64_t n, int k, int E, int g) { return plan_words(n, k, E, g); }
+extern "C" int64_t bibo_moe_plan_off_counts(void) { return plan_off_counts(); }
+extern "C" int64_t bibo_moe_plan_off_expert_off(int E) { return plan_off_expert_off(E); }
+extern "C" int64_t bibo_moe_plan_off_block_base(int E, int g) { return plan_off_block_base(E, g); }
+extern "C" int64_t bibo_moe_plan_off_tiles(int64_t n, int E, int g) { return plan_off_tiles(n, E, g); }

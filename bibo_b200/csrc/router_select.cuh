@@ -1,0 +1,123 @@
+// Selection stage of the router, shared by the CUDA-core and the tensor-core logits kernels.
+//
+// Input: a shared-memory tile of fp32 logits, one row per token of the block.
+// Follows BiBoMoERouter.forward (src/modeling/ffn/router.py:31-51): score = sigmoid(logit);
+// selection on score + bias; weights gathered from the un-biased scores; "sum" normalisation
+// divides by (sum + 1e-20).  Ties go to the lower expert index, and the k experts are written in
+// ascending expert index.
+#pragma once
+#include "common.cuh"
+
+namespace bibo {
+
+// Shared-memory words select_and_rank needs after the logits tile.
+__host__ __device__ inline size_t select_smem_bytes(int n_experts) {
+  return sizeof(uint32_t) * (size_t)n_experts * (BIBO_ROUTER_BLOCK_TOKENS / 32) +
+         sizeof(float) * (size_t)n_experts;
+}
+
+// lg: [BIBO_ROUTER_BLOCK_TOKENS][ld] logits (overwritten with scores); scratch: select_smem_bytes.
+// Must be called by every thread of the block (blockDim.x >= BIBO_ROUTER_BLOCK_TOKENS) after the
+// tile is complete and visible (the caller synchronises before the call).
+__device__ __forceinline__ void select_and_rank(
+    float* lg, int ld, uint32_t* scratch, const float* __restrict__ bias, int64_t t0, int rows,
+    int n_experts, int top_k, int norm_mode, float scale, int32_t* __restrict__ topk_idx,
+    float* __restrict__ topk_w, int32_t* __restrict__ slot_rank,
+    int32_t* __restrict__ block_counts_row) {
+  constexpr int WORDS = BIBO_ROUTER_BLOCK_TOKENS / 32;
+  uint32_t* mask = scratch;                                            // [n_experts][WORDS]
+  float* bias_s = reinterpret_cast<float*>(scratch + n_experts * WORDS);  // [n_experts]
+  const int tid = threadIdx.x;
+  for (int i = tid; i < n_experts * WORDS; i += blockDim.x) mask[i] = 0u;
+  for (int i = tid; i < n_experts; i += blockDim.x) bias_s[i] = bias[i];
+  __syncthreads();
+
+  int sel_idx[BIBO_MAX_TOP_K];
+  float sel_s[BIBO_MAX_TOP_K];
+  const bool active = tid < rows;
+  if (active) {
+    float* row = lg + tid * ld;
+    for (int e = 0; e < n_experts; ++e) row[e] = sigmoid_accurate(row[e]);
+#pragma unroll
+    for (int j = 0; j < BIBO_MAX_TOP_K; ++j) {
+      if (j < top_k) {
+        float best = -INFINITY;
+        int bi = -1;
+        for (int e = 0; e < n_experts; ++e) {
+          float s = row[e];
+          float v = s + bias_s[e];
+          // taken entries hold -inf; strict '>' keeps the lowest index among equal keys
+          if (s != -INFINITY && (bi < 0 || v > best)) { best = v; bi = e; }
+        }
+        sel_idx[j] = bi;
+        sel_s[j] = row[bi];
+        row[bi] = -INFINITY;
+      }
+    }
+    // ascending expert index (insertion sort, k <= 8)
+#pragma unroll
+    for (int a = 1; a < BIBO_MAX_TOP_K; ++a) {
+      if (a < top_k) {
+#pragma unroll
+        for (int b = a; b > 0; --b) {
+          if (sel_idx[b] < sel_idx[b - 1]) {
+            int ti = sel_idx[b]; sel_idx[b] = sel_idx[b - 1]; sel_idx[b - 1] = ti;
+            float tf = sel_s[b]; sel_s[b] = sel_s[b - 1]; sel_s[b - 1] = tf;
+          }
+        }
+      }
+    }
+    float w[BIBO_MAX_TOP_K];
+    if (top_k > 1 && norm_mode == BIBO_NORM_SUM) {
+      float tot = 0.f;
+#pragma unroll
+      for (int j = 0; j < BIBO_MAX_TOP_K; ++j) if (j < top_k) tot += sel_s[j];
+      tot += 1e-20f;
+#pragma unroll
+      for (int j = 0; j < BIBO_MAX_TOP_K; ++j) if (j < top_k) w[j] = __fdiv_rn(sel_s[j], tot);
+    } else if (top_k > 1 && norm_mode == BIBO_NORM_SOFTMAX) {
+      float m = -INFINITY, tot = 0.f;
+#pragma unroll
+      for (int j = 0; j < BIBO_MAX_TOP_K; ++j) if (j < top_k) m = fmaxf(m, sel_s[j]);
+#pragma unroll
+      for (int j = 0; j < BIBO_MAX_TOP_K; ++j) if (j < top_k) { w[j] = expf(sel_s[j] - m); tot += w[j]; }
+#pragma unroll
+      for (int j = 0; j < BIBO_MAX_TOP_K; ++j) if (j < top_k) w[j] = __fdiv_rn(w[j], tot);
+    } else {
+#pragma unroll
+      for (int j = 0; j < BIBO_MAX_TOP_K; ++j) if (j < top_k) w[j] = sel_s[j];
+    }
+    const int64_t base = (t0 + tid) * top_k;
+#pragma unroll
+    for (int j = 0; j < BIBO_MAX_TOP_K; ++j) {
+      if (j < top_k) {
+        topk_idx[base + j] = sel_idx[j];
+        topk_w[base + j] = (scale == 1.0f) ? w[j] : w[j] * scale;
+        atomicOr(&mask[sel_idx[j] * WORDS + (tid >> 5)], 1u << (tid & 31));
+      }
+    }
+  }
+  __syncthreads();
+  if (active) {
+    const int64_t base = (t0 + tid) * top_k;
+    const int wq = tid >> 5;
+    const uint32_t lt = (1u << (tid & 31)) - 1u;
+#pragma unroll
+    for (int j = 0; j < BIBO_MAX_TOP_K; ++j) {
+      if (j < top_k) {
+        const uint32_t* m = mask + sel_idx[j] * WORDS;
+        int r = __popc(m[wq] & lt);
+        for (int q = 0; q < wq; ++q) r += __popc(m[q]);
+        slot_rank[base + j] = r;
+      }
+    }
+  }
+  for (int e = tid; e < n_experts; e += blockDim.x) {
+    int c = 0;
+#pragma unroll
+    for (int q = 0; q < WORDS; ++q) c += __popc(mask[e * WORDS + q]);
+    block_counts_row[e] = c;
+  }
+}
+
+}  // namespace bibo

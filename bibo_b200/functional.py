@@ -1,0 +1,295 @@
+"""Host-side driver of the kernel chain: buffers, launches, and the stage-by-stage entry points.
+
+All arithmetic happens in libbibo_moe.so.  This module only allocates torch tensors (outputs and
+one workspace per shape) and passes their raw pointers through ctypes.
+"""
+from __future__ import annotations
+
+import ctypes as C
+from dataclasses import dataclass
+from typing import Dict, Optional, Tuple
+
+import torch
+
+from . import _lib
+
+_DTYPES = {torch.float32: _lib.F32, torch.bfloat16: _lib.BF16}
+_NORMS = {"sum": _lib.NORM_SUM, True: _lib.NORM_SUM, "softmax": _lib.NORM_SOFTMAX,
+          False: _lib.NORM_RAW, None: _lib.NORM_RAW}
+
+
+def dtype_code(dt: torch.dtype) -> int:
+    if dt not in _DTYPES:
+        raise RuntimeError(f"bibo_b200 kernels take float32 or bfloat16 tensors, got {dt}")
+    return _DTYPES[dt]
+
+
+def norm_code(mode) -> int:
+    if mode not in _NORMS:
+        raise RuntimeError(f"unknown norm_topk_prob {mode!r}")
+    return _NORMS[mode]
+
+
+def _stream(dev) -> int:
+    return torch.cuda.current_stream(dev).cuda_stream
+
+
+def _need_cuda(t: torch.Tensor, name: str) -> None:
+    if not t.is_cuda:
+        raise RuntimeError(
+            f"{name} is on {t.device}: the bibo_b200 MoE block runs only as CUDA kernels "
+            "(there is no CPU implementation)")
+    if not t.is_contiguous():
+        raise RuntimeError(f"{name} must be contiguous")
+
+
+@dataclass(frozen=True)
+class Geometry:
+    n_tokens: int
+    hidden: int
+    inter: int
+    n_experts: int
+    n_glu: int
+    n_pos: int
+    top_k: int
+    dtype: torch.dtype
+
+    @property
+    def rows_cap(self) -> int:
+        return int(_lib.load().bibo_moe_rows_cap(self.n_tokens, self.top_k, self.n_glu))
+
+    @property
+    def router_blocks(self) -> int:
+        return int(_lib.load().bibo_moe_router_blocks(self.n_tokens))
+
+    @property
+    def plan_words(self) -> int:
+        return int(_lib.load().bibo_moe_plan_words(self.n_tokens, self.top_k, self.n_experts, self.n_glu))
+
+
+class MoEWorkspace:
+    """Every intermediate buffer of one forward, allocated once per (device, geometry)."""
+
+    def __init__(self, geo: Geometry, device, keep_logits: bool = False, keep_gate_up: bool = True):
+        n, k, e = geo.n_tokens, geo.top_k, geo.n_experts
+        rows = geo.rows_cap
+        i32 = dict(dtype=torch.int32, device=device)
+        self.geo = geo
+        self.topk_idx = torch.empty(n, k, **i32)
+        self.topk_w = torch.empty(n, k, dtype=torch.float32, device=device)
+        self.slot_rank = torch.empty(n, k, **i32)
+        self.block_counts = torch.empty(geo.router_blocks, e, **i32)
+        self.plan = torch.zeros(geo.plan_words, **i32)
+        self.slot_row = torch.empty(n, k, **i32)
+        self.row_token = torch.empty(rows, **i32)
+        self.xp = torch.empty(rows, geo.hidden, dtype=geo.dtype, device=device)
+        self.h = torch.empty(rows, geo.inter, dtype=geo.dtype, device=device)
+        self.y = torch.empty(rows, geo.hidden, dtype=geo.dtype, device=device)
+        self.gate_up = (torch.empty(rows, 2 * geo.inter, dtype=geo.dtype, device=device)
+                        if keep_gate_up else None)
+        self.rnorm = torch.empty(rows, dtype=torch.float32, device=device) if keep_gate_up else None
+        self.logits = torch.empty(n, e, dtype=torch.float32, device=device) if keep_logits else None
+        self.status = torch.zeros(1, **i32)
+        self.stage_events = None      # optional list of 7 torch.cuda.Event(enable_timing=True)
+        self._stage_event_array = None
+
+    def c_struct(self) -> _lib.Workspace:
+        p = _lib.ptr
+        ev = None
+        if self.stage_events is not None:
+            # torch creates the CUDA event lazily on first record
+            for e in self.stage_events:
+                if e.cuda_event == 0:
+                    e.record()
+            self._stage_event_array = (C.c_void_p * 7)(*[e.cuda_event for e in self.stage_events])
+            ev = C.cast(self._stage_event_array, C.c_void_p)
+        return _lib.Workspace(p(self.topk_idx), p(self.topk_w), p(self.slot_rank), p(self.block_counts),
+                              p(self.plan), p(self.slot_row), p(self.row_token), p(self.xp), p(self.h),
+                              p(self.y), p(self.gate_up), p(self.rnorm), p(self.logits), ev)
+
+    def enable_stage_timing(self) -> None:
+        """Ask bibo_moe_forward to record an event around every stage (see stage_ms)."""
+        self.stage_events = [torch.cuda.Event(enable_timing=True) for _ in range(7)]
+
+    STAGES = ("router", "plan", "permute", "gemm1_radial", "gemm2", "combine")
+
+    def stage_ms(self):
+        """Per-stage device time of the last forward (call after a synchronize)."""
+        ev = self.stage_events
+        return {n: ev[i].elapsed_time(ev[i + 1]) for i, n in enumerate(self.STAGES)}
+
+    # views into the plan buffer
+    def counts(self) -> torch.Tensor:
+        o = int(_lib.load().bibo_moe_plan_off_counts())
+        return self.plan[o:o + self.geo.n_experts]
+
+    def expert_off(self) -> torch.Tensor:
+        o = int(_lib.load().bibo_moe_plan_off_expert_off(self.geo.n_experts))
+        return self.plan[o:o + self.geo.n_glu + 1]
+
+    def tiles(self) -> torch.Tensor:
+        g = self.geo
+        o = int(_lib.load().bibo_moe_plan_off_tiles(g.n_tokens, g.n_experts, g.n_glu))
+        return self.plan[o:].view(-1, 4)
+
+
+_WS_CACHE: Dict[Tuple, MoEWorkspace] = {}
+
+
+def get_workspace(geo: Geometry, device, keep_logits=False, keep_gate_up=True, fresh=False) -> MoEWorkspace:
+    key = (torch.device(device), geo, keep_logits, keep_gate_up)
+    if fresh:
+        return MoEWorkspace(geo, device, keep_logits, keep_gate_up)
+    ws = _WS_CACHE.get(key)
+    if ws is None:
+        if len(_WS_CACHE) > 8:
+            _WS_CACHE.clear()
+        ws = _WS_CACHE[key] = MoEWorkspace(geo, device, keep_logits, keep_gate_up)
+    return ws
+
+
+def _shape(geo: Geometry, norm_mode, scale: float, zero_padding: bool) -> _lib.Shape:
+    return _lib.Shape(geo.n_tokens, geo.hidden, geo.inter, geo.n_experts, geo.n_glu, geo.n_pos, geo.top_k,
+                      norm_code(norm_mode), dtype_code(geo.dtype), float(scale), int(zero_padding))
+
+
+# ---------------------------------------------------------------------------------------------------
+# stage entry points (each is one C-ABI call)
+# ---------------------------------------------------------------------------------------------------
+def router_forward(x: Optional[torch.Tensor], w_router: Optional[torch.Tensor], bias: torch.Tensor,
+                   top_k: int, norm_mode="sum", scale: float = 1.0, ws: Optional[MoEWorkspace] = None,
+                   logits_in: Optional[torch.Tensor] = None, want_logits: bool = False):
+    """K1.  Returns (topk_idx int32 [N,k] ascending, topk_w fp32 [N,k], slot_rank, block_counts, logits|None)."""
+    lib = _lib.load()
+    src = x if logits_in is None else logits_in
+    _need_cuda(src, "router input")
+    n = src.shape[0]
+    e = bias.shape[0]
+    dev = src.device
+    hidden = x.shape[1] if x is not None else 0
+    dt = dtype_code(x.dtype) if x is not None else _lib.F32
+    if x is not None and w_router is not None and w_router.dtype != x.dtype:
+        raise RuntimeError(f"router weight dtype {w_router.dtype} != activation dtype {x.dtype}")
+    if ws is None:
+        i32 = dict(dtype=torch.int32, device=dev)
+        idx = torch.empty(n, top_k, **i32)
+        w = torch.empty(n, top_k, dtype=torch.float32, device=dev)
+        rank = torch.empty(n, top_k, **i32)
+        bc = torch.empty(int(lib.bibo_moe_router_blocks(n)), e, **i32)
+    else:
+        idx, w, rank, bc = ws.topk_idx, ws.topk_w, ws.slot_rank, ws.block_counts
+    logits = torch.empty(n, e, dtype=torch.float32, device=dev) if want_logits else None
+    bias32 = bias if bias.dtype == torch.float32 else bias.float()
+    rc = lib.bibo_moe_router_fwd(_lib.ptr(x), _lib.ptr(w_router), _lib.ptr(bias32), _lib.ptr(logits_in), n, hidden,
+                                 e, top_k, norm_code(norm_mode), float(scale), dt, _lib.ptr(logits),
+                                 _lib.ptr(idx), _lib.ptr(w), _lib.ptr(rank), _lib.ptr(bc), _stream(dev))
+    _lib.check(rc, "bibo_moe_router_fwd")
+    return idx, w, rank, bc, logits
+
+
+def launch_count() -> int:
+    return int(_lib.load().bibo_moe_launch_count())
+
+
+def moe_forward(x: torch.Tensor, w_router: torch.Tensor, bias: torch.Tensor, gate_up_proj: torch.Tensor,
+                down_proj: torch.Tensor, theta: torch.Tensor, top_k: int, norm_mode="sum", scale: float = 1.0,
+                n_pos: int = 0, n_neg: int = 0, ws: Optional[MoEWorkspace] = None, out: Optional[torch.Tensor] = None,
+                zero_padding: bool = False, keep_logits: bool = False) -> Tuple[torch.Tensor, MoEWorkspace]:
+    """The whole block on flat tokens x [N,H]: one call of bibo_moe_forward.  Returns (out, workspace)."""
+    lib = _lib.load()
+    for name, t in (("x", x), ("w_router", w_router), ("bias", bias), ("gate_up_proj", gate_up_proj),
+                    ("down_proj", down_proj), ("radial_theta", theta)):
+        _need_cuda(t, name)
+    n, hidden = x.shape
+    n_glu, two_i, _ = gate_up_proj.shape
+    geo = Geometry(n, hidden, two_i // 2, w_router.shape[0], n_glu, n_pos, top_k, x.dtype)
+    if geo.n_experts != n_glu + n_pos + n_neg:
+        raise RuntimeError(f"{geo.n_experts} routed experts != {n_glu} GLU + {n_pos} + {n_neg} identity experts")
+    for name, t in (("w_router", w_router), ("gate_up_proj", gate_up_proj), ("down_proj", down_proj)):
+        if t.dtype != x.dtype:
+            raise RuntimeError(f"{name} dtype {t.dtype} != activation dtype {x.dtype}")
+    if ws is None:
+        ws = get_workspace(geo, x.device, keep_logits=keep_logits)
+    if out is None:
+        out = torch.empty_like(x)
+    if n == 0:
+        return out, ws
+    bias32 = bias if bias.dtype == torch.float32 else bias.float()
+    theta32 = theta if theta.dtype == torch.float32 else theta.float()
+    shape = _shape(geo, norm_mode, scale, zero_padding)
+    cws = ws.c_struct()
+    rc = lib.bibo_moe_forward(C.byref(shape), _lib.ptr(x), _lib.ptr(w_router), _lib.ptr(bias32),
+                              _lib.ptr(gate_up_proj), _lib.ptr(down_proj), _lib.ptr(theta32), C.byref(cws),
+                              _lib.ptr(out), _stream(x.device))
+    _lib.check(rc, "bibo_moe_forward")
+    return out, ws
+
+
+def moe_forward_host(x_host: torch.Tensor, out_host: torch.Tensor, x_dev: torch.Tensor, out_dev: torch.Tensor,
+                     w_router, bias, gate_up_proj, down_proj, theta, top_k: int, norm_mode="sum",
+                     scale: float = 1.0, ws: Optional[MoEWorkspace] = None) -> torch.Tensor:
+    """Host-buffer variant (bibo_moe_forward_host): x_host -> device, block, -> out_host, then waits."""
+    lib = _lib.load()
+    n, hidden = x_host.shape
+    n_glu, two_i, _ = gate_up_proj.shape
+    geo = Geometry(n, hidden, two_i // 2, w_router.shape[0], n_glu, 0, top_k, x_host.dtype)
+    if ws is None:
+        ws = get_workspace(geo, x_dev.device)
+    shape = _shape(geo, norm_mode, scale, False)
+    cws = ws.c_struct()
+    rc = lib.bibo_moe_forward_host(C.byref(shape), _lib.ptr(x_host), _lib.ptr(x_dev), _lib.ptr(w_router),
+                                   _lib.ptr(bias), _lib.ptr(gate_up_proj), _lib.ptr(down_proj), _lib.ptr(theta),
+                                   C.byref(cws), _lib.ptr(out_dev), _lib.ptr(out_host), _stream(x_dev.device))
+    _lib.check(rc, "bibo_moe_forward_host")
+    return out_host
+
+
+def experts_forward(x: torch.Tensor, topk_idx: torch.Tensor, topk_w: torch.Tensor, gate_up_proj: torch.Tensor,
+                    down_proj: torch.Tensor, theta: torch.Tensor, n_experts: int, n_pos: int = 0,
+                    ws: Optional[MoEWorkspace] = None, zero_padding: bool = False) -> Tuple[torch.Tensor, MoEWorkspace]:
+    """Experts on routing decided by the caller (the BiBoFusedExperts.forward seam): rank, plan,
+    permute, the two grouped GEMMs and the combine as separate C-ABI calls."""
+    lib = _lib.load()
+    for name, t in (("x", x), ("top_k_indices", topk_idx), ("top_k_weights", topk_w)):
+        _need_cuda(t, name)
+    n, hidden = x.shape
+    k = topk_idx.shape[1]
+    n_glu, two_i, _ = gate_up_proj.shape
+    inter = two_i // 2
+    geo = Geometry(n, hidden, inter, n_experts, n_glu, n_pos, k, x.dtype)
+    if ws is None:
+        ws = get_workspace(geo, x.device)
+    out = torch.empty_like(x)
+    if n == 0:
+        return out, ws
+    dt, st = dtype_code(x.dtype), _stream(x.device)
+    idx32 = topk_idx.to(torch.int32).contiguous()
+    w32 = topk_w.to(torch.float32).contiguous()
+    theta32 = theta if theta.dtype == torch.float32 else theta.float()
+    p = _lib.ptr
+    ws.status.zero_()
+    _lib.check(lib.bibo_moe_route_from_indices(p(idx32), n, n_experts, k, p(ws.slot_rank), p(ws.block_counts),
+                                               p(ws.status), st), "bibo_moe_route_from_indices")
+    _lib.check(lib.bibo_moe_plan(p(ws.block_counts), n, k, n_experts, n_glu, p(ws.plan), st), "bibo_moe_plan")
+    _lib.check(lib.bibo_moe_permute_fwd(p(x), p(idx32), p(ws.slot_rank), p(ws.plan), n, hidden, n_experts, n_glu, k,
+                                        dt, int(zero_padding), p(ws.xp), p(ws.slot_row), p(ws.row_token), st),
+               "bibo_moe_permute_fwd")
+    _lib.check(lib.bibo_moe_gemm1_radial_fwd(p(ws.xp), p(gate_up_proj), p(theta32), p(ws.plan), n, hidden, inter,
+                                             n_experts, n_glu, k, dt, p(ws.h), p(ws.gate_up), p(ws.rnorm), st),
+               "bibo_moe_gemm1_radial_fwd")
+    _lib.check(lib.bibo_moe_gemm2_fwd(p(ws.h), p(down_proj), p(ws.plan), n, hidden, inter, n_experts, n_glu, k, dt,
+                                      p(ws.y), st), "bibo_moe_gemm2_fwd")
+    _lib.check(lib.bibo_moe_combine_fwd(p(ws.y), p(x), p(ws.slot_row), p(idx32), p(w32), n, hidden, k, n_glu, n_pos,
+                                        dt, p(out), st), "bibo_moe_combine_fwd")
+    ws.topk_idx_external = idx32  # keep alive until the stream has consumed it
+    ws.topk_w_external = w32
+    return out, ws
+
+
+def plan_header(ws: MoEWorkspace):
+    """Debug: (n_tiles, rows_used, status) read back from the device (synchronises the stream)."""
+    lib = _lib.load()
+    hdr = (C.c_int32 * 4)()
+    rc = lib.bibo_moe_debug_plan_header(_lib.ptr(ws.plan), C.cast(hdr, C.c_void_p), _stream(ws.plan.device))
+    _lib.check(rc, "bibo_moe_debug_plan_header")
+    return int(hdr[0]), int(hdr[1]), int(hdr[2])

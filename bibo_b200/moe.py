@@ -1,0 +1,228 @@
+"""Drop-in modules for the BiBo sparse-MoE block, backed by libbibo_moe.so.
+
+The three classes mirror the reference's module API so that checkpoints, hooks and callers keep
+working when the classes are swapped (``bibo_b200.install``):
+
+* ``BiBoMoERouter``     <- src/modeling/ffn/router.py:10-51
+* ``BiBoFusedExperts``  <- src/modeling/ffn/moe.py:19-101
+* ``BiBoMoELayer``      <- src/modeling/ffn/moe.py:104-183
+
+Parameter / buffer names and shapes are the reference's: ``gate.gate_proj.weight [E,H]``,
+``gate.bias [E]`` (a Parameter with requires_grad=False), ``experts.gate_up_proj [E_glu,2I,H]``,
+``experts.down_proj [E_glu,H,I]``, ``experts.radial_theta [E_glu]``, buffer ``accumulated_tpe [E]``.
+
+Every forward runs CUDA kernels; CPU tensors raise.  Configurations outside the kernels' coverage
+(shared expert, float16) raise at construction or call time instead of silently taking another
+path.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass
+from typing import Optional
+
+import torch
+import torch.distributed as dist
+import torch.nn as nn
+
+from . import functional as Fn
+
+
+@dataclass
+class MoEConfig:
+    """The fields of the reference's BiBoConfig this block reads (src/configuration_bibo.py:39-59,
+    103-137).  Any object with these attributes works, including the reference's own config."""
+    hidden_size: int = 2048
+    moe_intermediate_size: int = 512
+    num_routed_experts: int = 64
+    num_experts_per_tok: int = 6
+    num_pos_identity_experts: int = 0
+    num_neg_identity_experts: int = 0
+    norm_topk_prob: object = "sum"
+    bias_update_factor: float = 0.4
+    bias_update_threshold: int = 8000
+    initializer_range: float = 0.02
+    use_shared_expert: bool = False
+    routed_scaling_factor: float = 1.0
+
+    @property
+    def num_glu_experts(self) -> int:
+        return self.num_routed_experts - self.num_pos_identity_experts - self.num_neg_identity_experts
+
+    @property
+    def special_expert_pairs(self) -> int:
+        return max(self.num_pos_identity_experts, self.num_neg_identity_experts)
+
+
+def _cfg(config, name, default=None):
+    v = getattr(config, name, default)
+    return default if v is None else v
+
+
+class BiBoMoERouter(nn.Module):
+    """Sigmoid router with bias-adjusted top-k selection (src/modeling/ffn/router.py:10-51)."""
+
+    def __init__(self, config):
+        super().__init__()
+        self.num_routed_experts = config.num_routed_experts
+        self.top_k = config.num_experts_per_tok
+        norm = _cfg(config, "norm_topk_prob", "sum")
+        self.norm_topk_prob = "sum" if norm is True else norm
+        self.routed_scaling_factor = float(_cfg(config, "routed_scaling_factor", 1.0))
+        self.bias = nn.Parameter(torch.zeros(self.num_routed_experts), requires_grad=False)
+        self._probe_gap = False
+        self.boundary_gap = None
+        self.gate_proj = nn.Linear(config.hidden_size, self.num_routed_experts, bias=False)
+        nn.init.normal_(self.gate_proj.weight, mean=0.0, std=_cfg(config, "initializer_range", 0.02))
+
+    def router_logits(self, hidden_states: torch.Tensor) -> torch.Tensor:
+        """fp32 logits [N,E] from the router kernel (router.py:25-26)."""
+        flat = hidden_states.reshape(-1, hidden_states.shape[-1]).contiguous()
+        return Fn.router_forward(flat, self.gate_proj.weight, self.bias, self.top_k, self.norm_topk_prob,
+                                 self.routed_scaling_factor, want_logits=True)[4]
+
+    def _set_gap(self, logits: torch.Tensor) -> None:
+        # diagnostic only (router.py:33-36); a handful of torch ops on the fp32 logits
+        with torch.no_grad():
+            tk = torch.sigmoid(logits).topk(self.top_k + 1, dim=-1).values
+            self.boundary_gap = (tk[..., self.top_k - 1] - tk[..., self.top_k]).mean()
+
+    def forward(self, hidden_states: torch.Tensor):
+        b, s, h = hidden_states.shape
+        flat = hidden_states.reshape(b * s, h).contiguous()
+        want_gap = self._probe_gap and self.top_k < self.num_routed_experts
+        idx, w, _, _, logits = Fn.router_forward(flat, self.gate_proj.weight, self.bias, self.top_k,
+                                                 self.norm_topk_prob, self.routed_scaling_factor,
+                                                 want_logits=want_gap)
+        if want_gap:
+            self._set_gap(logits)
+        return idx.view(b, s, -1).long(), w.view(b, s, -1)
+
+
+class BiBoFusedExperts(nn.Module):
+    """Stacked expert weights + the expert kernels on caller-supplied routing
+    (src/modeling/ffn/moe.py:19-101)."""
+
+    def __init__(self, config):
+        super().__init__()
+        n_pos = int(_cfg(config, "num_pos_identity_experts", _cfg(config, "special_expert_pairs", 0)))
+        n_neg = int(_cfg(config, "num_neg_identity_experts", _cfg(config, "special_expert_pairs", 0)))
+        self.num_routed_experts = config.num_routed_experts
+        self.num_glu_experts = int(_cfg(config, "num_glu_experts", self.num_routed_experts - n_pos - n_neg))
+        self.special_expert_pairs = int(_cfg(config, "special_expert_pairs", 0))
+        self.hidden_size = config.hidden_size
+        self.intermediate_size = config.moe_intermediate_size
+        std = _cfg(config, "initializer_range", 0.02)
+        self.gate_up_proj = nn.Parameter(torch.empty(self.num_glu_experts, 2 * self.intermediate_size, self.hidden_size))
+        self.down_proj = nn.Parameter(torch.empty(self.num_glu_experts, self.hidden_size, self.intermediate_size))
+        nn.init.normal_(self.gate_up_proj, mean=0.0, std=std)
+        nn.init.normal_(self.down_proj, mean=0.0, std=std)
+        self.radial_theta = nn.Parameter(torch.zeros(self.num_glu_experts))
+        self.pos_start = self.num_glu_experts
+        self.pos_end = self.pos_start + n_pos
+        self.neg_start = self.pos_end
+        self.neg_end = self.neg_start + n_neg
+
+    @property
+    def num_pos(self) -> int:
+        return self.pos_end - self.pos_start
+
+    @property
+    def num_neg(self) -> int:
+        return self.neg_end - self.neg_start
+
+    def forward(self, hidden_states: torch.Tensor, top_k_indices: torch.Tensor,
+                top_k_weights: torch.Tensor) -> torch.Tensor:
+        _refuse_grad(self, hidden_states, top_k_weights)
+        out, _ = Fn.experts_forward(hidden_states.contiguous(), top_k_indices, top_k_weights, self.gate_up_proj,
+                                    self.down_proj, self.radial_theta, self.num_routed_experts, self.num_pos)
+        return out
+
+
+def _refuse_grad(module: nn.Module, *tensors) -> None:
+    if not torch.is_grad_enabled():
+        return
+    if module.training or any(t.requires_grad for t in tensors):
+        raise NotImplementedError(
+            "bibo_b200: this build has forward kernels only; call under torch.no_grad() / in eval() "
+            "with inputs that do not require grad")
+
+
+class BiBoMoELayer(nn.Module):
+    """Router -> experts -> weighted combine, one C-ABI call (src/modeling/ffn/moe.py:104-183)."""
+
+    def __init__(self, config):
+        super().__init__()
+        self.hidden_size = config.hidden_size
+        self.num_routed_experts = config.num_routed_experts
+        self.num_experts_per_tok = config.num_experts_per_tok
+        self.bias_update_factor = _cfg(config, "bias_update_factor", 0.4)
+        self.bias_update_threshold = _cfg(config, "bias_update_threshold", 8000)
+        self.register_buffer("accumulated_tpe", torch.zeros(config.num_routed_experts, dtype=torch.float))
+        self._fwd_step = 0
+        self._update_every = None
+        self.experts = BiBoFusedExperts(config)
+        self.use_shared_expert = bool(_cfg(config, "use_shared_expert", False))
+        self.shared_experts_list = nn.ModuleList()
+        if self.use_shared_expert:
+            raise NotImplementedError(
+                "bibo_b200.BiBoMoELayer: use_shared_expert=True is outside the kernels' coverage "
+                "(the reference's default and every benchmark configuration have it off)")
+        self.gate = BiBoMoERouter(config)
+        self.last_workspace: Optional[Fn.MoEWorkspace] = None
+
+    # ---- load balancer: host logic unchanged from the reference (moe.py:131-155) --------------------
+    @torch.no_grad()
+    def update_bias(self, tokens_per_expert: torch.Tensor):
+        if self.bias_update_factor <= 0:
+            return
+        share = tokens_per_expert.detach().float()
+        share = share / share.sum().clamp_min(1.0)
+        self.gate.bias.add_(self.bias_update_factor * (share.mean() - share))
+
+    @torch.no_grad()
+    def _balance_from_counts(self, counts: torch.Tensor, num_tokens: int):
+        self.accumulated_tpe += counts.float()
+        if self._update_every is None:
+            self._update_every = max(1, round(self.bias_update_threshold / max(num_tokens, 1)))
+        self._fwd_step += 1
+        if self._fwd_step % self._update_every == 0:
+            if dist.is_available() and dist.is_initialized():
+                dist.all_reduce(self.accumulated_tpe, op=dist.ReduceOp.SUM)
+            tpe = self.accumulated_tpe.clone()
+            self.accumulated_tpe.zero_()
+            return tpe
+        return None
+
+    @torch.no_grad()
+    def _balance_step(self, top_k_indices: torch.Tensor, num_tokens: int):
+        """Reference signature (indices [B,S,k]); the forward itself feeds the kernel's histogram."""
+        counts = torch.bincount(top_k_indices.reshape(-1), minlength=self.num_routed_experts)
+        return self._balance_from_counts(counts, num_tokens)
+
+    # ---- forward -------------------------------------------------------------------------------------
+    def forward(self, hidden_states: torch.Tensor) -> torch.Tensor:
+        bsz, seq_len, hidden = hidden_states.shape
+        n = bsz * seq_len
+        _refuse_grad(self, hidden_states)
+        flat = hidden_states.reshape(n, hidden).contiguous()
+        gate, ex = self.gate, self.experts
+        want_gap = gate._probe_gap and gate.top_k < gate.num_routed_experts
+        out, ws = Fn.moe_forward(flat, gate.gate_proj.weight, gate.bias, ex.gate_up_proj, ex.down_proj,
+                                 ex.radial_theta, gate.top_k, gate.norm_topk_prob, gate.routed_scaling_factor,
+                                 n_pos=ex.num_pos, n_neg=ex.num_neg, keep_logits=want_gap)
+        self.last_workspace = ws
+        if want_gap:
+            gate._set_gap(ws.logits)
+        # replay the reference's diagnostic hook points only when someone is listening
+        if ex._forward_pre_hooks:
+            for hook in ex._forward_pre_hooks.values():
+                hook(ex, (flat, ws.topk_idx.long(), ws.topk_w))
+        if gate._forward_hooks:
+            res = (ws.topk_idx.view(bsz, seq_len, -1).long(), ws.topk_w.view(bsz, seq_len, -1))
+            for hook in gate._forward_hooks.values():
+                hook(gate, (hidden_states,), res)
+        if self.training and self.bias_update_factor > 0:
+            tpe = self._balance_from_counts(ws.counts(), n)
+            if tpe is not None:
+                self.update_bias(tpe)
+        return out.view(bsz, seq_len, hidden)

@@ -1,0 +1,198 @@
+/*
+ * bibo_moe.h -- C ABI of libbibo_moe.so: the BiBo sparse-MoE feed-forward block as a chain of
+ * sm_100a CUDA kernels.
+ *
+ * The reference project has no native plug-in interface for this path: it swaps kernels in by
+ * assigning Python callables onto its module classes (ablate/common/patches.py:177-180 assigns
+ * BiBoFusedExperts.forward, patches.py:290 assigns BiBoDecoderLayer._ffn_forward).  The entry
+ * points below sit UNDER that Python seam; each comment names the reference code the call
+ * replaces (paths inside the reference project).
+ *
+ * Conventions
+ *   - every pointer is a DEVICE pointer unless the parameter name ends in _host;
+ *   - nothing here allocates device memory, synchronises the device or throws (the two _host
+ *     entry points and the explicitly named debug calls are the exceptions, documented at the call);
+ *   - work is enqueued on `stream` (a cudaStream_t passed as void*);
+ *   - return value 0 = success, negative = error; bibo_moe_last_error_string() describes the
+ *     last error of the calling thread;
+ *   - dtype: 0 = float32, 1 = bfloat16 (activations and weights share one dtype; router scores,
+ *     routing weights and all accumulation are float32).
+ *
+ * Row layout shared by the calls ("the plan")
+ *   N tokens, k slots per token, E routed experts of which the first E_glu own weights.  Rows of
+ *   expert e occupy [expert_off[e], expert_off[e] + counts[e]) of every expert-contiguous buffer;
+ *   expert_off[e] is a multiple of BIBO_TILE_M, so a BIBO_TILE_M-row tile never straddles two
+ *   experts.  Inside an expert, rows are in ascending token order.  plan_tiles[] lists the row
+ *   tiles: {expert, first row, valid rows, 0}.
+ */
+#ifndef BIBO_MOE_H_
+#define BIBO_MOE_H_
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define BIBO_TILE_M 128
+#define BIBO_ROUTER_BLOCK_TOKENS 128
+#define BIBO_MAX_TOP_K 8
+#define BIBO_MAX_EXPERTS 256
+
+enum { BIBO_F32 = 0, BIBO_BF16 = 1 };
+enum { BIBO_NORM_RAW = 0, BIBO_NORM_SUM = 1, BIBO_NORM_SOFTMAX = 2 };
+
+/* error codes */
+enum {
+  BIBO_OK = 0,
+  BIBO_ERR_ARG = -1,          /* bad size / null pointer / unsupported combination */
+  BIBO_ERR_ALIGN = -2,        /* pointer or leading dimension not 16-byte aligned   */
+  BIBO_ERR_CUDA = -3,         /* a CUDA runtime/driver call failed                  */
+  BIBO_ERR_UNSUPPORTED = -4,  /* shape outside what the kernels cover               */
+  BIBO_ERR_DEVICE_STATUS = -5 /* a kernel reported a non-zero status word           */
+};
+
+int bibo_moe_version(void);
+const char* bibo_moe_last_error_string(void);
+
+/* ---- sizes the caller needs to allocate buffers --------------------------------------------- */
+/* Upper bound of rows in an expert-contiguous buffer: N*k + E_glu*(BIBO_TILE_M-1), rounded up.  */
+int64_t bibo_moe_rows_cap(int64_t n_tokens, int top_k, int n_glu);
+/* Upper bound of row tiles.                                                                      */
+int64_t bibo_moe_tiles_cap(int64_t n_tokens, int top_k, int n_glu);
+/* Blocks the router kernel splits the tokens into (rows of block_counts / block_base).           */
+int64_t bibo_moe_router_blocks(int64_t n_tokens);
+/* int32 words in a plan buffer for these sizes (see bibo_moe_plan).                              */
+int64_t bibo_moe_plan_words(int64_t n_tokens, int top_k, int n_experts, int n_glu);
+
+/* ---- K1: router ------------------------------------------------------------------------------
+ * Replaces BiBoMoERouter.router_logits + forward (src/modeling/ffn/router.py:25-51) and the
+ * bincount of BiBoFusedExperts.forward / _balance_step (src/modeling/ffn/moe.py:65,140-143).
+ * logits = x @ w_router^T with fp32 accumulation; score = sigmoid(logit); selection on
+ * score + bias, ties to the lower expert index; weights from the un-biased scores, normalised per
+ * norm_mode and multiplied by scale.  The k experts of a token are written in ASCENDING expert
+ * index.  Also writes, per block of BIBO_ROUTER_BLOCK_TOKENS tokens, the per-expert histogram
+ * (block_counts [blocks, E]) and each slot's rank among the block's earlier tokens that picked
+ * the same expert (slot_rank [N, k]).
+ * logits_out may be NULL.  If logits_in is non-NULL the matrix product is skipped and the
+ * selection runs on the given fp32 logits (test entry: selection parity on identical logits).   */
+int bibo_moe_router_fwd(const void* x, const void* w_router, const float* bias,
+                        const float* logits_in, int64_t n_tokens, int hidden, int n_experts,
+                        int top_k, int norm_mode, float scale, int dtype,
+                        float* logits_out, int32_t* topk_idx, float* topk_w,
+                        int32_t* slot_rank, int32_t* block_counts, void* stream);
+
+/* Histogram and ranks for routing decided by the caller: the BiBoFusedExperts.forward(x, idx, w)
+ * seam (src/modeling/ffn/moe.py:47-52).  topk_idx [N,k] int32 in any order.  status (optional
+ * device int32, zeroed by the caller) is set to 2 for an index outside [0,E) (treated as expert 0)
+ * and to 3 when a token names one expert twice.                                                  */
+int bibo_moe_route_from_indices(const int32_t* topk_idx, int64_t n_tokens, int n_experts, int top_k,
+                                int32_t* slot_rank, int32_t* block_counts, int32_t* status,
+                                void* stream);
+
+/* ---- plan: histogram -> offsets ---------------------------------------------------------------
+ * Replaces the sort / bincount / cumsum / .tolist() of BiBoFusedExperts.forward
+ * (src/modeling/ffn/moe.py:56-68) without a host synchronisation.
+ * plan layout (int32 words): [0]=n_tiles [1]=rows used [2]=status [3]=reserved,
+ * then counts[E], expert_off[E_glu+1], block_base[blocks*E] (exclusive prefix of block_counts over
+ * blocks), tiles[tiles_cap*4].  Accessors below return the word offsets.                         */
+int bibo_moe_plan(const int32_t* block_counts, int64_t n_tokens, int top_k, int n_experts,
+                  int n_glu, int32_t* plan, void* stream);
+int64_t bibo_moe_plan_off_counts(void);
+int64_t bibo_moe_plan_off_expert_off(int n_experts);
+int64_t bibo_moe_plan_off_block_base(int n_experts, int n_glu);
+int64_t bibo_moe_plan_off_tiles(int64_t n_tokens, int n_experts, int n_glu);
+
+/* ---- K2: permute ------------------------------------------------------------------------------
+ * Replaces `current_state = hidden_states[token_idx]` (src/modeling/ffn/moe.py:77,81) for all
+ * experts at once: writes x rows into expert-contiguous rows xp [rows_cap, H]; also writes
+ * slot_row [N,k] (row of every slot, -1 for an expert without weights) and row_token [rows_cap]
+ * (token of every row, -1 for padding).  zero_padding != 0 also zero-fills the padding rows of xp
+ * (needed when a later reduction runs over rows, i.e. for weight gradients).                     */
+int bibo_moe_permute_fwd(const void* x, const int32_t* topk_idx, const int32_t* slot_rank,
+                         const int32_t* plan, int64_t n_tokens, int hidden, int n_experts,
+                         int n_glu, int top_k, int dtype, int zero_padding,
+                         void* xp, int32_t* slot_row, int32_t* row_token, void* stream);
+
+/* ---- K3: grouped gate/up GEMM + Radial NormSiLU -----------------------------------------------
+ * Replaces F.linear(x_e, gate_up_proj[e]), chunk, r = sqrt(mean g^2 + 1e-6), p = sigmoid(theta_e),
+ * a = silu(g/r) * r^p, a * up  (src/modeling/ffn/moe.py:84-92 up to the input of the down
+ * projection).  xp [rows_cap,H], gate_up_proj [E_glu, 2I, H], theta fp32 [E_glu] -> h [rows_cap,I].
+ * gate_up_out (optional, [rows_cap, 2I] in dtype) receives the raw gate|up rows, rnorm_out
+ * (optional fp32 [rows_cap]) receives r; both are what the backward pass re-reads.               */
+int bibo_moe_gemm1_radial_fwd(const void* xp, const void* gate_up_proj, const float* theta,
+                              const int32_t* plan, int64_t n_tokens, int hidden, int inter,
+                              int n_experts, int n_glu, int top_k, int dtype,
+                              void* h, void* gate_up_out, float* rnorm_out, void* stream);
+
+/* ---- K4: grouped down GEMM ---------------------------------------------------------------------
+ * Replaces F.linear(activated * up, down_proj[e]) (src/modeling/ffn/moe.py:92).
+ * h [rows_cap, I], down_proj [E_glu, H, I] -> y [rows_cap, H].                                    */
+int bibo_moe_gemm2_fwd(const void* h, const void* down_proj, const int32_t* plan,
+                       int64_t n_tokens, int hidden, int inter, int n_experts, int n_glu,
+                       int top_k, int dtype, void* y, void* stream);
+
+/* ---- K5: weighted combine ----------------------------------------------------------------------
+ * Replaces output.index_add_(0, token_idx, expert_output * weights) over all experts and the final
+ * cast (src/modeling/ffn/moe.py:70-71,93-101): out[t] = sum_j w[t,j] * y[slot_row[t,j]], fp32
+ * accumulation in ascending expert order, one cast at the end.  Slots of +Identity / -Identity
+ * experts (index >= n_glu; the first n_pos of them positive) add +w*x[t] / -w*x[t].               */
+int bibo_moe_combine_fwd(const void* y, const void* x, const int32_t* slot_row,
+                         const int32_t* topk_idx, const float* topk_w, int64_t n_tokens,
+                         int hidden, int top_k, int n_glu, int n_pos, int dtype, void* out,
+                         void* stream);
+
+/* ---- whole block -------------------------------------------------------------------------------
+ * Replaces BiBoMoELayer.forward in eval mode without shared expert
+ * (src/modeling/ffn/moe.py:157-183).  All buffers are caller-allocated; `ws` groups the
+ * intermediates so a caller can keep one set per (device, shape).                                 */
+typedef struct {
+  int32_t* topk_idx;      /* [N,k]                      */
+  float* topk_w;          /* [N,k]                      */
+  int32_t* slot_rank;     /* [N,k]                      */
+  int32_t* block_counts;  /* [router_blocks, E]         */
+  int32_t* plan;          /* [plan_words]               */
+  int32_t* slot_row;      /* [N,k]                      */
+  int32_t* row_token;     /* [rows_cap]                 */
+  void* xp;               /* [rows_cap, H]  dtype       */
+  void* h;                /* [rows_cap, I]  dtype       */
+  void* y;                /* [rows_cap, H]  dtype       */
+  void* gate_up;          /* optional [rows_cap, 2I]    */
+  float* rnorm;           /* optional [rows_cap]        */
+  float* logits;          /* optional [N,E]             */
+  void* const* stage_events; /* optional HOST array of 7 cudaEvent_t: [i] is recorded on the stream
+                                before stage i (router, plan, permute, gate/up, down, combine) and
+                                [6] after the last; lets a caller time each kernel without extra
+                                launches or synchronisation                                        */
+} bibo_moe_workspace;
+
+typedef struct {
+  int64_t n_tokens;
+  int hidden, inter, n_experts, n_glu, n_pos, top_k, norm_mode, dtype;
+  float scale;            /* routed_scaling_factor */
+  int zero_padding;
+} bibo_moe_shape;
+
+int bibo_moe_forward(const bibo_moe_shape* shape, const void* x, const void* w_router,
+                     const float* bias, const void* gate_up_proj, const void* down_proj,
+                     const float* theta, const bibo_moe_workspace* ws, void* out, void* stream);
+
+/* Same block with HOST input and output: copies x_host to x_dev, runs bibo_moe_forward, copies the
+ * result into out_host and waits for it.  x_dev / out_dev are caller-allocated device staging
+ * buffers [N,H]; weights stay resident on the device.  This is the call the end-to-end timing
+ * uses (host->device and device->host copies inside the call).                                    */
+int bibo_moe_forward_host(const bibo_moe_shape* shape, const void* x_host, void* x_dev,
+                          const void* w_router, const float* bias, const void* gate_up_proj,
+                          const void* down_proj, const float* theta, const bibo_moe_workspace* ws,
+                          void* out_dev, void* out_host, void* stream);
+
+/* Debug: copies plan[0..3] to the host (synchronises `stream`) and returns plan[2] (status).     */
+int bibo_moe_debug_plan_header(const int32_t* plan, int32_t* header4_host, void* stream);
+
+/* Number of kernels this library has launched from the calling process so far.                   */
+int64_t bibo_moe_launch_count(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* BIBO_MOE_H_ */
