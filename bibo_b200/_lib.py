@@ -42,7 +42,7 @@ SIGNATURES = {
     "bibo_moe_router_blocks": (_i64, [_i64]),
     "bibo_moe_plan_words": (_i64, [_i64, _i32, _i32, _i32]),
     "bibo_moe_router_fwd": (_i32, [_vp, _vp, _vp, _vp, _i64, _i32, _i32, _i32, _i32, _f32, _i32,
-                                   _vp, _vp, _vp, _vp, _vp, _vp]),
+                                   _vp, _vp, _vp, _vp, _vp, _vp, _vp]),
     "bibo_moe_route_from_indices": (_i32, [_vp, _i64, _i32, _i32, _vp, _vp, _vp, _vp]),
     "bibo_moe_plan": (_i32, [_vp, _i64, _i32, _i32, _i32, _vp, _vp]),
     "bibo_moe_plan_off_counts": (_i64, []),
@@ -53,6 +53,7 @@ SIGNATURES = {
                                     _vp, _vp, _vp, _vp]),
     "bibo_moe_gemm1_radial_fwd": (_i32, [_vp, _vp, _vp, _vp, _i64, _i32, _i32, _i32, _i32, _i32,
                                          _i32, _vp, _vp, _vp, _vp]),
+    "bibo_moe_gemm1_is_fused": (_i32, [_i32, _i32, _i32]),
     "bibo_moe_gemm2_fwd": (_i32, [_vp, _vp, _vp, _i64, _i32, _i32, _i32, _i32, _i32, _i32, _vp, _vp]),
     "bibo_moe_combine_fwd": (_i32, [_vp, _vp, _vp, _vp, _vp, _i64, _i32, _i32, _i32, _i32, _i32,
                                     _vp, _vp]),

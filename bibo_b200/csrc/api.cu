@@ -60,6 +60,10 @@ extern "C" int bibo_moe_gemm1_radial_fwd(const void* xp, const void* gate_up_pro
                             rnorm_out, st);
 }
 
+extern "C" int bibo_moe_gemm1_is_fused(int hidden, int inter, int dtype) {
+  return gemm1_tc_supported(hidden, inter, dtype);
+}
+
 extern "C" int bibo_moe_gemm2_fwd(const void* h, const void* down_proj, const int32_t* plan,
                                   int64_t n_tokens, int hidden, int inter, int n_experts, int n_glu,
                                   int top_k, int dtype, void* y, void* stream) {
@@ -86,7 +90,7 @@ extern "C" int bibo_moe_forward(const bibo_moe_shape* s, const void* x, const vo
   BIBO_STAGE(0);
   int rc = bibo_moe_router_fwd(x, w_router, bias, nullptr, s->n_tokens, s->hidden, s->n_experts, s->top_k,
                                s->norm_mode, s->scale, s->dtype, ws->logits, ws->topk_idx, ws->topk_w,
-                               ws->slot_rank, ws->block_counts, stream);
+                               ws->slot_rank, ws->block_counts, ws->plan ? ws->plan + PLAN_STATUS : nullptr, stream);
   if (rc) return rc;
   BIBO_STAGE(1);
   rc = bibo_moe_plan(ws->block_counts, s->n_tokens, s->top_k, s->n_experts, s->n_glu, ws->plan, stream);

@@ -1,19 +1,553 @@
-// Tensor-core (tcgen05 / TMEM / TMA) kernels: placeholder until the kernels land.
-#include "common.cuh"
+// K3 / K4 on the 5th-generation tensor cores: grouped bf16 GEMMs over the plan's row tiles with
+// TMA-fed shared-memory pipelines, tcgen05.mma accumulating in tensor memory, and warp-specialised
+// persistent CTAs (warp 0 = TMA producer, warp 1 = MMA issuer, warps 2-5 = epilogue).
+//
+//  gemm2_tc_kernel : y[rows, H]  = h[rows, I] x down_proj[e][H, I]^T
+//  gemm1_tc_kernel : gate|up     = xp[rows, H] x gate_up_proj[e][2I, H]^T, then the Radial NormSiLU
+//                    epilogue r = sqrt(mean g^2 + 1e-6), a = silu(g/r) r^p, h = a * up.  The row
+//                    reduction spans all I gate columns: a CTA owns NC <= 256 of them (gate and up
+//                    accumulators = 2*NC tensor-memory columns), so for I = 512 two CTAs of a
+//                    cluster split the columns and exchange their partial sums of squares through
+//                    distributed shared memory.
+#include <map>
+#include <mutex>
+#include <tuple>
+
+#include "tc_common.cuh"
+
 namespace bibo {
-int router_tc_supported(int, int, int) { return 0; }
-int router_tc_launch(const void*, const void*, const float*, int64_t, int, int, int, int, float, float*,
-                     int32_t*, float*, int32_t*, int32_t*, cudaStream_t) {
-  return fail(BIBO_ERR_UNSUPPORTED, "router_tc: not built");
+namespace tc {
+
+constexpr int BM = BIBO_TILE_M;   // rows per tile (TMEM lanes)
+constexpr int BK = 64;            // k-block: 64 bf16 = one 128-byte swizzle row
+constexpr int UK = 16;            // k per tcgen05.mma
+constexpr int A_BYTES = BM * BK * 2;
+constexpr int C_SUB = BM * 128;   // one [128 rows x 64 cols] bf16 staging sub-tile
+constexpr int NUM_THREADS = 192;
+constexpr int EPI_THREADS = 128;
+
+__device__ __forceinline__ uint32_t pack_bf16(float a, float b) {
+  __nv_bfloat162 v = __floats2bfloat162_rn(a, b);
+  return *reinterpret_cast<uint32_t*>(&v);
 }
-int gemm1_tc_supported(int, int, int) { return 0; }
-int gemm1_tc_launch(const void*, const void*, const float*, const int32_t*, int64_t, int, int, int, int, int,
-                    void*, void*, float*, cudaStream_t) {
-  return fail(BIBO_ERR_UNSUPPORTED, "gemm1_tc: not built");
+__device__ __forceinline__ float bf16_lo(uint32_t v) { return __uint_as_float(v << 16); }
+__device__ __forceinline__ float bf16_hi(uint32_t v) { return __uint_as_float(v & 0xffff0000u); }
+__device__ __forceinline__ float round_bf16(float v) { return __bfloat162float(__float2bfloat16_rn(v)); }
+
+// byte offset of 16-byte chunk `chunk` (0..7) of row `row` inside a 128B-swizzled [128][128B] sub-tile
+__device__ __forceinline__ uint32_t swz(int row, int chunk) { return row * 128 + ((chunk ^ (row & 7)) << 4); }
+
+struct PipeState {
+  int stage = 0;
+  uint32_t phase = 0;
+  template <int STAGES> __device__ __forceinline__ void next() {
+    if (++stage == STAGES) { stage = 0; phase ^= 1; }
+  }
+};
+
+// =====================================================================================================
+// K4: down projection
+// =====================================================================================================
+template <int BN, int STAGES>
+struct G2Layout {
+  static constexpr int B_BYTES = BN * BK * 2;
+  static constexpr int OFF_A = 0;
+  static constexpr int OFF_B = OFF_A + STAGES * A_BYTES;
+  static constexpr int OFF_C = OFF_B + STAGES * B_BYTES;
+  static constexpr int OFF_BAR = OFF_C + 2 * C_SUB;
+  static constexpr int BYTES = OFF_BAR + 256 + 1024;  // barriers + alignment slack
+};
+
+template <int BN, int STAGES>
+__global__ void __launch_bounds__(NUM_THREADS, 1)
+gemm2_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
+                const __grid_constant__ CUtensorMap tmC, int32_t* __restrict__ plan, int64_t tiles_off,
+                int n_chunks, int k_blocks, int n_out) {
+  using L = G2Layout<BN, STAGES>;
+  extern __shared__ unsigned char smem_dyn[];
+  unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_dyn) + 1023) & ~uintptr_t(1023));
+  uint64_t* full = reinterpret_cast<uint64_t*>(smem + L::OFF_BAR);
+  uint64_t* empty = full + STAGES;
+  uint64_t* tfull = empty + STAGES;
+  uint64_t* tempty = tfull + 2;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tempty + 2);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1); }
+    for (int b = 0; b < 2; ++b) { mbar_init(&tfull[b], 1); mbar_init(&tempty[b], 4); }
+    *abort_flag = 0;
+    fence_barrier_init();
+    prefetch_tmap(&tmA); prefetch_tmap(&tmB); prefetch_tmap(&tmC);
+  }
+  if (warp == 1) { tmem_alloc(tmem_slot, 2 * BN); tmem_relinquish(); }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+  const int n_work = plan[PLAN_N_TILES] * n_chunks;
+  const int4* tiles = reinterpret_cast<const int4*>(plan + tiles_off);
+
+  if (warp == 0) {
+    if (elect_one()) {
+      PipeState ps;
+      for (int w = blockIdx.x; w < n_work; w += gridDim.x) {
+        const int4 t = tiles[w / n_chunks];
+        const int n0 = (w % n_chunks) * BN;
+        bool ok = true;
+        for (int kb = 0; kb < k_blocks && ok; ++kb) {
+          ok = mbar_wait(&empty[ps.stage], ps.phase ^ 1, abort_flag);
+          if (!ok) break;
+          mbar_expect_tx(&full[ps.stage], A_BYTES + L::B_BYTES);
+          tma_load_2d(smem + L::OFF_A + ps.stage * A_BYTES, &tmA, &full[ps.stage], kb * BK, t.y);
+          tma_load_2d(smem + L::OFF_B + ps.stage * L::B_BYTES, &tmB, &full[ps.stage], kb * BK, t.x * n_out + n0);
+          ps.next<STAGES>();
+        }
+        if (!ok) break;
+      }
+    }
+  } else if (warp == 1) {
+    if (elect_one()) {
+      constexpr uint32_t idesc = make_idesc_bf16(BM, BN);
+      PipeState ps;
+      int acc = 0;
+      uint32_t acc_phase = 0;
+      for (int w = blockIdx.x; w < n_work; w += gridDim.x) {
+        if (!mbar_wait(&tempty[acc], acc_phase ^ 1, abort_flag)) break;
+        tc_fence_after();
+        bool ok = true;
+        for (int kb = 0; kb < k_blocks; ++kb) {
+          ok = mbar_wait(&full[ps.stage], ps.phase, abort_flag);
+          if (!ok) break;
+          tc_fence_after();
+          const uint64_t da = make_sdesc_k128(smem_u32(smem + L::OFF_A + ps.stage * A_BYTES));
+          const uint64_t db = make_sdesc_k128(smem_u32(smem + L::OFF_B + ps.stage * L::B_BYTES));
+#pragma unroll
+          for (int k = 0; k < BK / UK; ++k)
+            umma_bf16(tmem_base + acc * BN, da + k * 2, db + k * 2, idesc, (kb | k) != 0);
+          umma_commit(&empty[ps.stage]);
+          ps.next<STAGES>();
+        }
+        if (!ok) break;
+        umma_commit(&tfull[acc]);
+        acc ^= 1;
+        if (acc == 0) acc_phase ^= 1;
+      }
+    }
+  } else {
+    const int q = warp & 3;                     // TMEM lane quadrant this warp may read
+    const int row = q * 32 + lane;
+    const bool issuer = (threadIdx.x == 64);
+    int acc = 0, buf = 0;
+    uint32_t acc_phase = 0;
+    for (int w = blockIdx.x; w < n_work; w += gridDim.x) {
+      const int4 t = tiles[w / n_chunks];
+      const int n0 = (w % n_chunks) * BN;
+      if (!mbar_wait(&tfull[acc], acc_phase, abort_flag)) break;
+      tc_fence_after();
+#pragma unroll 1
+      for (int g = 0; g < BN / 64; ++g) {
+        if (issuer) asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory");
+        named_bar_sync(1, EPI_THREADS);
+        unsigned char* cbuf = smem + L::OFF_C + buf * C_SUB;
+#pragma unroll
+        for (int hh = 0; hh < 2; ++hh) {
+          uint32_t r[32];
+          tmem_ld32(tmem_base + ((uint32_t)(q * 32) << 16) + acc * BN + g * 64 + hh * 32, r);
+          tmem_ld_wait();
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            uint4 v;
+            v.x = pack_bf16(__uint_as_float(r[8 * j + 0]), __uint_as_float(r[8 * j + 1]));
+            v.y = pack_bf16(__uint_as_float(r[8 * j + 2]), __uint_as_float(r[8 * j + 3]));
+            v.z = pack_bf16(__uint_as_float(r[8 * j + 4]), __uint_as_float(r[8 * j + 5]));
+            v.w = pack_bf16(__uint_as_float(r[8 * j + 6]), __uint_as_float(r[8 * j + 7]));
+            *reinterpret_cast<uint4*>(cbuf + swz(row, hh * 4 + j)) = v;
+          }
+        }
+        if (g == BN / 64 - 1) {  // accumulator fully read: hand it back to the MMA warp
+          tc_fence_before();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(&tempty[acc]);
+        }
+        fence_proxy_async_smem();
+        named_bar_sync(1, EPI_THREADS);
+        if (issuer) {
+          tma_store_2d(&tmC, cbuf, n0 + g * 64, t.y);
+          tma_store_commit();
+        }
+        buf ^= 1;
+      }
+      acc ^= 1;
+      if (acc == 0) acc_phase ^= 1;
+    }
+    if (issuer) tma_store_wait_all();
+  }
+  __syncwarp();
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) { tc_fence_after(); tmem_dealloc(tmem_base, 2 * BN); }
+  if (threadIdx.x == 0 && *abort_flag) atomicExch(&plan[PLAN_STATUS], 100);
 }
-int gemm2_tc_supported(int, int, int) { return 0; }
-int gemm2_tc_launch(const void*, const void*, const int32_t*, int64_t, int, int, int, int, int, void*,
-                    cudaStream_t) {
-  return fail(BIBO_ERR_UNSUPPORTED, "gemm2_tc: not built");
+
+// =====================================================================================================
+// K3: gate/up projection + Radial NormSiLU
+// =====================================================================================================
+template <int NC, int STAGES>
+struct G1Layout {
+  static constexpr int B_BYTES = NC * BK * 2;
+  static constexpr int OFF_A = 0;
+  static constexpr int OFF_B = OFF_A + STAGES * A_BYTES;
+  static constexpr int OFF_STASH = OFF_B + STAGES * B_BYTES;        // [NC/64][128][128B] bf16 gate, then h
+  static constexpr int OFF_PART = OFF_STASH + (NC / 64) * C_SUB;    // float [2][128] partial sums from the peer
+  static constexpr int OFF_BAR = OFF_PART + 2 * BM * 4;
+  static constexpr int BYTES = OFF_BAR + 256 + 1024;
+};
+
+template <int NC, int CL, int STAGES>
+__global__ void __launch_bounds__(NUM_THREADS, 1)
+gemm1_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
+                const __grid_constant__ CUtensorMap tmH, const float* __restrict__ theta,
+                int32_t* __restrict__ plan, int64_t tiles_off, int k_blocks, int inter,
+                __nv_bfloat16* __restrict__ gate_up_out, float* __restrict__ rnorm_out) {
+  using L = G1Layout<NC, STAGES>;
+  extern __shared__ unsigned char smem_dyn[];
+  unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_dyn) + 1023) & ~uintptr_t(1023));
+  float* part = reinterpret_cast<float*>(smem + L::OFF_PART);
+  uint64_t* full = reinterpret_cast<uint64_t*>(smem + L::OFF_BAR);
+  uint64_t* empty = full + STAGES;
+  uint64_t* gfull = empty + STAGES;   // gate accumulator complete
+  uint64_t* gempty = gfull + 1;       // gate accumulator drained
+  uint64_t* ufull = gempty + 1;
+  uint64_t* uempty = ufull + 1;
+  uint64_t* xbar = uempty + 1;        // [2] partial-sum exchange, arrivals come from the peer CTA
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(xbar + 2);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const uint32_t cr = (CL > 1) ? cluster_ctarank() : 0;   // column block of this CTA
+  const int cluster_id = blockIdx.x / CL, n_clusters = gridDim.x / CL;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1); }
+    mbar_init(gfull, 1); mbar_init(ufull, 1);
+    mbar_init(gempty, 4); mbar_init(uempty, 4);
+    mbar_init(&xbar[0], EPI_THREADS); mbar_init(&xbar[1], EPI_THREADS);
+    *abort_flag = 0;
+    fence_barrier_init();
+    prefetch_tmap(&tmA); prefetch_tmap(&tmB); prefetch_tmap(&tmH);
+  }
+  if (warp == 1) { tmem_alloc(tmem_slot, 2 * NC); tmem_relinquish(); }
+  tc_fence_before();
+  __syncthreads();
+  if (CL > 1) cluster_sync_all();   // peer barriers are initialised before anyone arrives on them
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+  const int n_tiles = plan[PLAN_N_TILES];
+  const int4* tiles = reinterpret_cast<const int4*>(plan + tiles_off);
+
+  if (warp == 0) {
+    if (elect_one()) {
+      PipeState ps;
+      bool ok = true;
+      for (int ti = cluster_id; ti < n_tiles && ok; ti += n_clusters) {
+        const int4 t = tiles[ti];
+        for (int pass = 0; pass < 2 && ok; ++pass) {
+          const int brow = t.x * 2 * inter + pass * inter + cr * NC;   // gate rows, then up rows
+          for (int kb = 0; kb < k_blocks; ++kb) {
+            ok = mbar_wait(&empty[ps.stage], ps.phase ^ 1, abort_flag);
+            if (!ok) break;
+            mbar_expect_tx(&full[ps.stage], A_BYTES + L::B_BYTES);
+            tma_load_2d(smem + L::OFF_A + ps.stage * A_BYTES, &tmA, &full[ps.stage], kb * BK, t.y);
+            tma_load_2d(smem + L::OFF_B + ps.stage * L::B_BYTES, &tmB, &full[ps.stage], kb * BK, brow);
+            ps.next<STAGES>();
+          }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    if (elect_one()) {
+      constexpr uint32_t idesc = make_idesc_bf16(BM, NC);
+      PipeState ps;
+      uint32_t it = 0;
+      bool ok = true;
+      for (int ti = cluster_id; ti < n_tiles && ok; ti += n_clusters, ++it) {
+        for (int pass = 0; pass < 2 && ok; ++pass) {
+          ok = mbar_wait(pass == 0 ? gempty : uempty, (it & 1) ^ 1, abort_flag);
+          if (!ok) break;
+          tc_fence_after();
+          for (int kb = 0; kb < k_blocks; ++kb) {
+            ok = mbar_wait(&full[ps.stage], ps.phase, abort_flag);
+            if (!ok) break;
+            tc_fence_after();
+            const uint64_t da = make_sdesc_k128(smem_u32(smem + L::OFF_A + ps.stage * A_BYTES));
+            const uint64_t db = make_sdesc_k128(smem_u32(smem + L::OFF_B + ps.stage * L::B_BYTES));
+#pragma unroll
+            for (int k = 0; k < BK / UK; ++k)
+              umma_bf16(tmem_base + pass * NC, da + k * 2, db + k * 2, idesc, (kb | k) != 0);
+            umma_commit(&empty[ps.stage]);
+            ps.next<STAGES>();
+          }
+          if (ok) umma_commit(pass == 0 ? gfull : ufull);
+        }
+      }
+    }
+  } else {
+    const int q = warp & 3;
+    const int row = q * 32 + lane;
+    const bool issuer = (threadIdx.x == 64);
+    const uint32_t lane_addr = tmem_base + ((uint32_t)(q * 32) << 16);
+    unsigned char* stash = smem + L::OFF_STASH;
+    uint32_t it = 0;
+    for (int ti = cluster_id; ti < n_tiles; ti += n_clusters, ++it) {
+      const int4 t = tiles[ti];
+      // the previous tile's stores must have finished reading the stash before it is overwritten
+      if (issuer) tma_store_wait_read();
+      named_bar_sync(1, EPI_THREADS);
+      if (!mbar_wait(gfull, it & 1, abort_flag)) break;
+      tc_fence_after();
+      float ss = 0.f;
+#pragma unroll 1
+      for (int c = 0; c < NC / 32; ++c) {
+        uint32_t r[32];
+        tmem_ld32(lane_addr + c * 32, r);
+        tmem_ld_wait();
+        unsigned char* sub = stash + (c >> 1) * C_SUB;
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          uint4 v;
+          uint32_t* pv = reinterpret_cast<uint32_t*>(&v);
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            const uint32_t pk = pack_bf16(__uint_as_float(r[8 * j + 2 * i]), __uint_as_float(r[8 * j + 2 * i + 1]));
+            const float a = bf16_lo(pk), b = bf16_hi(pk);   // the reference squares the bf16-rounded gate
+            ss = fmaf(a, a, ss);
+            ss = fmaf(b, b, ss);
+            pv[i] = pk;
+          }
+          *reinterpret_cast<uint4*>(sub + swz(row, (c & 1) * 4 + j)) = v;
+        }
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(gempty);
+      if (CL > 1) {
+        const uint32_t peer = cr ^ 1u;
+        st_remote_f32(&part[(it & 1) * BM + row], peer, ss);
+        mbar_arrive_remote(&xbar[it & 1], peer);
+        if (!mbar_wait<true>(&xbar[it & 1], (it >> 1) & 1, abort_flag)) break;
+        ss += part[(it & 1) * BM + row];
+      }
+      const float rn = sqrtf(ss / (float)inter + 1e-6f);
+      const float p = sigmoid_accurate(__ldg(theta + t.x));
+      const float gain = powf(rn, p);
+      const float inv_r = __fdiv_rn(1.0f, rn);
+      if (rnorm_out != nullptr && cr == 0) rnorm_out[t.y + row] = rn;
+
+      if (!mbar_wait(ufull, it & 1, abort_flag)) break;
+      tc_fence_after();
+      __nv_bfloat16* gu_row = gate_up_out ? gate_up_out + (int64_t)(t.y + row) * 2 * inter + cr * NC : nullptr;
+#pragma unroll 1
+      for (int c = 0; c < NC / 32; ++c) {
+        uint32_t r[32];
+        tmem_ld32(lane_addr + NC + c * 32, r);
+        tmem_ld_wait();
+        unsigned char* sub = stash + (c >> 1) * C_SUB;
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          uint4* slot = reinterpret_cast<uint4*>(sub + swz(row, (c & 1) * 4 + j));
+          const uint4 gv = *slot;
+          const uint32_t* pg = reinterpret_cast<const uint32_t*>(&gv);
+          uint4 hv, uv;
+          uint32_t* ph = reinterpret_cast<uint32_t*>(&hv);
+          uint32_t* pu = reinterpret_cast<uint32_t*>(&uv);
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            const uint32_t upk = pack_bf16(__uint_as_float(r[8 * j + 2 * i]), __uint_as_float(r[8 * j + 2 * i + 1]));
+            pu[i] = upk;
+            float hval[2];
+#pragma unroll
+            for (int s = 0; s < 2; ++s) {
+              const float g = s ? bf16_hi(pg[i]) : bf16_lo(pg[i]);
+              const float u = s ? bf16_hi(upk) : bf16_lo(upk);
+              const float z = g * inv_r;
+              const float a = round_bf16(__fdividef(z, 1.0f + __expf(-z)) * gain);   // activation is cast to bf16
+              hval[s] = a * u;                                                       // then multiplied in bf16
+            }
+            ph[i] = pack_bf16(hval[0], hval[1]);
+          }
+          *slot = hv;
+          if (gu_row != nullptr) {
+            *reinterpret_cast<uint4*>(gu_row + c * 32 + j * 8) = gv;
+            *reinterpret_cast<uint4*>(gu_row + inter + c * 32 + j * 8) = uv;
+          }
+        }
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(uempty);
+      fence_proxy_async_smem();
+      named_bar_sync(1, EPI_THREADS);
+      if (issuer) {
+#pragma unroll
+        for (int s = 0; s < NC / 64; ++s) tma_store_2d(&tmH, stash + s * C_SUB, cr * NC + s * 64, t.y);
+        tma_store_commit();
+      }
+    }
+    if (issuer) tma_store_wait_all();
+  }
+  __syncwarp();
+  tc_fence_before();
+  __syncthreads();
+  if (CL > 1) cluster_sync_all();   // nobody leaves while a peer may still write into this CTA
+  if (warp == 1) { tc_fence_after(); tmem_dealloc(tmem_base, 2 * NC); }
+  if (threadIdx.x == 0 && *abort_flag) atomicExch(&plan[PLAN_STATUS], 101);
 }
+
+// =====================================================================================================
+// host side
+// =====================================================================================================
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn encode_fn() {
+  static EncodeTiledFn fn = [] {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) != cudaSuccess ||
+        q != cudaDriverEntryPointSuccess)
+      p = nullptr;
+    return reinterpret_cast<EncodeTiledFn>(p);
+  }();
+  return fn;
+}
+
+int make_tmap_bf16_2d(CUtensorMap* out, const void* base, uint64_t rows, uint64_t cols, uint64_t pitch_elems,
+                      uint32_t box_rows) {
+  using Key = std::tuple<const void*, uint64_t, uint64_t, uint64_t, uint32_t>;
+  static std::mutex mu;
+  static std::map<Key, CUtensorMap> cache;
+  const Key key{base, rows, cols, pitch_elems, box_rows};
+  {
+    std::lock_guard<std::mutex> g(mu);
+    auto it = cache.find(key);
+    if (it != cache.end()) { *out = it->second; return BIBO_OK; }
+  }
+  EncodeTiledFn fn = encode_fn();
+  if (!fn) return fail(BIBO_ERR_CUDA, "cuTensorMapEncodeTiled is not available from this driver");
+  cuuint64_t gdim[2] = {cols, rows};
+  cuuint64_t gstride[1] = {pitch_elems * 2};
+  cuuint32_t box[2] = {64, box_rows};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = fn(out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), gdim, gstride, box, estr,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS)
+    return fail(BIBO_ERR_CUDA, "cuTensorMapEncodeTiled(rows=%llu cols=%llu box_rows=%u) -> %d",
+                (unsigned long long)rows, (unsigned long long)cols, box_rows, (int)r);
+  std::lock_guard<std::mutex> g(mu);
+  if (cache.size() > 256) cache.clear();
+  cache[key] = *out;
+  return BIBO_OK;
+}
+
+static int sm_count() {
+  static int n = [] {
+    int dev = 0, v = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&v, cudaDevAttrMultiProcessorCount, dev);
+    return v > 0 ? v : 148;
+  }();
+  return n;
+}
+
+template <typename Kern>
+static int set_smem(Kern kern, int bytes) {
+  BIBO_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes));
+  return BIBO_OK;
+}
+
+}  // namespace tc
+
+using namespace tc;
+
+int gemm2_tc_supported(int hidden, int inter, int dtype) {
+  return dtype == BIBO_BF16 && hidden % 256 == 0 && inter % 64 == 0 && inter >= 64;
+}
+
+int gemm2_tc_launch(const void* h, const void* down_proj, const int32_t* plan, int64_t n_tokens, int hidden,
+                    int inter, int n_experts, int n_glu, int top_k, void* y, cudaStream_t st) {
+  constexpr int BN = 256, STAGES = 4;
+  using L = G2Layout<BN, STAGES>;
+  const uint64_t rows = rows_cap(n_tokens, top_k, n_glu);
+  CUtensorMap tmA, tmB, tmC;
+  int rc;
+  if ((rc = make_tmap_bf16_2d(&tmA, h, rows, inter, inter, BM))) return rc;
+  if ((rc = make_tmap_bf16_2d(&tmB, down_proj, (uint64_t)n_glu * hidden, inter, inter, BN))) return rc;
+  if ((rc = make_tmap_bf16_2d(&tmC, y, rows, hidden, hidden, BM))) return rc;
+  auto kern = gemm2_tc_kernel<BN, STAGES>;
+  static bool attr_done = false;
+  if (!attr_done) { if ((rc = set_smem(kern, L::BYTES))) return rc; attr_done = true; }
+  const int64_t work_cap = tiles_cap(n_tokens, top_k, n_glu) * (hidden / BN);
+  const int grid = (int)std::min<int64_t>(sm_count(), work_cap);
+  kern<<<grid, NUM_THREADS, L::BYTES, st>>>(tmA, tmB, tmC, const_cast<int32_t*>(plan),
+                                           plan_off_tiles(n_tokens, n_experts, n_glu), hidden / BN, inter / BK, hidden);
+  BIBO_CHECK_LAUNCH("gemm2_tc_kernel");
+  return BIBO_OK;
+}
+
+int gemm1_tc_supported(int hidden, int inter, int dtype) {
+  return dtype == BIBO_BF16 && hidden % 64 == 0 && hidden >= 64 && (inter == 128 || inter == 256 || inter == 512);
+}
+
+template <int NC, int CL, int STAGES>
+static int gemm1_launch_t(const CUtensorMap& tmA, const CUtensorMap& tmB, const CUtensorMap& tmH, const float* theta,
+                          const int32_t* plan, int64_t tiles_off, int64_t tile_cap, int k_blocks, int inter,
+                          void* gate_up_out, float* rnorm_out, cudaStream_t st) {
+  using L = G1Layout<NC, STAGES>;
+  auto kern = gemm1_tc_kernel<NC, CL, STAGES>;
+  static bool attr_done = false;
+  int rc;
+  if (!attr_done) { if ((rc = set_smem(kern, L::BYTES))) return rc; attr_done = true; }
+  int clusters = (int)std::min<int64_t>(sm_count() / CL, tile_cap);
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(clusters * CL);
+  cfg.blockDim = dim3(NUM_THREADS);
+  cfg.dynamicSmemBytes = L::BYTES;
+  cfg.stream = st;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = CL;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  BIBO_CUDA(cudaLaunchKernelEx(&cfg, kern, tmA, tmB, tmH, theta, const_cast<int32_t*>(plan), tiles_off, k_blocks, inter,
+                               reinterpret_cast<__nv_bfloat16*>(gate_up_out), rnorm_out));
+  launch_counter().fetch_add(1, std::memory_order_relaxed);
+  return BIBO_OK;
+}
+
+int gemm1_tc_launch(const void* xp, const void* gate_up_proj, const float* theta, const int32_t* plan,
+                    int64_t n_tokens, int hidden, int inter, int n_experts, int n_glu, int top_k, void* h,
+                    void* gate_up_out, float* rnorm_out, cudaStream_t st) {
+  const uint64_t rows = rows_cap(n_tokens, top_k, n_glu);
+  const int nc = inter >= 256 ? 256 : 128;
+  CUtensorMap tmA, tmB, tmH;
+  int rc;
+  if ((rc = make_tmap_bf16_2d(&tmA, xp, rows, hidden, hidden, BM))) return rc;
+  if ((rc = make_tmap_bf16_2d(&tmB, gate_up_proj, (uint64_t)n_glu * 2 * inter, hidden, hidden, nc))) return rc;
+  if ((rc = make_tmap_bf16_2d(&tmH, h, rows, inter, inter, BM))) return rc;
+  const int64_t toff = plan_off_tiles(n_tokens, n_experts, n_glu);
+  const int64_t tcap = tiles_cap(n_tokens, top_k, n_glu);
+  if (inter == 512)
+    return gemm1_launch_t<256, 2, 3>(tmA, tmB, tmH, theta, plan, toff, tcap, hidden / BK, inter, gate_up_out, rnorm_out, st);
+  if (inter == 256)
+    return gemm1_launch_t<256, 1, 3>(tmA, tmB, tmH, theta, plan, toff, tcap, hidden / BK, inter, gate_up_out, rnorm_out, st);
+  return gemm1_launch_t<128, 1, 4>(tmA, tmB, tmH, theta, plan, toff, tcap, hidden / BK, inter, gate_up_out, rnorm_out, st);
+}
+
+// router on tensor cores: see router_tc.cu
 }  // namespace bibo

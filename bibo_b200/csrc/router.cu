@@ -182,8 +182,7 @@ plan_kernel(const int32_t* __restrict__ block_counts, int64_t n_tokens, int top_
     s_padded[n_glu] = acc;
     plan[PLAN_N_TILES] = acc / BIBO_TILE_M;
     plan[PLAN_ROWS_USED] = acc;
-    plan[PLAN_STATUS] = (s_total == (long long)n_tokens * top_k) ? 0 : 1;
-    plan[3] = 0;
+    if (s_total != (long long)n_tokens * top_k) atomicMax(&plan[PLAN_STATUS], 1);  // sticky
   }
   __syncthreads();
   if (e <= n_glu) expert_off[e] = s_padded[e];
@@ -203,21 +202,22 @@ extern "C" int bibo_moe_router_fwd(const void* x, const void* w_router, const fl
                                    const float* logits_in, int64_t n_tokens, int hidden,
                                    int n_experts, int top_k, int norm_mode, float scale, int dtype,
                                    float* logits_out, int32_t* topk_idx, float* topk_w,
-                                   int32_t* slot_rank, int32_t* block_counts, void* stream);
+                                   int32_t* slot_rank, int32_t* block_counts, int32_t* status,
+                                   void* stream);
 
 namespace bibo {
 int router_tc_supported(int hidden, int n_experts, int dtype);
 int router_tc_launch(const void* x, const void* w_router, const float* bias, int64_t n_tokens,
                      int hidden, int n_experts, int top_k, int norm_mode, float scale,
                      float* logits_out, int32_t* topk_idx, float* topk_w, int32_t* slot_rank,
-                     int32_t* block_counts, cudaStream_t st);
+                     int32_t* block_counts, int32_t* status, cudaStream_t st);
 }
 
 int bibo_moe_router_fwd(const void* x, const void* w_router, const float* bias,
                         const float* logits_in, int64_t n_tokens, int hidden, int n_experts,
                         int top_k, int norm_mode, float scale, int dtype, float* logits_out,
                         int32_t* topk_idx, float* topk_w, int32_t* slot_rank,
-                        int32_t* block_counts, void* stream) {
+                        int32_t* block_counts, int32_t* status, void* stream) {
   if (n_tokens <= 0) return BIBO_OK;
   if (!bias || !topk_idx || !topk_w || !slot_rank || !block_counts)
     return fail(BIBO_ERR_ARG, "router_fwd: null output or bias pointer");
@@ -234,7 +234,7 @@ int bibo_moe_router_fwd(const void* x, const void* w_router, const float* bias,
 
   if (!logits_in && router_tc_supported(hidden, n_experts, dtype) && aligned16(x) && aligned16(w_router))
     return router_tc_launch(x, w_router, bias, n_tokens, hidden, n_experts, top_k, norm_mode,
-                            scale, logits_out, topk_idx, topk_w, slot_rank, block_counts, st);
+                            scale, logits_out, topk_idx, topk_w, slot_rank, block_counts, status, st);
 
   const int ld = n_experts | 1;
   size_t smem = sizeof(float) * ((size_t)RB * ld + RK * (RB + 1) + RK * (RE + 1)) +

@@ -85,6 +85,8 @@ class MoEWorkspace:
         self.xp = torch.empty(rows, geo.hidden, dtype=geo.dtype, device=device)
         self.h = torch.empty(rows, geo.inter, dtype=geo.dtype, device=device)
         self.y = torch.empty(rows, geo.hidden, dtype=geo.dtype, device=device)
+        fused = bool(_lib.load().bibo_moe_gemm1_is_fused(geo.hidden, geo.inter, dtype_code(geo.dtype)))
+        keep_gate_up = keep_gate_up or not fused   # the two-kernel path always needs the buffer
         self.gate_up = (torch.empty(rows, 2 * geo.inter, dtype=geo.dtype, device=device)
                         if keep_gate_up else None)
         self.rnorm = torch.empty(rows, dtype=torch.float32, device=device) if keep_gate_up else None
@@ -182,7 +184,8 @@ def router_forward(x: Optional[torch.Tensor], w_router: Optional[torch.Tensor], 
     bias32 = bias if bias.dtype == torch.float32 else bias.float()
     rc = lib.bibo_moe_router_fwd(_lib.ptr(x), _lib.ptr(w_router), _lib.ptr(bias32), _lib.ptr(logits_in), n, hidden,
                                  e, top_k, norm_code(norm_mode), float(scale), dt, _lib.ptr(logits),
-                                 _lib.ptr(idx), _lib.ptr(w), _lib.ptr(rank), _lib.ptr(bc), _stream(dev))
+                                 _lib.ptr(idx), _lib.ptr(w), _lib.ptr(rank), _lib.ptr(bc),
+                                 _lib.ptr(ws.plan[2:]) if ws is not None else None, _stream(dev))
     _lib.check(rc, "bibo_moe_router_fwd")
     return idx, w, rank, bc, logits
 

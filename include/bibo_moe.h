@@ -75,12 +75,13 @@ int64_t bibo_moe_plan_words(int64_t n_tokens, int top_k, int n_experts, int n_gl
  * (block_counts [blocks, E]) and each slot's rank among the block's earlier tokens that picked
  * the same expert (slot_rank [N, k]).
  * logits_out may be NULL.  If logits_in is non-NULL the matrix product is skipped and the
- * selection runs on the given fp32 logits (test entry: selection parity on identical logits).   */
+ * selection runs on the given fp32 logits (test entry: selection parity on identical logits).
+ * status (optional device int32) is set non-zero if a bounded wait inside the kernel gave up.    */
 int bibo_moe_router_fwd(const void* x, const void* w_router, const float* bias,
                         const float* logits_in, int64_t n_tokens, int hidden, int n_experts,
                         int top_k, int norm_mode, float scale, int dtype,
                         float* logits_out, int32_t* topk_idx, float* topk_w,
-                        int32_t* slot_rank, int32_t* block_counts, void* stream);
+                        int32_t* slot_rank, int32_t* block_counts, int32_t* status, void* stream);
 
 /* Histogram and ranks for routing decided by the caller: the BiBoFusedExperts.forward(x, idx, w)
  * seam (src/modeling/ffn/moe.py:47-52).  topk_idx [N,k] int32 in any order.  status (optional
@@ -93,7 +94,9 @@ int bibo_moe_route_from_indices(const int32_t* topk_idx, int64_t n_tokens, int n
 /* ---- plan: histogram -> offsets ---------------------------------------------------------------
  * Replaces the sort / bincount / cumsum / .tolist() of BiBoFusedExperts.forward
  * (src/modeling/ffn/moe.py:56-68) without a host synchronisation.
- * plan layout (int32 words): [0]=n_tiles [1]=rows used [2]=status [3]=reserved,
+ * plan layout (int32 words): [0]=n_tiles [1]=rows used [2]=status [3]=reserved; the status word is
+ * STICKY: the caller zeroes it once, kernels only ever raise it (1 = histogram total != N*k,
+ * 100/101/102 = a bounded wait in the down / gate-up / router kernel gave up),
  * then counts[E], expert_off[E_glu+1], block_base[blocks*E] (exclusive prefix of block_counts over
  * blocks), tiles[tiles_cap*4].  Accessors below return the word offsets.                         */
 int bibo_moe_plan(const int32_t* block_counts, int64_t n_tokens, int top_k, int n_experts,
@@ -124,6 +127,9 @@ int bibo_moe_gemm1_radial_fwd(const void* xp, const void* gate_up_proj, const fl
                               const int32_t* plan, int64_t n_tokens, int hidden, int inter,
                               int n_experts, int n_glu, int top_k, int dtype,
                               void* h, void* gate_up_out, float* rnorm_out, void* stream);
+
+/* 1 when the fused tensor-core kernel covers this shape (gate_up_out may then be NULL), else 0.   */
+int bibo_moe_gemm1_is_fused(int hidden, int inter, int dtype);
 
 /* ---- K4: grouped down GEMM ---------------------------------------------------------------------
  * Replaces F.linear(activated * up, down_proj[e]) (src/modeling/ffn/moe.py:92).

@@ -79,7 +79,8 @@ def test_forward_bf16_matches_fp32_reference_fixture():
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize("n,h,i,e,k,bias_mode", [
     (1, 64, 64, 8, 2, "zero"), (127, 64, 32, 8, 2, "uniform"), (129, 128, 64, 64, 6, "uniform"),
-    (1000, 256, 128, 64, 6, "zipf"), (2048, 512, 128, 64, 6, "zero"), (700, 1024, 256, 64, 6, "uniform")])
+    (1000, 256, 128, 64, 6, "zipf"), (2048, 512, 128, 64, 6, "zero"), (700, 1024, 256, 64, 6, "uniform"),
+    (900, 512, 512, 64, 6, "uniform"), (4096, 1024, 512, 64, 6, "zipf")])
 def test_forward_matches_oracle(dtype, n, h, i, e, k, bias_mode):
     """Ragged token counts, near-empty experts (zipf bias), both dtypes."""
     inp = orc.make_inputs(n, h, i, e, seed=n, bias_mode=bias_mode, theta_std=0.5, zipf_alpha=1.0)
@@ -93,6 +94,26 @@ def test_forward_matches_oracle(dtype, n, h, i, e, k, bias_mode):
         assert rel_err(o, r) < FP32_TOL
     else:
         assert rel_err(o, r) < BF16_MAX and mean_rel_err(o, r) < BF16_MEAN
+
+
+@pytest.mark.parametrize("n,h,i", [(700, 256, 128), (1500, 512, 256), (1100, 256, 512)])
+def test_saved_gate_up_and_rnorm_bf16(n, h, i):
+    """The tensors K3 keeps for the backward pass: raw gate|up rows and the row norm r."""
+    from bibo_b200 import functional as Fn
+    inp = orc.make_inputs(n, h, i, 64, seed=n, bias_mode="uniform", theta_std=0.5)
+    out, ws = _run(inp, dtype=torch.bfloat16, top_k=6)
+    rows = Fn.plan_header(ws)[1]
+    tok = ws.row_token[:rows].long()
+    valid = tok >= 0
+    tiles = ws.tiles()[: rows // 128]
+    expert_of_row = tiles[:, 0].long().repeat_interleave(128)
+    xg = inp["x"].to(torch.bfloat16).to(DEV)[tok[valid]].float()
+    wg = inp["gate_up_proj"].to(torch.bfloat16).to(DEV).float()[expert_of_row[valid]]
+    gu_ref = torch.einsum("rh,rnh->rn", xg, wg)
+    gu = ws.gate_up[:rows][valid].float()
+    assert rel_err(gu, gu_ref) < 1e-2 and mean_rel_err(gu, gu_ref) < 5e-3
+    r_ref = torch.sqrt(ws.gate_up[:rows][valid][:, :i].float().square().mean(-1) + 1e-6)
+    assert torch.allclose(ws.rnorm[:rows][valid], r_ref, rtol=1e-5, atol=0)
 
 
 def test_forward_is_deterministic():
