@@ -2,5 +2,6 @@
 the reference's PyTorch module API.  See include/bibo_moe.h for the C ABI underneath."""
 from .moe import BiBoFusedExperts, BiBoMoELayer, BiBoMoERouter, MoEConfig  # noqa: F401
 from . import functional  # noqa: F401
+from .install import install, uninstall  # noqa: F401
 
-__all__ = ["BiBoMoELayer", "BiBoMoERouter", "BiBoFusedExperts", "MoEConfig", "functional"]
+__all__ = ["BiBoMoELayer", "BiBoMoERouter", "BiBoFusedExperts", "MoEConfig", "functional", "install", "uninstall"]

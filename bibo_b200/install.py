@@ -1,0 +1,45 @@
+"""Swap the CUDA kernel chain into the reference's own classes, the way the reference swaps kernels
+itself: class-level assignment wrapped in ``torch.compiler.disable``
+(ablate/common/patches.py:20-23,177-180,290).
+
+    import bibo_b200
+    bibo_b200.install()                      # BiBoMoELayer.forward -> kernel chain
+    bibo_b200.install(seam="experts")        # only BiBoFusedExperts.forward(x, idx, w)
+    bibo_b200.uninstall()
+
+``ref_moe_module`` is the reference's ``src.modeling.ffn.moe`` module (imported by default; pass it
+explicitly when the checkout lives under another package name).  Parameters stay owned by the
+reference's modules; nothing is copied.
+"""
+from __future__ import annotations
+
+import torch
+
+from . import moe as _moe
+
+_saved = {}
+
+
+def _nc(fn):
+    return torch.compiler.disable(fn) if hasattr(torch, "compiler") else fn
+
+
+def install(ref_moe_module=None, seam: str = "layer") -> None:
+    if ref_moe_module is None:
+        from src.modeling.ffn import moe as ref_moe_module  # the reference checkout must be importable
+    if seam == "layer":
+        cls = ref_moe_module.BiBoMoELayer
+        _saved.setdefault((cls, "forward"), cls.forward)
+        cls.forward = _nc(_moe.layer_forward)
+    elif seam == "experts":
+        cls = ref_moe_module.BiBoFusedExperts
+        _saved.setdefault((cls, "forward"), cls.forward)
+        cls.forward = _nc(_moe.experts_forward_seam)
+    else:
+        raise ValueError(f"seam must be 'layer' or 'experts', got {seam!r}")
+
+
+def uninstall() -> None:
+    for (cls, name), fn in _saved.items():
+        setattr(cls, name, fn)
+    _saved.clear()

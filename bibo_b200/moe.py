@@ -132,10 +132,7 @@ class BiBoFusedExperts(nn.Module):
 
     def forward(self, hidden_states: torch.Tensor, top_k_indices: torch.Tensor,
                 top_k_weights: torch.Tensor) -> torch.Tensor:
-        _refuse_grad(self, hidden_states, top_k_weights)
-        out, _ = Fn.experts_forward(hidden_states.contiguous(), top_k_indices, top_k_weights, self.gate_up_proj,
-                                    self.down_proj, self.radial_theta, self.num_routed_experts, self.num_pos)
-        return out
+        return experts_forward_seam(self, hidden_states, top_k_indices, top_k_weights)
 
 
 def _refuse_grad(module: nn.Module, *tensors) -> None:
@@ -180,49 +177,76 @@ class BiBoMoELayer(nn.Module):
         self.gate.bias.add_(self.bias_update_factor * (share.mean() - share))
 
     @torch.no_grad()
-    def _balance_from_counts(self, counts: torch.Tensor, num_tokens: int):
-        self.accumulated_tpe += counts.float()
-        if self._update_every is None:
-            self._update_every = max(1, round(self.bias_update_threshold / max(num_tokens, 1)))
-        self._fwd_step += 1
-        if self._fwd_step % self._update_every == 0:
-            if dist.is_available() and dist.is_initialized():
-                dist.all_reduce(self.accumulated_tpe, op=dist.ReduceOp.SUM)
-            tpe = self.accumulated_tpe.clone()
-            self.accumulated_tpe.zero_()
-            return tpe
-        return None
-
-    @torch.no_grad()
     def _balance_step(self, top_k_indices: torch.Tensor, num_tokens: int):
         """Reference signature (indices [B,S,k]); the forward itself feeds the kernel's histogram."""
         counts = torch.bincount(top_k_indices.reshape(-1), minlength=self.num_routed_experts)
-        return self._balance_from_counts(counts, num_tokens)
+        return _balance_from_counts(self, counts, num_tokens)
 
     # ---- forward -------------------------------------------------------------------------------------
     def forward(self, hidden_states: torch.Tensor) -> torch.Tensor:
-        bsz, seq_len, hidden = hidden_states.shape
-        n = bsz * seq_len
-        _refuse_grad(self, hidden_states)
-        flat = hidden_states.reshape(n, hidden).contiguous()
-        gate, ex = self.gate, self.experts
-        want_gap = gate._probe_gap and gate.top_k < gate.num_routed_experts
-        out, ws = Fn.moe_forward(flat, gate.gate_proj.weight, gate.bias, ex.gate_up_proj, ex.down_proj,
-                                 ex.radial_theta, gate.top_k, gate.norm_topk_prob, gate.routed_scaling_factor,
-                                 n_pos=ex.num_pos, n_neg=ex.num_neg, keep_logits=want_gap)
-        self.last_workspace = ws
-        if want_gap:
-            gate._set_gap(ws.logits)
-        # replay the reference's diagnostic hook points only when someone is listening
-        if ex._forward_pre_hooks:
-            for hook in ex._forward_pre_hooks.values():
-                hook(ex, (flat, ws.topk_idx.long(), ws.topk_w))
-        if gate._forward_hooks:
-            res = (ws.topk_idx.view(bsz, seq_len, -1).long(), ws.topk_w.view(bsz, seq_len, -1))
-            for hook in gate._forward_hooks.values():
-                hook(gate, (hidden_states,), res)
-        if self.training and self.bias_update_factor > 0:
-            tpe = self._balance_from_counts(ws.counts(), n)
-            if tpe is not None:
-                self.update_bias(tpe)
-        return out.view(bsz, seq_len, hidden)
+        return layer_forward(self, hidden_states)
+
+
+def _balance_from_counts(layer, counts: torch.Tensor, num_tokens: int):
+    """`_balance_step` of the reference (moe.py:139-155) fed with the kernel's histogram."""
+    with torch.no_grad():
+        layer.accumulated_tpe += counts.float()
+        if layer._update_every is None:
+            layer._update_every = max(1, round(layer.bias_update_threshold / max(num_tokens, 1)))
+        layer._fwd_step += 1
+        if layer._fwd_step % layer._update_every == 0:
+            if dist.is_available() and dist.is_initialized():
+                dist.all_reduce(layer.accumulated_tpe, op=dist.ReduceOp.SUM)
+            tpe = layer.accumulated_tpe.clone()
+            layer.accumulated_tpe.zero_()
+            return tpe
+    return None
+
+
+def layer_forward(layer, hidden_states: torch.Tensor) -> torch.Tensor:
+    """``BiBoMoELayer.forward`` (src/modeling/ffn/moe.py:157-183) on the CUDA kernel chain.
+
+    Written against the REFERENCE's attribute names only, so it serves both this package's layer
+    and, through ``bibo_b200.install``, an instance of the reference's own class.
+    """
+    bsz, seq_len, hidden = hidden_states.shape
+    n = bsz * seq_len
+    if getattr(layer, "use_shared_expert", False):
+        raise NotImplementedError("bibo_b200: use_shared_expert=True is outside the kernels' coverage")
+    _refuse_grad(layer, hidden_states)
+    flat = hidden_states.reshape(n, hidden).contiguous()
+    gate, ex = layer.gate, layer.experts
+    n_pos, n_neg = ex.pos_end - ex.pos_start, ex.neg_end - ex.neg_start
+    want_gap = gate._probe_gap and gate.top_k < gate.num_routed_experts
+    out, ws = Fn.moe_forward(flat, gate.gate_proj.weight, gate.bias, ex.gate_up_proj, ex.down_proj,
+                             ex.radial_theta, gate.top_k, gate.norm_topk_prob,
+                             float(getattr(gate, "routed_scaling_factor", 1.0)),
+                             n_pos=n_pos, n_neg=n_neg, keep_logits=want_gap)
+    layer.last_workspace = ws
+    if want_gap:
+        with torch.no_grad():
+            tk = torch.sigmoid(ws.logits).topk(gate.top_k + 1, dim=-1).values
+            gate.boundary_gap = (tk[..., gate.top_k - 1] - tk[..., gate.top_k]).mean()
+    # replay the reference's diagnostic hook points only when someone is listening
+    if ex._forward_pre_hooks:
+        for hook in ex._forward_pre_hooks.values():
+            hook(ex, (flat, ws.topk_idx.long(), ws.topk_w))
+    if gate._forward_hooks:
+        res = (ws.topk_idx.view(bsz, seq_len, -1).long(), ws.topk_w.view(bsz, seq_len, -1))
+        for hook in gate._forward_hooks.values():
+            hook(gate, (hidden_states,), res)
+    if layer.training and layer.bias_update_factor > 0:
+        tpe = _balance_from_counts(layer, ws.counts(), n)
+        if tpe is not None:
+            layer.update_bias(tpe)
+    return out.view(bsz, seq_len, hidden)
+
+
+def experts_forward_seam(experts, hidden_states: torch.Tensor, top_k_indices: torch.Tensor,
+                         top_k_weights: torch.Tensor) -> torch.Tensor:
+    """``BiBoFusedExperts.forward(x, idx, w)`` (src/modeling/ffn/moe.py:47-101) on the kernels."""
+    _refuse_grad(experts, hidden_states, top_k_weights)
+    out, _ = Fn.experts_forward(hidden_states.contiguous(), top_k_indices, top_k_weights, experts.gate_up_proj,
+                                experts.down_proj, experts.radial_theta, experts.num_routed_experts,
+                                experts.pos_end - experts.pos_start)
+    return out

@@ -1,0 +1,99 @@
+"""Host-side logic that needs no GPU: library symbols, module API, balancer, install seam."""
+import ctypes
+import os
+import pathlib
+import re
+import sys
+
+import pytest
+import torch
+
+ROOT = pathlib.Path(__file__).resolve().parents[1]
+REF = pathlib.Path("/root/reference")
+
+
+def test_library_exports_every_declared_symbol():
+    from bibo_b200 import _lib, build
+    build.build()
+    lib = _lib.load()
+    header = (ROOT / "include" / "bibo_moe.h").read_text()
+    declared = set(re.findall(r"\b(bibo_moe_\w+)\s*\(", header))
+    assert declared == set(_lib.SIGNATURES), declared ^ set(_lib.SIGNATURES)
+    for name in declared:
+        assert hasattr(lib, name)
+    assert lib.bibo_moe_version() >= 100
+
+
+def test_size_helpers_and_argument_errors_without_a_gpu():
+    from bibo_b200 import _lib
+    lib = _lib.load()
+    assert lib.bibo_moe_rows_cap(1000, 6, 64) == (6000 + 64 * 127 + 127) // 128 * 128
+    assert lib.bibo_moe_router_blocks(129) == 2
+    assert lib.bibo_moe_tiles_cap(1000, 6, 64) * 128 == lib.bibo_moe_rows_cap(1000, 6, 64)
+    # argument validation happens before any CUDA call
+    rc = lib.bibo_moe_router_fwd(None, None, None, None, 10, 64, 64, 6, 1, 1.0, 1, None, None, None, None, None, None, None)
+    assert rc == -1 and b"null" in lib.bibo_moe_last_error_string()
+    rc = lib.bibo_moe_plan(None, 10, 6, 64, 64, None, None)
+    assert rc == -1
+    one = ctypes.c_int(0)
+    p = ctypes.addressof(one)
+    rc = lib.bibo_moe_router_fwd(p, p, p, None, 10, 64, 1000, 6, 1, 1.0, 1, None, p, p, p, p, None, None)
+    assert rc == -4
+
+
+def test_module_mirrors_reference_names_and_shapes():
+    from bibo_b200 import BiBoMoELayer, MoEConfig
+    cfg = MoEConfig(hidden_size=64, moe_intermediate_size=96, num_routed_experts=8, num_experts_per_tok=2,
+                    num_pos_identity_experts=1, num_neg_identity_experts=1)
+    layer = BiBoMoELayer(cfg)
+    sd = layer.state_dict()
+    assert sd["experts.gate_up_proj"].shape == (6, 192, 64) and sd["experts.down_proj"].shape == (6, 64, 96)
+    assert sd["experts.radial_theta"].shape == (6,) and sd["gate.gate_proj.weight"].shape == (8, 64)
+    assert sd["gate.bias"].shape == (8,) and sd["accumulated_tpe"].dtype == torch.float32
+    assert layer.gate.bias.requires_grad is False
+    e = layer.experts
+    assert (e.pos_start, e.pos_end, e.neg_start, e.neg_end) == (6, 7, 7, 8)
+    with pytest.raises(NotImplementedError):
+        BiBoMoELayer(MoEConfig(use_shared_expert=True, hidden_size=64, moe_intermediate_size=32, num_routed_experts=8))
+
+
+def test_balancer_host_logic_matches_reference_tests():
+    # tests/test_moe.py:206-249,278-310
+    from bibo_b200 import BiBoMoELayer, MoEConfig
+    cfg = MoEConfig(hidden_size=64, moe_intermediate_size=32, num_routed_experts=8, num_experts_per_tok=2,
+                    bias_update_threshold=48)
+    layer = BiBoMoELayer(cfg).train()
+    idx = torch.zeros(2, 8, 2, dtype=torch.long)
+    fired = [layer._balance_step(idx, 16) is not None for _ in range(7)]
+    assert layer._update_every == 3 and fired == [False, False, True, False, False, True, False]
+    tpe = torch.full((8,), 10.0)
+    tpe[0] = 100.0
+    layer.update_bias(tpe)
+    assert layer.gate.bias[0] < 0 and (layer.gate.bias[1:] > 0).all()
+    assert abs(float(layer.gate.bias.mean())) < 1e-6
+
+
+@pytest.mark.skipif(not REF.exists(), reason="reference checkout not present on this machine")
+def test_install_patches_reference_classes_and_state_dict_is_compatible():
+    sys.path.insert(0, str(REF))
+    os.environ.setdefault("PYTHONDONTWRITEBYTECODE", "1")
+    sys.dont_write_bytecode = True
+    from src.configuration_bibo import BiBoConfig
+    from src.modeling.ffn import moe as ref
+    import bibo_b200
+    cfg = BiBoConfig(vocab_size=512, hidden_size=64, num_hidden_layers=4, num_attention_heads=4, num_key_value_heads=2,
+                     intermediate_size=96, moe_intermediate_size=96, num_routed_experts=8, special_expert_pairs=1,
+                     num_experts_per_tok=2)
+    ref_layer = ref.BiBoMoELayer(cfg)
+    mine = bibo_b200.BiBoMoELayer(cfg)                 # the reference's config object is accepted as is
+    mine.load_state_dict(ref_layer.state_dict())       # identical names and shapes
+    assert mine.experts.num_glu_experts == 6 and mine.experts.neg_end == 8
+    orig = ref.BiBoMoELayer.forward
+    bibo_b200.install(ref)
+    try:
+        assert ref.BiBoMoELayer.forward is not orig
+        with torch.no_grad(), pytest.raises(RuntimeError, match="no CPU implementation"):
+            ref_layer.eval()(torch.randn(1, 4, 64))    # the patched class refuses CPU tensors loudly
+    finally:
+        bibo_b200.uninstall()
+    assert ref.BiBoMoELayer.forward is orig
