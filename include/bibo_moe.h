@@ -192,6 +192,22 @@ int bibo_moe_forward_host(const bibo_moe_shape* shape, const void* x_host, void*
                           const void* down_proj, const float* theta, const bibo_moe_workspace* ws,
                           void* out_dev, void* out_host, void* stream);
 
+/* ---- routing without any allocation -------------------------------------------------------------
+ * No counterpart in the reference: added for callers that cannot allocate device memory (a runtime
+ * that reserves all memory up front, or a loop that must not incur cudaMalloc's implicit device
+ * synchronisation).  Same routing as bibo_moe_router_fwd followed by bibo_moe_plan, but the three
+ * intermediates (slot ranks, per-block histograms, plan) live in a fixed device array inside the
+ * library (about 0.8 MB per GPU), so the caller passes only inputs and outputs:
+ * topk_idx [N,k] int32 ascending, topk_w [N,k] fp32, counts [E] int32 (tokens per expert).
+ * At most BIBO_NOALLOC_MAX_TOKENS tokens per call, otherwise BIBO_ERR_UNSUPPORTED.  The first call
+ * on a device resolves the array's address (do it before any stream capture).  All calls on a
+ * device share the array: calls whose kernels overlap on the GPU race; serialise them.           */
+#define BIBO_NOALLOC_MAX_TOKENS 16384
+int bibo_moe_route_noalloc(const void* x, const void* w_router, const float* bias, int64_t n_tokens,
+                           int hidden, int n_experts, int top_k, int norm_mode, float scale, int dtype,
+                           int32_t* topk_idx, float* topk_w, int32_t* counts, void* stream);
+int64_t bibo_moe_route_noalloc_max_tokens(void);
+
 /* Debug: copies plan[0..3] to the host (synchronises `stream`) and returns plan[2] (status).     */
 int bibo_moe_debug_plan_header(const int32_t* plan, int32_t* header4_host, void* stream);
 
