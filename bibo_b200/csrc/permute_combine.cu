@@ -92,53 +92,105 @@ template <> struct Vec16<__nv_bfloat16> {
   }
 };
 
+// 16 bytes of T -> fp32 multiply-accumulate
+template <typename T> struct Acc16;
+template <> struct Acc16<float> {
+  static constexpr int N = 4;
+  static __device__ __forceinline__ void fma(const uint4& v, float w, float* acc) {
+    acc[0] = fmaf(__uint_as_float(v.x), w, acc[0]);
+    acc[1] = fmaf(__uint_as_float(v.y), w, acc[1]);
+    acc[2] = fmaf(__uint_as_float(v.z), w, acc[2]);
+    acc[3] = fmaf(__uint_as_float(v.w), w, acc[3]);
+  }
+};
+template <> struct Acc16<__nv_bfloat16> {
+  static constexpr int N = 8;
+  static __device__ __forceinline__ void fma(const uint4& v, float w, float* acc) {
+    const uint32_t u[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      acc[2 * i] = fmaf(__uint_as_float(u[i] << 16), w, acc[2 * i]);
+      acc[2 * i + 1] = fmaf(__uint_as_float(u[i] & 0xffff0000u), w, acc[2 * i + 1]);
+    }
+  }
+};
+
 // One warp per token; the k rows are summed in slot order (= ascending expert index), fp32.
-template <typename T>
-__global__ void __launch_bounds__(PW * 32)
+// All k 16-byte loads of a chunk are issued before the first is used (raw registers, converted
+// only at accumulation), and two chunks are in flight per lane, to keep HBM busy.
+template <typename T, int K>
+__global__ void __launch_bounds__(PW * 32, 4)
 combine_kernel(const T* __restrict__ y, const T* __restrict__ x, const int32_t* __restrict__ slot_row,
                const int32_t* __restrict__ topk_idx, const float* __restrict__ topk_w,
-               int64_t n_tokens, int hidden, int top_k, int n_glu, int n_pos, T* __restrict__ out) {
-  constexpr int VN = Vec16<T>::N;
+               int64_t n_tokens, int hidden, int n_glu, int n_pos, T* __restrict__ out) {
+  constexpr int VN = Acc16<T>::N;
   const int lane = threadIdx.x & 31;
   const int64_t t = (int64_t)blockIdx.x * PW + (threadIdx.x >> 5);
   if (t >= n_tokens) return;
   int my_row = -1;
   float my_w = 0.f;
-  if (lane < top_k) {
-    my_row = slot_row[t * top_k + lane];
-    my_w = topk_w[t * top_k + lane];
+  if (lane < K) {
+    my_row = slot_row[t * K + lane];
+    my_w = topk_w[t * K + lane];
     if (my_row < 0) {  // +Identity / -Identity expert: contributes +w*x or -w*x
-      const int e = topk_idx[t * top_k + lane];
+      const int e = topk_idx[t * K + lane];
       if (e >= n_glu + n_pos) my_w = -my_w;
     }
   }
-  int rows[BIBO_MAX_TOP_K];
-  float ws[BIBO_MAX_TOP_K];
+  const uint4* src[K];
+  float ws[K];
 #pragma unroll
-  for (int j = 0; j < BIBO_MAX_TOP_K; ++j) {
-    rows[j] = __shfl_sync(0xffffffffu, my_row, j);
+  for (int j = 0; j < K; ++j) {
+    const int r = __shfl_sync(0xffffffffu, my_row, j);
     ws[j] = __shfl_sync(0xffffffffu, my_w, j);
+    src[j] = reinterpret_cast<const uint4*>(r >= 0 ? y + (int64_t)r * hidden : x + t * hidden);
   }
+  uint4* dst = reinterpret_cast<uint4*>(out + t * hidden);
   const int chunks = hidden / VN;
-  for (int c = lane; c < chunks; c += 32) {
-    float v[BIBO_MAX_TOP_K][VN];
+  int c = lane;
+  for (; c + 32 < chunks; c += 64) {
+    uint4 v0[K], v1[K];
 #pragma unroll
-    for (int j = 0; j < BIBO_MAX_TOP_K; ++j) {
-      if (j < top_k) {
-        const T* src = rows[j] >= 0 ? y + (int64_t)rows[j] * hidden : x + t * hidden;
-        Vec16<T>::load(src + c * VN, v[j]);
-      }
-    }
-    float acc[VN];
+    for (int j = 0; j < K; ++j) { v0[j] = __ldcs(src[j] + c); v1[j] = __ldcs(src[j] + c + 32); }
+    float a0[VN], a1[VN];
 #pragma unroll
-    for (int i = 0; i < VN; ++i) acc[i] = 0.f;
+    for (int i = 0; i < VN; ++i) a0[i] = a1[i] = 0.f;
 #pragma unroll
-    for (int j = 0; j < BIBO_MAX_TOP_K; ++j)
-      if (j < top_k)
-#pragma unroll
-        for (int i = 0; i < VN; ++i) acc[i] += v[j][i] * ws[j];
-    Vec16<T>::store(out + t * hidden + c * VN, acc);
+    for (int j = 0; j < K; ++j) { Acc16<T>::fma(v0[j], ws[j], a0); Acc16<T>::fma(v1[j], ws[j], a1); }
+    Vec16<T>::store(dst + c, a0);
+    Vec16<T>::store(dst + c + 32, a1);
   }
+  for (; c < chunks; c += 32) {
+    uint4 v0[K];
+#pragma unroll
+    for (int j = 0; j < K; ++j) v0[j] = __ldcs(src[j] + c);
+    float a0[VN];
+#pragma unroll
+    for (int i = 0; i < VN; ++i) a0[i] = 0.f;
+#pragma unroll
+    for (int j = 0; j < K; ++j) Acc16<T>::fma(v0[j], ws[j], a0);
+    Vec16<T>::store(dst + c, a0);
+  }
+}
+
+template <typename T>
+static int combine_launch(const void* y, const void* x, const int32_t* slot_row, const int32_t* topk_idx,
+                          const float* topk_w, int64_t n_tokens, int hidden, int top_k, int n_glu, int n_pos,
+                          void* out, cudaStream_t st) {
+  dim3 grid((unsigned)((n_tokens + PW - 1) / PW));
+#define BIBO_COMBINE_CASE(KK)                                                                                   \
+  case KK:                                                                                                       \
+    combine_kernel<T, KK><<<grid, PW * 32, 0, st>>>((const T*)y, (const T*)x, slot_row, topk_idx, topk_w,        \
+                                                    n_tokens, hidden, n_glu, n_pos, (T*)out);                    \
+    break;
+  switch (top_k) {
+    BIBO_COMBINE_CASE(1) BIBO_COMBINE_CASE(2) BIBO_COMBINE_CASE(3) BIBO_COMBINE_CASE(4)
+    BIBO_COMBINE_CASE(5) BIBO_COMBINE_CASE(6) BIBO_COMBINE_CASE(7) BIBO_COMBINE_CASE(8)
+    default: return fail(BIBO_ERR_UNSUPPORTED, "combine_fwd: top_k=%d", top_k);
+  }
+#undef BIBO_COMBINE_CASE
+  BIBO_CHECK_LAUNCH("combine_kernel");
+  return BIBO_OK;
 }
 
 }  // namespace bibo
@@ -181,16 +233,8 @@ extern "C" int bibo_moe_combine_fwd(const void* y, const void* x, const int32_t*
     return fail(BIBO_ERR_UNSUPPORTED, "combine_fwd: row of %d bytes is not a multiple of 16", row_bytes);
   if (!aligned16(y) || !aligned16(x) || !aligned16(out))
     return fail(BIBO_ERR_ALIGN, "combine_fwd: y / x / out not 16-byte aligned");
-  dim3 grid((unsigned)((n_tokens + PW - 1) / PW));
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   if (dtype == BIBO_F32)
-    combine_kernel<float><<<grid, PW * 32, 0, st>>>((const float*)y, (const float*)x, slot_row, topk_idx,
-                                                    topk_w, n_tokens, hidden, top_k, n_glu, n_pos,
-                                                    (float*)out);
-  else
-    combine_kernel<__nv_bfloat16><<<grid, PW * 32, 0, st>>>(
-        (const __nv_bfloat16*)y, (const __nv_bfloat16*)x, slot_row, topk_idx, topk_w, n_tokens,
-        hidden, top_k, n_glu, n_pos, (__nv_bfloat16*)out);
-  BIBO_CHECK_LAUNCH("combine_kernel");
-  return BIBO_OK;
+    return combine_launch<float>(y, x, slot_row, topk_idx, topk_w, n_tokens, hidden, top_k, n_glu, n_pos, out, st);
+  return combine_launch<__nv_bfloat16>(y, x, slot_row, topk_idx, topk_w, n_tokens, hidden, top_k, n_glu, n_pos, out, st);
 }

@@ -144,53 +144,75 @@ rank_kernel(const int32_t* __restrict__ topk_idx, int64_t n_tokens, int n_expert
 }
 
 // ---- plan -----------------------------------------------------------------------------------------
-// One block of BIBO_MAX_EXPERTS threads; thread e scans its expert's column of block_counts.
-__global__ void __launch_bounds__(BIBO_MAX_EXPERTS)
+// One block of 1024 threads.  Expert e is served by SUB = 1024 / EP threads (EP = experts rounded up
+// to a power of two); each sums a contiguous run of blocks, the partial sums are scanned through
+// shared memory, and a second pass writes the exclusive prefix per block.  Thread (sub, e) has
+// index sub * EP + e, so a warp reads consecutive experts of one block row.
+constexpr int PLAN_THREADS = 1024;
+__global__ void __launch_bounds__(PLAN_THREADS)
 plan_kernel(const int32_t* __restrict__ block_counts, int64_t n_tokens, int top_k, int n_experts,
-            int n_glu, int32_t* __restrict__ plan) {
+            int n_glu, int ep, int32_t* __restrict__ plan) {
+  __shared__ int s_part[PLAN_THREADS];
   __shared__ int s_padded[BIBO_MAX_EXPERTS + 1];
-  __shared__ int s_total;
-  const int e = threadIdx.x;
+  __shared__ int s_count[BIBO_MAX_EXPERTS];
+  const int tid = threadIdx.x;
+  const int e = tid % ep, sub = tid / ep, n_sub = PLAN_THREADS / ep;
   const int nb = (int)router_blocks(n_tokens);
+  const int per = (nb + n_sub - 1) / n_sub;
+  const int b0 = min(sub * per, nb), b1 = min(b0 + per, nb);
   int32_t* counts = plan + plan_off_counts();
   int32_t* expert_off = plan + plan_off_expert_off(n_experts);
   int32_t* block_base = plan + plan_off_block_base(n_experts, n_glu);
   int4* tiles = reinterpret_cast<int4*>(plan + plan_off_tiles(n_tokens, n_experts, n_glu));
 
-  if (e == 0) s_total = 0;
+  int sum = 0;
+  if (e < n_experts)
+    for (int b = b0; b < b1; ++b) sum += block_counts[(int64_t)b * n_experts + e];
+  s_part[tid] = sum;
   __syncthreads();
-  int run = 0;
-  if (e < n_experts) {
-#pragma unroll 8
-    for (int b = 0; b < nb; ++b) {
-      int c = block_counts[(int64_t)b * n_experts + e];
-      block_base[(int64_t)b * n_experts + e] = run;
-      run += c;
-    }
-    counts[e] = run;
-    atomicAdd(&s_total, run);
-  }
-  s_padded[e] = (e < n_glu) ? (run + BIBO_TILE_M - 1) / BIBO_TILE_M * BIBO_TILE_M : 0;
-  __syncthreads();
-  if (e == 0) {  // exclusive scan over <= 256 entries
+  if (tid < ep) {  // one thread per expert scans its n_sub partial sums
     int acc = 0;
+    for (int q = 0; q < n_sub; ++q) {
+      const int v = s_part[q * ep + tid];
+      s_part[q * ep + tid] = acc;
+      acc += v;
+    }
+    if (tid < n_experts) {
+      counts[tid] = acc;
+      s_count[tid] = acc;
+    }
+    s_padded[tid] = (tid < n_glu) ? (acc + BIBO_TILE_M - 1) / BIBO_TILE_M * BIBO_TILE_M : 0;
+  }
+  __syncthreads();
+  if (tid == 0) {  // exclusive scan of the padded row counts (<= 256 entries) and the total check
+    int acc = 0, total = 0;
+    for (int i = 0; i < n_experts; ++i) total += s_count[i];
     for (int i = 0; i < n_glu; ++i) {
-      int v = s_padded[i];
+      const int v = s_padded[i];
       s_padded[i] = acc;
       acc += v;
     }
     s_padded[n_glu] = acc;
     plan[PLAN_N_TILES] = acc / BIBO_TILE_M;
     plan[PLAN_ROWS_USED] = acc;
-    if (s_total != (long long)n_tokens * top_k) atomicMax(&plan[PLAN_STATUS], 1);  // sticky
+    if (total != (long long)n_tokens * top_k) atomicMax(&plan[PLAN_STATUS], 1);  // sticky
+  }
+  if (e < n_experts) {
+    int run = s_part[tid];
+    for (int b = b0; b < b1; ++b) {
+      const int c = block_counts[(int64_t)b * n_experts + e];
+      block_base[(int64_t)b * n_experts + e] = run;
+      run += c;
+    }
   }
   __syncthreads();
-  if (e <= n_glu) expert_off[e] = s_padded[e];
+  if (tid <= n_glu) expert_off[tid] = s_padded[tid];
+  // tile list: thread (sub, e) writes every n_sub-th tile of expert e
   if (e < n_glu) {
-    int row0 = s_padded[e];
-    int t = row0 / BIBO_TILE_M;
-    for (int r = 0; r < run; r += BIBO_TILE_M, ++t)
-      tiles[t] = make_int4(e, row0 + r, min(BIBO_TILE_M, run - r), 0);
+    const int row0 = s_padded[e], cnt = s_count[e];
+    const int t0 = row0 / BIBO_TILE_M;
+    for (int i = sub; i * BIBO_TILE_M < cnt; i += n_sub)
+      tiles[t0 + i] = make_int4(e, row0 + i * BIBO_TILE_M, min(BIBO_TILE_M, cnt - i * BIBO_TILE_M), 0);
   }
 }
 
@@ -277,8 +299,10 @@ extern "C" int bibo_moe_plan(const int32_t* block_counts, int64_t n_tokens, int 
   if (n_experts < 1 || n_experts > BIBO_MAX_EXPERTS || n_glu < 0 || n_glu > n_experts)
     return fail(BIBO_ERR_UNSUPPORTED, "plan: n_experts=%d n_glu=%d", n_experts, n_glu);
   if (n_tokens <= 0) return fail(BIBO_ERR_ARG, "plan: n_tokens=%lld", (long long)n_tokens);
-  plan_kernel<<<1, BIBO_MAX_EXPERTS, 0, static_cast<cudaStream_t>(stream)>>>(
-      block_counts, n_tokens, top_k, n_experts, n_glu, plan);
+  int ep = 1;
+  while (ep < n_experts) ep <<= 1;
+  plan_kernel<<<1, PLAN_THREADS, 0, static_cast<cudaStream_t>(stream)>>>(block_counts, n_tokens, top_k, n_experts,
+                                                                       n_glu, ep, plan);
   BIBO_CHECK_LAUNCH("plan_kernel");
   return BIBO_OK;
 }
