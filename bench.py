@@ -50,12 +50,15 @@ def peaks():
     return dict(hbm=6650.0, tf=1590.0, tf_sus=1400.0, src="fallback")
 
 
-def synth(wl, device, seed, dtype=torch.bfloat16):
-    """Seeded synthetic tensors generated on `device`: x ~ N(0,1); weights ~ N(0,0.02); theta ~ N(0,0.5)."""
+def synth(wl, device, seed, rank=0, dtype=torch.bfloat16):
+    """Seeded synthetic tensors generated on `device`: x ~ N(0,1) (rank-seeded); weights ~ N(0,0.02) and
+    theta ~ N(0,0.5) from a seed common to all ranks."""
     g = torch.Generator(device=device).manual_seed(seed)
+    gx = torch.Generator(device=device).manual_seed(seed + 7919 * (rank + 1))
     n, h, i = wl["n_tokens"], wl["hidden"], wl["inter"]
     rn = lambda *s: torch.randn(*s, generator=g, device=device, dtype=torch.float32)
-    t = dict(x=rn(n, h).to(dtype), gate_up_proj=(rn(N_EXPERTS, 2 * i, h) * 0.02).to(dtype),
+    t = dict(x=torch.randn(n, h, generator=gx, device=device, dtype=torch.float32).to(dtype),
+             gate_up_proj=(rn(N_EXPERTS, 2 * i, h) * 0.02).to(dtype),
              down_proj=(rn(N_EXPERTS, h, i) * 0.02).to(dtype), w_router=(rn(N_EXPERTS, h) * 0.02).to(dtype),
              radial_theta=rn(N_EXPERTS) * 0.5)
     if wl["bias"] == "zero":
@@ -192,13 +195,13 @@ def main():
     dev = torch.device("cuda", local)
     if world > 1:
         dist.init_process_group("nccl", device_id=dev)
-    t = synth(wl, dev, seed=1234 + rank)
+    t = synth(wl, dev, seed=1234, rank=rank)
     n, h, i = wl["n_tokens"], wl["hidden"], wl["inter"]
     dtype = torch.bfloat16
 
     if world > 1:
         from bibo_b200 import ep
-        runner = ep.ExpertParallelMoE(t, TOP_K, dist.group.WORLD)
+        runner = ep.ExpertParallelMoE(t, TOP_K, dist.group.WORLD, n_tokens=wl["n_tokens"])
         step = lambda: runner.forward(t["x"])
         ws = None
     else:

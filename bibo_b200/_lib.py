@@ -61,6 +61,13 @@ SIGNATURES = {
                                 C.POINTER(Workspace), _vp, _vp]),
     "bibo_moe_forward_host": (_i32, [C.POINTER(Shape), _vp, _vp, _vp, _vp, _vp, _vp, _vp,
                                      C.POINTER(Workspace), _vp, _vp, _vp]),
+    "bibo_moe_ep_plan_words": (_i64, [_i32, _i64]),
+    "bibo_moe_ep_plan_off": (_i64, [_i32, _i32]),
+    "bibo_moe_ep_plan": (_i32, [_vp, _i32, _i32, _i32, _i64, _vp, _vp]),
+    "bibo_moe_ep_dispatch": (_i32, [_vp, _vp, _vp, _vp, _vp, _vp, _i64, _i32, _i32, _i32, _i32, _i32, _i64, _vp, _vp]),
+    "bibo_moe_ep_experts": (_i32, [_vp, _vp, _vp, _vp, _vp, _i32, _i32, _i32, _i32, _i64, _i32, _vp, _vp, _vp]),
+    "bibo_moe_ep_barrier": (_i32, [_vp, _i32, _i32, _i32, _vp, _vp]),
+    "bibo_moe_ep_combine": (_i32, [_vp, _vp, _vp, _vp, _i64, _i32, _i32, _i32, _i64, _vp, _vp]),
     "bibo_moe_route_noalloc": (_i32, [_vp, _vp, _vp, _i64, _i32, _i32, _i32, _i32, _f32, _i32, _vp, _vp, _vp, _vp]),
     "bibo_moe_route_noalloc_max_tokens": (_i64, []),
     "bibo_moe_debug_plan_header": (_i32, [_vp, _vp, _vp]),

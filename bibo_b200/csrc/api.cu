@@ -3,21 +3,17 @@
 
 namespace bibo {
 // gemm_simt.cu
-int gemm_simt_launch(const void* A, const void* B, void* C, const int32_t* plan, int64_t n_tokens,
-                     int n_experts, int n_glu, int top_k, int k_dim, int n_out, int dtype,
+int gemm_simt_launch(const void* A, const void* B, void* C, const PlanView& pv, int k_dim, int n_out, int dtype,
                      cudaStream_t st);
-int radial_rows_launch(const void* gate_up, const float* theta, const int32_t* plan,
-                       int64_t n_tokens, int n_experts, int n_glu, int top_k, int inter, int dtype,
-                       void* h, float* rnorm_out, cudaStream_t st);
+int radial_rows_launch(const void* gate_up, const float* theta, const PlanView& pv, int inter, int dtype, void* h,
+                       float* rnorm_out, cudaStream_t st);
 // gemm_tc.cu
 int gemm1_tc_supported(int hidden, int inter, int dtype);
-int gemm1_tc_launch(const void* xp, const void* gate_up_proj, const float* theta, const int32_t* plan,
-                    int64_t n_tokens, int hidden, int inter, int n_experts, int n_glu, int top_k,
-                    void* h, void* gate_up_out, float* rnorm_out, cudaStream_t st);
+int gemm1_tc_launch(const void* xp, const void* gate_up_proj, const float* theta, const PlanView& pv, int hidden,
+                    int inter, int n_weight_experts, void* h, void* gate_up_out, float* rnorm_out, cudaStream_t st);
 int gemm2_tc_supported(int hidden, int inter, int dtype);
-int gemm2_tc_launch(const void* h, const void* down_proj, const int32_t* plan, int64_t n_tokens,
-                    int hidden, int inter, int n_experts, int n_glu, int top_k, void* y,
-                    cudaStream_t st);
+int gemm2_tc_launch(const void* h, const void* down_proj, const PlanView& pv, int hidden, int inter,
+                    int n_weight_experts, void* y, cudaStream_t st);
 }  // namespace bibo
 
 using namespace bibo;
@@ -46,18 +42,16 @@ extern "C" int bibo_moe_gemm1_radial_fwd(const void* xp, const void* gate_up_pro
   if (n_glu == 0) return BIBO_OK;
   if (!xp || !gate_up_proj || !theta || !plan || !h) return fail(BIBO_ERR_ARG, "gemm1_radial_fwd: null pointer");
   cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const PlanView pv = local_plan_view(plan, n_tokens, top_k, n_experts, n_glu);
   if (gemm1_tc_supported(hidden, inter, dtype) && aligned16(xp) && aligned16(gate_up_proj) && aligned16(h) &&
       aligned16(gate_up_out))
-    return gemm1_tc_launch(xp, gate_up_proj, theta, plan, n_tokens, hidden, inter, n_experts, n_glu, top_k,
-                           h, gate_up_out, rnorm_out, st);
+    return gemm1_tc_launch(xp, gate_up_proj, theta, pv, hidden, inter, n_glu, h, gate_up_out, rnorm_out, st);
   if (!gate_up_out)
     return fail(BIBO_ERR_ARG,
                 "gemm1_radial_fwd: this dtype/shape runs the two-kernel path and needs the gate_up buffer");
-  rc = gemm_simt_launch(xp, gate_up_proj, gate_up_out, plan, n_tokens, n_experts, n_glu, top_k, hidden,
-                        2 * inter, dtype, st);
+  rc = gemm_simt_launch(xp, gate_up_proj, gate_up_out, pv, hidden, 2 * inter, dtype, st);
   if (rc) return rc;
-  return radial_rows_launch(gate_up_out, theta, plan, n_tokens, n_experts, n_glu, top_k, inter, dtype, h,
-                            rnorm_out, st);
+  return radial_rows_launch(gate_up_out, theta, pv, inter, dtype, h, rnorm_out, st);
 }
 
 extern "C" int bibo_moe_gemm1_is_fused(int hidden, int inter, int dtype) {
@@ -72,9 +66,10 @@ extern "C" int bibo_moe_gemm2_fwd(const void* h, const void* down_proj, const in
   if (n_glu == 0) return BIBO_OK;
   if (!h || !down_proj || !plan || !y) return fail(BIBO_ERR_ARG, "gemm2_fwd: null pointer");
   cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const PlanView pv = local_plan_view(plan, n_tokens, top_k, n_experts, n_glu);
   if (gemm2_tc_supported(hidden, inter, dtype) && aligned16(h) && aligned16(down_proj) && aligned16(y))
-    return gemm2_tc_launch(h, down_proj, plan, n_tokens, hidden, inter, n_experts, n_glu, top_k, y, st);
-  return gemm_simt_launch(h, down_proj, y, plan, n_tokens, n_experts, n_glu, top_k, inter, hidden, dtype, st);
+    return gemm2_tc_launch(h, down_proj, pv, hidden, inter, n_glu, y, st);
+  return gemm_simt_launch(h, down_proj, y, pv, inter, hidden, dtype, st);
 }
 
 extern "C" int bibo_moe_forward(const bibo_moe_shape* s, const void* x, const void* w_router,

@@ -69,6 +69,20 @@ __host__ __device__ inline int64_t plan_words(int64_t n, int k, int E, int n_glu
   return plan_off_tiles(n, E, n_glu) + tiles_cap(n, k, n_glu) * 4;
 }
 
+// What a grouped-GEMM launcher needs to know about a row plan: where the header / tile list live and
+// how many rows / tiles the expert-contiguous buffers were allocated for.
+struct PlanView {
+  const int32_t* plan;   // header at [0..3]
+  int64_t tiles_off;     // word offset of the int4 tile records
+  int64_t tiles_cap;     // upper bound of tiles (grid sizing)
+  int64_t rows_alloc;    // rows of the expert-contiguous buffers
+  int max_ctas;          // 0 = all SMs; otherwise an upper bound for persistent grids
+};
+inline PlanView local_plan_view(const int32_t* plan, int64_t n_tokens, int top_k, int n_experts, int n_glu) {
+  return PlanView{plan, plan_off_tiles(n_tokens, n_experts, n_glu), tiles_cap(n_tokens, top_k, n_glu),
+                  rows_cap(n_tokens, top_k, n_glu), 0};
+}
+
 // ---- dtype helpers ------------------------------------------------------------------------------
 template <typename T> __device__ __forceinline__ float to_f32(T v);
 template <> __device__ __forceinline__ float to_f32<float>(float v) { return v; }

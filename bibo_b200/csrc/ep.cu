@@ -1,0 +1,351 @@
+// Expert-parallel forward: the 64 experts are sharded contiguously over R GPUs of one NVSwitch box
+// (rank d owns experts [d*E/R, (d+1)*E/R)), tokens stay data-parallel, the router is replicated.
+//
+// There is no separate all-to-all pass.  The two exchange steps are fused into the kernels on either
+// side of the grouped GEMMs, over peer (NVLink) memory:
+//   dispatch = the permute kernel writes each token row straight into the OWNER rank's
+//              expert-contiguous receive buffer (16-byte remote stores);
+//   combine  = the combine kernel of the token's home rank reads the k result rows straight out of
+//              the owner ranks' y buffers (16-byte remote loads).
+// Row positions are agreed without host involvement: every rank holds the all-gathered per-rank
+// histograms cnt[R][E] and computes every rank's receive layout itself (ep_plan_kernel).
+//
+// Receive layout of rank d: for local expert le (ascending), for source rank s (ascending): the
+// cnt[s][d*EL+le] rows of (le, s), padded to a multiple of BIBO_TILE_M, so a row tile never mixes
+// two (expert, source) groups; tiles carry the LOCAL expert index for the weight lookup.
+// Cross-rank ordering (all stores landed before the GEMMs start; all y written before the combine
+// reads) is provided by the caller with device-side barriers between the launches.
+#include "common.cuh"
+
+namespace bibo {
+
+constexpr int EP_MAX_RANKS = 8;
+struct PeerPtrs { void* p[EP_MAX_RANKS]; };
+
+// EP plan words: [0]=n_tiles [1]=rows used [2]=status (sticky) [3]=reserved,
+// send_base[E] (row in the owner's buffer where this rank's rows of expert e start),
+// recv_off[E+1] and recv_cnt[E] (groups g = le*R + s of this rank), then int4 tiles.
+__host__ __device__ inline int64_t ep_off_send_base() { return PLAN_HDR; }
+__host__ __device__ inline int64_t ep_off_recv_off(int E) { return PLAN_HDR + E; }
+__host__ __device__ inline int64_t ep_off_recv_cnt(int E) { return PLAN_HDR + 2 * E + 1; }
+__host__ __device__ inline int64_t ep_off_tiles(int E) { return (PLAN_HDR + 3 * E + 1 + 3) / 4 * 4; }
+__host__ __device__ inline int64_t ep_plan_words(int E, int64_t rows_cap_recv) {
+  return ep_off_tiles(E) + rows_cap_recv / BIBO_TILE_M * 4;
+}
+
+// One block, E threads.  Thread d < R scans destination d's layout.
+__global__ void __launch_bounds__(BIBO_MAX_EXPERTS)
+ep_plan_kernel(const int32_t* __restrict__ cnt_all, int rank, int world, int n_experts, int rows_cap_recv,
+               int32_t* __restrict__ plan) {
+  const int el = n_experts / world;
+  int32_t* send_base = plan + ep_off_send_base();
+  int32_t* recv_off = plan + ep_off_recv_off(n_experts);
+  int32_t* recv_cnt = plan + ep_off_recv_cnt(n_experts);
+  int4* tiles = reinterpret_cast<int4*>(plan + ep_off_tiles(n_experts));
+  __shared__ int s_off[BIBO_MAX_EXPERTS + 1];
+  __shared__ int s_cnt[BIBO_MAX_EXPERTS];
+  __shared__ int s_over;
+  const int tid = threadIdx.x;
+  if (tid == 0) s_over = 0;
+  __syncthreads();
+  if (tid < world) {
+    const int d = tid;
+    int run = 0;
+    for (int le = 0; le < el; ++le)
+      for (int s = 0; s < world; ++s) {
+        const int c = cnt_all[s * n_experts + d * el + le];
+        if (s == rank) send_base[d * el + le] = run;
+        if (d == rank) { s_off[le * world + s] = run; s_cnt[le * world + s] = c; }
+        run += (c + BIBO_TILE_M - 1) / BIBO_TILE_M * BIBO_TILE_M;
+      }
+    if (run > rows_cap_recv) s_over = 1;   // some rank's buffer would overflow: everyone learns it
+    if (d == rank) s_off[n_experts] = run;
+  }
+  __syncthreads();
+  const bool over = s_over != 0;
+  if (tid == 0) {
+    const int rows = over ? 0 : s_off[n_experts];
+    plan[PLAN_N_TILES] = rows / BIBO_TILE_M;
+    plan[PLAN_ROWS_USED] = rows;
+    if (over) atomicMax(&plan[PLAN_STATUS], 4);
+  }
+  if (tid <= n_experts) recv_off[tid] = s_off[tid];
+  if (tid < n_experts) {
+    recv_cnt[tid] = s_cnt[tid];
+    if (!over) {
+      const int row0 = s_off[tid], cnt = s_cnt[tid], le = tid / world, src = tid % world;
+      int t = row0 / BIBO_TILE_M;
+      for (int r = 0; r < cnt; r += BIBO_TILE_M, ++t)
+        tiles[t] = make_int4(le, row0 + r, min(BIBO_TILE_M, cnt - r), src);
+    }
+  }
+}
+
+constexpr int EPW = 8;
+
+// Dispatch: warp per token; x[t] is read once and written to the k owner ranks' receive buffers.
+// slot_row[t][j] = owner * rows_cap_recv + row (the address the combine reads back from).
+__global__ void __launch_bounds__(EPW * 32)
+ep_dispatch_kernel(const uint8_t* __restrict__ x, const int32_t* __restrict__ topk_idx,
+                   const int32_t* __restrict__ slot_rank, const int32_t* __restrict__ local_plan,
+                   const int32_t* __restrict__ ep_plan, PeerPtrs xp_peers, int64_t n_tokens, int row_bytes,
+                   int n_experts, int world, int top_k, int rows_cap_recv, int32_t* __restrict__ slot_row) {
+  const int lane = threadIdx.x & 31;
+  const int64_t w = (int64_t)blockIdx.x * EPW + (threadIdx.x >> 5);
+  if (w >= n_tokens) return;
+  if (ep_plan[PLAN_STATUS] != 0) return;   // overflow or earlier error: write nothing
+  const int el = n_experts / world;
+  const int32_t* block_base = local_plan + plan_off_block_base(n_experts, n_experts);
+  const int32_t* send_base = ep_plan + ep_off_send_base();
+  int my_row = -1, my_owner = 0;
+  if (lane < top_k) {
+    const int e = topk_idx[w * top_k + lane];
+    const int64_t b = w / BIBO_ROUTER_BLOCK_TOKENS;
+    my_owner = e / el;
+    my_row = send_base[e] + block_base[b * n_experts + e] + slot_rank[w * top_k + lane];
+    slot_row[w * top_k + lane] = my_owner * rows_cap_recv + my_row;
+  }
+  uint4* dst[BIBO_MAX_TOP_K];
+#pragma unroll
+  for (int j = 0; j < BIBO_MAX_TOP_K; ++j) {
+    const int r = __shfl_sync(0xffffffffu, my_row, j);
+    const int o = __shfl_sync(0xffffffffu, my_owner, j);
+    dst[j] = reinterpret_cast<uint4*>(static_cast<uint8_t*>(xp_peers.p[o]) + (int64_t)r * row_bytes);
+  }
+  const uint4* src = reinterpret_cast<const uint4*>(x + w * row_bytes);
+  const int chunks = row_bytes / 16;
+  for (int c = lane; c < chunks; c += 32) {
+    const uint4 v = __ldg(src + c);
+#pragma unroll
+    for (int j = 0; j < BIBO_MAX_TOP_K; ++j)
+      if (j < top_k) dst[j][c] = v;
+  }
+}
+
+__device__ __forceinline__ void fma_bf16x8(const uint4& v, float w, float* acc) {
+  const uint32_t u[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    acc[2 * i] = fmaf(__uint_as_float(u[i] << 16), w, acc[2 * i]);
+    acc[2 * i + 1] = fmaf(__uint_as_float(u[i] & 0xffff0000u), w, acc[2 * i + 1]);
+  }
+}
+
+// Combine: warp per token; the k rows are read from the owner ranks' y buffers (peer loads), summed
+// in slot order (ascending expert) in fp32, cast once.
+template <int K>
+__global__ void __launch_bounds__(EPW * 32, 4)
+ep_combine_kernel(PeerPtrs y_peers, const int32_t* __restrict__ slot_row, const float* __restrict__ topk_w,
+                  const int32_t* __restrict__ ep_plan, int64_t n_tokens, int hidden, int rows_cap_recv,
+                  __nv_bfloat16* __restrict__ out) {
+  const int lane = threadIdx.x & 31;
+  const int64_t t = (int64_t)blockIdx.x * EPW + (threadIdx.x >> 5);
+  if (t >= n_tokens) return;
+  if (ep_plan[PLAN_STATUS] != 0) return;
+  int my_g = 0;
+  float my_w = 0.f;
+  if (lane < K) { my_g = slot_row[t * K + lane]; my_w = topk_w[t * K + lane]; }
+  const uint4* src[K];
+  float ws[K];
+#pragma unroll
+  for (int j = 0; j < K; ++j) {
+    const int g = __shfl_sync(0xffffffffu, my_g, j);
+    ws[j] = __shfl_sync(0xffffffffu, my_w, j);
+    const int o = g / rows_cap_recv, r = g % rows_cap_recv;
+    src[j] = reinterpret_cast<const uint4*>(static_cast<const __nv_bfloat16*>(y_peers.p[o]) + (int64_t)r * hidden);
+  }
+  uint4* dst = reinterpret_cast<uint4*>(out + t * hidden);
+  const int chunks = hidden / 8;
+  int c = lane;
+  for (; c + 32 < chunks; c += 64) {
+    uint4 v0[K], v1[K];
+#pragma unroll
+    for (int j = 0; j < K; ++j) { v0[j] = src[j][c]; v1[j] = src[j][c + 32]; }
+    float a0[8], a1[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) a0[i] = a1[i] = 0.f;
+#pragma unroll
+    for (int j = 0; j < K; ++j) { fma_bf16x8(v0[j], ws[j], a0); fma_bf16x8(v1[j], ws[j], a1); }
+    uint4 o0, o1;
+    __nv_bfloat162* h0 = reinterpret_cast<__nv_bfloat162*>(&o0);
+    __nv_bfloat162* h1 = reinterpret_cast<__nv_bfloat162*>(&o1);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      h0[i] = __floats2bfloat162_rn(a0[2 * i], a0[2 * i + 1]);
+      h1[i] = __floats2bfloat162_rn(a1[2 * i], a1[2 * i + 1]);
+    }
+    dst[c] = o0;
+    dst[c + 32] = o1;
+  }
+  for (; c < chunks; c += 32) {
+    uint4 v0[K];
+#pragma unroll
+    for (int j = 0; j < K; ++j) v0[j] = src[j][c];
+    float a0[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) a0[i] = 0.f;
+#pragma unroll
+    for (int j = 0; j < K; ++j) fma_bf16x8(v0[j], ws[j], a0);
+    uint4 o0;
+    __nv_bfloat162* h0 = reinterpret_cast<__nv_bfloat162*>(&o0);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) h0[i] = __floats2bfloat162_rn(a0[2 * i], a0[2 * i + 1]);
+    dst[c] = o0;
+  }
+}
+
+// gemm_tc.cu
+int gemm1_tc_supported(int hidden, int inter, int dtype);
+int gemm1_tc_launch(const void* xp, const void* gate_up_proj, const float* theta, const PlanView& pv, int hidden,
+                    int inter, int n_weight_experts, void* h, void* gate_up_out, float* rnorm_out, cudaStream_t st);
+int gemm2_tc_supported(int hidden, int inter, int dtype);
+int gemm2_tc_launch(const void* h, const void* down_proj, const PlanView& pv, int hidden, int inter,
+                    int n_weight_experts, void* y, cudaStream_t st);
+
+}  // namespace bibo
+
+using namespace bibo;
+
+static int ep_check(const char* who, int world, int rank, int n_experts, int64_t rows_cap_recv) {
+  if (world < 1 || world > EP_MAX_RANKS || rank < 0 || rank >= world)
+    return fail(BIBO_ERR_ARG, "%s: rank %d of %d (max %d ranks)", who, rank, world, EP_MAX_RANKS);
+  if (n_experts < world || n_experts > BIBO_MAX_EXPERTS || n_experts % world != 0)
+    return fail(BIBO_ERR_UNSUPPORTED, "%s: %d experts do not shard evenly over %d ranks", who, n_experts, world);
+  if (rows_cap_recv <= 0 || rows_cap_recv % BIBO_TILE_M != 0 || rows_cap_recv * world > 0x7fffffffLL)
+    return fail(BIBO_ERR_ARG, "%s: rows_cap_recv=%lld must be a positive multiple of %d", who,
+                (long long)rows_cap_recv, BIBO_TILE_M);
+  return BIBO_OK;
+}
+
+extern "C" int64_t bibo_moe_ep_plan_words(int n_experts, int64_t rows_cap_recv) {
+  return ep_plan_words(n_experts, rows_cap_recv);
+}
+extern "C" int64_t bibo_moe_ep_plan_off(int which, int n_experts) {
+  switch (which) {
+    case 0: return ep_off_send_base();
+    case 1: return ep_off_recv_off(n_experts);
+    case 2: return ep_off_recv_cnt(n_experts);
+    default: return ep_off_tiles(n_experts);
+  }
+}
+
+extern "C" int bibo_moe_ep_plan(const int32_t* cnt_all, int rank, int world, int n_experts, int64_t rows_cap_recv,
+                                int32_t* ep_plan, void* stream) {
+  int rc = ep_check("ep_plan", world, rank, n_experts, rows_cap_recv);
+  if (rc) return rc;
+  if (!cnt_all || !ep_plan) return fail(BIBO_ERR_ARG, "ep_plan: null pointer");
+  ep_plan_kernel<<<1, BIBO_MAX_EXPERTS, 0, static_cast<cudaStream_t>(stream)>>>(cnt_all, rank, world, n_experts,
+                                                                               (int)rows_cap_recv, ep_plan);
+  BIBO_CHECK_LAUNCH("ep_plan_kernel");
+  return BIBO_OK;
+}
+
+extern "C" int bibo_moe_ep_dispatch(const void* x, const int32_t* topk_idx, const int32_t* slot_rank,
+                                    const int32_t* local_plan, const int32_t* ep_plan, void* const* xp_peers,
+                                    int64_t n_tokens, int hidden, int n_experts, int rank, int world, int top_k,
+                                    int64_t rows_cap_recv, int32_t* slot_row, void* stream) {
+  int rc = ep_check("ep_dispatch", world, rank, n_experts, rows_cap_recv);
+  if (rc) return rc;
+  if (n_tokens <= 0) return BIBO_OK;
+  if (!x || !topk_idx || !slot_rank || !local_plan || !ep_plan || !xp_peers || !slot_row)
+    return fail(BIBO_ERR_ARG, "ep_dispatch: null pointer");
+  if (top_k < 1 || top_k > BIBO_MAX_TOP_K) return fail(BIBO_ERR_UNSUPPORTED, "ep_dispatch: top_k=%d", top_k);
+  const int row_bytes = hidden * 2;
+  if (row_bytes % 16 != 0) return fail(BIBO_ERR_UNSUPPORTED, "ep_dispatch: hidden=%d", hidden);
+  PeerPtrs pp = {};
+  for (int i = 0; i < world; ++i) {
+    if (!xp_peers[i] || !aligned16(xp_peers[i])) return fail(BIBO_ERR_ALIGN, "ep_dispatch: peer buffer %d", i);
+    pp.p[i] = xp_peers[i];
+  }
+  dim3 grid((unsigned)((n_tokens + EPW - 1) / EPW));
+  ep_dispatch_kernel<<<grid, EPW * 32, 0, static_cast<cudaStream_t>(stream)>>>(
+      (const uint8_t*)x, topk_idx, slot_rank, local_plan, ep_plan, pp, n_tokens, row_bytes, n_experts, world, top_k,
+      (int)rows_cap_recv, slot_row);
+  BIBO_CHECK_LAUNCH("ep_dispatch_kernel");
+  return BIBO_OK;
+}
+
+extern "C" int bibo_moe_ep_experts(const void* xp_recv, const void* gate_up_proj, const void* down_proj,
+                                   const float* theta, const int32_t* ep_plan, int hidden, int inter, int n_experts,
+                                   int world, int64_t rows_cap_recv, int max_ctas, void* h, void* y_recv,
+                                   void* stream) {
+  int rc = ep_check("ep_experts", world, 0, n_experts, rows_cap_recv);
+  if (rc) return rc;
+  if (!xp_recv || !gate_up_proj || !down_proj || !theta || !ep_plan || !h || !y_recv)
+    return fail(BIBO_ERR_ARG, "ep_experts: null pointer");
+  if (!gemm1_tc_supported(hidden, inter, BIBO_BF16) || !gemm2_tc_supported(hidden, inter, BIBO_BF16))
+    return fail(BIBO_ERR_UNSUPPORTED, "ep_experts: hidden=%d inter=%d is outside the tensor-core kernels", hidden, inter);
+  const PlanView pv{ep_plan, ep_off_tiles(n_experts), rows_cap_recv / BIBO_TILE_M, rows_cap_recv, max_ctas};
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const int el = n_experts / world;
+  rc = gemm1_tc_launch(xp_recv, gate_up_proj, theta, pv, hidden, inter, el, h, nullptr, nullptr, st);
+  if (rc) return rc;
+  return gemm2_tc_launch(h, down_proj, pv, hidden, inter, el, y_recv, st);
+}
+
+extern "C" int bibo_moe_ep_combine(void* const* y_peers, const int32_t* slot_row, const float* topk_w,
+                                   const int32_t* ep_plan, int64_t n_tokens, int hidden, int world, int top_k,
+                                   int64_t rows_cap_recv, void* out, void* stream) {
+  if (n_tokens <= 0) return BIBO_OK;
+  if (!y_peers || !slot_row || !topk_w || !ep_plan || !out) return fail(BIBO_ERR_ARG, "ep_combine: null pointer");
+  if (world < 1 || world > EP_MAX_RANKS) return fail(BIBO_ERR_ARG, "ep_combine: world=%d", world);
+  if (hidden % 8 != 0) return fail(BIBO_ERR_UNSUPPORTED, "ep_combine: hidden=%d", hidden);
+  PeerPtrs pp = {};
+  for (int i = 0; i < world; ++i) {
+    if (!y_peers[i] || !aligned16(y_peers[i])) return fail(BIBO_ERR_ALIGN, "ep_combine: peer buffer %d", i);
+    pp.p[i] = y_peers[i];
+  }
+  dim3 grid((unsigned)((n_tokens + EPW - 1) / EPW));
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+#define BIBO_EPC(KK)                                                                                              \
+  case KK:                                                                                                        \
+    ep_combine_kernel<KK><<<grid, EPW * 32, 0, st>>>(pp, slot_row, topk_w, ep_plan, n_tokens, hidden,             \
+                                                     (int)rows_cap_recv, (__nv_bfloat16*)out);                    \
+    break;
+  switch (top_k) {
+    BIBO_EPC(1) BIBO_EPC(2) BIBO_EPC(3) BIBO_EPC(4) BIBO_EPC(5) BIBO_EPC(6) BIBO_EPC(7) BIBO_EPC(8)
+    default: return fail(BIBO_ERR_UNSUPPORTED, "ep_combine: top_k=%d", top_k);
+  }
+#undef BIBO_EPC
+  BIBO_CHECK_LAUNCH("ep_combine_kernel");
+  return BIBO_OK;
+}
+
+// ---- cross-rank barrier on the stream -------------------------------------------------------------
+// flags_peers[r] = rank r's int32[EP_MAX_RANKS] flag array as mapped into this process (zeroed once
+// at set-up).  Thread p publishes `epoch` into slot [rank] of peer p (release, system scope: every
+// earlier write of this GPU, including the previous kernels' peer stores, is visible first) and then
+// waits until slot [p] of its own array reaches `epoch`.  The wait is bounded: after about two
+// seconds the kernel gives up, raises the status word to 5 and returns.
+namespace bibo {
+__global__ void ep_barrier_kernel(PeerPtrs flags, int rank, int world, int epoch, int32_t* status) {
+  const int p = threadIdx.x;
+  if (p >= world) return;
+  int* remote = static_cast<int*>(flags.p[p]) + rank;
+  int* mine = static_cast<int*>(flags.p[rank]) + p;
+  __threadfence_system();
+  asm volatile("st.release.sys.global.s32 [%0], %1;" ::"l"(remote), "r"(epoch) : "memory");
+  for (uint32_t i = 0; i < (1u << 22); ++i) {
+    int v;
+    asm volatile("ld.acquire.sys.global.s32 %0, [%1];" : "=r"(v) : "l"(mine) : "memory");
+    if (v >= epoch) return;
+    __nanosleep(400);
+  }
+  if (status) atomicMax(status, 5);
+}
+}  // namespace bibo
+
+extern "C" int bibo_moe_ep_barrier(void* const* flags_peers, int rank, int world, int epoch, int32_t* status,
+                                   void* stream) {
+  if (!flags_peers) return fail(BIBO_ERR_ARG, "ep_barrier: null pointer");
+  if (world < 1 || world > EP_MAX_RANKS || rank < 0 || rank >= world)
+    return fail(BIBO_ERR_ARG, "ep_barrier: rank %d of %d", rank, world);
+  PeerPtrs pp = {};
+  for (int i = 0; i < world; ++i) {
+    if (!flags_peers[i]) return fail(BIBO_ERR_ARG, "ep_barrier: peer %d has no flag array", i);
+    pp.p[i] = flags_peers[i];
+  }
+  ep_barrier_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(pp, rank, world, epoch, status);
+  BIBO_CHECK_LAUNCH("ep_barrier_kernel");
+  return BIBO_OK;
+}

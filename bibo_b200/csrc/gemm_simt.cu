@@ -92,33 +92,28 @@ radial_rows_kernel(const T* __restrict__ gate_up, const float* __restrict__ thet
   }
 }
 
-int gemm_simt_launch(const void* A, const void* B, void* C, const int32_t* plan, int64_t n_tokens,
-                     int n_experts, int n_glu, int top_k, int k_dim, int n_out, int dtype,
+int gemm_simt_launch(const void* A, const void* B, void* C, const PlanView& pv, int k_dim, int n_out, int dtype,
                      cudaStream_t st) {
-  dim3 grid((unsigned)tiles_cap(n_tokens, top_k, n_glu), (unsigned)((n_out + GN - 1) / GN));
-  const int64_t toff = plan_off_tiles(n_tokens, n_experts, n_glu);
+  dim3 grid((unsigned)pv.tiles_cap, (unsigned)((n_out + GN - 1) / GN));
   if (dtype == BIBO_F32)
-    grouped_gemm_simt_kernel<float><<<grid, 256, 0, st>>>((const float*)A, (const float*)B, (float*)C,
-                                                          plan, toff, k_dim, n_out);
+    grouped_gemm_simt_kernel<float><<<grid, 256, 0, st>>>((const float*)A, (const float*)B, (float*)C, pv.plan,
+                                                          pv.tiles_off, k_dim, n_out);
   else
     grouped_gemm_simt_kernel<__nv_bfloat16><<<grid, 256, 0, st>>>(
-        (const __nv_bfloat16*)A, (const __nv_bfloat16*)B, (__nv_bfloat16*)C, plan, toff, k_dim, n_out);
+        (const __nv_bfloat16*)A, (const __nv_bfloat16*)B, (__nv_bfloat16*)C, pv.plan, pv.tiles_off, k_dim, n_out);
   BIBO_CHECK_LAUNCH("grouped_gemm_simt_kernel");
   return BIBO_OK;
 }
 
-int radial_rows_launch(const void* gate_up, const float* theta, const int32_t* plan,
-                       int64_t n_tokens, int n_experts, int n_glu, int top_k, int inter, int dtype,
-                       void* h, float* rnorm_out, cudaStream_t st) {
-  const int64_t rows = rows_cap(n_tokens, top_k, n_glu);
-  dim3 grid((unsigned)((rows + 7) / 8));
-  const int64_t toff = plan_off_tiles(n_tokens, n_experts, n_glu);
+int radial_rows_launch(const void* gate_up, const float* theta, const PlanView& pv, int inter, int dtype, void* h,
+                       float* rnorm_out, cudaStream_t st) {
+  dim3 grid((unsigned)((pv.rows_alloc + 7) / 8));
   if (dtype == BIBO_F32)
-    radial_rows_kernel<float><<<grid, 256, 0, st>>>((const float*)gate_up, theta, plan, toff, inter,
+    radial_rows_kernel<float><<<grid, 256, 0, st>>>((const float*)gate_up, theta, pv.plan, pv.tiles_off, inter,
                                                     (float*)h, rnorm_out);
   else
-    radial_rows_kernel<__nv_bfloat16><<<grid, 256, 0, st>>>((const __nv_bfloat16*)gate_up, theta, plan,
-                                                            toff, inter, (__nv_bfloat16*)h, rnorm_out);
+    radial_rows_kernel<__nv_bfloat16><<<grid, 256, 0, st>>>((const __nv_bfloat16*)gate_up, theta, pv.plan,
+                                                            pv.tiles_off, inter, (__nv_bfloat16*)h, rnorm_out);
   BIBO_CHECK_LAUNCH("radial_rows_kernel");
   return BIBO_OK;
 }

@@ -477,23 +477,23 @@ int gemm2_tc_supported(int hidden, int inter, int dtype) {
   return dtype == BIBO_BF16 && hidden % 256 == 0 && inter % 64 == 0 && inter >= 64;
 }
 
-int gemm2_tc_launch(const void* h, const void* down_proj, const int32_t* plan, int64_t n_tokens, int hidden,
-                    int inter, int n_experts, int n_glu, int top_k, void* y, cudaStream_t st) {
+int gemm2_tc_launch(const void* h, const void* down_proj, const PlanView& pv, int hidden, int inter,
+                    int n_weight_experts, void* y, cudaStream_t st) {
   constexpr int BN = 256, STAGES = 4;
   using L = G2Layout<BN, STAGES>;
-  const uint64_t rows = rows_cap(n_tokens, top_k, n_glu);
   CUtensorMap tmA, tmB, tmC;
   int rc;
-  if ((rc = make_tmap_bf16_2d(&tmA, h, rows, inter, inter, BM))) return rc;
-  if ((rc = make_tmap_bf16_2d(&tmB, down_proj, (uint64_t)n_glu * hidden, inter, inter, BN))) return rc;
-  if ((rc = make_tmap_bf16_2d(&tmC, y, rows, hidden, hidden, BM))) return rc;
+  if ((rc = make_tmap_bf16_2d(&tmA, h, pv.rows_alloc, inter, inter, BM))) return rc;
+  if ((rc = make_tmap_bf16_2d(&tmB, down_proj, (uint64_t)n_weight_experts * hidden, inter, inter, BN))) return rc;
+  if ((rc = make_tmap_bf16_2d(&tmC, y, pv.rows_alloc, hidden, hidden, BM))) return rc;
   auto kern = gemm2_tc_kernel<BN, STAGES>;
   static bool attr_done = false;
   if (!attr_done) { if ((rc = set_smem(kern, L::BYTES))) return rc; attr_done = true; }
-  const int64_t work_cap = tiles_cap(n_tokens, top_k, n_glu) * (hidden / BN);
-  const int grid = (int)std::min<int64_t>(sm_count(), work_cap);
-  kern<<<grid, NUM_THREADS, L::BYTES, st>>>(tmA, tmB, tmC, const_cast<int32_t*>(plan),
-                                           plan_off_tiles(n_tokens, n_experts, n_glu), hidden / BN, inter / BK, hidden);
+  const int64_t work_cap = pv.tiles_cap * (hidden / BN);
+  const int sms = pv.max_ctas > 0 ? std::min(pv.max_ctas, sm_count()) : sm_count();
+  const int grid = (int)std::min<int64_t>(sms, work_cap);
+  kern<<<grid, NUM_THREADS, L::BYTES, st>>>(tmA, tmB, tmC, const_cast<int32_t*>(pv.plan), pv.tiles_off, hidden / BN,
+                                           inter / BK, hidden);
   BIBO_CHECK_LAUNCH("gemm2_tc_kernel");
   return BIBO_OK;
 }
@@ -504,14 +504,15 @@ int gemm1_tc_supported(int hidden, int inter, int dtype) {
 
 template <int NC, int CL, int STAGES>
 static int gemm1_launch_t(const CUtensorMap& tmA, const CUtensorMap& tmB, const CUtensorMap& tmH, const float* theta,
-                          const int32_t* plan, int64_t tiles_off, int64_t tile_cap, int k_blocks, int inter,
-                          void* gate_up_out, float* rnorm_out, cudaStream_t st) {
+                          const int32_t* plan, int64_t tiles_off, int64_t tile_cap, int max_ctas, int k_blocks,
+                          int inter, void* gate_up_out, float* rnorm_out, cudaStream_t st) {
   using L = G1Layout<NC, STAGES>;
   auto kern = gemm1_tc_kernel<NC, CL, STAGES>;
   static bool attr_done = false;
   int rc;
   if (!attr_done) { if ((rc = set_smem(kern, L::BYTES))) return rc; attr_done = true; }
-  int clusters = (int)std::min<int64_t>(sm_count() / CL, tile_cap);
+  const int sms = max_ctas > 0 ? std::min(max_ctas, sm_count()) : sm_count();
+  int clusters = (int)std::min<int64_t>(sms / CL, tile_cap);
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(clusters * CL);
   cfg.blockDim = dim3(NUM_THREADS);
@@ -530,23 +531,22 @@ static int gemm1_launch_t(const CUtensorMap& tmA, const CUtensorMap& tmB, const 
   return BIBO_OK;
 }
 
-int gemm1_tc_launch(const void* xp, const void* gate_up_proj, const float* theta, const int32_t* plan,
-                    int64_t n_tokens, int hidden, int inter, int n_experts, int n_glu, int top_k, void* h,
-                    void* gate_up_out, float* rnorm_out, cudaStream_t st) {
-  const uint64_t rows = rows_cap(n_tokens, top_k, n_glu);
+int gemm1_tc_launch(const void* xp, const void* gate_up_proj, const float* theta, const PlanView& pv, int hidden,
+                    int inter, int n_weight_experts, void* h, void* gate_up_out, float* rnorm_out, cudaStream_t st) {
   const int nc = inter >= 256 ? 256 : 128;
   CUtensorMap tmA, tmB, tmH;
   int rc;
-  if ((rc = make_tmap_bf16_2d(&tmA, xp, rows, hidden, hidden, BM))) return rc;
-  if ((rc = make_tmap_bf16_2d(&tmB, gate_up_proj, (uint64_t)n_glu * 2 * inter, hidden, hidden, nc))) return rc;
-  if ((rc = make_tmap_bf16_2d(&tmH, h, rows, inter, inter, BM))) return rc;
-  const int64_t toff = plan_off_tiles(n_tokens, n_experts, n_glu);
-  const int64_t tcap = tiles_cap(n_tokens, top_k, n_glu);
+  if ((rc = make_tmap_bf16_2d(&tmA, xp, pv.rows_alloc, hidden, hidden, BM))) return rc;
+  if ((rc = make_tmap_bf16_2d(&tmB, gate_up_proj, (uint64_t)n_weight_experts * 2 * inter, hidden, hidden, nc))) return rc;
+  if ((rc = make_tmap_bf16_2d(&tmH, h, pv.rows_alloc, inter, inter, BM))) return rc;
   if (inter == 512)
-    return gemm1_launch_t<256, 2, 3>(tmA, tmB, tmH, theta, plan, toff, tcap, hidden / BK, inter, gate_up_out, rnorm_out, st);
+    return gemm1_launch_t<256, 2, 3>(tmA, tmB, tmH, theta, pv.plan, pv.tiles_off, pv.tiles_cap, pv.max_ctas,
+                                     hidden / BK, inter, gate_up_out, rnorm_out, st);
   if (inter == 256)
-    return gemm1_launch_t<256, 1, 3>(tmA, tmB, tmH, theta, plan, toff, tcap, hidden / BK, inter, gate_up_out, rnorm_out, st);
-  return gemm1_launch_t<128, 1, 4>(tmA, tmB, tmH, theta, plan, toff, tcap, hidden / BK, inter, gate_up_out, rnorm_out, st);
+    return gemm1_launch_t<256, 1, 3>(tmA, tmB, tmH, theta, pv.plan, pv.tiles_off, pv.tiles_cap, pv.max_ctas,
+                                     hidden / BK, inter, gate_up_out, rnorm_out, st);
+  return gemm1_launch_t<128, 1, 4>(tmA, tmB, tmH, theta, pv.plan, pv.tiles_off, pv.tiles_cap, pv.max_ctas,
+                                   hidden / BK, inter, gate_up_out, rnorm_out, st);
 }
 
 // router on tensor cores: see router_tc.cu

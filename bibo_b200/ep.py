@@ -1,0 +1,177 @@
+"""Expert-parallel forward of the MoE block over the GPUs of one NVSwitch box.
+
+One process per GPU (``torch.distributed``, NCCL).  Rank d owns experts ``[d*E/R, (d+1)*E/R)``; tokens
+stay on their home rank; the router is replicated.  The exchange steps are not separate collectives:
+the dispatch kernel stores token rows straight into the owner ranks' receive buffers and the combine
+kernel loads result rows straight from the owners' buffers, both over NVLink peer memory
+(``include/bibo_moe.h``, section "expert-parallel forward").  torch supplies the plumbing only:
+symmetric (peer-mapped) buffers and one tiny NCCL all-gather of the per-rank histograms.
+
+The reference has no expert parallelism; the oracle for this path is the single-process block on the
+concatenation of all ranks' tokens with the full set of expert weights.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import os
+from typing import Optional
+
+import torch
+import torch.distributed as dist
+
+from . import _lib
+from . import functional as Fn
+
+TILE_M = _lib.TILE_M
+
+
+def ep_layout(cnt_all: torch.Tensor, rank: int, world: int):
+    """Host mirror of ``ep_plan_kernel`` (used to size buffers and to check the kernel).
+
+    cnt_all [world, E] = tokens-per-expert histogram of every rank.  Returns a dict with
+    ``send_base [E]`` (row in the owner's receive buffer where THIS rank's rows of expert e start),
+    ``recv_off [E+1]`` / ``recv_cnt [E]`` of this rank's groups g = le*world + s, ``rows`` per rank.
+    """
+    cnt = cnt_all.to(torch.int64).cpu()
+    n_exp = cnt.shape[1]
+    el = n_exp // world
+    pad = (cnt + TILE_M - 1) // TILE_M * TILE_M
+    send_base = torch.zeros(n_exp, dtype=torch.int64)
+    rows = torch.zeros(world, dtype=torch.int64)
+    recv_off = torch.zeros(n_exp + 1, dtype=torch.int64)
+    recv_cnt = torch.zeros(n_exp, dtype=torch.int64)
+    for d in range(world):
+        run = 0
+        for le in range(el):
+            for s in range(world):
+                if s == rank:
+                    send_base[d * el + le] = run
+                if d == rank:
+                    recv_off[le * world + s] = run
+                    recv_cnt[le * world + s] = cnt[s, d * el + le]
+                run += int(pad[s, d * el + le])
+        rows[d] = run
+        if d == rank:
+            recv_off[n_exp] = run
+    return dict(send_base=send_base, recv_off=recv_off, recv_cnt=recv_cnt, rows=rows)
+
+
+def recv_rows_cap(n_tokens: int, top_k: int, n_experts: int, world: int, capacity_factor: float) -> int:
+    """Rows provisioned per rank for received tokens: capacity_factor x the balanced share, plus the
+    worst-case padding of the E groups, rounded to the tile size (never more than every row of every
+    rank)."""
+    balanced = n_tokens * top_k                      # world * N * k / world
+    worst = world * n_tokens * top_k
+    rows = min(int(balanced * capacity_factor), worst) + n_experts * (TILE_M - 1)
+    return (rows + TILE_M - 1) // TILE_M * TILE_M
+
+
+class _Symmetric:
+    """A tensor every rank allocates identically, mapped into every process of the group."""
+
+    def __init__(self, shape, dtype, device, group):
+        import torch.distributed._symmetric_memory as symm_mem
+        self.tensor = symm_mem.empty(*shape, dtype=dtype, device=device)
+        self.handle = symm_mem.rendezvous(self.tensor, group.group_name)
+        self.ptrs = [int(p) for p in self.handle.buffer_ptrs]
+        self.ptr_array = (C.c_void_p * len(self.ptrs))(*self.ptrs)
+
+
+class ExpertParallelMoE:
+    """Forward of the MoE block with the experts sharded over ``group``.
+
+    ``weights`` holds the FULL tensors (``w_router [E,H]``, ``bias [E]``, ``gate_up_proj [E,2I,H]``,
+    ``down_proj [E,H,I]``, ``radial_theta [E]``) or already-sharded expert tensors (leading dimension
+    E/world); only this rank's shard is kept.
+    """
+
+    def __init__(self, weights, top_k: int, group=None, n_tokens: Optional[int] = None, norm_mode="sum",
+                 scale: float = 1.0, capacity_factor: float = 2.0, max_ctas: int = 0):
+        os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")   # plain peer loads/stores only
+        self.group = group if group is not None else dist.group.WORLD
+        self.rank, self.world = dist.get_rank(self.group), dist.get_world_size(self.group)
+        self.top_k, self.norm_mode, self.scale = top_k, norm_mode, scale
+        self.capacity_factor, self.max_ctas = capacity_factor, max_ctas
+        w_r = weights["w_router"]
+        self.device = w_r.device
+        self.n_experts, self.hidden = w_r.shape
+        if self.n_experts % self.world:
+            raise RuntimeError(f"{self.n_experts} experts do not shard evenly over {self.world} ranks")
+        self.el = self.n_experts // self.world
+        lo, hi = self.rank * self.el, (self.rank + 1) * self.el
+        shard = lambda t: (t[lo:hi] if t.shape[0] == self.n_experts else t).contiguous()
+        self.w_router, self.bias = w_r.contiguous(), weights["bias"].float().contiguous()
+        self.gate_up, self.down = shard(weights["gate_up_proj"]), shard(weights["down_proj"])
+        self.theta = shard(weights["radial_theta"]).float().contiguous()
+        self.inter = self.gate_up.shape[1] // 2
+        if w_r.dtype != torch.bfloat16:
+            raise RuntimeError("the expert-parallel path runs the bf16 tensor-core kernels only")
+        self._n = None
+        self._epoch = 0
+        if n_tokens is not None:
+            self._allocate(n_tokens)
+
+    # ---- buffers --------------------------------------------------------------------------------------
+    def _allocate(self, n_tokens: int) -> None:
+        lib = _lib.load()
+        dev, k, e = self.device, self.top_k, self.n_experts
+        self._n = n_tokens
+        self.cap = recv_rows_cap(n_tokens, k, e, self.world, self.capacity_factor)
+        geo = Fn.Geometry(n_tokens, self.hidden, self.inter, e, e, 0, k, torch.bfloat16)
+        i32 = dict(dtype=torch.int32, device=dev)
+        self.topk_idx = torch.empty(n_tokens, k, **i32)
+        self.topk_w = torch.empty(n_tokens, k, dtype=torch.float32, device=dev)
+        self.slot_rank = torch.empty(n_tokens, k, **i32)
+        self.block_counts = torch.empty(geo.router_blocks, e, **i32)
+        self.local_plan = torch.zeros(geo.plan_words, **i32)
+        self.slot_row = torch.empty(n_tokens, k, **i32)
+        self.ep_plan = torch.zeros(int(lib.bibo_moe_ep_plan_words(e, self.cap)), **i32)
+        self.cnt_all = torch.zeros(self.world, e, **i32)
+        self.h = torch.empty(self.cap, self.inter, dtype=torch.bfloat16, device=dev)
+        self.xp = _Symmetric((self.cap, self.hidden), torch.bfloat16, dev, self.group)
+        self.y = _Symmetric((self.cap, self.hidden), torch.bfloat16, dev, self.group)
+        self.flags = _Symmetric((64,), torch.int32, dev, self.group)
+        self.flags.tensor.zero_()
+        torch.cuda.synchronize(dev)
+        dist.barrier(self.group)            # every rank's flags are zero before the first device barrier
+        o = int(lib.bibo_moe_plan_off_counts())
+        self._counts = self.local_plan[o:o + e]
+
+    def _barrier(self, st) -> None:
+        self._epoch += 1
+        _lib.check(_lib.load().bibo_moe_ep_barrier(self.flags.ptr_array, self.rank, self.world, self._epoch,
+                                                   _lib.ptr(self.ep_plan[2:]), st), "bibo_moe_ep_barrier")
+
+    # ---- forward ----------------------------------------------------------------------------------------
+    def forward(self, x: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+        lib, p = _lib.load(), _lib.ptr
+        n, hidden = x.shape
+        if self._n != n:
+            self._allocate(n)
+        if out is None:
+            out = torch.empty_like(x)
+        k, e, st = self.top_k, self.n_experts, torch.cuda.current_stream(self.device).cuda_stream
+        _lib.check(lib.bibo_moe_router_fwd(p(x), p(self.w_router), p(self.bias), None, n, hidden, e, k,
+                                           Fn.norm_code(self.norm_mode), float(self.scale), _lib.BF16, None,
+                                           p(self.topk_idx), p(self.topk_w), p(self.slot_rank), p(self.block_counts),
+                                           p(self.local_plan[2:]), st), "bibo_moe_router_fwd")
+        _lib.check(lib.bibo_moe_plan(p(self.block_counts), n, k, e, e, p(self.local_plan), st), "bibo_moe_plan")
+        dist.all_gather_into_tensor(self.cnt_all.view(-1), self._counts, group=self.group)
+        _lib.check(lib.bibo_moe_ep_plan(p(self.cnt_all), self.rank, self.world, e, self.cap, p(self.ep_plan), st),
+                   "bibo_moe_ep_plan")
+        _lib.check(lib.bibo_moe_ep_dispatch(p(x), p(self.topk_idx), p(self.slot_rank), p(self.local_plan),
+                                            p(self.ep_plan), self.xp.ptr_array, n, hidden, e, self.rank, self.world, k,
+                                            self.cap, p(self.slot_row), st), "bibo_moe_ep_dispatch")
+        self._barrier(st)                   # every rank's rows have landed
+        _lib.check(lib.bibo_moe_ep_experts(p(self.xp.tensor), p(self.gate_up), p(self.down), p(self.theta),
+                                           p(self.ep_plan), hidden, self.inter, e, self.world, self.cap, self.max_ctas,
+                                           p(self.h), p(self.y.tensor), st), "bibo_moe_ep_experts")
+        self._barrier(st)                   # every rank's results are written
+        _lib.check(lib.bibo_moe_ep_combine(self.y.ptr_array, p(self.slot_row), p(self.topk_w), p(self.ep_plan), n,
+                                           hidden, self.world, k, self.cap, p(out), st), "bibo_moe_ep_combine")
+        return out
+
+    def status(self) -> int:
+        """Sticky status words of both plans (synchronises): 0 = fine, 4 = receive buffer overflow,
+        5 = a cross-rank barrier timed out, 100-102 = a bounded wait in a kernel gave up."""
+        return max(int(self.ep_plan[2].item()), int(self.local_plan[2].item()))

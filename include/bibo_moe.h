@@ -192,6 +192,42 @@ int bibo_moe_forward_host(const bibo_moe_shape* shape, const void* x_host, void*
                           const void* down_proj, const float* theta, const bibo_moe_workspace* ws,
                           void* out_dev, void* out_host, void* stream);
 
+/* ---- expert-parallel forward over NVLink peer memory ------------------------------------------------
+ * No counterpart in the reference (it has no expert parallelism; its only collective is the
+ * all_reduce of accumulated_tpe, src/modeling/ffn/moe.py:150-151).  Experts are sharded contiguously
+ * over `world` GPUs of one box, tokens stay on their home rank, the router is replicated.  The two
+ * exchange steps are fused into the neighbouring kernels: bibo_moe_ep_dispatch writes token rows
+ * straight into the owner ranks' receive buffers (peer stores), bibo_moe_ep_combine reads result rows
+ * straight from the owner ranks' y buffers (peer loads).  The caller provides peer-mapped buffers
+ * (xp_peers[r], y_peers[r] = rank r's receive / result buffer [rows_cap_recv, H] as mapped into THIS
+ * process), the all-gathered histograms cnt_all [world, E] (counts of bibo_moe_plan of every rank),
+ * and a cross-rank barrier on the stream between dispatch -> experts and experts -> combine.
+ * ep_plan layout: [0]=n_tiles [1]=rows used [2]=sticky status (4 = a receive buffer would overflow:
+ * nothing is written, the caller must raise rows_cap_recv) then send_base[E], recv_off[E+1],
+ * recv_cnt[E], tiles; bibo_moe_ep_plan_off(which, E) returns the word offsets (0..3).              */
+int64_t bibo_moe_ep_plan_words(int n_experts, int64_t rows_cap_recv);
+int64_t bibo_moe_ep_plan_off(int which, int n_experts);
+int bibo_moe_ep_plan(const int32_t* cnt_all, int rank, int world, int n_experts, int64_t rows_cap_recv,
+                     int32_t* ep_plan, void* stream);
+int bibo_moe_ep_dispatch(const void* x, const int32_t* topk_idx, const int32_t* slot_rank,
+                         const int32_t* local_plan, const int32_t* ep_plan, void* const* xp_peers,
+                         int64_t n_tokens, int hidden, int n_experts, int rank, int world, int top_k,
+                         int64_t rows_cap_recv, int32_t* slot_row, void* stream);
+/* gate/up + radial + down on the rows this rank received; gate_up_proj / down_proj / theta hold only
+ * this rank's E/world experts.  max_ctas > 0 bounds the persistent grids (leaves SMs to concurrent
+ * dispatch / combine kernels of another token chunk).                                              */
+int bibo_moe_ep_experts(const void* xp_recv, const void* gate_up_proj, const void* down_proj,
+                        const float* theta, const int32_t* ep_plan, int hidden, int inter, int n_experts,
+                        int world, int64_t rows_cap_recv, int max_ctas, void* h, void* y_recv, void* stream);
+/* Stream-ordered barrier over the ranks: flags_peers[r] = rank r's zero-initialised int32[8] flag array
+ * as mapped into this process; epoch must grow by one per call.  The wait inside is bounded (about
+ * two seconds); on timeout *status is raised to 5 and the kernel returns.                          */
+int bibo_moe_ep_barrier(void* const* flags_peers, int rank, int world, int epoch, int32_t* status,
+                        void* stream);
+int bibo_moe_ep_combine(void* const* y_peers, const int32_t* slot_row, const float* topk_w,
+                        const int32_t* ep_plan, int64_t n_tokens, int hidden, int world, int top_k,
+                        int64_t rows_cap_recv, void* out, void* stream);
+
 /* ---- routing without any allocation -------------------------------------------------------------
  * No counterpart in the reference: added for callers that cannot allocate device memory (a runtime
  * that reserves all memory up front, or a loop that must not incur cudaMalloc's implicit device

@@ -1,0 +1,59 @@
+"""Host-side logic of the expert-parallel path on CPU ranks (gloo, world_size 2 and 4)."""
+import os
+import tempfile
+
+import pytest
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+
+def _worker(rank, world, path, n_exp):
+    from bibo_b200.ep import ep_layout, recv_rows_cap
+    dist.init_process_group("gloo", init_method=f"file://{path}", rank=rank, world_size=world)
+    g = torch.Generator().manual_seed(100 + rank)
+    counts = torch.randint(0, 700, (n_exp,), generator=g, dtype=torch.int32)
+    counts[rank] = 0                                   # an empty (expert, source) group
+    cnt_all = torch.zeros(world, n_exp, dtype=torch.int32)
+    dist.all_gather_into_tensor(cnt_all.view(-1), counts)
+    lay = ep_layout(cnt_all, rank, world)
+    el = n_exp // world
+    # every rank's view of "where do rank s's rows of expert e start in owner d's buffer" must agree
+    send = [torch.zeros(n_exp, dtype=torch.int64) for _ in range(world)]
+    recv = [torch.zeros(n_exp + 1, dtype=torch.int64) for _ in range(world)]
+    dist.all_gather(send, lay["send_base"])
+    dist.all_gather(recv, lay["recv_off"])
+    for s in range(world):
+        for e in range(n_exp):
+            d, le = divmod(e, el)
+            assert int(send[s][e]) == int(recv[d][le * world + s])
+    # groups are tile-aligned, disjoint and in (expert, source) order
+    off, cnt = lay["recv_off"], lay["recv_cnt"]
+    assert (off % 128 == 0).all()
+    assert (off[1:] - off[:-1] >= cnt).all() and (off[1:] - off[:-1] < cnt + 128).all()
+    assert int(lay["rows"][rank]) == int(off[-1])
+    total = int(cnt_all.sum())
+    assert int(lay["recv_cnt"].sum()) == int(cnt_all[:, rank * el:(rank + 1) * el].sum())
+    cap = recv_rows_cap(1000, 6, n_exp, world, 2.0)
+    assert cap % 128 == 0 and cap >= 2 * 6000
+    assert total > 0
+    dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("world", [2, 4])
+def test_ep_layout_is_consistent_across_ranks(world):
+    with tempfile.TemporaryDirectory() as d:
+        mp.spawn(_worker, args=(world, os.path.join(d, "store"), 64), nprocs=world, join=True)
+
+
+def test_ep_layout_matches_hand_example():
+    from bibo_b200.ep import ep_layout
+    cnt = torch.tensor([[130, 0, 5, 128], [1, 300, 0, 0]], dtype=torch.int32)   # 2 ranks, 4 experts
+    l0, l1 = ep_layout(cnt, 0, 2), ep_layout(cnt, 1, 2)
+    # rank 0 owns experts 0,1: groups (e0,s0) 130->256, (e0,s1) 1->128, (e1,s0) 0, (e1,s1) 300->384
+    assert l0["recv_off"].tolist() == [0, 256, 384, 384, 768]
+    assert l0["recv_cnt"].tolist() == [130, 1, 0, 300]
+    # rank 1 owns experts 2,3: (e2,s0) 5->128, (e2,s1) 0, (e3,s0) 128->128, (e3,s1) 0
+    assert l1["recv_off"].tolist() == [0, 128, 128, 256, 256]
+    assert l0["send_base"].tolist() == [0, 384, 0, 128] and l1["send_base"].tolist() == [256, 384, 128, 256]
+    assert l0["rows"].tolist() == [768, 256]

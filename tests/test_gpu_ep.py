@@ -1,0 +1,27 @@
+"""Expert-parallel forward on 2+ GPUs (skipped on a single-GPU box): child processes, one per GPU."""
+import os
+import pathlib
+import subprocess
+import sys
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+ROOT = pathlib.Path(__file__).resolve().parents[1]
+
+
+def _run(world, args, env_extra=None, port=29541):
+    env = dict(os.environ, NCCL_NVLS_ENABLE="0", **(env_extra or {}))
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={world}",
+           "--master-addr", "127.0.0.1", "--master-port", str(port), str(ROOT / "tests" / "ep_worker.py"), *map(str, args)]
+    return subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=600)
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs at least 2 GPUs")
+@pytest.mark.parametrize("args", [(1000, 256, 128, 64, 6, "uniform"), (3000, 1024, 512, 64, 6, "zipf")])
+def test_expert_parallel_matches_single_gpu_and_oracle(args):
+    world = 2 if torch.cuda.device_count() < 4 else 4
+    r = _run(world, args)
+    assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]
+    assert "identical to single-GPU chain: True" in r.stdout
