@@ -27,6 +27,10 @@ class Workspace(C.Structure):
         "xp", "h", "y", "gate_up", "rnorm", "logits", "stage_events")]
 
 
+class BwdWorkspace(C.Structure):
+    _fields_ = [(n, _vp) for n in ("dy", "dh", "dw", "dlogit", "dlogit_row", "dtheta_row")]
+
+
 class Shape(C.Structure):
     _fields_ = [("n_tokens", _i64), ("hidden", _i32), ("inter", _i32), ("n_experts", _i32),
                 ("n_glu", _i32), ("n_pos", _i32), ("top_k", _i32), ("norm_mode", _i32),
@@ -61,6 +65,8 @@ SIGNATURES = {
                                 C.POINTER(Workspace), _vp, _vp]),
     "bibo_moe_forward_host": (_i32, [C.POINTER(Shape), _vp, _vp, _vp, _vp, _vp, _vp, _vp,
                                      C.POINTER(Workspace), _vp, _vp, _vp]),
+    "bibo_moe_backward": (_i32, [C.POINTER(Shape), _vp, _vp, _vp, _vp, _vp, C.POINTER(Workspace), _vp,
+                                 C.POINTER(BwdWorkspace), _vp, _vp, _vp, _vp, _vp, _vp]),
     "bibo_moe_ep_plan_words": (_i64, [_i32, _i64]),
     "bibo_moe_ep_plan_off": (_i64, [_i32, _i32]),
     "bibo_moe_ep_plan": (_i32, [_vp, _i32, _i32, _i32, _i64, _vp, _vp]),

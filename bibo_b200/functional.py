@@ -289,6 +289,42 @@ def experts_forward(x: torch.Tensor, topk_idx: torch.Tensor, topk_w: torch.Tenso
     return out, ws
 
 
+def moe_backward(dout: torch.Tensor, x: torch.Tensor, w_router: torch.Tensor, gate_up_proj: torch.Tensor,
+                 down_proj: torch.Tensor, theta: torch.Tensor, ws: MoEWorkspace, norm_mode="sum", scale: float = 1.0):
+    """Gradients of the block (one call of bibo_moe_backward).  ``ws`` is the workspace of the matching
+    forward (kept gate_up / rnorm); it is consumed.  Returns (dx, d_w_router, d_gate_up_proj,
+    d_down_proj, d_theta fp32)."""
+    lib = _lib.load()
+    geo = ws.geo
+    for name, t in (("dout", dout), ("x", x)):
+        _need_cuda(t, name)
+    if ws.gate_up is None or ws.rnorm is None:
+        raise RuntimeError("the forward workspace was created without the tensors the backward needs")
+    dev, rows = x.device, geo.rows_cap
+    f32 = dict(dtype=torch.float32, device=dev)
+    dy = torch.empty(rows, geo.hidden, dtype=geo.dtype, device=dev)
+    dh = torch.empty(rows, geo.inter, dtype=geo.dtype, device=dev)
+    dw = torch.empty(geo.n_tokens, geo.top_k, **f32)
+    dlogit = torch.empty(geo.n_tokens, geo.top_k, **f32)
+    dlogit_row = torch.empty(rows, **f32)
+    dtheta_row = torch.empty(rows, **f32)
+    dx = torch.empty_like(x)
+    d_wr = torch.zeros_like(w_router)
+    d_gu = torch.zeros_like(gate_up_proj)
+    d_dn = torch.zeros_like(down_proj)
+    d_theta = torch.zeros(geo.n_glu, **f32)
+    p = _lib.ptr
+    bws = _lib.BwdWorkspace(p(dy), p(dh), p(dw), p(dlogit), p(dlogit_row), p(dtheta_row))
+    shape = _shape(geo, norm_mode, scale, False)
+    cws = ws.c_struct()
+    theta32 = theta if theta.dtype == torch.float32 else theta.float()
+    rc = lib.bibo_moe_backward(C.byref(shape), p(x), p(w_router), p(gate_up_proj), p(down_proj), p(theta32),
+                               C.byref(cws), p(dout), C.byref(bws), p(dx), p(d_wr), p(d_gu), p(d_dn), p(d_theta),
+                               _stream(dev))
+    _lib.check(rc, "bibo_moe_backward")
+    return dx, d_wr, d_gu, d_dn, d_theta
+
+
 def plan_header(ws: MoEWorkspace):
     """Debug: (n_tiles, rows_used, status) read back from the device (synchronises the stream)."""
     lib = _lib.load()

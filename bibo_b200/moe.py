@@ -136,12 +136,43 @@ class BiBoFusedExperts(nn.Module):
 
 
 def _refuse_grad(module: nn.Module, *tensors) -> None:
+    """The experts-only seam has no backward kernels for caller-supplied routing weights."""
     if not torch.is_grad_enabled():
         return
-    if module.training or any(t.requires_grad for t in tensors):
+    if any(t.requires_grad for t in tensors) or any(p.requires_grad for p in module.parameters()):
         raise NotImplementedError(
-            "bibo_b200: this build has forward kernels only; call under torch.no_grad() / in eval() "
-            "with inputs that do not require grad")
+            "bibo_b200: BiBoFusedExperts.forward(x, idx, w) is forward-only; train through BiBoMoELayer "
+            "(whole-block backward) or call this seam under torch.no_grad()")
+
+
+class _MoEBlockFunction(torch.autograd.Function):
+    """Whole-block forward/backward as one autograd node (the reference relies on autograd over ~900
+    eager ops per layer; here both directions are single C-ABI calls)."""
+
+    @staticmethod
+    def forward(ctx, x, w_router, gate_up_proj, down_proj, theta, bias, cfg, holder):
+        top_k, norm, scale, n_pos, n_neg, keep_logits = cfg
+        n, hidden = x.shape
+        geo = Fn.Geometry(n, hidden, gate_up_proj.shape[1] // 2, w_router.shape[0], gate_up_proj.shape[0], n_pos, top_k,
+                          x.dtype)
+        # a private workspace: its tensors are what the backward pass re-reads
+        ws = Fn.MoEWorkspace(geo, x.device, keep_logits=keep_logits, keep_gate_up=True)
+        out, ws = Fn.moe_forward(x, w_router, bias, gate_up_proj, down_proj, theta, top_k, norm, scale, n_pos=n_pos,
+                                 n_neg=n_neg, ws=ws)
+        ctx.save_for_backward(x, w_router, gate_up_proj, down_proj, theta)
+        ctx.ws, ctx.norm, ctx.scale = ws, norm, scale
+        holder["ws"] = ws
+        return out
+
+    @staticmethod
+    def backward(ctx, dout):
+        x, w_router, gate_up_proj, down_proj, theta = ctx.saved_tensors
+        if ctx.ws is None:
+            raise RuntimeError("bibo_b200: the MoE block's backward ran twice (its workspace is consumed)")
+        dx, d_wr, d_gu, d_dn, d_th = Fn.moe_backward(dout.contiguous(), x, w_router, gate_up_proj, down_proj, theta,
+                                                     ctx.ws, ctx.norm, ctx.scale)
+        ctx.ws = None
+        return dx, d_wr, d_gu, d_dn, d_th.to(theta.dtype), None, None, None
 
 
 class BiBoMoELayer(nn.Module):
@@ -213,15 +244,21 @@ def layer_forward(layer, hidden_states: torch.Tensor) -> torch.Tensor:
     n = bsz * seq_len
     if getattr(layer, "use_shared_expert", False):
         raise NotImplementedError("bibo_b200: use_shared_expert=True is outside the kernels' coverage")
-    _refuse_grad(layer, hidden_states)
     flat = hidden_states.reshape(n, hidden).contiguous()
     gate, ex = layer.gate, layer.experts
     n_pos, n_neg = ex.pos_end - ex.pos_start, ex.neg_end - ex.neg_start
     want_gap = gate._probe_gap and gate.top_k < gate.num_routed_experts
-    out, ws = Fn.moe_forward(flat, gate.gate_proj.weight, gate.bias, ex.gate_up_proj, ex.down_proj,
-                             ex.radial_theta, gate.top_k, gate.norm_topk_prob,
-                             float(getattr(gate, "routed_scaling_factor", 1.0)),
-                             n_pos=n_pos, n_neg=n_neg, keep_logits=want_gap)
+    scale = float(getattr(gate, "routed_scaling_factor", 1.0))
+    params = (gate.gate_proj.weight, ex.gate_up_proj, ex.down_proj, ex.radial_theta)
+    if torch.is_grad_enabled() and (flat.requires_grad or any(p.requires_grad for p in params)):
+        holder = {}
+        out = _MoEBlockFunction.apply(flat, *params, gate.bias.detach(),
+                                      (gate.top_k, gate.norm_topk_prob, scale, n_pos, n_neg, want_gap), holder)
+        ws = holder["ws"]
+    else:
+        out, ws = Fn.moe_forward(flat, gate.gate_proj.weight, gate.bias, ex.gate_up_proj, ex.down_proj,
+                                 ex.radial_theta, gate.top_k, gate.norm_topk_prob, scale,
+                                 n_pos=n_pos, n_neg=n_neg, keep_logits=want_gap)
     layer.last_workspace = ws
     if want_gap:
         with torch.no_grad():

@@ -192,6 +192,31 @@ int bibo_moe_forward_host(const bibo_moe_shape* shape, const void* x_host, void*
                           const void* down_proj, const float* theta, const bibo_moe_workspace* ws,
                           void* out_dev, void* out_host, void* stream);
 
+/* ---- backward ----------------------------------------------------------------------------------------
+ * The reference derives its gradients by autograd over src/modeling/ffn/router.py:25-51 and
+ * src/modeling/ffn/moe.py:47-101 (there is no hand-written backward to cite); this call computes the
+ * same gradients in closed form on the forward's expert-contiguous layout.
+ * `ws` is the workspace of the matching bibo_moe_forward call, run with zero_padding = 0 or 1 and
+ * with xp, h, y, gate_up, rnorm kept; it is CONSUMED: y is overwritten (dXp) and gate_up becomes
+ * dGate|dUp.  dout [N,H] is the gradient of the block output.  Outputs: dx [N,H], d_w_router [E,H],
+ * d_gate_up_proj [E_glu,2I,H], d_down_proj [E_glu,H,I] in the model dtype (overwritten, not
+ * accumulated), d_theta fp32 [E_glu].  gate.bias receives no gradient (requires_grad=False in the
+ * reference).  Every reduction runs in a fixed order: results are bit-reproducible.               */
+typedef struct {
+  void* dy;           /* [rows_cap, H] dtype */
+  void* dh;           /* [rows_cap, I] dtype */
+  float* dw;          /* [N,k]               */
+  float* dlogit;      /* [N,k]               */
+  float* dlogit_row;  /* [rows_cap]          */
+  float* dtheta_row;  /* [rows_cap]          */
+} bibo_moe_bwd_workspace;
+
+int bibo_moe_backward(const bibo_moe_shape* shape, const void* x, const void* w_router,
+                      const void* gate_up_proj, const void* down_proj, const float* theta,
+                      const bibo_moe_workspace* ws, const void* dout, const bibo_moe_bwd_workspace* bws,
+                      void* dx, void* d_w_router, void* d_gate_up_proj, void* d_down_proj, float* d_theta,
+                      void* stream);
+
 /* ---- expert-parallel forward over NVLink peer memory ------------------------------------------------
  * No counterpart in the reference (it has no expert parallelism; its only collective is the
  * all_reduce of accumulated_tpe, src/modeling/ffn/moe.py:150-151).  Experts are sharded contiguously
