@@ -45,7 +45,7 @@ inline std::atomic<long long>& launch_counter() {
 inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 
 // ---- plan layout (int32 words) ------------------------------------------------------------------
-constexpr int PLAN_N_TILES = 0, PLAN_ROWS_USED = 1, PLAN_STATUS = 2, PLAN_HDR = 4;
+constexpr int PLAN_N_TILES = 0, PLAN_ROWS_USED = 1, PLAN_STATUS = 2, PLAN_N_PAIRS = 3, PLAN_HDR = 4;
 __host__ __device__ inline int64_t router_blocks(int64_t n_tokens) {
   return (n_tokens + BIBO_ROUTER_BLOCK_TOKENS - 1) / BIBO_ROUTER_BLOCK_TOKENS;
 }
@@ -65,8 +65,13 @@ __host__ __device__ inline int64_t plan_off_tiles(int64_t n, int E, int n_glu) {
   int64_t o = plan_off_block_base(E, n_glu) + router_blocks(n) * E;
   return (o + 3) / 4 * 4;  // int4-aligned tile records
 }
-__host__ __device__ inline int64_t plan_words(int64_t n, int k, int E, int n_glu) {
+// tile pairs (int2 {tile a, tile b or -1}: two consecutive tiles of one expert, for the kernels that
+// run a row-tile pair on a two-CTA tensor-core instruction)
+__host__ __device__ inline int64_t plan_off_pairs(int64_t n, int k, int E, int n_glu) {
   return plan_off_tiles(n, E, n_glu) + tiles_cap(n, k, n_glu) * 4;
+}
+__host__ __device__ inline int64_t plan_words(int64_t n, int k, int E, int n_glu) {
+  return plan_off_pairs(n, k, E, n_glu) + tiles_cap(n, k, n_glu) * 2;
 }
 
 // What a grouped-GEMM launcher needs to know about a row plan: where the header / tile list live and
@@ -74,13 +79,14 @@ __host__ __device__ inline int64_t plan_words(int64_t n, int k, int E, int n_glu
 struct PlanView {
   const int32_t* plan;   // header at [0..3]
   int64_t tiles_off;     // word offset of the int4 tile records
+  int64_t pairs_off;     // word offset of the int2 tile-pair records
   int64_t tiles_cap;     // upper bound of tiles (grid sizing)
   int64_t rows_alloc;    // rows of the expert-contiguous buffers
   int max_ctas;          // 0 = all SMs; otherwise an upper bound for persistent grids
 };
 inline PlanView local_plan_view(const int32_t* plan, int64_t n_tokens, int top_k, int n_experts, int n_glu) {
-  return PlanView{plan, plan_off_tiles(n_tokens, n_experts, n_glu), tiles_cap(n_tokens, top_k, n_glu),
-                  rows_cap(n_tokens, top_k, n_glu), 0};
+  return PlanView{plan, plan_off_tiles(n_tokens, n_experts, n_glu), plan_off_pairs(n_tokens, top_k, n_experts, n_glu),
+                  tiles_cap(n_tokens, top_k, n_glu), rows_cap(n_tokens, top_k, n_glu), 0};
 }
 
 // ---- dtype helpers ------------------------------------------------------------------------------

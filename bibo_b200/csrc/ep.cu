@@ -29,8 +29,11 @@ __host__ __device__ inline int64_t ep_off_send_base() { return PLAN_HDR; }
 __host__ __device__ inline int64_t ep_off_recv_off(int E) { return PLAN_HDR + E; }
 __host__ __device__ inline int64_t ep_off_recv_cnt(int E) { return PLAN_HDR + 2 * E + 1; }
 __host__ __device__ inline int64_t ep_off_tiles(int E) { return (PLAN_HDR + 3 * E + 1 + 3) / 4 * 4; }
-__host__ __device__ inline int64_t ep_plan_words(int E, int64_t rows_cap_recv) {
+__host__ __device__ inline int64_t ep_off_pairs(int E, int64_t rows_cap_recv) {
   return ep_off_tiles(E) + rows_cap_recv / BIBO_TILE_M * 4;
+}
+__host__ __device__ inline int64_t ep_plan_words(int E, int64_t rows_cap_recv) {
+  return ep_off_pairs(E, rows_cap_recv) + rows_cap_recv / BIBO_TILE_M * 2;
 }
 
 // One block, E threads.  Thread d < R scans destination d's layout.
@@ -42,6 +45,8 @@ ep_plan_kernel(const int32_t* __restrict__ cnt_all, int rank, int world, int n_e
   int32_t* recv_off = plan + ep_off_recv_off(n_experts);
   int32_t* recv_cnt = plan + ep_off_recv_cnt(n_experts);
   int4* tiles = reinterpret_cast<int4*>(plan + ep_off_tiles(n_experts));
+  int2* pairs = reinterpret_cast<int2*>(plan + ep_off_pairs(n_experts, rows_cap_recv));
+  __shared__ int s_pair_off[BIBO_MAX_EXPERTS + 1];
   __shared__ int s_off[BIBO_MAX_EXPERTS + 1];
   __shared__ int s_cnt[BIBO_MAX_EXPERTS];
   __shared__ int s_over;
@@ -65,18 +70,27 @@ ep_plan_kernel(const int32_t* __restrict__ cnt_all, int rank, int world, int n_e
   const bool over = s_over != 0;
   if (tid == 0) {
     const int rows = over ? 0 : s_off[n_experts];
+    int pacc = 0;
+    for (int g = 0; g < n_experts; ++g) {
+      s_pair_off[g] = pacc;
+      pacc += ((s_cnt[g] + BIBO_TILE_M - 1) / BIBO_TILE_M + 1) / 2;
+    }
     plan[PLAN_N_TILES] = rows / BIBO_TILE_M;
     plan[PLAN_ROWS_USED] = rows;
+    plan[PLAN_N_PAIRS] = over ? 0 : pacc;
     if (over) atomicMax(&plan[PLAN_STATUS], 4);
   }
+  __syncthreads();
   if (tid <= n_experts) recv_off[tid] = s_off[tid];
   if (tid < n_experts) {
     recv_cnt[tid] = s_cnt[tid];
     if (!over) {
       const int row0 = s_off[tid], cnt = s_cnt[tid], le = tid / world, src = tid % world;
-      int t = row0 / BIBO_TILE_M;
-      for (int r = 0; r < cnt; r += BIBO_TILE_M, ++t)
-        tiles[t] = make_int4(le, row0 + r, min(BIBO_TILE_M, cnt - r), src);
+      const int t0 = row0 / BIBO_TILE_M, nt = (cnt + BIBO_TILE_M - 1) / BIBO_TILE_M;
+      for (int i = 0; i < nt; ++i) {
+        tiles[t0 + i] = make_int4(le, row0 + i * BIBO_TILE_M, min(BIBO_TILE_M, cnt - i * BIBO_TILE_M), src);
+        if ((i & 1) == 0) pairs[s_pair_off[tid] + i / 2] = make_int2(t0 + i, i + 1 < nt ? t0 + i + 1 : -1);
+      }
     }
   }
 }
@@ -275,7 +289,8 @@ extern "C" int bibo_moe_ep_experts(const void* xp_recv, const void* gate_up_proj
     return fail(BIBO_ERR_ARG, "ep_experts: null pointer");
   if (!gemm1_tc_supported(hidden, inter, BIBO_BF16) || !gemm2_tc_supported(hidden, inter, BIBO_BF16))
     return fail(BIBO_ERR_UNSUPPORTED, "ep_experts: hidden=%d inter=%d is outside the tensor-core kernels", hidden, inter);
-  const PlanView pv{ep_plan, ep_off_tiles(n_experts), rows_cap_recv / BIBO_TILE_M, rows_cap_recv, max_ctas};
+  const PlanView pv{ep_plan, ep_off_tiles(n_experts), ep_off_pairs(n_experts, rows_cap_recv),
+                    rows_cap_recv / BIBO_TILE_M, rows_cap_recv, max_ctas};
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   const int el = n_experts / world;
   rc = gemm1_tc_launch(xp_recv, gate_up_proj, theta, pv, hidden, inter, el, h, nullptr, nullptr, st);

@@ -9,6 +9,7 @@
 //                    accumulators = 2*NC tensor-memory columns), so for I = 512 two CTAs of a
 //                    cluster split the columns and exchange their partial sums of squares through
 //                    distributed shared memory.
+#include <cstdlib>
 #include <map>
 #include <mutex>
 #include <tuple>
@@ -406,6 +407,246 @@ gemm1_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
 }
 
 // =====================================================================================================
+// K3 on CTA pairs.  Cluster of 2*CLN CTAs: rank r -> pr = r & 1 (position in the MMA pair, i.e. which
+// of the two row tiles), ch = r >> 1 (which 256-column block of the gate / up projections).  The pair
+// (r, r^1) runs 256-row tcgen05.mma.cta_group::2 instructions: each CTA stages its own A tile and 128
+// of the 256 B rows, so a k-block costs 32 KB of shared memory per CTA instead of 48 KB (five pipeline
+// stages beside the 64 KB gate stash).  For I = 512 the CTAs r and r^2 hold the two column blocks of
+// the same rows and exchange their partial sums of squares exactly as the one-CTA kernel does.
+// =====================================================================================================
+template <int STAGES>
+struct G1PairLayout {
+  static constexpr int NC = 256;
+  static constexpr int BH_BYTES = (NC / 2) * BK * 2;
+  static constexpr int OFF_A = 0;
+  static constexpr int OFF_B = OFF_A + STAGES * A_BYTES;
+  static constexpr int OFF_STASH = OFF_B + STAGES * BH_BYTES;
+  static constexpr int OFF_PART = OFF_STASH + (NC / 64) * C_SUB;
+  static constexpr int OFF_BAR = OFF_PART + 2 * BM * 4;
+  static constexpr int BYTES = OFF_BAR + 256 + 1024;
+};
+
+template <int CLN, int STAGES>
+__global__ void __launch_bounds__(NUM_THREADS, 1)
+gemm1_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
+                  const __grid_constant__ CUtensorMap tmH, const float* __restrict__ theta,
+                  int32_t* __restrict__ plan, int64_t tiles_off, int64_t pairs_off, int k_blocks, int inter,
+                  __nv_bfloat16* __restrict__ gate_up_out, float* __restrict__ rnorm_out) {
+  using L = G1PairLayout<STAGES>;
+  constexpr int NC = L::NC;
+  constexpr int CL = 2 * CLN;
+  extern __shared__ unsigned char smem_dyn[];
+  unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_dyn) + 1023) & ~uintptr_t(1023));
+  float* part = reinterpret_cast<float*>(smem + L::OFF_PART);
+  uint64_t* full = reinterpret_cast<uint64_t*>(smem + L::OFF_BAR);   // used in the pair leader only
+  uint64_t* empty = full + STAGES;
+  uint64_t* gfull = empty + STAGES;
+  uint64_t* gempty = gfull + 1;       // pair leader: 8 arrivals (4 epilogue warps of each CTA)
+  uint64_t* ufull = gempty + 1;
+  uint64_t* uempty = ufull + 1;       // pair leader
+  uint64_t* xbar = uempty + 1;        // [2] partial-sum exchange with CTA r^2
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(xbar + 2);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const uint32_t cr = cluster_ctarank();
+  const uint32_t pr = cr & 1u, ch = cr >> 1, leader = cr & ~1u;
+  const uint16_t pair_mask = (uint16_t)(3u << leader);
+  const int cluster_id = blockIdx.x / CL, n_clusters = gridDim.x / CL;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1); }
+    mbar_init(gfull, 1); mbar_init(ufull, 1);
+    mbar_init(gempty, 8); mbar_init(uempty, 8);
+    mbar_init(&xbar[0], EPI_THREADS); mbar_init(&xbar[1], EPI_THREADS);
+    *abort_flag = 0;
+    fence_barrier_init();
+    prefetch_tmap(&tmA); prefetch_tmap(&tmB); prefetch_tmap(&tmH);
+  }
+  if (warp == 1) { tmem_alloc_cg2(tmem_slot, 2 * NC); tmem_relinquish_cg2(); }
+  tc_fence_before();
+  __syncthreads();
+  cluster_sync_all();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+  const int n_pairs = plan[PLAN_N_PAIRS];
+  const int4* tiles = reinterpret_cast<const int4*>(plan + tiles_off);
+  const int2* pairs = reinterpret_cast<const int2*>(plan + pairs_off);
+
+  if (warp == 0) {
+    if (elect_one()) {
+      PipeState ps;
+      bool ok = true;
+      for (int p = cluster_id; p < n_pairs && ok; p += n_clusters) {
+        const int2 pp = pairs[p];
+        const int4 t = tiles[(pr == 1 && pp.y >= 0) ? pp.y : pp.x];
+        for (int pass = 0; pass < 2 && ok; ++pass) {
+          const int brow = t.x * 2 * inter + pass * inter + (int)ch * NC + (int)pr * (NC / 2);
+          for (int kb = 0; kb < k_blocks; ++kb) {
+            ok = mbar_wait(&empty[ps.stage], ps.phase ^ 1, abort_flag);
+            if (!ok) break;
+            if (pr == 0) mbar_expect_tx(&full[ps.stage], 2 * (A_BYTES + L::BH_BYTES));
+            const uint32_t bar0 = map_to_cta(&full[ps.stage], leader);
+            tma_load_2d_cg2(smem + L::OFF_A + ps.stage * A_BYTES, &tmA, bar0, kb * BK, t.y);
+            tma_load_2d_cg2(smem + L::OFF_B + ps.stage * L::BH_BYTES, &tmB, bar0, kb * BK, brow);
+            ps.next<STAGES>();
+          }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    if (pr == 0 && elect_one()) {
+      constexpr uint32_t idesc = make_idesc_bf16(2 * BM, NC);
+      PipeState ps;
+      uint32_t it = 0;
+      bool ok = true;
+      for (int p = cluster_id; p < n_pairs && ok; p += n_clusters, ++it) {
+        for (int pass = 0; pass < 2 && ok; ++pass) {
+          ok = mbar_wait<true>(pass == 0 ? gempty : uempty, (it & 1) ^ 1, abort_flag);
+          if (!ok) break;
+          tc_fence_after();
+          for (int kb = 0; kb < k_blocks; ++kb) {
+            ok = mbar_wait<true>(&full[ps.stage], ps.phase, abort_flag);
+            if (!ok) break;
+            tc_fence_after();
+            const uint64_t da = make_sdesc_k128(smem_u32(smem + L::OFF_A + ps.stage * A_BYTES));
+            const uint64_t db = make_sdesc_k128(smem_u32(smem + L::OFF_B + ps.stage * L::BH_BYTES));
+#pragma unroll
+            for (int k = 0; k < BK / UK; ++k)
+              umma_bf16_cg2(tmem_base + pass * NC, da + k * 2, db + k * 2, idesc, (kb | k) != 0);
+            umma_commit_cg2_mc(&empty[ps.stage], pair_mask);
+            ps.next<STAGES>();
+          }
+          if (ok) umma_commit_cg2_mc(pass == 0 ? gfull : ufull, pair_mask);
+        }
+      }
+    }
+  } else {
+    const int q = warp & 3;
+    const int row = q * 32 + lane;
+    const bool issuer = (threadIdx.x == 64);
+    const uint32_t lane_addr = tmem_base + ((uint32_t)(q * 32) << 16);
+    unsigned char* stash = smem + L::OFF_STASH;
+    uint32_t it = 0;
+    for (int p = cluster_id; p < n_pairs; p += n_clusters, ++it) {
+      const int2 pp = pairs[p];
+      const bool twin = (pr == 1 && pp.y < 0);     // duplicate of the leader's tile: compute, write nothing
+      const int4 t = tiles[(pr == 1 && pp.y >= 0) ? pp.y : pp.x];
+      if (issuer) tma_store_wait_read();           // the previous tile's stores are done with the stash
+      named_bar_sync(1, EPI_THREADS);
+      if (!mbar_wait(gfull, it & 1, abort_flag)) break;
+      tc_fence_after();
+      float ss = 0.f;
+#pragma unroll 1
+      for (int c = 0; c < NC / 64; ++c) {
+        uint32_t r0[32], r1[32];
+        tmem_ld32(lane_addr + c * 64, r0);
+        tmem_ld32(lane_addr + c * 64 + 32, r1);
+        tmem_ld_wait();
+        unsigned char* sub = stash + c * C_SUB;
+#pragma unroll
+        for (int hh = 0; hh < 2; ++hh) {
+          const uint32_t* r = hh ? r1 : r0;
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            uint4 v;
+            uint32_t* pv = reinterpret_cast<uint32_t*>(&v);
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+              const uint32_t pk = pack_bf16(__uint_as_float(r[8 * j + 2 * i]), __uint_as_float(r[8 * j + 2 * i + 1]));
+              const float a = bf16_lo(pk), b = bf16_hi(pk);
+              ss = fmaf(a, a, ss);
+              ss = fmaf(b, b, ss);
+              pv[i] = pk;
+            }
+            *reinterpret_cast<uint4*>(sub + swz(row, hh * 4 + j)) = v;
+          }
+        }
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive_cluster_addr(map_to_cta(gempty, leader));
+      if (CLN > 1) {
+        const uint32_t peer = cr ^ 2u;
+        st_remote_f32(&part[(it & 1) * BM + row], peer, ss);
+        mbar_arrive_remote(&xbar[it & 1], peer);
+        if (!mbar_wait<true>(&xbar[it & 1], (it >> 1) & 1, abort_flag)) break;
+        ss += part[(it & 1) * BM + row];
+      }
+      const float rn = sqrtf(ss / (float)inter + 1e-6f);
+      const float pw = sigmoid_accurate(__ldg(theta + t.x));
+      const float gain = powf(rn, pw);
+      const float inv_r_half = 0.5f * __fdiv_rn(1.0f, rn);
+      if (rnorm_out != nullptr && ch == 0 && !twin) rnorm_out[t.y + row] = rn;
+
+      if (!mbar_wait(ufull, it & 1, abort_flag)) break;
+      tc_fence_after();
+      __nv_bfloat16* gu_row =
+          (gate_up_out && !twin) ? gate_up_out + (int64_t)(t.y + row) * 2 * inter + ch * NC : nullptr;
+#pragma unroll 1
+      for (int c2 = 0; c2 < NC / 64; ++c2) {
+        uint32_t rr0[32], rr1[32];
+        tmem_ld32(lane_addr + NC + c2 * 64, rr0);
+        tmem_ld32(lane_addr + NC + c2 * 64 + 32, rr1);
+        tmem_ld_wait();
+        unsigned char* sub = stash + c2 * C_SUB;
+#pragma unroll
+        for (int jj = 0; jj < 8; ++jj) {
+          const int c = c2 * 2 + (jj >> 2), j = jj & 3;
+          const uint32_t* r = (jj >> 2) ? rr1 : rr0;
+          uint4* slot = reinterpret_cast<uint4*>(sub + swz(row, jj));
+          const uint4 gv = *slot;
+          const uint32_t* pg = reinterpret_cast<const uint32_t*>(&gv);
+          uint4 hv, uv;
+          uint32_t* ph = reinterpret_cast<uint32_t*>(&hv);
+          uint32_t* pu = reinterpret_cast<uint32_t*>(&uv);
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            const uint32_t upk = pack_bf16(__uint_as_float(r[8 * j + 2 * i]), __uint_as_float(r[8 * j + 2 * i + 1]));
+            pu[i] = upk;
+            float hval[2];
+#pragma unroll
+            for (int s = 0; s < 2; ++s) {
+              const float g = s ? bf16_hi(pg[i]) : bf16_lo(pg[i]);
+              const float u = s ? bf16_hi(upk) : bf16_lo(upk);
+              // z * sigmoid(z) = zh + zh * tanh(zh), zh = z / 2  (one special-function op per element)
+              const float zh = g * inv_r_half;
+              float th;
+              asm("tanh.approx.f32 %0, %1;" : "=f"(th) : "f"(zh));
+              const float a = round_bf16(fmaf(zh, th, zh) * gain);
+              hval[s] = a * u;
+            }
+            ph[i] = pack_bf16(hval[0], hval[1]);
+          }
+          *slot = hv;
+          if (gu_row != nullptr) {
+            *reinterpret_cast<uint4*>(gu_row + c * 32 + j * 8) = gv;
+            *reinterpret_cast<uint4*>(gu_row + inter + c * 32 + j * 8) = uv;
+          }
+        }
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive_cluster_addr(map_to_cta(uempty, leader));
+      fence_proxy_async_smem();
+      named_bar_sync(1, EPI_THREADS);
+      if (issuer && !twin) {
+#pragma unroll
+        for (int s = 0; s < NC / 64; ++s) tma_store_2d(&tmH, stash + s * C_SUB, ch * NC + s * 64, t.y);
+        tma_store_commit();
+      }
+    }
+    if (issuer) tma_store_wait_all();
+  }
+  __syncwarp();
+  tc_fence_before();
+  __syncthreads();
+  cluster_sync_all();   // nobody leaves while a cluster peer may still signal or write into this CTA
+  if (warp == 1) { tc_fence_after(); tmem_dealloc_cg2(tmem_base, 2 * NC); }
+  if (threadIdx.x == 0 && *abort_flag) atomicExch(&plan[PLAN_STATUS], 104);
+}
+
+// =====================================================================================================
 // host side
 // =====================================================================================================
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
@@ -477,9 +718,9 @@ int gemm2_tc_supported(int hidden, int inter, int dtype) {
   return dtype == BIBO_BF16 && hidden % 256 == 0 && inter % 64 == 0 && inter >= 64;
 }
 
-int gemm2_tc_launch(const void* h, const void* down_proj, const PlanView& pv, int hidden, int inter,
-                    int n_weight_experts, void* y, cudaStream_t st) {
-  constexpr int BN = 256, STAGES = 4;
+template <int BN, int STAGES>
+static int gemm2_launch_t(const void* h, const void* down_proj, const PlanView& pv, int hidden, int inter,
+                          int n_weight_experts, void* y, cudaStream_t st) {
   using L = G2Layout<BN, STAGES>;
   CUtensorMap tmA, tmB, tmC;
   int rc;
@@ -496,6 +737,11 @@ int gemm2_tc_launch(const void* h, const void* down_proj, const PlanView& pv, in
                                            inter / BK, hidden);
   BIBO_CHECK_LAUNCH("gemm2_tc_kernel");
   return BIBO_OK;
+}
+
+int gemm2_tc_launch(const void* h, const void* down_proj, const PlanView& pv, int hidden, int inter,
+                    int n_weight_experts, void* y, cudaStream_t st) {
+  return gemm2_launch_t<256, 4>(h, down_proj, pv, hidden, inter, n_weight_experts, y, st);
 }
 
 int gemm1_tc_supported(int hidden, int inter, int dtype) {
@@ -531,11 +777,58 @@ static int gemm1_launch_t(const CUtensorMap& tmA, const CUtensorMap& tmB, const 
   return BIBO_OK;
 }
 
+template <int CLN, int STAGES>
+static int gemm1_pair_launch_t(const CUtensorMap& tmA, const CUtensorMap& tmB, const CUtensorMap& tmH,
+                               const float* theta, const PlanView& pv, int k_blocks, int inter, void* gate_up_out,
+                               float* rnorm_out, cudaStream_t st) {
+  using L = G1PairLayout<STAGES>;
+  constexpr int CL = 2 * CLN;
+  auto kern = gemm1_pair_kernel<CLN, STAGES>;
+  static int max_clusters = 0;
+  int rc;
+  cudaLaunchConfig_t cfg = {};
+  cfg.blockDim = dim3(NUM_THREADS);
+  cfg.dynamicSmemBytes = L::BYTES;
+  cfg.stream = st;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = CL;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  if (max_clusters == 0) {
+    if ((rc = set_smem(kern, L::BYTES))) return rc;
+    cfg.gridDim = dim3((sm_count() / CL) * CL);
+    int n = 0;
+    BIBO_CUDA(cudaOccupancyMaxActiveClusters(&n, kern, &cfg));   // clusters of CL CTAs that fit at once
+    max_clusters = n > 0 ? n : 1;
+  }
+  const int sms = pv.max_ctas > 0 ? std::min(pv.max_ctas, sm_count()) : sm_count();
+  const int clusters = (int)std::max<int64_t>(1, std::min<int64_t>(std::min(max_clusters, sms / CL), pv.tiles_cap));
+  cfg.gridDim = dim3(clusters * CL);
+  BIBO_CUDA(cudaLaunchKernelEx(&cfg, kern, tmA, tmB, tmH, theta, const_cast<int32_t*>(pv.plan), pv.tiles_off,
+                               pv.pairs_off, k_blocks, inter, reinterpret_cast<__nv_bfloat16*>(gate_up_out),
+                               rnorm_out));
+  launch_counter().fetch_add(1, std::memory_order_relaxed);
+  return BIBO_OK;
+}
+
 int gemm1_tc_launch(const void* xp, const void* gate_up_proj, const float* theta, const PlanView& pv, int hidden,
                     int inter, int n_weight_experts, void* h, void* gate_up_out, float* rnorm_out, cudaStream_t st) {
   const int nc = inter >= 256 ? 256 : 128;
   CUtensorMap tmA, tmB, tmH;
   int rc;
+  // BIBO_G1_SINGLE=1 selects the one-CTA-per-tile kernel (kept for A/B measurements)
+  static const bool single = [] { const char* e = getenv("BIBO_G1_SINGLE"); return e && atoi(e) != 0; }();
+  if (!single && inter >= 256) {
+    if ((rc = make_tmap_bf16_2d(&tmA, xp, pv.rows_alloc, hidden, hidden, BM))) return rc;
+    if ((rc = make_tmap_bf16_2d(&tmB, gate_up_proj, (uint64_t)n_weight_experts * 2 * inter, hidden, hidden, 128))) return rc;
+    if ((rc = make_tmap_bf16_2d(&tmH, h, pv.rows_alloc, inter, inter, BM))) return rc;
+    if (inter == 512)
+      return gemm1_pair_launch_t<2, 5>(tmA, tmB, tmH, theta, pv, hidden / BK, inter, gate_up_out, rnorm_out, st);
+    return gemm1_pair_launch_t<1, 5>(tmA, tmB, tmH, theta, pv, hidden / BK, inter, gate_up_out, rnorm_out, st);
+  }
   if ((rc = make_tmap_bf16_2d(&tmA, xp, pv.rows_alloc, hidden, hidden, BM))) return rc;
   if ((rc = make_tmap_bf16_2d(&tmB, gate_up_proj, (uint64_t)n_weight_experts * 2 * inter, hidden, hidden, nc))) return rc;
   if ((rc = make_tmap_bf16_2d(&tmH, h, pv.rows_alloc, inter, inter, BM))) return rc;

@@ -164,6 +164,8 @@ plan_kernel(const int32_t* __restrict__ block_counts, int64_t n_tokens, int top_
   int32_t* expert_off = plan + plan_off_expert_off(n_experts);
   int32_t* block_base = plan + plan_off_block_base(n_experts, n_glu);
   int4* tiles = reinterpret_cast<int4*>(plan + plan_off_tiles(n_tokens, n_experts, n_glu));
+  int2* pairs = reinterpret_cast<int2*>(plan + plan_off_pairs(n_tokens, top_k, n_experts, n_glu));
+  __shared__ int s_pair_off[BIBO_MAX_EXPERTS + 1];
 
   int sum = 0;
   if (e < n_experts)
@@ -185,16 +187,19 @@ plan_kernel(const int32_t* __restrict__ block_counts, int64_t n_tokens, int top_
   }
   __syncthreads();
   if (tid == 0) {  // exclusive scan of the padded row counts (<= 256 entries) and the total check
-    int acc = 0, total = 0;
+    int acc = 0, total = 0, pacc = 0;
     for (int i = 0; i < n_experts; ++i) total += s_count[i];
     for (int i = 0; i < n_glu; ++i) {
       const int v = s_padded[i];
       s_padded[i] = acc;
+      s_pair_off[i] = pacc;
       acc += v;
+      pacc += (v / BIBO_TILE_M + 1) / 2;
     }
     s_padded[n_glu] = acc;
     plan[PLAN_N_TILES] = acc / BIBO_TILE_M;
     plan[PLAN_ROWS_USED] = acc;
+    plan[PLAN_N_PAIRS] = pacc;
     if (total != (long long)n_tokens * top_k) atomicMax(&plan[PLAN_STATUS], 1);  // sticky
   }
   if (e < n_experts) {
@@ -211,8 +216,11 @@ plan_kernel(const int32_t* __restrict__ block_counts, int64_t n_tokens, int top_
   if (e < n_glu) {
     const int row0 = s_padded[e], cnt = s_count[e];
     const int t0 = row0 / BIBO_TILE_M;
-    for (int i = sub; i * BIBO_TILE_M < cnt; i += n_sub)
+    const int nt = (cnt + BIBO_TILE_M - 1) / BIBO_TILE_M;
+    for (int i = sub; i < nt; i += n_sub) {
       tiles[t0 + i] = make_int4(e, row0 + i * BIBO_TILE_M, min(BIBO_TILE_M, cnt - i * BIBO_TILE_M), 0);
+      if ((i & 1) == 0) pairs[s_pair_off[e] + i / 2] = make_int2(t0 + i, i + 1 < nt ? t0 + i + 1 : -1);
+    }
   }
 }
 

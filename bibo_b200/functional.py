@@ -132,7 +132,8 @@ class MoEWorkspace:
     def tiles(self) -> torch.Tensor:
         g = self.geo
         o = int(_lib.load().bibo_moe_plan_off_tiles(g.n_tokens, g.n_experts, g.n_glu))
-        return self.plan[o:].view(-1, 4)
+        n_rec = self.geo.rows_cap // _lib.TILE_M
+        return self.plan[o:o + 4 * n_rec].view(-1, 4)
 
 
 _WS_CACHE: Dict[Tuple, MoEWorkspace] = {}
