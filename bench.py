@@ -180,6 +180,10 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="c4", choices=sorted(WORKLOADS))
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--ep-chunks", type=int, default=1, help="token slices pipelined on separate streams (N>1)")
+    ap.add_argument("--comm-sms", type=int, default=20, help="SMs left to the exchange kernels (N>1)")
+    ap.add_argument("--mode", default="fwd", choices=["fwd", "fwdbwd"],
+                    help="fwd = the headline metric; fwdbwd = forward + backward of the block (1 GPU)")
     args = ap.parse_args()
     wl = WORKLOADS[args.workload]
     rank, world = int(os.environ.get("RANK", 0)), int(os.environ.get("WORLD_SIZE", 1))
@@ -201,7 +205,8 @@ def main():
 
     if world > 1:
         from bibo_b200 import ep
-        runner = ep.ExpertParallelMoE(t, TOP_K, dist.group.WORLD, n_tokens=wl["n_tokens"])
+        runner = ep.PipelinedExpertParallelMoE(t, TOP_K, dist.group.WORLD, n_tokens=wl["n_tokens"], chunks=args.ep_chunks,
+                                               comm_sms=args.comm_sms)
         step = lambda: runner.forward(t["x"])
         ws = None
     else:
@@ -210,6 +215,16 @@ def main():
         out = torch.empty_like(t["x"])
         step = lambda: Fn.moe_forward(t["x"], t["w_router"], t["bias"], t["gate_up_proj"], t["down_proj"],
                                       t["radial_theta"], TOP_K, "sum", ws=ws, out=out)
+        if args.mode == "fwdbwd":
+            ws = None                       # no per-kernel events: the backward consumes its workspace
+            dout = torch.randn_like(t["x"])
+            ws_b = Fn.MoEWorkspace(geo, dev, keep_gate_up=True)
+
+            def step():
+                o, w = Fn.moe_forward(t["x"], t["w_router"], t["bias"], t["gate_up_proj"], t["down_proj"],
+                                      t["radial_theta"], TOP_K, "sum", ws=ws_b, out=out)
+                return Fn.moe_backward(dout, t["x"], t["w_router"], t["gate_up_proj"], t["down_proj"],
+                                       t["radial_theta"], w, "sum")
 
     def barrier():
         if world > 1:
@@ -272,6 +287,18 @@ def main():
         dist.all_reduce(e2e_s, op=dist.ReduceOp.MAX)
     e2e_val = n * world * args.steps / float(e2e_s)
 
+    ep_phases = None
+    if world > 1:      # one extra profiled step: when each phase of each token slice ended (ms from step start)
+        for lane in runner.lanes:
+            lane.profile = True
+        t_start = torch.cuda.Event(enable_timing=True)
+        barrier()
+        t_start.record()
+        step()
+        barrier()
+        ep_phases = [{n: round(t_start.elapsed_time(ev), 3) for n, ev in lane.marks} for lane in runner.lanes]
+        for lane in runner.lanes:
+            lane.profile = False
     if rank != 0:
         if world > 1:
             dist.destroy_process_group()
@@ -307,12 +334,12 @@ def main():
                 "peak_source": f"of {pk['src']} (burst figure)", "ms_per_launch": stages[top]["ms"]}
     layer_flops = 36.0 * n * h * i + 2.0 * n * h * N_EXPERTS
     line = {
-        "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+        "metric": METRIC if args.mode == "fwd" else "moe_layer_fwdbwd_tokens_per_s", "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
         "ms_per_step": ms_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
         "data": "synthetic", "config": workload_config(args, wl, world),
         "layer_tflops": round(layer_flops * world / (ms_step * 1e-3) / 1e12, 2),
         "layer_frac_of_bf16_peak": round(layer_flops / (ms_step * 1e-3) / 1e12 / pk["tf"], 4),
-        "roofline": roof, "stages": stages, "clocks": clocks, "gpu_launches": launches,
+        "roofline": roof, "stages": stages, "ep_phases_ms": ep_phases, "clocks": clocks, "gpu_launches": launches,
         "e2e": {"value": e2e_val, "unit": UNIT, "h2d_bytes_per_step": x_host.numel() * 2 * world,
                 "d2h_bytes_per_step": out_host.numel() * 2 * world},
     }

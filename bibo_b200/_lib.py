@@ -31,6 +31,16 @@ class BwdWorkspace(C.Structure):
     _fields_ = [(n, _vp) for n in ("dy", "dh", "dw", "dlogit", "dlogit_row", "dtheta_row")]
 
 
+class EpArgs(C.Structure):
+    _fields_ = ([("n_tokens", _i64), ("rows_cap_recv", _i64)] +
+                [(n, _i32) for n in ("hidden", "inter", "n_experts", "top_k", "norm_mode", "rank", "world", "max_ctas",
+                                     "comm_ctas", "epoch_base")] +
+                [("scale", _f32)] +
+                [(n, _vp) for n in ("x", "w_router", "bias", "gate_up_proj", "down_proj", "theta", "topk_idx", "topk_w",
+                                    "slot_rank", "block_counts", "local_plan", "ep_plan", "slot_row", "h", "xp_peers",
+                                    "y_peers", "flags_peers", "cnt_peers", "out")])
+
+
 class Shape(C.Structure):
     _fields_ = [("n_tokens", _i64), ("hidden", _i32), ("inter", _i32), ("n_experts", _i32),
                 ("n_glu", _i32), ("n_pos", _i32), ("top_k", _i32), ("norm_mode", _i32),
@@ -70,10 +80,11 @@ SIGNATURES = {
     "bibo_moe_ep_plan_words": (_i64, [_i32, _i64]),
     "bibo_moe_ep_plan_off": (_i64, [_i32, _i32]),
     "bibo_moe_ep_plan": (_i32, [_vp, _i32, _i32, _i32, _i64, _vp, _vp]),
-    "bibo_moe_ep_dispatch": (_i32, [_vp, _vp, _vp, _vp, _vp, _vp, _i64, _i32, _i32, _i32, _i32, _i32, _i64, _vp, _vp]),
+    "bibo_moe_ep_dispatch": (_i32, [_vp, _vp, _vp, _vp, _vp, _vp, _i64, _i32, _i32, _i32, _i32, _i32, _i64, _i32, _vp, _vp]),
+    "bibo_moe_ep_forward": (_i32, [C.POINTER(EpArgs), _vp]),
     "bibo_moe_ep_experts": (_i32, [_vp, _vp, _vp, _vp, _vp, _i32, _i32, _i32, _i32, _i64, _i32, _vp, _vp, _vp]),
     "bibo_moe_ep_barrier": (_i32, [_vp, _i32, _i32, _i32, _vp, _vp]),
-    "bibo_moe_ep_combine": (_i32, [_vp, _vp, _vp, _vp, _i64, _i32, _i32, _i32, _i64, _vp, _vp]),
+    "bibo_moe_ep_combine": (_i32, [_vp, _vp, _vp, _vp, _i64, _i32, _i32, _i32, _i64, _i32, _vp, _vp]),
     "bibo_moe_route_noalloc": (_i32, [_vp, _vp, _vp, _i64, _i32, _i32, _i32, _i32, _f32, _i32, _vp, _vp, _vp, _vp]),
     "bibo_moe_route_noalloc_max_tokens": (_i64, []),
     "bibo_moe_debug_plan_header": (_i32, [_vp, _vp, _vp]),

@@ -15,6 +15,8 @@
 // two (expert, source) groups; tiles carry the LOCAL expert index for the weight lookup.
 // Cross-rank ordering (all stores landed before the GEMMs start; all y written before the combine
 // reads) is provided by the caller with device-side barriers between the launches.
+#include <algorithm>
+
 #include "common.cuh"
 
 namespace bibo {
@@ -105,12 +107,12 @@ ep_dispatch_kernel(const uint8_t* __restrict__ x, const int32_t* __restrict__ to
                    const int32_t* __restrict__ ep_plan, PeerPtrs xp_peers, int64_t n_tokens, int row_bytes,
                    int n_experts, int world, int top_k, int rows_cap_recv, int32_t* __restrict__ slot_row) {
   const int lane = threadIdx.x & 31;
-  const int64_t w = (int64_t)blockIdx.x * EPW + (threadIdx.x >> 5);
-  if (w >= n_tokens) return;
   if (ep_plan[PLAN_STATUS] != 0) return;   // overflow or earlier error: write nothing
   const int el = n_experts / world;
   const int32_t* block_base = local_plan + plan_off_block_base(n_experts, n_experts);
   const int32_t* send_base = ep_plan + ep_off_send_base();
+  // grid-stride over tokens: the grid may be capped to a few CTAs per SM subset (see comm_ctas)
+  for (int64_t w = (int64_t)blockIdx.x * EPW + (threadIdx.x >> 5); w < n_tokens; w += (int64_t)gridDim.x * EPW) {
   int my_row = -1, my_owner = 0;
   if (lane < top_k) {
     const int e = topk_idx[w * top_k + lane];
@@ -134,6 +136,7 @@ ep_dispatch_kernel(const uint8_t* __restrict__ x, const int32_t* __restrict__ to
     for (int j = 0; j < BIBO_MAX_TOP_K; ++j)
       if (j < top_k) dst[j][c] = v;
   }
+  }
 }
 
 __device__ __forceinline__ void fma_bf16x8(const uint4& v, float w, float* acc) {
@@ -153,9 +156,8 @@ ep_combine_kernel(PeerPtrs y_peers, const int32_t* __restrict__ slot_row, const 
                   const int32_t* __restrict__ ep_plan, int64_t n_tokens, int hidden, int rows_cap_recv,
                   __nv_bfloat16* __restrict__ out) {
   const int lane = threadIdx.x & 31;
-  const int64_t t = (int64_t)blockIdx.x * EPW + (threadIdx.x >> 5);
-  if (t >= n_tokens) return;
   if (ep_plan[PLAN_STATUS] != 0) return;
+  for (int64_t t = (int64_t)blockIdx.x * EPW + (threadIdx.x >> 5); t < n_tokens; t += (int64_t)gridDim.x * EPW) {
   int my_g = 0;
   float my_w = 0.f;
   if (lane < K) { my_g = slot_row[t * K + lane]; my_w = topk_w[t * K + lane]; }
@@ -206,7 +208,20 @@ ep_combine_kernel(PeerPtrs y_peers, const int32_t* __restrict__ slot_row, const 
     for (int i = 0; i < 4; ++i) h0[i] = __floats2bfloat162_rn(a0[2 * i], a0[2 * i + 1]);
     dst[c] = o0;
   }
+  }
 }
+
+// Every rank publishes its histogram row into every peer's cnt_all[rank][:] (peer stores); a
+// barrier after this kernel makes all rows visible everywhere, replacing a library all-gather.
+__global__ void __launch_bounds__(BIBO_MAX_EXPERTS)
+ep_share_counts_kernel(const int32_t* __restrict__ counts, PeerPtrs cnt_peers, int rank, int world, int n_experts) {
+  const int e = threadIdx.x;
+  if (e >= n_experts) return;
+  const int32_t c = counts[e];
+  for (int p = 0; p < world; ++p) static_cast<int32_t*>(cnt_peers.p[p])[rank * n_experts + e] = c;
+}
+
+__global__ void ep_barrier_kernel(PeerPtrs flags, int rank, int world, int epoch, int32_t* status);
 
 // gemm_tc.cu
 int gemm1_tc_supported(int hidden, int inter, int dtype);
@@ -219,6 +234,27 @@ int gemm2_tc_launch(const void* h, const void* down_proj, const PlanView& pv, in
 }  // namespace bibo
 
 using namespace bibo;
+
+// The grouped GEMMs run with the shared-memory carve-out at its maximum.  An SM can only change its
+// carve-out while it is idle, so the small kernels of this path ask for the same carve-out: otherwise a
+// dispatch / combine kernel of one token slice, resident on every SM, would keep the GEMM kernel of
+// another slice from starting and the two would serialise instead of overlapping.
+template <typename Kern>
+static void prefer_max_smem(Kern kern) {
+  cudaFuncSetAttribute(kern, cudaFuncAttributePreferredSharedMemoryCarveout, (int)cudaSharedmemCarveoutMaxShared);
+}
+static void ep_set_carveouts() {
+  static bool done = false;
+  if (done) return;
+  prefer_max_smem(ep_plan_kernel);
+  prefer_max_smem(ep_dispatch_kernel);
+  prefer_max_smem(ep_barrier_kernel);
+  prefer_max_smem(ep_share_counts_kernel);
+  prefer_max_smem(ep_combine_kernel<1>); prefer_max_smem(ep_combine_kernel<2>); prefer_max_smem(ep_combine_kernel<3>);
+  prefer_max_smem(ep_combine_kernel<4>); prefer_max_smem(ep_combine_kernel<5>); prefer_max_smem(ep_combine_kernel<6>);
+  prefer_max_smem(ep_combine_kernel<7>); prefer_max_smem(ep_combine_kernel<8>);
+  done = true;
+}
 
 static int ep_check(const char* who, int world, int rank, int n_experts, int64_t rows_cap_recv) {
   if (world < 1 || world > EP_MAX_RANKS || rank < 0 || rank >= world)
@@ -248,6 +284,7 @@ extern "C" int bibo_moe_ep_plan(const int32_t* cnt_all, int rank, int world, int
   int rc = ep_check("ep_plan", world, rank, n_experts, rows_cap_recv);
   if (rc) return rc;
   if (!cnt_all || !ep_plan) return fail(BIBO_ERR_ARG, "ep_plan: null pointer");
+  ep_set_carveouts();
   ep_plan_kernel<<<1, BIBO_MAX_EXPERTS, 0, static_cast<cudaStream_t>(stream)>>>(cnt_all, rank, world, n_experts,
                                                                                (int)rows_cap_recv, ep_plan);
   BIBO_CHECK_LAUNCH("ep_plan_kernel");
@@ -257,7 +294,7 @@ extern "C" int bibo_moe_ep_plan(const int32_t* cnt_all, int rank, int world, int
 extern "C" int bibo_moe_ep_dispatch(const void* x, const int32_t* topk_idx, const int32_t* slot_rank,
                                     const int32_t* local_plan, const int32_t* ep_plan, void* const* xp_peers,
                                     int64_t n_tokens, int hidden, int n_experts, int rank, int world, int top_k,
-                                    int64_t rows_cap_recv, int32_t* slot_row, void* stream) {
+                                    int64_t rows_cap_recv, int comm_ctas, int32_t* slot_row, void* stream) {
   int rc = ep_check("ep_dispatch", world, rank, n_experts, rows_cap_recv);
   if (rc) return rc;
   if (n_tokens <= 0) return BIBO_OK;
@@ -271,7 +308,9 @@ extern "C" int bibo_moe_ep_dispatch(const void* x, const int32_t* topk_idx, cons
     if (!xp_peers[i] || !aligned16(xp_peers[i])) return fail(BIBO_ERR_ALIGN, "ep_dispatch: peer buffer %d", i);
     pp.p[i] = xp_peers[i];
   }
-  dim3 grid((unsigned)((n_tokens + EPW - 1) / EPW));
+  int64_t blocks = (n_tokens + EPW - 1) / EPW;
+  if (comm_ctas > 0) blocks = std::min<int64_t>(blocks, comm_ctas);
+  dim3 grid((unsigned)blocks);
   ep_dispatch_kernel<<<grid, EPW * 32, 0, static_cast<cudaStream_t>(stream)>>>(
       (const uint8_t*)x, topk_idx, slot_rank, local_plan, ep_plan, pp, n_tokens, row_bytes, n_experts, world, top_k,
       (int)rows_cap_recv, slot_row);
@@ -300,7 +339,7 @@ extern "C" int bibo_moe_ep_experts(const void* xp_recv, const void* gate_up_proj
 
 extern "C" int bibo_moe_ep_combine(void* const* y_peers, const int32_t* slot_row, const float* topk_w,
                                    const int32_t* ep_plan, int64_t n_tokens, int hidden, int world, int top_k,
-                                   int64_t rows_cap_recv, void* out, void* stream) {
+                                   int64_t rows_cap_recv, int comm_ctas, void* out, void* stream) {
   if (n_tokens <= 0) return BIBO_OK;
   if (!y_peers || !slot_row || !topk_w || !ep_plan || !out) return fail(BIBO_ERR_ARG, "ep_combine: null pointer");
   if (world < 1 || world > EP_MAX_RANKS) return fail(BIBO_ERR_ARG, "ep_combine: world=%d", world);
@@ -310,7 +349,9 @@ extern "C" int bibo_moe_ep_combine(void* const* y_peers, const int32_t* slot_row
     if (!y_peers[i] || !aligned16(y_peers[i])) return fail(BIBO_ERR_ALIGN, "ep_combine: peer buffer %d", i);
     pp.p[i] = y_peers[i];
   }
-  dim3 grid((unsigned)((n_tokens + EPW - 1) / EPW));
+  int64_t blocks = (n_tokens + EPW - 1) / EPW;
+  if (comm_ctas > 0) blocks = std::min<int64_t>(blocks, comm_ctas);
+  dim3 grid((unsigned)blocks);
   cudaStream_t st = static_cast<cudaStream_t>(stream);
 #define BIBO_EPC(KK)                                                                                              \
   case KK:                                                                                                        \
@@ -363,4 +404,52 @@ extern "C" int bibo_moe_ep_barrier(void* const* flags_peers, int rank, int world
   ep_barrier_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(pp, rank, world, epoch, status);
   BIBO_CHECK_LAUNCH("ep_barrier_kernel");
   return BIBO_OK;
+}
+
+// ---- the whole expert-parallel forward of one token slice as ONE call ---------------------------------
+// router -> local plan -> publish histogram to peers -> barrier -> EP plan -> dispatch (peer stores) ->
+// barrier -> gate/up + radial + down on received rows -> barrier -> combine (peer loads).
+// Uses barrier epochs epoch_base+1 .. epoch_base+3 on `flags_peers`.
+extern "C" int bibo_moe_ep_forward(const bibo_moe_ep_args* a, void* stream) {
+  if (!a) return fail(BIBO_ERR_ARG, "ep_forward: null args");
+  int rc = ep_check("ep_forward", a->world, a->rank, a->n_experts, a->rows_cap_recv);
+  if (rc) return rc;
+  if (!a->cnt_peers || !a->flags_peers || !a->xp_peers || !a->y_peers || !a->local_plan || !a->ep_plan)
+    return fail(BIBO_ERR_ARG, "ep_forward: null peer table / plan");
+  ep_set_carveouts();
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  int32_t* status = a->ep_plan + PLAN_STATUS;
+  rc = bibo_moe_router_fwd(a->x, a->w_router, a->bias, nullptr, a->n_tokens, a->hidden, a->n_experts, a->top_k,
+                           a->norm_mode, a->scale, BIBO_BF16, nullptr, a->topk_idx, a->topk_w, a->slot_rank,
+                           a->block_counts, a->local_plan + PLAN_STATUS, stream);
+  if (rc) return rc;
+  rc = bibo_moe_plan(a->block_counts, a->n_tokens, a->top_k, a->n_experts, a->n_experts, a->local_plan, stream);
+  if (rc) return rc;
+  PeerPtrs cp = {};
+  for (int i = 0; i < a->world; ++i) {
+    if (!a->cnt_peers[i]) return fail(BIBO_ERR_ARG, "ep_forward: peer %d has no histogram buffer", i);
+    cp.p[i] = a->cnt_peers[i];
+  }
+  ep_share_counts_kernel<<<1, BIBO_MAX_EXPERTS, 0, st>>>(a->local_plan + plan_off_counts(), cp, a->rank, a->world,
+                                                         a->n_experts);
+  BIBO_CHECK_LAUNCH("ep_share_counts_kernel");
+  rc = bibo_moe_ep_barrier(a->flags_peers, a->rank, a->world, a->epoch_base + 1, status, stream);
+  if (rc) return rc;
+  rc = bibo_moe_ep_plan(static_cast<const int32_t*>(a->cnt_peers[a->rank]), a->rank, a->world, a->n_experts,
+                        a->rows_cap_recv, a->ep_plan, stream);
+  if (rc) return rc;
+  rc = bibo_moe_ep_dispatch(a->x, a->topk_idx, a->slot_rank, a->local_plan, a->ep_plan, a->xp_peers, a->n_tokens,
+                            a->hidden, a->n_experts, a->rank, a->world, a->top_k, a->rows_cap_recv, a->comm_ctas,
+                            a->slot_row, stream);
+  if (rc) return rc;
+  rc = bibo_moe_ep_barrier(a->flags_peers, a->rank, a->world, a->epoch_base + 2, status, stream);
+  if (rc) return rc;
+  rc = bibo_moe_ep_experts(a->xp_peers[a->rank], a->gate_up_proj, a->down_proj, a->theta, a->ep_plan, a->hidden,
+                           a->inter, a->n_experts, a->world, a->rows_cap_recv, a->max_ctas, a->h, a->y_peers[a->rank],
+                           stream);
+  if (rc) return rc;
+  rc = bibo_moe_ep_barrier(a->flags_peers, a->rank, a->world, a->epoch_base + 3, status, stream);
+  if (rc) return rc;
+  return bibo_moe_ep_combine(a->y_peers, a->slot_row, a->topk_w, a->ep_plan, a->n_tokens, a->hidden, a->world,
+                             a->top_k, a->rows_cap_recv, a->comm_ctas, a->out, stream);
 }

@@ -307,6 +307,11 @@ extern "C" int bibo_moe_plan(const int32_t* block_counts, int64_t n_tokens, int 
   if (n_experts < 1 || n_experts > BIBO_MAX_EXPERTS || n_glu < 0 || n_glu > n_experts)
     return fail(BIBO_ERR_UNSUPPORTED, "plan: n_experts=%d n_glu=%d", n_experts, n_glu);
   if (n_tokens <= 0) return fail(BIBO_ERR_ARG, "plan: n_tokens=%lld", (long long)n_tokens);
+  static bool carve = false;
+  if (!carve) {  // same carve-out as the grouped GEMMs, so this kernel can share SMs with them (see ep.cu)
+    cudaFuncSetAttribute(plan_kernel, cudaFuncAttributePreferredSharedMemoryCarveout, (int)cudaSharedmemCarveoutMaxShared);
+    carve = true;
+  }
   int ep = 1;
   while (ep < n_experts) ep <<= 1;
   plan_kernel<<<1, PLAN_THREADS, 0, static_cast<cudaStream_t>(stream)>>>(block_counts, n_tokens, top_k, n_experts,

@@ -129,6 +129,9 @@ int router_tc_launch(const void* x, const void* w_router, const float* bias, int
   static bool attr_done = false;
   if (!attr_done) {
     BIBO_CUDA(cudaFuncSetAttribute(router_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, R_SMEM));
+    // same carve-out as the grouped GEMMs, so this kernel can share SMs with them (see ep.cu)
+    cudaFuncSetAttribute(router_tc_kernel, cudaFuncAttributePreferredSharedMemoryCarveout,
+                         (int)cudaSharedmemCarveoutMaxShared);
     attr_done = true;
   }
   router_tc_kernel<<<(unsigned)router_blocks(n_tokens), 128, R_SMEM, st>>>(

@@ -86,12 +86,12 @@ class ExpertParallelMoE:
     """
 
     def __init__(self, weights, top_k: int, group=None, n_tokens: Optional[int] = None, norm_mode="sum",
-                 scale: float = 1.0, capacity_factor: float = 2.0, max_ctas: int = 0):
+                 scale: float = 1.0, capacity_factor: float = 2.0, max_ctas: int = 0, comm_ctas: int = 0):
         os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")   # plain peer loads/stores only
         self.group = group if group is not None else dist.group.WORLD
         self.rank, self.world = dist.get_rank(self.group), dist.get_world_size(self.group)
         self.top_k, self.norm_mode, self.scale = top_k, norm_mode, scale
-        self.capacity_factor, self.max_ctas = capacity_factor, max_ctas
+        self.capacity_factor, self.max_ctas, self.comm_ctas = capacity_factor, max_ctas, comm_ctas
         w_r = weights["w_router"]
         self.device = w_r.device
         self.n_experts, self.hidden = w_r.shape
@@ -126,7 +126,8 @@ class ExpertParallelMoE:
         self.local_plan = torch.zeros(geo.plan_words, **i32)
         self.slot_row = torch.empty(n_tokens, k, **i32)
         self.ep_plan = torch.zeros(int(lib.bibo_moe_ep_plan_words(e, self.cap)), **i32)
-        self.cnt_all = torch.zeros(self.world, e, **i32)
+        self.cnt = _Symmetric((self.world, e), torch.int32, dev, self.group)   # histograms, written by peers
+        self.cnt_all = self.cnt.tensor
         self.h = torch.empty(self.cap, self.inter, dtype=torch.bfloat16, device=dev)
         self.xp = _Symmetric((self.cap, self.hidden), torch.bfloat16, dev, self.group)
         self.y = _Symmetric((self.cap, self.hidden), torch.bfloat16, dev, self.group)
@@ -136,6 +137,7 @@ class ExpertParallelMoE:
         dist.barrier(self.group)            # every rank's flags are zero before the first device barrier
         o = int(lib.bibo_moe_plan_off_counts())
         self._counts = self.local_plan[o:o + e]
+        self._args = None
 
     def _barrier(self, st) -> None:
         self._epoch += 1
@@ -151,27 +153,121 @@ class ExpertParallelMoE:
         if out is None:
             out = torch.empty_like(x)
         k, e, st = self.top_k, self.n_experts, torch.cuda.current_stream(self.device).cuda_stream
+        if not getattr(self, "profile", False):
+            return self._forward_one_call(x, out, st)
+        ev = self._mark
+        ev("start")
         _lib.check(lib.bibo_moe_router_fwd(p(x), p(self.w_router), p(self.bias), None, n, hidden, e, k,
                                            Fn.norm_code(self.norm_mode), float(self.scale), _lib.BF16, None,
                                            p(self.topk_idx), p(self.topk_w), p(self.slot_rank), p(self.block_counts),
                                            p(self.local_plan[2:]), st), "bibo_moe_router_fwd")
         _lib.check(lib.bibo_moe_plan(p(self.block_counts), n, k, e, e, p(self.local_plan), st), "bibo_moe_plan")
+        ev("route")
         dist.all_gather_into_tensor(self.cnt_all.view(-1), self._counts, group=self.group)
         _lib.check(lib.bibo_moe_ep_plan(p(self.cnt_all), self.rank, self.world, e, self.cap, p(self.ep_plan), st),
                    "bibo_moe_ep_plan")
+        ev("gather_plan")
         _lib.check(lib.bibo_moe_ep_dispatch(p(x), p(self.topk_idx), p(self.slot_rank), p(self.local_plan),
                                             p(self.ep_plan), self.xp.ptr_array, n, hidden, e, self.rank, self.world, k,
-                                            self.cap, p(self.slot_row), st), "bibo_moe_ep_dispatch")
+                                            self.cap, self.comm_ctas, p(self.slot_row), st), "bibo_moe_ep_dispatch")
+        ev("dispatch")
         self._barrier(st)                   # every rank's rows have landed
+        ev("barrier1")
         _lib.check(lib.bibo_moe_ep_experts(p(self.xp.tensor), p(self.gate_up), p(self.down), p(self.theta),
                                            p(self.ep_plan), hidden, self.inter, e, self.world, self.cap, self.max_ctas,
                                            p(self.h), p(self.y.tensor), st), "bibo_moe_ep_experts")
+        ev("experts")
         self._barrier(st)                   # every rank's results are written
+        ev("barrier2")
         _lib.check(lib.bibo_moe_ep_combine(self.y.ptr_array, p(self.slot_row), p(self.topk_w), p(self.ep_plan), n,
-                                           hidden, self.world, k, self.cap, p(out), st), "bibo_moe_ep_combine")
+                                           hidden, self.world, k, self.cap, self.comm_ctas, p(out), st),
+                   "bibo_moe_ep_combine")
+        ev("combine")
         return out
+
+    def _forward_one_call(self, x: torch.Tensor, out: torch.Tensor, st: int) -> torch.Tensor:
+        """The product path: bibo_moe_ep_forward (histograms exchanged through peer memory, no library
+        collective)."""
+        p = _lib.ptr
+        C_vp = C.c_void_p
+        cast = lambda arr: C.cast(arr, C_vp)
+        a = _lib.EpArgs(
+            x.shape[0], self.cap, self.hidden, self.inter, self.n_experts, self.top_k, Fn.norm_code(self.norm_mode),
+            self.rank, self.world, self.max_ctas, self.comm_ctas, self._epoch, float(self.scale),
+            p(x), p(self.w_router), p(self.bias), p(self.gate_up), p(self.down), p(self.theta),
+            p(self.topk_idx), p(self.topk_w), p(self.slot_rank), p(self.block_counts), p(self.local_plan),
+            p(self.ep_plan), p(self.slot_row), p(self.h), cast(self.xp.ptr_array), cast(self.y.ptr_array),
+            cast(self.flags.ptr_array), cast(self.cnt.ptr_array), p(out))
+        self._epoch += 3
+        _lib.check(_lib.load().bibo_moe_ep_forward(C.byref(a), st), "bibo_moe_ep_forward")
+        return out
+
+    def _mark(self, name: str) -> None:
+        """profile=True: record a timing event after each phase of the current forward."""
+        if name == "start":
+            self.marks = []
+        e = torch.cuda.Event(enable_timing=True)
+        e.record()
+        self.marks.append((name, e))
+
+    def phase_ms(self):
+        """Device time of each phase of the last profiled forward (call after a synchronize)."""
+        return {n: self.marks[i - 1][1].elapsed_time(ev) for i, (n, ev) in enumerate(self.marks) if i > 0}
 
     def status(self) -> int:
         """Sticky status words of both plans (synchronises): 0 = fine, 4 = receive buffer overflow,
         5 = a cross-rank barrier timed out, 100-102 = a bounded wait in a kernel gave up."""
         return max(int(self.ep_plan[2].item()), int(self.local_plan[2].item()))
+
+
+class PipelinedExpertParallelMoE:
+    """The expert-parallel forward on ``chunks`` token slices, each on its own CUDA stream.
+
+    A slice is a complete, independent forward (tokens are independent), with its own peer buffers,
+    plans and barrier flags.  Running the slices on separate streams lets the GPU overlap the NVLink
+    phases of one slice (dispatch stores, combine loads) with the grouped GEMMs of another; the GEMM
+    grids are capped at ``148 - comm_sms`` CTAs so the exchange kernels always find free SMs.
+    Every rank issues the same sequence of launches per stream, so the per-slice barriers and the NCCL
+    all-gathers pair up across ranks in the same order.
+    """
+
+    def __init__(self, weights, top_k: int, group=None, n_tokens: Optional[int] = None, chunks: int = 2,
+                 comm_sms: int = 20, **kw):
+        self.chunks = max(1, int(chunks))
+        dev = weights["w_router"].device
+        sms = torch.cuda.get_device_properties(dev).multi_processor_count
+        max_ctas = max(8, sms - comm_sms) if self.chunks > 1 else 0
+        comm_ctas = comm_sms * 4 if self.chunks > 1 else 0      # 4 resident 8-warp blocks per exchange SM
+        self.lanes = [ExpertParallelMoE(weights, top_k, group, max_ctas=max_ctas, comm_ctas=comm_ctas, **kw)
+                      for _ in range(self.chunks)]
+        self.streams = [torch.cuda.Stream(device=dev) for _ in range(self.chunks)]
+        self.device = dev
+        if n_tokens is not None:
+            for lane, (lo, hi) in zip(self.lanes, self._bounds(n_tokens)):
+                lane._allocate(hi - lo)
+
+    def _bounds(self, n: int):
+        per = (n + self.chunks - 1) // self.chunks
+        return [(min(c * per, n), min((c + 1) * per, n)) for c in range(self.chunks)]
+
+    def forward(self, x: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+        if out is None:
+            out = torch.empty_like(x)
+        if self.chunks == 1:
+            return self.lanes[0].forward(x, out)
+        cur = torch.cuda.current_stream(self.device)
+        start = torch.cuda.Event()
+        start.record(cur)
+        for lane, st, (lo, hi) in zip(self.lanes, self.streams, self._bounds(x.shape[0])):
+            if hi <= lo:
+                continue
+            st.wait_event(start)
+            with torch.cuda.stream(st):
+                lane.forward(x[lo:hi], out[lo:hi])
+            done = torch.cuda.Event()
+            done.record(st)
+            cur.wait_event(done)
+        return out
+
+    def status(self) -> int:
+        return max(lane.status() for lane in self.lanes)

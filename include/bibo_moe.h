@@ -237,7 +237,7 @@ int bibo_moe_ep_plan(const int32_t* cnt_all, int rank, int world, int n_experts,
 int bibo_moe_ep_dispatch(const void* x, const int32_t* topk_idx, const int32_t* slot_rank,
                          const int32_t* local_plan, const int32_t* ep_plan, void* const* xp_peers,
                          int64_t n_tokens, int hidden, int n_experts, int rank, int world, int top_k,
-                         int64_t rows_cap_recv, int32_t* slot_row, void* stream);
+                         int64_t rows_cap_recv, int comm_ctas, int32_t* slot_row, void* stream);
 /* gate/up + radial + down on the rows this rank received; gate_up_proj / down_proj / theta hold only
  * this rank's E/world experts.  max_ctas > 0 bounds the persistent grids (leaves SMs to concurrent
  * dispatch / combine kernels of another token chunk).                                              */
@@ -251,7 +251,27 @@ int bibo_moe_ep_barrier(void* const* flags_peers, int rank, int world, int epoch
                         void* stream);
 int bibo_moe_ep_combine(void* const* y_peers, const int32_t* slot_row, const float* topk_w,
                         const int32_t* ep_plan, int64_t n_tokens, int hidden, int world, int top_k,
-                        int64_t rows_cap_recv, void* out, void* stream);
+                        int64_t rows_cap_recv, int comm_ctas, void* out, void* stream);
+
+/* The whole expert-parallel forward of one token slice in one call: router, local plan, histogram
+ * exchange through peer memory (cnt_peers[r] = rank r's int32 [world, E] table), EP plan, dispatch,
+ * experts, combine, with the three stream barriers in between (epochs epoch_base+1..+3; the caller
+ * advances epoch_base by 3 per call).  comm_ctas > 0 caps the dispatch / combine grids and max_ctas
+ * caps the GEMM grids, so that slices running on different streams overlap their NVLink phases with
+ * each other's GEMMs instead of competing for the same SMs.                                        */
+typedef struct {
+  int64_t n_tokens, rows_cap_recv;
+  int hidden, inter, n_experts, top_k, norm_mode, rank, world, max_ctas, comm_ctas, epoch_base;
+  float scale;
+  const void* x; const void* w_router; const float* bias;
+  const void* gate_up_proj; const void* down_proj; const float* theta;      /* this rank's E/world experts */
+  int32_t* topk_idx; float* topk_w; int32_t* slot_rank; int32_t* block_counts;
+  int32_t* local_plan; int32_t* ep_plan; int32_t* slot_row;
+  void* h;                                                                  /* [rows_cap_recv, I] local */
+  void* const* xp_peers; void* const* y_peers; void* const* flags_peers; void* const* cnt_peers;
+  void* out;
+} bibo_moe_ep_args;
+int bibo_moe_ep_forward(const bibo_moe_ep_args* args, void* stream);
 
 /* ---- routing without any allocation -------------------------------------------------------------
  * No counterpart in the reference: added for callers that cannot allocate device memory (a runtime
