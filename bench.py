@@ -222,7 +222,7 @@ def main():
 
             def step():
                 o, w = Fn.moe_forward(t["x"], t["w_router"], t["bias"], t["gate_up_proj"], t["down_proj"],
-                                      t["radial_theta"], TOP_K, "sum", ws=ws_b, out=out)
+                                      t["radial_theta"], TOP_K, "sum", ws=ws_b, out=out, zero_padding=True)
                 return Fn.moe_backward(dout, t["x"], t["w_router"], t["gate_up_proj"], t["down_proj"],
                                        t["radial_theta"], w, "sum")
 

@@ -16,6 +16,8 @@
 //   dtheta_e += p(1-p) ln r sum_i dA_i A_i.
 // All reductions run in a fixed order (no floating-point atomics), so gradients are deterministic.
 // These are CUDA-core kernels (fp32 accumulation) for both dtypes.
+#include <type_traits>
+
 #include "common.cuh"
 
 namespace bibo {
@@ -339,6 +341,30 @@ router_dw_scan_kernel(const float* __restrict__ dlogit, const int32_t* __restric
   dw_router[(int64_t)e * hidden + c] = from_f32<T>(acc);
 }
 
+// Zero the padding rows of an expert-contiguous buffer (one warp per possible padding row): the
+// weight-gradient GEMMs on the tensor cores reduce over whole 64-row blocks, padding included.
+__global__ void __launch_bounds__(BW * 32)
+zero_padding_rows_kernel(uint8_t* __restrict__ buf, const int32_t* __restrict__ counts,
+                         const int32_t* __restrict__ expert_off, int n_glu, int row_bytes) {
+  const int lane = threadIdx.x & 31;
+  const int64_t p = (int64_t)blockIdx.x * BW + (threadIdx.x >> 5);
+  const int e = (int)(p / (BIBO_TILE_M - 1));
+  if (e >= n_glu) return;
+  const int row = expert_off[e] + counts[e] + (int)(p % (BIBO_TILE_M - 1));
+  if (row >= expert_off[e + 1]) return;
+  uint4* dst = reinterpret_cast<uint4*>(buf + (int64_t)row * row_bytes);
+  for (int c = lane; c < row_bytes / 16; c += 32) dst[c] = make_uint4(0, 0, 0, 0);
+}
+
+// gemm_bwd_tc.cu
+int gemm_dx_tc_supported(int k_dim, int n_out);
+int gemm_dx_tc_launch(const void* A, const void* W, void* C, const PlanView& pv, int k_dim, int n_out,
+                      int n_weight_experts, cudaStream_t st);
+int gemm_dw_tc_supported(int m_dim, int n_dim);
+int gemm_dw_tc_launch(const void* A, const void* B, void* C, const int32_t* plan, int64_t counts_off,
+                      int64_t expert_off_off, int64_t rows_alloc, int n_experts, int m_dim, int n_dim,
+                      cudaStream_t st);
+
 template <typename T>
 static int backward_t(const bibo_moe_shape* s, const T* x, const T* w_router, const T* gate_up_proj, const T* down_proj,
                       const float* theta, const bibo_moe_workspace* ws, const T* dout, const bibo_moe_bwd_workspace* b,
@@ -352,29 +378,57 @@ static int backward_t(const bibo_moe_shape* s, const T* x, const T* w_router, co
   T* dh = static_cast<T*>(b->dh);
   T* gu = static_cast<T*>(ws->gate_up);   // becomes dGate|dUp in place
   T* dxp = static_cast<T*>(ws->y);        // y is dead after combine_bwd: reused for dXp
+  // tensor-core path: bf16, tile-friendly shapes, and a forward that zeroed the padding rows
+  const bool use_tc = std::is_same<T, __nv_bfloat16>::value && s->zero_padding && G > 0 && (H * 2) % 16 == 0 &&
+                      gemm_dx_tc_supported(H, I) && gemm_dx_tc_supported(2 * I, H) && gemm_dw_tc_supported(H, I) &&
+                      gemm_dw_tc_supported(2 * I, H) && aligned16(dy) && aligned16(dh) && aligned16(gu) &&
+                      aligned16(dxp) && aligned16(ws->h) && aligned16(ws->xp) && aligned16(d_down_proj) &&
+                      aligned16(d_gate_up_proj) && aligned16(down_proj) && aligned16(gate_up_proj);
+  int rc;
   dim3 tok_grid((unsigned)((n + BW - 1) / BW));
+  if (use_tc) {
+    const int64_t pad_warps = (int64_t)G * (BIBO_TILE_M - 1);
+    zero_padding_rows_kernel<<<(unsigned)((pad_warps + BW - 1) / BW), BW * 32, 0, st>>>(
+        reinterpret_cast<uint8_t*>(dy), counts, expert_off, G, H * 2);
+    BIBO_CHECK_LAUNCH("zero_padding_rows_kernel");
+  }
   combine_bwd_kernel<T><<<tok_grid, BW * 32, 0, st>>>(dout, static_cast<const T*>(ws->y), x, ws->slot_row, ws->topk_idx,
                                                       ws->topk_w, n, H, k, G, s->n_pos, dy, b->dw);
   BIBO_CHECK_LAUNCH("combine_bwd_kernel");
   if (G > 0) {
-    dim3 g1((unsigned)pv.tiles_cap, (unsigned)((I + 63) / 64));
-    grouped_gemm_bkn_kernel<T><<<g1, 256, 0, st>>>(dy, down_proj, dh, pv.plan, pv.tiles_off, H, I);
-    BIBO_CHECK_LAUNCH("grouped_gemm_bkn_kernel");
-    dim3 g2((unsigned)((H + 63) / 64), (unsigned)((I + 63) / 64), (unsigned)G);
-    grouped_gemm_dw_kernel<T><<<g2, 256, 0, st>>>(dy, static_cast<const T*>(ws->h), d_down_proj, counts, expert_off, H, I);
-    BIBO_CHECK_LAUNCH("grouped_gemm_dw_kernel");
+    if (use_tc) {
+      if ((rc = gemm_dx_tc_launch(dy, down_proj, dh, pv, H, I, G, st))) return rc;
+      if ((rc = gemm_dw_tc_launch(dy, ws->h, d_down_proj, ws->plan, plan_off_counts(), plan_off_expert_off(E),
+                                  pv.rows_alloc, G, H, I, st)))
+        return rc;
+    } else {
+      dim3 g1((unsigned)pv.tiles_cap, (unsigned)((I + 63) / 64));
+      grouped_gemm_bkn_kernel<T><<<g1, 256, 0, st>>>(dy, down_proj, dh, pv.plan, pv.tiles_off, H, I);
+      BIBO_CHECK_LAUNCH("grouped_gemm_bkn_kernel");
+      dim3 g2((unsigned)((H + 63) / 64), (unsigned)((I + 63) / 64), (unsigned)G);
+      grouped_gemm_dw_kernel<T><<<g2, 256, 0, st>>>(dy, static_cast<const T*>(ws->h), d_down_proj, counts, expert_off,
+                                                    H, I);
+      BIBO_CHECK_LAUNCH("grouped_gemm_dw_kernel");
+    }
     dim3 rgrid((unsigned)((pv.rows_alloc + BW - 1) / BW));
     radial_bwd_kernel<T><<<rgrid, BW * 32, 0, st>>>(dh, gu, ws->rnorm, theta, pv.plan, pv.tiles_off, I, b->dtheta_row);
     BIBO_CHECK_LAUNCH("radial_bwd_kernel");
     dtheta_reduce_kernel<<<G, 256, 0, st>>>(b->dtheta_row, counts, expert_off, d_theta);
     BIBO_CHECK_LAUNCH("dtheta_reduce_kernel");
-    dim3 g3((unsigned)pv.tiles_cap, (unsigned)((H + 63) / 64));
-    grouped_gemm_bkn_kernel<T><<<g3, 256, 0, st>>>(gu, gate_up_proj, dxp, pv.plan, pv.tiles_off, 2 * I, H);
-    BIBO_CHECK_LAUNCH("grouped_gemm_bkn_kernel");
-    dim3 g4((unsigned)((2 * I + 63) / 64), (unsigned)((H + 63) / 64), (unsigned)G);
-    grouped_gemm_dw_kernel<T><<<g4, 256, 0, st>>>(gu, static_cast<const T*>(ws->xp), d_gate_up_proj, counts, expert_off,
-                                                  2 * I, H);
-    BIBO_CHECK_LAUNCH("grouped_gemm_dw_kernel");
+    if (use_tc) {
+      if ((rc = gemm_dx_tc_launch(gu, gate_up_proj, dxp, pv, 2 * I, H, G, st))) return rc;
+      if ((rc = gemm_dw_tc_launch(gu, ws->xp, d_gate_up_proj, ws->plan, plan_off_counts(), plan_off_expert_off(E),
+                                  pv.rows_alloc, G, 2 * I, H, st)))
+        return rc;
+    } else {
+      dim3 g3((unsigned)pv.tiles_cap, (unsigned)((H + 63) / 64));
+      grouped_gemm_bkn_kernel<T><<<g3, 256, 0, st>>>(gu, gate_up_proj, dxp, pv.plan, pv.tiles_off, 2 * I, H);
+      BIBO_CHECK_LAUNCH("grouped_gemm_bkn_kernel");
+      dim3 g4((unsigned)((2 * I + 63) / 64), (unsigned)((H + 63) / 64), (unsigned)G);
+      grouped_gemm_dw_kernel<T><<<g4, 256, 0, st>>>(gu, static_cast<const T*>(ws->xp), d_gate_up_proj, counts,
+                                                    expert_off, 2 * I, H);
+      BIBO_CHECK_LAUNCH("grouped_gemm_dw_kernel");
+    }
   }
   gather_dx_kernel<T><<<tok_grid, BW * 32, 0, st>>>(dxp, dout, x, w_router, ws->slot_row, ws->topk_idx, ws->topk_w, b->dw,
                                                     n, H, k, G, s->n_pos, s->norm_mode, s->scale, dx, b->dlogit,

@@ -19,33 +19,6 @@
 namespace bibo {
 namespace tc {
 
-constexpr int BM = BIBO_TILE_M;   // rows per tile (TMEM lanes)
-constexpr int BK = 64;            // k-block: 64 bf16 = one 128-byte swizzle row
-constexpr int UK = 16;            // k per tcgen05.mma
-constexpr int A_BYTES = BM * BK * 2;
-constexpr int C_SUB = BM * 128;   // one [128 rows x 64 cols] bf16 staging sub-tile
-constexpr int NUM_THREADS = 192;
-constexpr int EPI_THREADS = 128;
-
-__device__ __forceinline__ uint32_t pack_bf16(float a, float b) {
-  __nv_bfloat162 v = __floats2bfloat162_rn(a, b);
-  return *reinterpret_cast<uint32_t*>(&v);
-}
-__device__ __forceinline__ float bf16_lo(uint32_t v) { return __uint_as_float(v << 16); }
-__device__ __forceinline__ float bf16_hi(uint32_t v) { return __uint_as_float(v & 0xffff0000u); }
-__device__ __forceinline__ float round_bf16(float v) { return __bfloat162float(__float2bfloat16_rn(v)); }
-
-// byte offset of 16-byte chunk `chunk` (0..7) of row `row` inside a 128B-swizzled [128][128B] sub-tile
-__device__ __forceinline__ uint32_t swz(int row, int chunk) { return row * 128 + ((chunk ^ (row & 7)) << 4); }
-
-struct PipeState {
-  int stage = 0;
-  uint32_t phase = 0;
-  template <int STAGES> __device__ __forceinline__ void next() {
-    if (++stage == STAGES) { stage = 0; phase ^= 1; }
-  }
-};
-
 // =====================================================================================================
 // K4: down projection
 // =====================================================================================================

@@ -291,7 +291,8 @@ def experts_forward(x: torch.Tensor, topk_idx: torch.Tensor, topk_w: torch.Tenso
 
 
 def moe_backward(dout: torch.Tensor, x: torch.Tensor, w_router: torch.Tensor, gate_up_proj: torch.Tensor,
-                 down_proj: torch.Tensor, theta: torch.Tensor, ws: MoEWorkspace, norm_mode="sum", scale: float = 1.0):
+                 down_proj: torch.Tensor, theta: torch.Tensor, ws: MoEWorkspace, norm_mode="sum", scale: float = 1.0,
+                 zero_padded: bool = True):
     """Gradients of the block (one call of bibo_moe_backward).  ``ws`` is the workspace of the matching
     forward (kept gate_up / rnorm); it is consumed.  Returns (dx, d_w_router, d_gate_up_proj,
     d_down_proj, d_theta fp32)."""
@@ -316,7 +317,8 @@ def moe_backward(dout: torch.Tensor, x: torch.Tensor, w_router: torch.Tensor, ga
     d_theta = torch.zeros(geo.n_glu, **f32)
     p = _lib.ptr
     bws = _lib.BwdWorkspace(p(dy), p(dh), p(dw), p(dlogit), p(dlogit_row), p(dtheta_row))
-    shape = _shape(geo, norm_mode, scale, False)
+    # zero_padded: the forward ran with zero_padding=True (lets the weight-gradient GEMMs use tensor cores)
+    shape = _shape(geo, norm_mode, scale, zero_padded)
     cws = ws.c_struct()
     theta32 = theta if theta.dtype == torch.float32 else theta.float()
     rc = lib.bibo_moe_backward(C.byref(shape), p(x), p(w_router), p(gate_up_proj), p(down_proj), p(theta32),

@@ -158,7 +158,7 @@ class _MoEBlockFunction(torch.autograd.Function):
         # a private workspace: its tensors are what the backward pass re-reads
         ws = Fn.MoEWorkspace(geo, x.device, keep_logits=keep_logits, keep_gate_up=True)
         out, ws = Fn.moe_forward(x, w_router, bias, gate_up_proj, down_proj, theta, top_k, norm, scale, n_pos=n_pos,
-                                 n_neg=n_neg, ws=ws)
+                                 n_neg=n_neg, ws=ws, zero_padding=True)
         ctx.save_for_backward(x, w_router, gate_up_proj, down_proj, theta)
         ctx.ws, ctx.norm, ctx.scale = ws, norm, scale
         holder["ws"] = ws

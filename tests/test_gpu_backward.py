@@ -72,7 +72,8 @@ def _oracle_grads(inp, dout, k, dtype):
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-@pytest.mark.parametrize("n,h,i,e,k", [(300, 128, 64, 64, 6), (700, 256, 128, 64, 6), (520, 512, 512, 64, 6)])
+@pytest.mark.parametrize("n,h,i,e,k", [(300, 128, 64, 64, 6), (700, 256, 128, 64, 6), (520, 512, 512, 64, 6),
+                                       (900, 256, 256, 64, 6), (2100, 1024, 512, 64, 6)])
 def test_backward_matches_oracle_autograd(dtype, n, h, i, e, k):
     inp = orc.make_inputs(n, h, i, e, seed=n + 1, bias_mode="uniform", theta_std=0.5)
     dout = torch.randn(n, h, generator=torch.Generator().manual_seed(5))
