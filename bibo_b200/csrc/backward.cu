@@ -18,6 +18,7 @@
 // These are CUDA-core kernels (fp32 accumulation) for both dtypes.
 #include <type_traits>
 
+#include "backward_vec.cuh"
 #include "common.cuh"
 
 namespace bibo {
@@ -392,8 +393,16 @@ static int backward_t(const bibo_moe_shape* s, const T* x, const T* w_router, co
         reinterpret_cast<uint8_t*>(dy), counts, expert_off, G, H * 2);
     BIBO_CHECK_LAUNCH("zero_padding_rows_kernel");
   }
-  combine_bwd_kernel<T><<<tok_grid, BW * 32, 0, st>>>(dout, static_cast<const T*>(ws->y), x, ws->slot_row, ws->topk_idx,
-                                                      ws->topk_w, n, H, k, G, s->n_pos, dy, b->dw);
+  // 16-byte vectorised row kernels when every row size is a multiple of 16 bytes
+  const bool vec = (H * sizeof(T)) % 16 == 0 && (I * sizeof(T)) % 16 == 0 && aligned16(dout) && aligned16(x) &&
+                   aligned16(dx) && aligned16(ws->y) && aligned16(dy) && aligned16(dh) && aligned16(gu) &&
+                   aligned16(w_router) && aligned16(d_w_router) && aligned16(ws->xp);
+  if (vec)
+    combine_bwd_vec_kernel<T><<<tok_grid, 256, 0, st>>>(dout, static_cast<const T*>(ws->y), x, ws->slot_row,
+                                                        ws->topk_idx, ws->topk_w, n, H, k, G, s->n_pos, dy, b->dw);
+  else
+    combine_bwd_kernel<T><<<tok_grid, BW * 32, 0, st>>>(dout, static_cast<const T*>(ws->y), x, ws->slot_row,
+                                                        ws->topk_idx, ws->topk_w, n, H, k, G, s->n_pos, dy, b->dw);
   BIBO_CHECK_LAUNCH("combine_bwd_kernel");
   if (G > 0) {
     if (use_tc) {
@@ -411,7 +420,10 @@ static int backward_t(const bibo_moe_shape* s, const T* x, const T* w_router, co
       BIBO_CHECK_LAUNCH("grouped_gemm_dw_kernel");
     }
     dim3 rgrid((unsigned)((pv.rows_alloc + BW - 1) / BW));
-    radial_bwd_kernel<T><<<rgrid, BW * 32, 0, st>>>(dh, gu, ws->rnorm, theta, pv.plan, pv.tiles_off, I, b->dtheta_row);
+    if (vec)
+      radial_bwd_vec_kernel<T><<<rgrid, 256, 0, st>>>(dh, gu, ws->rnorm, theta, pv.plan, pv.tiles_off, I, b->dtheta_row);
+    else
+      radial_bwd_kernel<T><<<rgrid, BW * 32, 0, st>>>(dh, gu, ws->rnorm, theta, pv.plan, pv.tiles_off, I, b->dtheta_row);
     BIBO_CHECK_LAUNCH("radial_bwd_kernel");
     dtheta_reduce_kernel<<<G, 256, 0, st>>>(b->dtheta_row, counts, expert_off, d_theta);
     BIBO_CHECK_LAUNCH("dtheta_reduce_kernel");
@@ -430,14 +442,35 @@ static int backward_t(const bibo_moe_shape* s, const T* x, const T* w_router, co
       BIBO_CHECK_LAUNCH("grouped_gemm_dw_kernel");
     }
   }
-  gather_dx_kernel<T><<<tok_grid, BW * 32, 0, st>>>(dxp, dout, x, w_router, ws->slot_row, ws->topk_idx, ws->topk_w, b->dw,
-                                                    n, H, k, G, s->n_pos, s->norm_mode, s->scale, dx, b->dlogit,
-                                                    b->dlogit_row);
+  if (vec) {
+#define BIBO_GDX(KK)                                                                                                \
+  case KK:                                                                                                          \
+    gather_dx_vec_kernel<T, KK><<<tok_grid, 256, 0, st>>>(dxp, dout, x, w_router, ws->slot_row, ws->topk_idx,       \
+                                                          ws->topk_w, b->dw, n, H, G, s->n_pos, s->norm_mode,       \
+                                                          s->scale, dx, b->dlogit, b->dlogit_row);                   \
+    break;
+    switch (k) {
+      BIBO_GDX(1) BIBO_GDX(2) BIBO_GDX(3) BIBO_GDX(4) BIBO_GDX(5) BIBO_GDX(6) BIBO_GDX(7) BIBO_GDX(8)
+      default: return fail(BIBO_ERR_UNSUPPORTED, "backward: top_k=%d", k);
+    }
+#undef BIBO_GDX
+  } else {
+    gather_dx_kernel<T><<<tok_grid, BW * 32, 0, st>>>(dxp, dout, x, w_router, ws->slot_row, ws->topk_idx, ws->topk_w,
+                                                      b->dw, n, H, k, G, s->n_pos, s->norm_mode, s->scale, dx,
+                                                      b->dlogit, b->dlogit_row);
+  }
   BIBO_CHECK_LAUNCH("gather_dx_kernel");
   if (G > 0) {
-    dim3 g5((unsigned)G, (unsigned)((H + 255) / 256));
-    router_dw_rows_kernel<T><<<g5, 256, 0, st>>>(b->dlogit_row, static_cast<const T*>(ws->xp), counts, expert_off, H,
-                                                 d_w_router);
+    if (vec) {
+      constexpr int cols = 32 * V16<T>::N;
+      dim3 g5v((unsigned)G, (unsigned)((H + cols - 1) / cols));
+      router_dw_rows_vec_kernel<T><<<g5v, 256, 0, st>>>(b->dlogit_row, static_cast<const T*>(ws->xp), counts,
+                                                        expert_off, H, d_w_router);
+    } else {
+      dim3 g5((unsigned)G, (unsigned)((H + 255) / 256));
+      router_dw_rows_kernel<T><<<g5, 256, 0, st>>>(b->dlogit_row, static_cast<const T*>(ws->xp), counts, expert_off, H,
+                                                   d_w_router);
+    }
     BIBO_CHECK_LAUNCH("router_dw_rows_kernel");
   }
   if (E > G) {
