@@ -38,7 +38,13 @@ class EpArgs(C.Structure):
                 [("scale", _f32)] +
                 [(n, _vp) for n in ("x", "w_router", "bias", "gate_up_proj", "down_proj", "theta", "topk_idx", "topk_w",
                                     "slot_rank", "block_counts", "local_plan", "ep_plan", "slot_row", "h", "xp_peers",
-                                    "y_peers", "flags_peers", "cnt_peers", "out")])
+                                    "y_peers", "flags_peers", "cnt_peers", "out", "gate_up_recv", "rnorm_recv",
+                                    "row_token")])
+
+
+class EpBwdArgs(C.Structure):
+    _fields_ = ([(n, _vp) for n in ("dout", "dy_peers", "dh", "dw", "dlogit_row", "dtheta_row", "dx", "d_w_router",
+                                    "d_gate_up_proj", "d_down_proj", "d_theta")] + [("epoch_base", _i32)])
 
 
 class Shape(C.Structure):
@@ -80,9 +86,12 @@ SIGNATURES = {
     "bibo_moe_ep_plan_words": (_i64, [_i32, _i64]),
     "bibo_moe_ep_plan_off": (_i64, [_i32, _i32]),
     "bibo_moe_ep_plan": (_i32, [_vp, _i32, _i32, _i32, _i64, _vp, _vp]),
-    "bibo_moe_ep_dispatch": (_i32, [_vp, _vp, _vp, _vp, _vp, _vp, _i64, _i32, _i32, _i32, _i32, _i32, _i64, _i32, _vp, _vp]),
+    "bibo_moe_ep_dispatch": (_i32, [_vp, _vp, _vp, _vp, _vp, _vp, _i64, _i32, _i32, _i32, _i32, _i32, _i64, _i32, _vp, _vp,
+                                    _vp]),
     "bibo_moe_ep_forward": (_i32, [C.POINTER(EpArgs), _vp]),
-    "bibo_moe_ep_experts": (_i32, [_vp, _vp, _vp, _vp, _vp, _i32, _i32, _i32, _i32, _i64, _i32, _vp, _vp, _vp]),
+    "bibo_moe_ep_backward": (_i32, [C.POINTER(EpArgs), C.POINTER(EpBwdArgs), _vp]),
+    "bibo_moe_ep_experts": (_i32, [_vp, _vp, _vp, _vp, _vp, _i32, _i32, _i32, _i32, _i64, _i32, _vp, _vp, _vp, _vp, _i32,
+                                   _vp]),
     "bibo_moe_ep_barrier": (_i32, [_vp, _i32, _i32, _i32, _vp, _vp]),
     "bibo_moe_ep_combine": (_i32, [_vp, _vp, _vp, _vp, _i64, _i32, _i32, _i32, _i64, _i32, _vp, _vp]),
     "bibo_moe_route_noalloc": (_i32, [_vp, _vp, _vp, _i64, _i32, _i32, _i32, _i32, _f32, _i32, _vp, _vp, _vp, _vp]),

@@ -17,26 +17,9 @@
 // reads) is provided by the caller with device-side barriers between the launches.
 #include <algorithm>
 
-#include "common.cuh"
+#include "ep_common.cuh"
 
 namespace bibo {
-
-constexpr int EP_MAX_RANKS = 8;
-struct PeerPtrs { void* p[EP_MAX_RANKS]; };
-
-// EP plan words: [0]=n_tiles [1]=rows used [2]=status (sticky) [3]=reserved,
-// send_base[E] (row in the owner's buffer where this rank's rows of expert e start),
-// recv_off[E+1] and recv_cnt[E] (groups g = le*R + s of this rank), then int4 tiles.
-__host__ __device__ inline int64_t ep_off_send_base() { return PLAN_HDR; }
-__host__ __device__ inline int64_t ep_off_recv_off(int E) { return PLAN_HDR + E; }
-__host__ __device__ inline int64_t ep_off_recv_cnt(int E) { return PLAN_HDR + 2 * E + 1; }
-__host__ __device__ inline int64_t ep_off_tiles(int E) { return (PLAN_HDR + 3 * E + 1 + 3) / 4 * 4; }
-__host__ __device__ inline int64_t ep_off_pairs(int E, int64_t rows_cap_recv) {
-  return ep_off_tiles(E) + rows_cap_recv / BIBO_TILE_M * 4;
-}
-__host__ __device__ inline int64_t ep_plan_words(int E, int64_t rows_cap_recv) {
-  return ep_off_pairs(E, rows_cap_recv) + rows_cap_recv / BIBO_TILE_M * 2;
-}
 
 // One block, E threads.  Thread d < R scans destination d's layout.
 __global__ void __launch_bounds__(BIBO_MAX_EXPERTS)
@@ -84,6 +67,11 @@ ep_plan_kernel(const int32_t* __restrict__ cnt_all, int rank, int world, int n_e
   }
   __syncthreads();
   if (tid <= n_experts) recv_off[tid] = s_off[tid];
+  if (tid < el) {   // row range of local expert tid: its `world` groups are contiguous
+    plan[ep_off_le_off(n_experts) + tid] = s_off[tid * world];
+    plan[ep_off_le_span(n_experts) + tid] = over ? 0 : s_off[(tid + 1) * world] - s_off[tid * world];
+    if (tid == el - 1) plan[ep_off_le_off(n_experts) + el] = s_off[n_experts];
+  }
   if (tid < n_experts) {
     recv_cnt[tid] = s_cnt[tid];
     if (!over) {
@@ -105,7 +93,8 @@ __global__ void __launch_bounds__(EPW * 32)
 ep_dispatch_kernel(const uint8_t* __restrict__ x, const int32_t* __restrict__ topk_idx,
                    const int32_t* __restrict__ slot_rank, const int32_t* __restrict__ local_plan,
                    const int32_t* __restrict__ ep_plan, PeerPtrs xp_peers, int64_t n_tokens, int row_bytes,
-                   int n_experts, int world, int top_k, int rows_cap_recv, int32_t* __restrict__ slot_row) {
+                   int n_experts, int world, int top_k, int rows_cap_recv, int32_t* __restrict__ slot_row,
+                   int32_t* __restrict__ row_token) {
   const int lane = threadIdx.x & 31;
   if (ep_plan[PLAN_STATUS] != 0) return;   // overflow or earlier error: write nothing
   const int el = n_experts / world;
@@ -120,6 +109,9 @@ ep_dispatch_kernel(const uint8_t* __restrict__ x, const int32_t* __restrict__ to
     my_owner = e / el;
     my_row = send_base[e] + block_base[b * n_experts + e] + slot_rank[w * top_k + lane];
     slot_row[w * top_k + lane] = my_owner * rows_cap_recv + my_row;
+    if (row_token != nullptr)   // token of each row of the LOCAL expert-sorted order (router weight gradient)
+      row_token[local_plan[plan_off_expert_off(n_experts) + e] + block_base[b * n_experts + e] +
+                slot_rank[w * top_k + lane]] = (int32_t)w;
   }
   uint4* dst[BIBO_MAX_TOP_K];
 #pragma unroll
@@ -211,6 +203,19 @@ ep_combine_kernel(PeerPtrs y_peers, const int32_t* __restrict__ slot_row, const 
   }
 }
 
+// Zero the rows of every tile that lie beyond its valid rows (block per tile).
+__global__ void __launch_bounds__(128)
+ep_zero_tile_padding_kernel(uint8_t* __restrict__ buf, const int32_t* __restrict__ plan, int64_t tiles_off,
+                            int row_bytes) {
+  if ((int)blockIdx.x >= plan[PLAN_N_TILES]) return;
+  const int4 t = reinterpret_cast<const int4*>(plan + tiles_off)[blockIdx.x];
+  const int chunks = row_bytes / 16;
+  for (int r = t.z + (threadIdx.x >> 5); r < BIBO_TILE_M; r += 4) {
+    uint4* dst = reinterpret_cast<uint4*>(buf + (int64_t)(t.y + r) * row_bytes);
+    for (int c = threadIdx.x & 31; c < chunks; c += 32) dst[c] = make_uint4(0, 0, 0, 0);
+  }
+}
+
 // Every rank publishes its histogram row into every peer's cnt_all[rank][:] (peer stores); a
 // barrier after this kernel makes all rows visible everywhere, replacing a library all-gather.
 __global__ void __launch_bounds__(BIBO_MAX_EXPERTS)
@@ -275,6 +280,8 @@ extern "C" int64_t bibo_moe_ep_plan_off(int which, int n_experts) {
     case 0: return ep_off_send_base();
     case 1: return ep_off_recv_off(n_experts);
     case 2: return ep_off_recv_cnt(n_experts);
+    case 4: return ep_off_le_off(n_experts);
+    case 5: return ep_off_le_span(n_experts);
     default: return ep_off_tiles(n_experts);
   }
 }
@@ -294,7 +301,8 @@ extern "C" int bibo_moe_ep_plan(const int32_t* cnt_all, int rank, int world, int
 extern "C" int bibo_moe_ep_dispatch(const void* x, const int32_t* topk_idx, const int32_t* slot_rank,
                                     const int32_t* local_plan, const int32_t* ep_plan, void* const* xp_peers,
                                     int64_t n_tokens, int hidden, int n_experts, int rank, int world, int top_k,
-                                    int64_t rows_cap_recv, int comm_ctas, int32_t* slot_row, void* stream) {
+                                    int64_t rows_cap_recv, int comm_ctas, int32_t* slot_row, int32_t* row_token,
+                                    void* stream) {
   int rc = ep_check("ep_dispatch", world, rank, n_experts, rows_cap_recv);
   if (rc) return rc;
   if (n_tokens <= 0) return BIBO_OK;
@@ -313,7 +321,7 @@ extern "C" int bibo_moe_ep_dispatch(const void* x, const int32_t* topk_idx, cons
   dim3 grid((unsigned)blocks);
   ep_dispatch_kernel<<<grid, EPW * 32, 0, static_cast<cudaStream_t>(stream)>>>(
       (const uint8_t*)x, topk_idx, slot_rank, local_plan, ep_plan, pp, n_tokens, row_bytes, n_experts, world, top_k,
-      (int)rows_cap_recv, slot_row);
+      (int)rows_cap_recv, slot_row, row_token);
   BIBO_CHECK_LAUNCH("ep_dispatch_kernel");
   return BIBO_OK;
 }
@@ -321,18 +329,22 @@ extern "C" int bibo_moe_ep_dispatch(const void* x, const int32_t* topk_idx, cons
 extern "C" int bibo_moe_ep_experts(const void* xp_recv, const void* gate_up_proj, const void* down_proj,
                                    const float* theta, const int32_t* ep_plan, int hidden, int inter, int n_experts,
                                    int world, int64_t rows_cap_recv, int max_ctas, void* h, void* y_recv,
-                                   void* stream) {
+                                   void* gate_up_out, float* rnorm_out, int zero_padding, void* stream) {
   int rc = ep_check("ep_experts", world, 0, n_experts, rows_cap_recv);
   if (rc) return rc;
   if (!xp_recv || !gate_up_proj || !down_proj || !theta || !ep_plan || !h || !y_recv)
     return fail(BIBO_ERR_ARG, "ep_experts: null pointer");
   if (!gemm1_tc_supported(hidden, inter, BIBO_BF16) || !gemm2_tc_supported(hidden, inter, BIBO_BF16))
     return fail(BIBO_ERR_UNSUPPORTED, "ep_experts: hidden=%d inter=%d is outside the tensor-core kernels", hidden, inter);
-  const PlanView pv{ep_plan, ep_off_tiles(n_experts), ep_off_pairs(n_experts, rows_cap_recv),
-                    rows_cap_recv / BIBO_TILE_M, rows_cap_recv, max_ctas};
+  const PlanView pv = ep_plan_view(ep_plan, n_experts, rows_cap_recv, max_ctas);
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   const int el = n_experts / world;
-  rc = gemm1_tc_launch(xp_recv, gate_up_proj, theta, pv, hidden, inter, el, h, nullptr, nullptr, st);
+  if (zero_padding) {   // training: rows between a group's last token and its tile boundary become zero
+    ep_zero_tile_padding_kernel<<<(unsigned)pv.tiles_cap, 128, 0, st>>>(
+        static_cast<uint8_t*>(const_cast<void*>(xp_recv)), ep_plan, pv.tiles_off, hidden * 2);
+    BIBO_CHECK_LAUNCH("ep_zero_tile_padding_kernel");
+  }
+  rc = gemm1_tc_launch(xp_recv, gate_up_proj, theta, pv, hidden, inter, el, h, gate_up_out, rnorm_out, st);
   if (rc) return rc;
   return gemm2_tc_launch(h, down_proj, pv, hidden, inter, el, y_recv, st);
 }
@@ -440,13 +452,13 @@ extern "C" int bibo_moe_ep_forward(const bibo_moe_ep_args* a, void* stream) {
   if (rc) return rc;
   rc = bibo_moe_ep_dispatch(a->x, a->topk_idx, a->slot_rank, a->local_plan, a->ep_plan, a->xp_peers, a->n_tokens,
                             a->hidden, a->n_experts, a->rank, a->world, a->top_k, a->rows_cap_recv, a->comm_ctas,
-                            a->slot_row, stream);
+                            a->slot_row, a->row_token, stream);
   if (rc) return rc;
   rc = bibo_moe_ep_barrier(a->flags_peers, a->rank, a->world, a->epoch_base + 2, status, stream);
   if (rc) return rc;
   rc = bibo_moe_ep_experts(a->xp_peers[a->rank], a->gate_up_proj, a->down_proj, a->theta, a->ep_plan, a->hidden,
                            a->inter, a->n_experts, a->world, a->rows_cap_recv, a->max_ctas, a->h, a->y_peers[a->rank],
-                           stream);
+                           a->gate_up_recv, a->rnorm_recv, a->gate_up_recv != nullptr, stream);
   if (rc) return rc;
   rc = bibo_moe_ep_barrier(a->flags_peers, a->rank, a->world, a->epoch_base + 3, status, stream);
   if (rc) return rc;

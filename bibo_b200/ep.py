@@ -169,13 +169,14 @@ class ExpertParallelMoE:
         ev("gather_plan")
         _lib.check(lib.bibo_moe_ep_dispatch(p(x), p(self.topk_idx), p(self.slot_rank), p(self.local_plan),
                                             p(self.ep_plan), self.xp.ptr_array, n, hidden, e, self.rank, self.world, k,
-                                            self.cap, self.comm_ctas, p(self.slot_row), st), "bibo_moe_ep_dispatch")
+                                            self.cap, self.comm_ctas, p(self.slot_row), None, st),
+                   "bibo_moe_ep_dispatch")
         ev("dispatch")
         self._barrier(st)                   # every rank's rows have landed
         ev("barrier1")
         _lib.check(lib.bibo_moe_ep_experts(p(self.xp.tensor), p(self.gate_up), p(self.down), p(self.theta),
                                            p(self.ep_plan), hidden, self.inter, e, self.world, self.cap, self.max_ctas,
-                                           p(self.h), p(self.y.tensor), st), "bibo_moe_ep_experts")
+                                           p(self.h), p(self.y.tensor), None, None, 0, st), "bibo_moe_ep_experts")
         ev("experts")
         self._barrier(st)                   # every rank's results are written
         ev("barrier2")
@@ -197,7 +198,7 @@ class ExpertParallelMoE:
             p(x), p(self.w_router), p(self.bias), p(self.gate_up), p(self.down), p(self.theta),
             p(self.topk_idx), p(self.topk_w), p(self.slot_rank), p(self.block_counts), p(self.local_plan),
             p(self.ep_plan), p(self.slot_row), p(self.h), cast(self.xp.ptr_array), cast(self.y.ptr_array),
-            cast(self.flags.ptr_array), cast(self.cnt.ptr_array), p(out))
+            cast(self.flags.ptr_array), cast(self.cnt.ptr_array), p(out), None, None, None)
         self._epoch += 3
         _lib.check(_lib.load().bibo_moe_ep_forward(C.byref(a), st), "bibo_moe_ep_forward")
         return out

@@ -237,13 +237,15 @@ int bibo_moe_ep_plan(const int32_t* cnt_all, int rank, int world, int n_experts,
 int bibo_moe_ep_dispatch(const void* x, const int32_t* topk_idx, const int32_t* slot_rank,
                          const int32_t* local_plan, const int32_t* ep_plan, void* const* xp_peers,
                          int64_t n_tokens, int hidden, int n_experts, int rank, int world, int top_k,
-                         int64_t rows_cap_recv, int comm_ctas, int32_t* slot_row, void* stream);
+                         int64_t rows_cap_recv, int comm_ctas, int32_t* slot_row, int32_t* row_token,
+                         void* stream);
 /* gate/up + radial + down on the rows this rank received; gate_up_proj / down_proj / theta hold only
  * this rank's E/world experts.  max_ctas > 0 bounds the persistent grids (leaves SMs to concurrent
  * dispatch / combine kernels of another token chunk).                                              */
 int bibo_moe_ep_experts(const void* xp_recv, const void* gate_up_proj, const void* down_proj,
                         const float* theta, const int32_t* ep_plan, int hidden, int inter, int n_experts,
-                        int world, int64_t rows_cap_recv, int max_ctas, void* h, void* y_recv, void* stream);
+                        int world, int64_t rows_cap_recv, int max_ctas, void* h, void* y_recv,
+                        void* gate_up_out, float* rnorm_out, int zero_padding, void* stream);
 /* Stream-ordered barrier over the ranks: flags_peers[r] = rank r's zero-initialised int32[8] flag array
  * as mapped into this process; epoch must grow by one per call.  The wait inside is bounded (about
  * two seconds); on timeout *status is raised to 5 and the kernel returns.                          */
@@ -270,8 +272,31 @@ typedef struct {
   void* h;                                                                  /* [rows_cap_recv, I] local */
   void* const* xp_peers; void* const* y_peers; void* const* flags_peers; void* const* cnt_peers;
   void* out;
+  /* training only (all NULL for inference): raw gate|up rows [rows_cap_recv, 2I] and row norms
+   * [rows_cap_recv] of the received rows, and the token of every row of the local expert-sorted
+   * order [N*k + E*127]; with these set the padding rows of the receive buffer are zeroed.       */
+  void* gate_up_recv; float* rnorm_recv; int32_t* row_token;
 } bibo_moe_ep_args;
 int bibo_moe_ep_forward(const bibo_moe_ep_args* args, void* stream);
+
+/* Backward of bibo_moe_ep_forward (bf16, shapes of the tensor-core backward kernels).  `fwd` is the
+ * argument block of the matching forward, run with gate_up_recv / rnorm_recv / row_token set; its
+ * buffers are consumed (y becomes dXp, gate_up_recv becomes dGate|dUp).  dy_peers[r] = rank r's
+ * dY receive buffer [rows_cap_recv, H] as mapped here.  Outputs: dx [N,H]; d_w_router [E,H] = the
+ * LOCAL tokens' contribution (all-reduce it across ranks like any replicated parameter);
+ * d_gate_up_proj / d_down_proj / d_theta for this rank's E/world experts.  Uses barrier epochs
+ * epoch_base+1 .. epoch_base+2.                                                                  */
+typedef struct {
+  const void* dout;            /* [N,H] */
+  void* const* dy_peers;
+  void* dh;                    /* [rows_cap_recv, I] */
+  float* dw;                   /* [N,k] */
+  float* dlogit_row;           /* [N*k + E*127] */
+  float* dtheta_row;           /* [rows_cap_recv] */
+  void* dx; void* d_w_router; void* d_gate_up_proj; void* d_down_proj; float* d_theta;
+  int epoch_base;
+} bibo_moe_ep_bwd_args;
+int bibo_moe_ep_backward(const bibo_moe_ep_args* fwd, const bibo_moe_ep_bwd_args* bwd, void* stream);
 
 /* ---- routing without any allocation -------------------------------------------------------------
  * No counterpart in the reference: added for callers that cannot allocate device memory (a runtime
