@@ -145,16 +145,17 @@ class ExpertParallelMoE:
                                                    _lib.ptr(self.ep_plan[2:]), st), "bibo_moe_ep_barrier")
 
     # ---- forward ----------------------------------------------------------------------------------------
-    def forward(self, x: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    def forward(self, x: torch.Tensor, out: Optional[torch.Tensor] = None, training: bool = False) -> torch.Tensor:
         lib, p = _lib.load(), _lib.ptr
         n, hidden = x.shape
         if self._n != n:
             self._allocate(n)
+            self._train_ready = False
         if out is None:
             out = torch.empty_like(x)
         k, e, st = self.top_k, self.n_experts, torch.cuda.current_stream(self.device).cuda_stream
-        if not getattr(self, "profile", False):
-            return self._forward_one_call(x, out, st)
+        if training or not getattr(self, "profile", False):
+            return self._forward_one_call(x, out, st, training)
         ev = self._mark
         ev("start")
         _lib.check(lib.bibo_moe_router_fwd(p(x), p(self.w_router), p(self.bias), None, n, hidden, e, k,
@@ -186,9 +187,46 @@ class ExpertParallelMoE:
         ev("combine")
         return out
 
-    def _forward_one_call(self, x: torch.Tensor, out: torch.Tensor, st: int) -> torch.Tensor:
+    def _allocate_training(self) -> None:
+        """Extra buffers the backward pass needs (allocated on the first training forward)."""
+        dev, n, k, e = self.device, self._n, self.top_k, self.n_experts
+        rows_local = Fn.Geometry(n, self.hidden, self.inter, e, e, 0, k, torch.bfloat16).rows_cap
+        f32 = dict(dtype=torch.float32, device=dev)
+        self.gate_up_recv = torch.empty(self.cap, 2 * self.inter, dtype=torch.bfloat16, device=dev)
+        self.rnorm_recv = torch.empty(self.cap, **f32)
+        self.row_token = torch.zeros(rows_local, dtype=torch.int32, device=dev)
+        self.dy = _Symmetric((self.cap, self.hidden), torch.bfloat16, dev, self.group)
+        self.dh = torch.empty(self.cap, self.inter, dtype=torch.bfloat16, device=dev)
+        self.dw = torch.empty(n, k, **f32)
+        self.dlogit_row = torch.zeros(rows_local, **f32)
+        self.dtheta_row = torch.zeros(self.cap, **f32)
+        self._train_ready = True
+
+    def backward(self, dout: torch.Tensor):
+        """Gradients of the last TRAINING forward (``forward(x, training=True)``): returns
+        (dx [N,H], d_w_router [E,H] = this rank's tokens only, d_gate_up_proj, d_down_proj, d_theta)
+        for this rank's experts."""
+        if getattr(self, "_last_args", None) is None:
+            raise RuntimeError("backward needs a preceding forward(x, training=True)")
+        p, dev = _lib.ptr, self.device
+        dout = dout.contiguous()
+        dx = torch.empty_like(dout)
+        d_wr = torch.zeros_like(self.w_router)
+        d_gu, d_dn = torch.zeros_like(self.gate_up), torch.zeros_like(self.down)
+        d_th = torch.zeros(self.el, dtype=torch.float32, device=dev)
+        b = _lib.EpBwdArgs(p(dout), C.cast(self.dy.ptr_array, C.c_void_p), p(self.dh), p(self.dw), p(self.dlogit_row),
+                           p(self.dtheta_row), p(dx), p(d_wr), p(d_gu), p(d_dn), p(d_th), self._epoch)
+        self._epoch += 2
+        st = torch.cuda.current_stream(dev).cuda_stream
+        _lib.check(_lib.load().bibo_moe_ep_backward(C.byref(self._last_args), C.byref(b), st), "bibo_moe_ep_backward")
+        self._last_args = None
+        return dx, d_wr, d_gu, d_dn, d_th
+
+    def _forward_one_call(self, x: torch.Tensor, out: torch.Tensor, st: int, training: bool = False) -> torch.Tensor:
         """The product path: bibo_moe_ep_forward (histograms exchanged through peer memory, no library
         collective)."""
+        if training and not getattr(self, "_train_ready", False):
+            self._allocate_training()
         p = _lib.ptr
         C_vp = C.c_void_p
         cast = lambda arr: C.cast(arr, C_vp)
@@ -198,9 +236,12 @@ class ExpertParallelMoE:
             p(x), p(self.w_router), p(self.bias), p(self.gate_up), p(self.down), p(self.theta),
             p(self.topk_idx), p(self.topk_w), p(self.slot_rank), p(self.block_counts), p(self.local_plan),
             p(self.ep_plan), p(self.slot_row), p(self.h), cast(self.xp.ptr_array), cast(self.y.ptr_array),
-            cast(self.flags.ptr_array), cast(self.cnt.ptr_array), p(out), None, None, None)
+            cast(self.flags.ptr_array), cast(self.cnt.ptr_array), p(out),
+            p(self.gate_up_recv) if training else None, p(self.rnorm_recv) if training else None,
+            p(self.row_token) if training else None)
         self._epoch += 3
         _lib.check(_lib.load().bibo_moe_ep_forward(C.byref(a), st), "bibo_moe_ep_forward")
+        self._last_args, self._last_x = (a, x) if training else (None, None)
         return out
 
     def _mark(self, name: str) -> None:

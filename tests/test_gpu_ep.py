@@ -11,10 +11,10 @@ pytestmark = pytest.mark.gpu
 ROOT = pathlib.Path(__file__).resolve().parents[1]
 
 
-def _run(world, args, env_extra=None, port=29541):
+def _run(world, args, env_extra=None, port=29541, worker="ep_worker.py"):
     env = dict(os.environ, NCCL_NVLS_ENABLE="0", **(env_extra or {}))
     cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={world}",
-           "--master-addr", "127.0.0.1", "--master-port", str(port), str(ROOT / "tests" / "ep_worker.py"), *map(str, args)]
+           "--master-addr", "127.0.0.1", "--master-port", str(port), str(ROOT / "tests" / worker), *map(str, args)]
     return subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=600)
 
 
@@ -25,3 +25,11 @@ def test_expert_parallel_matches_single_gpu_and_oracle(args):
     r = _run(world, args)
     assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]
     assert "identical to single-GPU chain: True" in r.stdout
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs at least 2 GPUs")
+@pytest.mark.parametrize("args", [(1500, 512, 256, 64, 6), (2500, 1024, 512, 64, 6)])
+def test_expert_parallel_backward_matches_oracle_autograd(args):
+    world = 2 if torch.cuda.device_count() < 4 else 4
+    r = _run(world, args, port=29547, worker="ep_bwd_worker.py")
+    assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]
