@@ -209,6 +209,13 @@ def main():
                                                comm_sms=args.comm_sms)
         step = lambda: runner.forward(t["x"])
         ws = None
+        if args.mode == "fwdbwd":
+            lane = runner.lanes[0]
+            dout = torch.randn_like(t["x"])
+
+            def step():
+                lane.forward(t["x"], training=True)
+                return lane.backward(dout)
     else:
         geo = Fn.Geometry(n, h, i, N_EXPERTS, N_EXPERTS, 0, TOP_K, dtype)
         ws = Fn.MoEWorkspace(geo, dev, keep_gate_up=False)
@@ -288,7 +295,7 @@ def main():
     e2e_val = n * world * args.steps / float(e2e_s)
 
     ep_phases = None
-    if world > 1:      # one extra profiled step: when each phase of each token slice ended (ms from step start)
+    if world > 1 and args.mode == "fwd":      # one extra profiled step: when each phase of each token slice ended (ms from step start)
         for lane in runner.lanes:
             lane.profile = True
         t_start = torch.cuda.Event(enable_timing=True)
