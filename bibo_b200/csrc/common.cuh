@@ -70,8 +70,16 @@ __host__ __device__ inline int64_t plan_off_tiles(int64_t n, int E, int n_glu) {
 __host__ __device__ inline int64_t plan_off_pairs(int64_t n, int k, int E, int n_glu) {
   return plan_off_tiles(n, E, n_glu) + tiles_cap(n, k, n_glu) * 4;
 }
-__host__ __device__ inline int64_t plan_words(int64_t n, int k, int E, int n_glu) {
+// scratch of the gate/up kernel: partial sums of squares and flags that two 2-CTA clusters (the two
+// column blocks of one row pair) exchange through global memory; per CTA 2 x 128 floats + 2 flags
+constexpr int XG_MAX_CTAS = 256;
+constexpr int64_t XG_PART_WORDS = (int64_t)XG_MAX_CTAS * 2 * 128;
+constexpr int64_t XG_WORDS = XG_PART_WORDS + XG_MAX_CTAS * 2;
+__host__ __device__ inline int64_t plan_off_scratch(int64_t n, int k, int E, int n_glu) {
   return plan_off_pairs(n, k, E, n_glu) + tiles_cap(n, k, n_glu) * 2;
+}
+__host__ __device__ inline int64_t plan_words(int64_t n, int k, int E, int n_glu) {
+  return plan_off_scratch(n, k, E, n_glu) + XG_WORDS;
 }
 
 // What a grouped-GEMM launcher needs to know about a row plan: where the header / tile list live and
@@ -80,13 +88,15 @@ struct PlanView {
   const int32_t* plan;   // header at [0..3]
   int64_t tiles_off;     // word offset of the int4 tile records
   int64_t pairs_off;     // word offset of the int2 tile-pair records
+  int64_t scratch_off;   // word offset of the XG_WORDS exchange scratch
   int64_t tiles_cap;     // upper bound of tiles (grid sizing)
   int64_t rows_alloc;    // rows of the expert-contiguous buffers
   int max_ctas;          // 0 = all SMs; otherwise an upper bound for persistent grids
 };
 inline PlanView local_plan_view(const int32_t* plan, int64_t n_tokens, int top_k, int n_experts, int n_glu) {
   return PlanView{plan, plan_off_tiles(n_tokens, n_experts, n_glu), plan_off_pairs(n_tokens, top_k, n_experts, n_glu),
-                  tiles_cap(n_tokens, top_k, n_glu), rows_cap(n_tokens, top_k, n_glu), 0};
+                  plan_off_scratch(n_tokens, top_k, n_experts, n_glu), tiles_cap(n_tokens, top_k, n_glu),
+                  rows_cap(n_tokens, top_k, n_glu), 0};
 }
 
 // ---- dtype helpers ------------------------------------------------------------------------------

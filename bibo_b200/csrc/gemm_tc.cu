@@ -399,15 +399,21 @@ struct G1PairLayout {
   static constexpr int BYTES = OFF_BAR + 256 + 1024;
 };
 
-template <int CLN, int STAGES>
+// XG: the two column blocks of a row pair live in two separate 2-CTA clusters (blockIdx.x ^ 2) and
+// exchange their partial sums through global memory (flag + 128 floats per CTA and parity) instead of
+// distributed shared memory, so the cluster size stays 2 and every SM can host a CTA; the launcher
+// guarantees that all CTAs are resident (grid <= SM count, one CTA per SM).
+template <int CLN, int STAGES, bool XG>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 gemm1_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                   const __grid_constant__ CUtensorMap tmH, const float* __restrict__ theta,
                   int32_t* __restrict__ plan, int64_t tiles_off, int64_t pairs_off, int k_blocks, int inter,
-                  __nv_bfloat16* __restrict__ gate_up_out, float* __restrict__ rnorm_out) {
+                  __nv_bfloat16* __restrict__ gate_up_out, float* __restrict__ rnorm_out, float* xg_part,
+                  int* xg_flags) {
   using L = G1PairLayout<STAGES>;
   constexpr int NC = L::NC;
-  constexpr int CL = 2 * CLN;
+  constexpr int CL = XG ? 2 : 2 * CLN;          // hardware cluster size
+  constexpr int GROUP = 2 * CLN;                // CTAs that share one row pair
   extern __shared__ unsigned char smem_dyn[];
   unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_dyn) + 1023) & ~uintptr_t(1023));
   float* part = reinterpret_cast<float*>(smem + L::OFF_PART);
@@ -423,9 +429,10 @@ gemm1_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const uint32_t cr = cluster_ctarank();
-  const uint32_t pr = cr & 1u, ch = cr >> 1, leader = cr & ~1u;
+  const uint32_t pr = cr & 1u, leader = cr & ~1u;
+  const uint32_t ch = XG ? ((blockIdx.x >> 1) & (CLN - 1)) : (cr >> 1);
   const uint16_t pair_mask = (uint16_t)(3u << leader);
-  const int cluster_id = blockIdx.x / CL, n_clusters = gridDim.x / CL;
+  const int cluster_id = blockIdx.x / GROUP, n_clusters = gridDim.x / GROUP;   // row-pair groups
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1); }
@@ -539,12 +546,30 @@ gemm1_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive_cluster_addr(map_to_cta(gempty, leader));
-      if (CLN > 1) {
+      if (CLN > 1 && !XG) {
         const uint32_t peer = cr ^ 2u;
         st_remote_f32(&part[(it & 1) * BM + row], peer, ss);
         mbar_arrive_remote(&xbar[it & 1], peer);
         if (!mbar_wait<true>(&xbar[it & 1], (it >> 1) & 1, abort_flag)) break;
         ss += part[(it & 1) * BM + row];
+      }
+      if (CLN > 1 && XG) {
+        const int par = it & 1, epoch = (int)(it >> 1) + 1;
+        xg_part[((int64_t)blockIdx.x * 2 + par) * BM + row] = ss;
+        __threadfence();
+        named_bar_sync(1, EPI_THREADS);
+        if (threadIdx.x == 64) asm volatile("st.release.gpu.global.s32 [%0], %1;" ::"l"(xg_flags + blockIdx.x * 2 + par), "r"(epoch) : "memory");
+        const int peer_cta = blockIdx.x ^ 2;
+        const int* pf = xg_flags + peer_cta * 2 + par;
+        bool got = false;
+        for (uint32_t spin = 0; spin < (1u << 22); ++spin) {
+          int v;
+          asm volatile("ld.acquire.gpu.global.s32 %0, [%1];" : "=r"(v) : "l"(pf) : "memory");
+          if (v >= epoch) { got = true; break; }
+          if ((spin & 255u) == 255u && *abort_flag) break;
+        }
+        if (!got) { *abort_flag = 1; break; }
+        ss += __ldcg(&xg_part[((int64_t)peer_cta * 2 + par) * BM + row]);
       }
       const float rn = sqrtf(ss / (float)inter + 1e-6f);
       const float pw = sigmoid_accurate(__ldg(theta + t.x));
@@ -750,13 +775,14 @@ static int gemm1_launch_t(const CUtensorMap& tmA, const CUtensorMap& tmB, const 
   return BIBO_OK;
 }
 
-template <int CLN, int STAGES>
+template <int CLN, int STAGES, bool XG>
 static int gemm1_pair_launch_t(const CUtensorMap& tmA, const CUtensorMap& tmB, const CUtensorMap& tmH,
                                const float* theta, const PlanView& pv, int k_blocks, int inter, void* gate_up_out,
                                float* rnorm_out, cudaStream_t st) {
   using L = G1PairLayout<STAGES>;
-  constexpr int CL = 2 * CLN;
-  auto kern = gemm1_pair_kernel<CLN, STAGES>;
+  constexpr int CL = XG ? 2 : 2 * CLN;      // hardware cluster size
+  constexpr int GROUP = 2 * CLN;            // CTAs per row pair
+  auto kern = gemm1_pair_kernel<CLN, STAGES, XG>;
   static int max_clusters = 0;
   int rc;
   cudaLaunchConfig_t cfg = {};
@@ -778,11 +804,17 @@ static int gemm1_pair_launch_t(const CUtensorMap& tmA, const CUtensorMap& tmB, c
     max_clusters = n > 0 ? n : 1;
   }
   const int sms = pv.max_ctas > 0 ? std::min(pv.max_ctas, sm_count()) : sm_count();
-  const int clusters = (int)std::max<int64_t>(1, std::min<int64_t>(std::min(max_clusters, sms / CL), pv.tiles_cap));
-  cfg.gridDim = dim3(clusters * CL);
+  // resident CTAs only: with XG the groups wait on one another through global memory
+  const int ctas = std::min(std::min(max_clusters * CL, sms), XG_MAX_CTAS);
+  const int groups = (int)std::max<int64_t>(1, std::min<int64_t>(ctas / GROUP, pv.tiles_cap));
+  cfg.gridDim = dim3(groups * GROUP);
+  int32_t* scratch = const_cast<int32_t*>(pv.plan) + pv.scratch_off;
+  float* xg_part = reinterpret_cast<float*>(scratch);
+  int* xg_flags = scratch + XG_PART_WORDS;
+  if (XG) BIBO_CUDA(cudaMemsetAsync(xg_flags, 0, sizeof(int) * XG_MAX_CTAS * 2, st));
   BIBO_CUDA(cudaLaunchKernelEx(&cfg, kern, tmA, tmB, tmH, theta, const_cast<int32_t*>(pv.plan), pv.tiles_off,
                                pv.pairs_off, k_blocks, inter, reinterpret_cast<__nv_bfloat16*>(gate_up_out),
-                               rnorm_out));
+                               rnorm_out, xg_part, xg_flags));
   launch_counter().fetch_add(1, std::memory_order_relaxed);
   return BIBO_OK;
 }
@@ -798,9 +830,13 @@ int gemm1_tc_launch(const void* xp, const void* gate_up_proj, const float* theta
     if ((rc = make_tmap_bf16_2d(&tmA, xp, pv.rows_alloc, hidden, hidden, BM))) return rc;
     if ((rc = make_tmap_bf16_2d(&tmB, gate_up_proj, (uint64_t)n_weight_experts * 2 * inter, hidden, hidden, 128))) return rc;
     if ((rc = make_tmap_bf16_2d(&tmH, h, pv.rows_alloc, inter, inter, BM))) return rc;
+    // BIBO_G1_DSMEM=1: 4-CTA clusters exchanging through distributed shared memory (A/B measurements)
+    static const bool dsmem = [] { const char* e = getenv("BIBO_G1_DSMEM"); return e && atoi(e) != 0; }();
+    if (inter == 512 && dsmem)
+      return gemm1_pair_launch_t<2, 5, false>(tmA, tmB, tmH, theta, pv, hidden / BK, inter, gate_up_out, rnorm_out, st);
     if (inter == 512)
-      return gemm1_pair_launch_t<2, 5>(tmA, tmB, tmH, theta, pv, hidden / BK, inter, gate_up_out, rnorm_out, st);
-    return gemm1_pair_launch_t<1, 5>(tmA, tmB, tmH, theta, pv, hidden / BK, inter, gate_up_out, rnorm_out, st);
+      return gemm1_pair_launch_t<2, 5, true>(tmA, tmB, tmH, theta, pv, hidden / BK, inter, gate_up_out, rnorm_out, st);
+    return gemm1_pair_launch_t<1, 5, false>(tmA, tmB, tmH, theta, pv, hidden / BK, inter, gate_up_out, rnorm_out, st);
   }
   if ((rc = make_tmap_bf16_2d(&tmA, xp, pv.rows_alloc, hidden, hidden, BM))) return rc;
   if ((rc = make_tmap_bf16_2d(&tmB, gate_up_proj, (uint64_t)n_weight_experts * 2 * inter, hidden, hidden, nc))) return rc;

@@ -11,7 +11,7 @@
 //
 // Limits and rules
 //   * at most BIBO_NOALLOC_MAX_TOKENS tokens per call (larger calls are refused with BIBO_ERR_UNSUPPORTED);
-//     the array costs about 0.8 MB on every GPU that loads the library, for the life of the process;
+//     the array costs about 1.1 MB on every GPU that loads the library, for the life of the process;
 //   * the FIRST call on each device looks up the array's device address (cudaGetSymbolAddress) and
 //     sets kernel attributes; make that first call outside any stream capture;
 //   * every call on a device shares the one array: the array keeps the previous call's contents (the
@@ -31,7 +31,7 @@ constexpr size_t NA_BLOCKS_BYTES =
     align256((NA_TOKENS / BIBO_ROUTER_BLOCK_TOKENS) * BIBO_MAX_EXPERTS * sizeof(int32_t));
 constexpr size_t NA_PLAN_BYTES = align256(
     (PLAN_HDR + BIBO_MAX_EXPERTS + BIBO_MAX_EXPERTS + 1 + 3 + (NA_TOKENS / BIBO_ROUTER_BLOCK_TOKENS) * BIBO_MAX_EXPERTS +
-     ((NA_TOKENS * BIBO_MAX_TOP_K + (int64_t)BIBO_MAX_EXPERTS * (BIBO_TILE_M - 1)) / BIBO_TILE_M + 1) * 6) *
+     ((NA_TOKENS * BIBO_MAX_TOP_K + (int64_t)BIBO_MAX_EXPERTS * (BIBO_TILE_M - 1)) / BIBO_TILE_M + 1) * 6 + XG_WORDS) *
     sizeof(int32_t));
 constexpr size_t NA_BYTES = NA_RANK_BYTES + NA_BLOCKS_BYTES + NA_PLAN_BYTES;
 

@@ -303,7 +303,7 @@ int bibo_moe_ep_backward(const bibo_moe_ep_args* fwd, const bibo_moe_ep_bwd_args
  * that reserves all memory up front, or a loop that must not incur cudaMalloc's implicit device
  * synchronisation).  Same routing as bibo_moe_router_fwd followed by bibo_moe_plan, but the three
  * intermediates (slot ranks, per-block histograms, plan) live in a fixed device array inside the
- * library (about 0.8 MB per GPU), so the caller passes only inputs and outputs:
+ * library (about 1.1 MB per GPU), so the caller passes only inputs and outputs:
  * topk_idx [N,k] int32 ascending, topk_w [N,k] fp32, counts [E] int32 (tokens per expert).
  * At most BIBO_NOALLOC_MAX_TOKENS tokens per call, otherwise BIBO_ERR_UNSUPPORTED.  The first call
  * on a device resolves the array's address (do it before any stream capture).  All calls on a
