@@ -1,4 +1,8 @@
 // extern "C" entry points that dispatch K3/K4 and chain the whole block.
+#include <algorithm>
+#include <map>
+#include <mutex>
+
 #include "common.cuh"
 
 namespace bibo {
@@ -113,6 +117,54 @@ extern "C" int bibo_moe_forward(const bibo_moe_shape* s, const void* x, const vo
   return BIBO_OK;
 }
 
+// ---- host-buffer call: copies overlapped with the kernels --------------------------------------------
+// Tokens are independent, so the batch is cut into slices: the host->device copy of slice i+1 and the
+// device->host copy of slice i-1 run on two copy streams while slice i is computed on the caller's
+// stream (the link is full duplex).  Streams and events are created once per device and kept.
+namespace {
+constexpr int HOST_MAX_SLICES = 16;
+struct HostPipe {
+  cudaStream_t in = nullptr, out = nullptr;
+  cudaEvent_t start = nullptr, done = nullptr, copied[HOST_MAX_SLICES] = {}, computed[HOST_MAX_SLICES] = {};
+  bool ready = false;
+};
+int host_pipe(HostPipe** out) {
+  static std::mutex mu;
+  static std::map<int, HostPipe> pipes;
+  int dev = 0;
+  BIBO_CUDA(cudaGetDevice(&dev));
+  std::lock_guard<std::mutex> g(mu);
+  HostPipe& p = pipes[dev];
+  if (!p.ready) {
+    BIBO_CUDA(cudaStreamCreateWithFlags(&p.in, cudaStreamNonBlocking));
+    BIBO_CUDA(cudaStreamCreateWithFlags(&p.out, cudaStreamNonBlocking));
+    BIBO_CUDA(cudaEventCreateWithFlags(&p.start, cudaEventDisableTiming));
+    BIBO_CUDA(cudaEventCreateWithFlags(&p.done, cudaEventDisableTiming));
+    for (int i = 0; i < HOST_MAX_SLICES; ++i) {
+      BIBO_CUDA(cudaEventCreateWithFlags(&p.copied[i], cudaEventDisableTiming));
+      BIBO_CUDA(cudaEventCreateWithFlags(&p.computed[i], cudaEventDisableTiming));
+    }
+    p.ready = true;
+  }
+  *out = &p;
+  return BIBO_OK;
+}
+// Slice lengths: equal slices of about 4096 tokens (a multiple of the router block), at most
+// HOST_MAX_SLICES of them.  A tapered tail (shorter last slices) and 2048 / 3072 / 6144 / 8192-token slices
+// all measured slower.  BIBO_HOST_SLICE_TOKENS overrides the length (0 = one slice, no overlap).
+int host_slices(int64_t n_tokens, int64_t* lens) {
+  static const int64_t forced = [] { const char* e = getenv("BIBO_HOST_SLICE_TOKENS"); return e ? atoll(e) : -1; }();
+  constexpr int64_t BLK = BIBO_ROUTER_BLOCK_TOKENS;
+  int64_t len = forced >= 0 ? forced : 4096;
+  if (len <= 0 || n_tokens < 2 * len) { lens[0] = n_tokens; return 1; }
+  const int64_t min_len = (n_tokens + HOST_MAX_SLICES - 1) / HOST_MAX_SLICES;
+  len = (std::max(len, min_len) + BLK - 1) / BLK * BLK;
+  int n = 0;
+  for (int64_t left = n_tokens; left > 0; left -= lens[n++]) lens[n] = std::min(len, left);
+  return n;
+}
+}  // namespace
+
 extern "C" int bibo_moe_forward_host(const bibo_moe_shape* s, const void* x_host, void* x_dev,
                                      const void* w_router, const float* bias, const void* gate_up_proj,
                                      const void* down_proj, const float* theta,
@@ -120,11 +172,47 @@ extern "C" int bibo_moe_forward_host(const bibo_moe_shape* s, const void* x_host
                                      void* stream) {
   if (!s || !x_host || !x_dev || !out_dev || !out_host) return fail(BIBO_ERR_ARG, "forward_host: null pointer");
   cudaStream_t st = static_cast<cudaStream_t>(stream);
-  const size_t bytes = (size_t)s->n_tokens * s->hidden * (s->dtype == BIBO_F32 ? 4 : 2);
-  BIBO_CUDA(cudaMemcpyAsync(x_dev, x_host, bytes, cudaMemcpyHostToDevice, st));
-  int rc = bibo_moe_forward(s, x_dev, w_router, bias, gate_up_proj, down_proj, theta, ws, out_dev, stream);
+  const size_t row_bytes = (size_t)s->hidden * (s->dtype == BIBO_F32 ? 4 : 2);
+  int64_t lens[HOST_MAX_SLICES];
+  const int n_slices = host_slices(s->n_tokens, lens);
+  if (n_slices == 1) {
+    const size_t bytes = (size_t)s->n_tokens * row_bytes;
+    BIBO_CUDA(cudaMemcpyAsync(x_dev, x_host, bytes, cudaMemcpyHostToDevice, st));
+    int rc = bibo_moe_forward(s, x_dev, w_router, bias, gate_up_proj, down_proj, theta, ws, out_dev, stream);
+    if (rc) return rc;
+    BIBO_CUDA(cudaMemcpyAsync(out_host, out_dev, bytes, cudaMemcpyDeviceToHost, st));
+    BIBO_CUDA(cudaStreamSynchronize(st));
+    return BIBO_OK;
+  }
+  HostPipe* hp = nullptr;
+  int rc = host_pipe(&hp);
   if (rc) return rc;
-  BIBO_CUDA(cudaMemcpyAsync(out_host, out_dev, bytes, cudaMemcpyDeviceToHost, st));
+  BIBO_CUDA(cudaEventRecord(hp->start, st));          // earlier work of the caller's stream owns the buffers until here
+  BIBO_CUDA(cudaStreamWaitEvent(hp->in, hp->start, 0));
+  BIBO_CUDA(cudaStreamWaitEvent(hp->out, hp->start, 0));
+  int64_t t0 = 0;
+  for (int i = 0; i < n_slices; t0 += lens[i++]) {
+    const int64_t nt = lens[i];
+    BIBO_CUDA(cudaMemcpyAsync(static_cast<char*>(x_dev) + t0 * row_bytes, static_cast<const char*>(x_host) + t0 * row_bytes,
+                              (size_t)nt * row_bytes, cudaMemcpyHostToDevice, hp->in));
+    BIBO_CUDA(cudaEventRecord(hp->copied[i], hp->in));
+  }
+  t0 = 0;
+  for (int i = 0; i < n_slices; t0 += lens[i++]) {
+    const int64_t nt = lens[i];
+    bibo_moe_shape part = *s;
+    part.n_tokens = nt;                               // the workspace of the whole batch is large enough for a slice
+    BIBO_CUDA(cudaStreamWaitEvent(st, hp->copied[i], 0));
+    rc = bibo_moe_forward(&part, static_cast<const char*>(x_dev) + t0 * row_bytes, w_router, bias, gate_up_proj,
+                          down_proj, theta, ws, static_cast<char*>(out_dev) + t0 * row_bytes, stream);
+    if (rc) return rc;
+    BIBO_CUDA(cudaEventRecord(hp->computed[i], st));
+    BIBO_CUDA(cudaStreamWaitEvent(hp->out, hp->computed[i], 0));
+    BIBO_CUDA(cudaMemcpyAsync(static_cast<char*>(out_host) + t0 * row_bytes, static_cast<const char*>(out_dev) + t0 * row_bytes,
+                              (size_t)nt * row_bytes, cudaMemcpyDeviceToHost, hp->out));
+  }
+  BIBO_CUDA(cudaEventRecord(hp->done, hp->out));
+  BIBO_CUDA(cudaStreamWaitEvent(st, hp->done, 0));
   BIBO_CUDA(cudaStreamSynchronize(st));
   return BIBO_OK;
 }

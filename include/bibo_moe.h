@@ -183,10 +183,14 @@ int bibo_moe_forward(const bibo_moe_shape* shape, const void* x, const void* w_r
                      const float* bias, const void* gate_up_proj, const void* down_proj,
                      const float* theta, const bibo_moe_workspace* ws, void* out, void* stream);
 
-/* Same block with HOST input and output: copies x_host to x_dev, runs bibo_moe_forward, copies the
- * result into out_host and waits for it.  x_dev / out_dev are caller-allocated device staging
- * buffers [N,H]; weights stay resident on the device.  This is the call the end-to-end timing
- * uses (host->device and device->host copies inside the call).                                    */
+/* Same block with HOST input and output: copies x_host to x_dev, runs the block, copies the result
+ * into out_host and waits for it.  x_dev / out_dev are caller-allocated device staging buffers
+ * [N,H]; weights stay resident on the device.  Batches of 8192 tokens or more are cut into slices
+ * of about 4096 tokens: the copies of neighbouring slices run on two internal copy streams
+ * (created once per device) while a slice is computed on `stream`; tokens are independent, so the
+ * result equals bibo_moe_forward bit for bit.  Afterwards the workspace describes the LAST slice
+ * only.  x_host / out_host should be pinned.  This is the call the end-to-end timing uses
+ * (host->device and device->host copies inside the call).                                         */
 int bibo_moe_forward_host(const bibo_moe_shape* shape, const void* x_host, void* x_dev,
                           const void* w_router, const float* bias, const void* gate_up_proj,
                           const void* down_proj, const float* theta, const bibo_moe_workspace* ws,

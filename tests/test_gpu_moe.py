@@ -116,6 +116,28 @@ def test_saved_gate_up_and_rnorm_bf16(n, h, i):
     assert torch.allclose(ws.rnorm[:rows][valid], r_ref, rtol=1e-5, atol=0)
 
 
+@pytest.mark.parametrize("n", [700, 9000, 70000])
+def test_host_buffer_call_equals_device_call(n):
+    """bibo_moe_forward_host cuts large batches into slices to overlap the copies with the kernels;
+    tokens are independent, so the result equals one device call bit for bit (9000: ragged last
+    slice; 70000: more slices than the default length allows, so the slice length grows)."""
+    from bibo_b200 import functional as Fn
+    h, i, k = 512, 256, 6
+    inp = orc.make_inputs(n, h, i, 64, seed=11, bias_mode="uniform", theta_std=0.5)
+    t = {kk: v.to(DEV) for kk, v in inp.items()}
+    for kk in ("x", "w_router", "gate_up_proj", "down_proj"):
+        t[kk] = t[kk].to(torch.bfloat16).contiguous()
+    ref, _ = Fn.moe_forward(t["x"], t["w_router"], t["bias"], t["gate_up_proj"], t["down_proj"], t["radial_theta"], k)
+    x_host = t["x"].cpu().pin_memory()
+    out_host = torch.empty_like(x_host).pin_memory()
+    x_dev, out_dev = torch.empty_like(t["x"]), torch.empty_like(t["x"])
+    for _ in range(2):                                   # twice: the streams and events are reused
+        out_host.zero_()
+        Fn.moe_forward_host(x_host, out_host, x_dev, out_dev, t["w_router"], t["bias"], t["gate_up_proj"],
+                            t["down_proj"], t["radial_theta"], k)
+        assert torch.equal(out_host, ref.cpu())
+
+
 def test_forward_is_deterministic():
     inp = orc.make_inputs(1500, 256, 128, 64, seed=4, bias_mode="uniform", theta_std=0.5)
     a, _ = _run(inp, dtype=torch.bfloat16, top_k=6)
