@@ -181,6 +181,7 @@ def main():
     ap.add_argument("--workload", default="c4", choices=sorted(WORKLOADS))
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--ep-chunks", type=int, default=1, help="token slices pipelined on separate streams (N>1)")
+    ap.add_argument("--e2e-chunks", type=int, default=4, help="token slices of the host-buffer (e2e) forward (N>1)")
     ap.add_argument("--comm-sms", type=int, default=20, help="SMs left to the exchange kernels (N>1)")
     ap.add_argument("--mode", default="fwd", choices=["fwd", "fwdbwd"],
                     help="fwd = the headline metric; fwdbwd = forward + backward of the block (1 GPU)")
@@ -273,10 +274,10 @@ def main():
     out_host = torch.empty_like(x_host).pin_memory()
     x_dev, out_dev = torch.empty_like(t["x"]), torch.empty_like(t["x"])
     if world > 1:
-        def e2e_step():
-            x_dev.copy_(x_host, non_blocking=True)
-            out_host.copy_(runner.forward(x_dev), non_blocking=True)
-            torch.cuda.synchronize()
+        # token slices on separate streams: the copies of one slice run under the kernels of another
+        e2e_runner = runner if args.e2e_chunks == args.ep_chunks else ep.PipelinedExpertParallelMoE(
+            t, TOP_K, dist.group.WORLD, n_tokens=wl["n_tokens"], chunks=args.e2e_chunks, comm_sms=args.comm_sms)
+        e2e_step = lambda: e2e_runner.forward_host(x_host, out_host, x_dev, out_dev)
     else:
         if ws is not None:
             ws.stage_events = None

@@ -311,5 +311,26 @@ class PipelinedExpertParallelMoE:
             cur.wait_event(done)
         return out
 
+    def forward_host(self, x_host: torch.Tensor, out_host: torch.Tensor, x_dev: torch.Tensor,
+                     out_dev: torch.Tensor) -> torch.Tensor:
+        """Host-buffer forward: every slice copies its tokens in, runs and copies its result out on its
+        own stream, so the copies of one slice overlap the kernels of another (pinned host tensors);
+        waits for the result."""
+        cur = torch.cuda.current_stream(self.device)
+        start = torch.cuda.Event()
+        start.record(cur)
+        streams = self.streams if self.chunks > 1 else [cur]
+        for lane, st, (lo, hi) in zip(self.lanes, streams, self._bounds(x_host.shape[0])):
+            if hi <= lo:
+                continue
+            st.wait_event(start)
+            with torch.cuda.stream(st):
+                x_dev[lo:hi].copy_(x_host[lo:hi], non_blocking=True)
+                lane.forward(x_dev[lo:hi], out_dev[lo:hi])
+                out_host[lo:hi].copy_(out_dev[lo:hi], non_blocking=True)
+        for st in streams:
+            st.synchronize()
+        return out_host
+
     def status(self) -> int:
         return max(lane.status() for lane in self.lanes)

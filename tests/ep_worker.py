@@ -40,6 +40,13 @@ def main():
     status = moe.status()
     assert status == 0, f"rank {rank}: status {status}"
     assert torch.equal(outs[0], outs[1]) and torch.equal(outs[0], outs[2]), "expert-parallel forward is not deterministic"
+    # host-buffer call on token slices (copies of one slice under the kernels of another): same result
+    piped = ep.PipelinedExpertParallelMoE(weights, k, dist.group.WORLD, chunks=3, comm_sms=20,
+                                          capacity_factor=float(os.environ.get("EP_CF", "2.0")))
+    x_host, out_host = x_local.cpu().pin_memory(), torch.empty_like(x_local, device="cpu").pin_memory()
+    piped.forward_host(x_host, out_host, torch.empty_like(x_local), torch.empty_like(x_local))
+    assert piped.status() == 0, f"rank {rank}: sliced status {piped.status()}"
+    assert torch.equal(out_host, outs[0].cpu()), "sliced host-buffer forward differs from the device forward"
     gathered = [torch.empty_like(outs[0]) for _ in range(world)] if rank == 0 else None
     dist.gather(outs[0], gathered, dst=0)
     ok = True
