@@ -42,6 +42,10 @@ class EpArgs(C.Structure):
                                     "row_token")])
 
 
+class EpDma(C.Structure):
+    _fields_ = [(n, _vp) for n in ("xp_send", "y_owner", "y_home_peers", "row_token", "cnt_host", "counts_ready")]
+
+
 class EpBwdArgs(C.Structure):
     _fields_ = ([(n, _vp) for n in ("dout", "dy_peers", "dh", "dw", "dlogit_row", "dtheta_row", "dx", "d_w_router",
                                     "d_gate_up_proj", "d_down_proj", "d_theta")] + [("epoch_base", _i32)])
@@ -89,6 +93,8 @@ SIGNATURES = {
     "bibo_moe_ep_dispatch": (_i32, [_vp, _vp, _vp, _vp, _vp, _vp, _i64, _i32, _i32, _i32, _i32, _i32, _i64, _i32, _vp, _vp,
                                     _vp]),
     "bibo_moe_ep_forward": (_i32, [C.POINTER(EpArgs), _vp]),
+    "bibo_moe_ep_forward_dma": (_i32, [C.POINTER(EpArgs), C.POINTER(EpDma), _i32, _vp]),
+    "bibo_moe_ep_plan_layout": (_i32, [_vp, _i32, _i32, _i32, _i64, _i32, _vp, _vp]),
     "bibo_moe_ep_backward": (_i32, [C.POINTER(EpArgs), C.POINTER(EpBwdArgs), _vp]),
     "bibo_moe_ep_experts": (_i32, [_vp, _vp, _vp, _vp, _vp, _i32, _i32, _i32, _i32, _i64, _i32, _vp, _vp, _vp, _vp, _i32,
                                    _vp]),

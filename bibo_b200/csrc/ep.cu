@@ -24,7 +24,7 @@ namespace bibo {
 // One block, E threads.  Thread d < R scans destination d's layout.
 __global__ void __launch_bounds__(BIBO_MAX_EXPERTS)
 ep_plan_kernel(const int32_t* __restrict__ cnt_all, int rank, int world, int n_experts, int rows_cap_recv,
-               int32_t* __restrict__ plan) {
+               int source_major, int32_t* __restrict__ plan) {
   const int el = n_experts / world;
   int32_t* send_base = plan + ep_off_send_base();
   int32_t* recv_off = plan + ep_off_recv_off(n_experts);
@@ -41,13 +41,15 @@ ep_plan_kernel(const int32_t* __restrict__ cnt_all, int rank, int world, int n_e
   if (tid < world) {
     const int d = tid;
     int run = 0;
-    for (int le = 0; le < el; ++le)
-      for (int s = 0; s < world; ++s) {
-        const int c = cnt_all[s * n_experts + d * el + le];
-        if (s == rank) send_base[d * el + le] = run;
-        if (d == rank) { s_off[le * world + s] = run; s_cnt[le * world + s] = c; }
-        run += (c + BIBO_TILE_M - 1) / BIBO_TILE_M * BIBO_TILE_M;
-      }
+    // expert-major: groups (le, s) in the order le, s; source-major: in the order s, le, so that all rows
+    // from one source rank form one contiguous block (what a block copy between ranks needs)
+    for (int i = 0; i < n_experts; ++i) {
+      const int le = source_major ? i % el : i / world, s = source_major ? i / el : i % world;
+      const int c = cnt_all[s * n_experts + d * el + le];
+      if (s == rank) send_base[d * el + le] = run;
+      if (d == rank) { s_off[le * world + s] = run; s_cnt[le * world + s] = c; }
+      run += (c + BIBO_TILE_M - 1) / BIBO_TILE_M * BIBO_TILE_M;
+    }
     if (run > rows_cap_recv) s_over = 1;   // some rank's buffer would overflow: everyone learns it
     if (d == rank) s_off[n_experts] = run;
   }
@@ -67,9 +69,11 @@ ep_plan_kernel(const int32_t* __restrict__ cnt_all, int rank, int world, int n_e
   }
   __syncthreads();
   if (tid <= n_experts) recv_off[tid] = s_off[tid];
-  if (tid < el) {   // row range of local expert tid: its `world` groups are contiguous
-    plan[ep_off_le_off(n_experts) + tid] = s_off[tid * world];
-    plan[ep_off_le_span(n_experts) + tid] = over ? 0 : s_off[(tid + 1) * world] - s_off[tid * world];
+  if (tid < el) {   // row range of local expert tid: its `world` groups are contiguous (expert-major only)
+    const bool em = !source_major && !over;
+    plan[ep_off_le_off(n_experts) + tid] = source_major ? 0 : s_off[tid * world];
+    plan[ep_off_le_span(n_experts) + tid] =
+        em ? (tid + 1 < el ? s_off[(tid + 1) * world] : s_off[n_experts]) - s_off[tid * world] : 0;
     if (tid == el - 1) plan[ep_off_le_off(n_experts) + el] = s_off[n_experts];
   }
   if (tid < n_experts) {
@@ -228,6 +232,18 @@ ep_share_counts_kernel(const int32_t* __restrict__ counts, PeerPtrs cnt_peers, i
 
 __global__ void ep_barrier_kernel(PeerPtrs flags, int rank, int world, int epoch, int32_t* status);
 
+int ep_share_counts_launch(const int32_t* counts, void* const* cnt_peers, int rank, int world, int n_experts,
+                           cudaStream_t st) {
+  PeerPtrs cp = {};
+  for (int i = 0; i < world; ++i) {
+    if (!cnt_peers[i]) return fail(BIBO_ERR_ARG, "peer %d has no histogram buffer", i);
+    cp.p[i] = cnt_peers[i];
+  }
+  ep_share_counts_kernel<<<1, BIBO_MAX_EXPERTS, 0, st>>>(counts, cp, rank, world, n_experts);
+  BIBO_CHECK_LAUNCH("ep_share_counts_kernel");
+  return BIBO_OK;
+}
+
 // gemm_tc.cu
 int gemm1_tc_supported(int hidden, int inter, int dtype);
 int gemm1_tc_launch(const void* xp, const void* gate_up_proj, const float* theta, const PlanView& pv, int hidden,
@@ -286,16 +302,21 @@ extern "C" int64_t bibo_moe_ep_plan_off(int which, int n_experts) {
   }
 }
 
-extern "C" int bibo_moe_ep_plan(const int32_t* cnt_all, int rank, int world, int n_experts, int64_t rows_cap_recv,
-                                int32_t* ep_plan, void* stream) {
+extern "C" int bibo_moe_ep_plan_layout(const int32_t* cnt_all, int rank, int world, int n_experts,
+                                       int64_t rows_cap_recv, int source_major, int32_t* ep_plan, void* stream) {
   int rc = ep_check("ep_plan", world, rank, n_experts, rows_cap_recv);
   if (rc) return rc;
   if (!cnt_all || !ep_plan) return fail(BIBO_ERR_ARG, "ep_plan: null pointer");
   ep_set_carveouts();
-  ep_plan_kernel<<<1, BIBO_MAX_EXPERTS, 0, static_cast<cudaStream_t>(stream)>>>(cnt_all, rank, world, n_experts,
-                                                                               (int)rows_cap_recv, ep_plan);
+  ep_plan_kernel<<<1, BIBO_MAX_EXPERTS, 0, static_cast<cudaStream_t>(stream)>>>(
+      cnt_all, rank, world, n_experts, (int)rows_cap_recv, source_major != 0, ep_plan);
   BIBO_CHECK_LAUNCH("ep_plan_kernel");
   return BIBO_OK;
+}
+
+extern "C" int bibo_moe_ep_plan(const int32_t* cnt_all, int rank, int world, int n_experts, int64_t rows_cap_recv,
+                                int32_t* ep_plan, void* stream) {
+  return bibo_moe_ep_plan_layout(cnt_all, rank, world, n_experts, rows_cap_recv, 0, ep_plan, stream);
 }
 
 extern "C" int bibo_moe_ep_dispatch(const void* x, const int32_t* topk_idx, const int32_t* slot_rank,
@@ -437,14 +458,8 @@ extern "C" int bibo_moe_ep_forward(const bibo_moe_ep_args* a, void* stream) {
   if (rc) return rc;
   rc = bibo_moe_plan(a->block_counts, a->n_tokens, a->top_k, a->n_experts, a->n_experts, a->local_plan, stream);
   if (rc) return rc;
-  PeerPtrs cp = {};
-  for (int i = 0; i < a->world; ++i) {
-    if (!a->cnt_peers[i]) return fail(BIBO_ERR_ARG, "ep_forward: peer %d has no histogram buffer", i);
-    cp.p[i] = a->cnt_peers[i];
-  }
-  ep_share_counts_kernel<<<1, BIBO_MAX_EXPERTS, 0, st>>>(a->local_plan + plan_off_counts(), cp, a->rank, a->world,
-                                                         a->n_experts);
-  BIBO_CHECK_LAUNCH("ep_share_counts_kernel");
+  rc = ep_share_counts_launch(a->local_plan + plan_off_counts(), a->cnt_peers, a->rank, a->world, a->n_experts, st);
+  if (rc) return rc;
   rc = bibo_moe_ep_barrier(a->flags_peers, a->rank, a->world, a->epoch_base + 1, status, stream);
   if (rc) return rc;
   rc = bibo_moe_ep_plan(static_cast<const int32_t*>(a->cnt_peers[a->rank]), a->rank, a->world, a->n_experts,

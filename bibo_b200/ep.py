@@ -25,8 +25,9 @@ from . import functional as Fn
 TILE_M = _lib.TILE_M
 
 
-def ep_layout(cnt_all: torch.Tensor, rank: int, world: int):
+def ep_layout(cnt_all: torch.Tensor, rank: int, world: int, source_major: bool = False):
     """Host mirror of ``ep_plan_kernel`` (used to size buffers and to check the kernel).
+    ``source_major``: groups in the order (source, local expert) instead of (local expert, source).
 
     cnt_all [world, E] = tokens-per-expert histogram of every rank.  Returns a dict with
     ``send_base [E]`` (row in the owner's receive buffer where THIS rank's rows of expert e start),
@@ -42,14 +43,15 @@ def ep_layout(cnt_all: torch.Tensor, rank: int, world: int):
     recv_cnt = torch.zeros(n_exp, dtype=torch.int64)
     for d in range(world):
         run = 0
-        for le in range(el):
-            for s in range(world):
-                if s == rank:
-                    send_base[d * el + le] = run
-                if d == rank:
-                    recv_off[le * world + s] = run
-                    recv_cnt[le * world + s] = cnt[s, d * el + le]
-                run += int(pad[s, d * el + le])
+        order = [(le, s) for s in range(world) for le in range(el)] if source_major else \
+                [(le, s) for le in range(el) for s in range(world)]
+        for le, s in order:
+            if s == rank:
+                send_base[d * el + le] = run
+            if d == rank:
+                recv_off[le * world + s] = run
+                recv_cnt[le * world + s] = cnt[s, d * el + le]
+            run += int(pad[s, d * el + le])
         rows[d] = run
         if d == rank:
             recv_off[n_exp] = run
@@ -86,12 +88,16 @@ class ExpertParallelMoE:
     """
 
     def __init__(self, weights, top_k: int, group=None, n_tokens: Optional[int] = None, norm_mode="sum",
-                 scale: float = 1.0, capacity_factor: float = 2.0, max_ctas: int = 0, comm_ctas: int = 0):
+                 scale: float = 1.0, capacity_factor: float = 2.0, max_ctas: int = 0, comm_ctas: int = 0,
+                 dma: bool = False):
         os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")   # plain peer loads/stores only
         self.group = group if group is not None else dist.group.WORLD
         self.rank, self.world = dist.get_rank(self.group), dist.get_world_size(self.group)
         self.top_k, self.norm_mode, self.scale = top_k, norm_mode, scale
         self.capacity_factor, self.max_ctas, self.comm_ctas = capacity_factor, max_ctas, comm_ctas
+        # dma: rows travel by asynchronous peer copies (copy engines) instead of the dispatch / combine
+        # kernels (bibo_moe_ep_forward_dma); inference forward only, training calls use the kernels
+        self.dma = bool(dma)
         w_r = weights["w_router"]
         self.device = w_r.device
         self.n_experts, self.hidden = w_r.shape
@@ -131,6 +137,14 @@ class ExpertParallelMoE:
         self.h = torch.empty(self.cap, self.inter, dtype=torch.bfloat16, device=dev)
         self.xp = _Symmetric((self.cap, self.hidden), torch.bfloat16, dev, self.group)
         self.y = _Symmetric((self.cap, self.hidden), torch.bfloat16, dev, self.group)
+        if self.dma:
+            self.xp_send = torch.empty(geo.rows_cap, self.hidden, dtype=torch.bfloat16, device=dev)
+            self.y_owner = torch.empty(self.cap, self.hidden, dtype=torch.bfloat16, device=dev)
+            self.y_home = _Symmetric((geo.rows_cap, self.hidden), torch.bfloat16, dev, self.group)
+            self.row_token_dma = torch.empty(geo.rows_cap, **i32)
+            self.cnt_host = torch.zeros(self.world * e, dtype=torch.int32).pin_memory()
+            self.counts_ready = torch.cuda.Event()
+            self.counts_ready.record()          # creates the underlying event
         self.flags = _Symmetric((64,), torch.int32, dev, self.group)
         self.flags.tensor.zero_()
         torch.cuda.synchronize(dev)
@@ -145,7 +159,10 @@ class ExpertParallelMoE:
                                                    _lib.ptr(self.ep_plan[2:]), st), "bibo_moe_ep_barrier")
 
     # ---- forward ----------------------------------------------------------------------------------------
-    def forward(self, x: torch.Tensor, out: Optional[torch.Tensor] = None, training: bool = False) -> torch.Tensor:
+    def forward(self, x: torch.Tensor, out: Optional[torch.Tensor] = None, training: bool = False,
+                phase: int = 0) -> torch.Tensor:
+        """``phase`` (copy-engine path only): 1 = issue the part before the host reads the histogram table
+        and return; ``finish()`` issues the rest."""
         lib, p = _lib.load(), _lib.ptr
         n, hidden = x.shape
         if self._n != n:
@@ -154,8 +171,8 @@ class ExpertParallelMoE:
         if out is None:
             out = torch.empty_like(x)
         k, e, st = self.top_k, self.n_experts, torch.cuda.current_stream(self.device).cuda_stream
-        if training or not getattr(self, "profile", False):
-            return self._forward_one_call(x, out, st, training)
+        if training or self.dma or not getattr(self, "profile", False):
+            return self._forward_one_call(x, out, st, training, phase if self.dma and not training else 0)
         ev = self._mark
         ev("start")
         _lib.check(lib.bibo_moe_router_fwd(p(x), p(self.w_router), p(self.bias), None, n, hidden, e, k,
@@ -222,7 +239,13 @@ class ExpertParallelMoE:
         self._last_args = None
         return dx, d_wr, d_gu, d_dn, d_th
 
-    def _forward_one_call(self, x: torch.Tensor, out: torch.Tensor, st: int, training: bool = False) -> torch.Tensor:
+    def finish(self) -> None:
+        """Second half of a ``forward(..., phase=1)`` of the copy-engine path (same stream)."""
+        a, d, st = self._dma_call
+        _lib.check(_lib.load().bibo_moe_ep_forward_dma(C.byref(a), C.byref(d), 2, st), "bibo_moe_ep_forward_dma")
+
+    def _forward_one_call(self, x: torch.Tensor, out: torch.Tensor, st: int, training: bool = False,
+                          phase: int = 0) -> torch.Tensor:
         """The product path: bibo_moe_ep_forward (histograms exchanged through peer memory, no library
         collective)."""
         if training and not getattr(self, "_train_ready", False):
@@ -240,6 +263,14 @@ class ExpertParallelMoE:
             p(self.gate_up_recv) if training else None, p(self.rnorm_recv) if training else None,
             p(self.row_token) if training else None)
         self._epoch += 3
+        if self.dma and not training:
+            d = _lib.EpDma(p(self.xp_send), p(self.y_owner), cast(self.y_home.ptr_array), p(self.row_token_dma),
+                           p(self.cnt_host), self.counts_ready.cuda_event)
+            self._dma_call = (a, d, st)
+            if phase != 2:
+                _lib.check(_lib.load().bibo_moe_ep_forward_dma(C.byref(a), C.byref(d), phase, st),
+                           "bibo_moe_ep_forward_dma")
+            return out
         _lib.check(_lib.load().bibo_moe_ep_forward(C.byref(a), st), "bibo_moe_ep_forward")
         self._last_args, self._last_x = (a, x) if training else (None, None)
         return out
@@ -278,8 +309,9 @@ class PipelinedExpertParallelMoE:
         self.chunks = max(1, int(chunks))
         dev = weights["w_router"].device
         sms = torch.cuda.get_device_properties(dev).multi_processor_count
-        max_ctas = max(8, sms - comm_sms) if self.chunks > 1 else 0
-        comm_ctas = comm_sms * 4 if self.chunks > 1 else 0      # 4 resident 8-warp blocks per exchange SM
+        sm_exchange = self.chunks > 1 and not kw.get("dma", False)   # copy-engine exchange needs no SMs
+        max_ctas = max(8, sms - comm_sms) if sm_exchange else 0
+        comm_ctas = comm_sms * 4 if sm_exchange else 0          # 4 resident 8-warp blocks per exchange SM
         self.lanes = [ExpertParallelMoE(weights, top_k, group, max_ctas=max_ctas, comm_ctas=comm_ctas, **kw)
                       for _ in range(self.chunks)]
         self.streams = [torch.cuda.Stream(device=dev) for _ in range(self.chunks)]
@@ -300,16 +332,32 @@ class PipelinedExpertParallelMoE:
         cur = torch.cuda.current_stream(self.device)
         start = torch.cuda.Event()
         start.record(cur)
-        for lane, st, (lo, hi) in zip(self.lanes, self.streams, self._bounds(x.shape[0])):
-            if hi <= lo:
-                continue
+        self._run_lanes(lambda lo, hi: (x[lo:hi], out[lo:hi]), x.shape[0], start, None)
+        for st in self.streams:
+            cur.wait_stream(st)
+        return out
+
+    def _run_lanes(self, views, n: int, start, after) -> None:
+        """Issue every slice on its stream.  Copy-engine lanes are issued in two passes (everything up to
+        the host's read of the histogram table for all slices, then the rest), so that no slice's router
+        waits behind another slice's host round trip.  ``after(lane_index, lo, hi)`` runs on the slice's
+        stream once its forward is issued."""
+        work = [(i, lane, st, lo, hi) for i, (lane, st, (lo, hi)) in
+                enumerate(zip(self.lanes, self.streams, self._bounds(n))) if hi > lo]
+        two_pass = all(lane.dma for lane in self.lanes)
+        for i, lane, st, lo, hi in work:
             st.wait_event(start)
             with torch.cuda.stream(st):
-                lane.forward(x[lo:hi], out[lo:hi])
-            done = torch.cuda.Event()
-            done.record(st)
-            cur.wait_event(done)
-        return out
+                xs, os_ = views(lo, hi)
+                lane.forward(xs, os_, phase=1 if two_pass else 0)
+                if not two_pass and after is not None:
+                    after(i, lo, hi)
+        if two_pass:
+            for i, lane, st, lo, hi in work:
+                with torch.cuda.stream(st):
+                    lane.finish()
+                    if after is not None:
+                        after(i, lo, hi)
 
     def forward_host(self, x_host: torch.Tensor, out_host: torch.Tensor, x_dev: torch.Tensor,
                      out_dev: torch.Tensor) -> torch.Tensor:
@@ -319,16 +367,20 @@ class PipelinedExpertParallelMoE:
         cur = torch.cuda.current_stream(self.device)
         start = torch.cuda.Event()
         start.record(cur)
-        streams = self.streams if self.chunks > 1 else [cur]
-        for lane, st, (lo, hi) in zip(self.lanes, streams, self._bounds(x_host.shape[0])):
-            if hi <= lo:
-                continue
-            st.wait_event(start)
-            with torch.cuda.stream(st):
-                x_dev[lo:hi].copy_(x_host[lo:hi], non_blocking=True)
-                lane.forward(x_dev[lo:hi], out_dev[lo:hi])
-                out_host[lo:hi].copy_(out_dev[lo:hi], non_blocking=True)
-        for st in streams:
+        if self.chunks == 1:
+            x_dev.copy_(x_host, non_blocking=True)
+            self.lanes[0].forward(x_dev, out_dev)
+            out_host.copy_(out_dev, non_blocking=True)
+            cur.synchronize()
+            return out_host
+
+        def views(lo, hi):
+            x_dev[lo:hi].copy_(x_host[lo:hi], non_blocking=True)      # on the slice's stream, before its router
+            return x_dev[lo:hi], out_dev[lo:hi]
+
+        self._run_lanes(views, x_host.shape[0], start,
+                        lambda i, lo, hi: out_host[lo:hi].copy_(out_dev[lo:hi], non_blocking=True))
+        for st in self.streams:
             st.synchronize()
         return out_host
 

@@ -238,6 +238,11 @@ int64_t bibo_moe_ep_plan_words(int n_experts, int64_t rows_cap_recv);
 int64_t bibo_moe_ep_plan_off(int which, int n_experts);
 int bibo_moe_ep_plan(const int32_t* cnt_all, int rank, int world, int n_experts, int64_t rows_cap_recv,
                      int32_t* ep_plan, void* stream);
+/* source_major != 0: the receive buffer holds all rows of source rank 0, then of source 1, ... (groups
+ * in the order s, le instead of le, s), so the rows exchanged between two ranks are one contiguous
+ * range on both sides (bibo_moe_ep_forward_dma); per-expert row ranges then do not exist.          */
+int bibo_moe_ep_plan_layout(const int32_t* cnt_all, int rank, int world, int n_experts,
+                            int64_t rows_cap_recv, int source_major, int32_t* ep_plan, void* stream);
 int bibo_moe_ep_dispatch(const void* x, const int32_t* topk_idx, const int32_t* slot_rank,
                          const int32_t* local_plan, const int32_t* ep_plan, void* const* xp_peers,
                          int64_t n_tokens, int hidden, int n_experts, int rank, int world, int top_k,
@@ -282,6 +287,27 @@ typedef struct {
   void* gate_up_recv; float* rnorm_recv; int32_t* row_token;
 } bibo_moe_ep_args;
 int bibo_moe_ep_forward(const bibo_moe_ep_args* args, void* stream);
+
+/* The same forward with the two exchange steps done by asynchronous peer copies (copy engines)
+ * instead of SM kernels, so that token slices on different streams overlap their exchange with each
+ * other's GEMMs without sharing SMs.  The home rank sorts its rows by expert into xp_send (the
+ * single-GPU permute); the rows for owner o are then one range, copied into o's receive buffer
+ * (source-major layout); results come back the same way into the home rank's y_home buffer, in its
+ * own expert-sorted layout, and the single-GPU combine finishes.  The copy sizes depend on the
+ * routing: the call reads the histogram table on the host (cnt_host, pinned int32 [world*E]) and
+ * therefore synchronises with `stream` once, after the router.  args->y_peers, comm_ctas and the
+ * training fields are not used; inference only.  Epochs as in bibo_moe_ep_forward.                 */
+typedef struct {
+  void* xp_send;               /* local [N*k + E*127 rounded, H]: this rank's rows sorted by expert      */
+  void* y_owner;               /* local [rows_cap_recv, H]: results of this rank's experts                */
+  void* const* y_home_peers;   /* y_home_peers[r] = rank r's [N*k + E*127 rounded, H] buffer, peer-mapped  */
+  int32_t* row_token;          /* local [N*k + E*127 rounded] scratch                                       */
+  int32_t* cnt_host;           /* pinned host int32 [world*E]                                               */
+  void* counts_ready;          /* a cudaEvent_t of the caller, one per token slice                          */
+} bibo_moe_ep_dma;
+/* phase 0 = the whole forward; 1 = up to the point where the host must read the table; 2 = the rest
+ * (a caller with several token slices issues phase 1 of all slices, then phase 2 of each).          */
+int bibo_moe_ep_forward_dma(const bibo_moe_ep_args* args, const bibo_moe_ep_dma* dma, int phase, void* stream);
 
 /* Backward of bibo_moe_ep_forward (bf16, shapes of the tensor-core backward kernels).  `fwd` is the
  * argument block of the matching forward, run with gate_up_recv / rnorm_recv / row_token set; its

@@ -47,6 +47,21 @@ def main():
     piped.forward_host(x_host, out_host, torch.empty_like(x_local), torch.empty_like(x_local))
     assert piped.status() == 0, f"rank {rank}: sliced status {piped.status()}"
     assert torch.equal(out_host, outs[0].cpu()), "sliced host-buffer forward differs from the device forward"
+    # exchange on the copy engines (block copies between ranks), single slice and three slices
+    cf = float(os.environ.get("EP_CF", "2.0"))
+    dma = ep.ExpertParallelMoE(weights, k, dist.group.WORLD, capacity_factor=cf, dma=True)
+    for _ in range(2):
+        o = dma.forward(x_local)
+        torch.cuda.synchronize()
+        assert dma.status() == 0, f"rank {rank}: copy-engine status {dma.status()}"
+        assert torch.equal(o, outs[0]), "copy-engine exchange differs from the kernel exchange"
+    dma3 = ep.PipelinedExpertParallelMoE(weights, k, dist.group.WORLD, chunks=3, capacity_factor=cf, dma=True)
+    o = dma3.forward(x_local)
+    torch.cuda.synchronize()
+    assert dma3.status() == 0 and torch.equal(o, outs[0]), "sliced copy-engine forward differs"
+    out_host.zero_()
+    dma3.forward_host(x_host, out_host, torch.empty_like(x_local), torch.empty_like(x_local))
+    assert torch.equal(out_host, outs[0].cpu()), "sliced copy-engine host-buffer forward differs"
     gathered = [torch.empty_like(outs[0]) for _ in range(world)] if rank == 0 else None
     dist.gather(outs[0], gathered, dst=0)
     ok = True

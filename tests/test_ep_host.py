@@ -57,3 +57,30 @@ def test_ep_layout_matches_hand_example():
     assert l1["recv_off"].tolist() == [0, 128, 128, 256, 256]
     assert l0["send_base"].tolist() == [0, 384, 0, 128] and l1["send_base"].tolist() == [256, 384, 128, 256]
     assert l0["rows"].tolist() == [768, 256]
+
+
+def test_source_major_layout_makes_each_exchange_one_block():
+    """Copy-engine exchange: owner d's buffer holds all rows of source 0, then source 1, ...; the rows
+    of one (source, owner) pair are one contiguous, tile-aligned range, in the source's own expert
+    order, so one peer copy moves them in either direction."""
+    from bibo_b200.ep import ep_layout
+    cnt = torch.tensor([[130, 0, 5, 128], [1, 300, 0, 0]], dtype=torch.int32)   # 2 ranks, 4 experts
+    l0, l1 = ep_layout(cnt, 0, 2, source_major=True), ep_layout(cnt, 1, 2, source_major=True)
+    # rank 0 owns experts 0,1: from s0: e0 130->256, e1 0 | from s1: e0 1->128, e1 300->384
+    assert l0["recv_off"].tolist() == [0, 256, 256, 384, 768]          # index g = le*2 + s
+    assert l0["recv_cnt"].tolist() == [130, 1, 0, 300]
+    assert l0["send_base"].tolist() == [0, 256, 0, 128] and l1["send_base"].tolist() == [256, 384, 256, 256]
+    g = torch.Generator().manual_seed(5)
+    world, n_exp = 4, 64
+    el = n_exp // world
+    cnt_all = torch.randint(0, 500, (world, n_exp), generator=g, dtype=torch.int32)
+    pad = (cnt_all.long() + 127) // 128 * 128
+    lays = [ep_layout(cnt_all, r, world, source_major=True) for r in range(world)]
+    for d in range(world):
+        run = 0
+        for s in range(world):
+            for le in range(el):
+                assert int(lays[d]["recv_off"][le * world + s]) == run
+                assert int(lays[s]["send_base"][d * el + le]) == run
+                run += int(pad[s, d * el + le])
+        assert int(lays[d]["rows"][d]) == run
