@@ -168,7 +168,8 @@ def workload_config(args, wl, world):
                         f"{N_EXPERTS} experts, top-{TOP_K}, intermediate {wl['inter']}, router bias {wl['bias']}"
                         + (f" (alpha {wl['zipf_alpha']})" if wl["bias"] == "zipf" else ""),
             "tokens_per_gpu": wl["n_tokens"], "global_tokens": wl["n_tokens"] * world,
-            "parallelism": "single GPU" if world == 1 else f"expert-parallel ep{world} (tokens data-parallel)",
+            "parallelism": "single GPU" if world == 1 else
+            f"expert-parallel ep{world} (tokens data-parallel), exchange by {args.ep_exchange}, {args.ep_chunks} token slice(s)",
             "l2": "per-step working set (activations + expert weights + intermediates) exceeds the 126 MB L2"}
 
 
@@ -181,6 +182,9 @@ def main():
     ap.add_argument("--workload", default="c4", choices=sorted(WORKLOADS))
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--ep-chunks", type=int, default=1, help="token slices pipelined on separate streams (N>1)")
+    ap.add_argument("--ep-exchange", default="kernel", choices=["copy", "kernel"],
+                    help="N>1: rows travel by peer copies on the copy engines, or by the dispatch/combine kernels")
+    ap.add_argument("--copy-streams", type=int, default=0, help="copy exchange: 1 = one stream per peer, 0 = one stream")
     ap.add_argument("--e2e-chunks", type=int, default=4, help="token slices of the host-buffer (e2e) forward (N>1)")
     ap.add_argument("--comm-sms", type=int, default=20, help="SMs left to the exchange kernels (N>1)")
     ap.add_argument("--mode", default="fwd", choices=["fwd", "fwdbwd"],
@@ -206,8 +210,9 @@ def main():
 
     if world > 1:
         from bibo_b200 import ep
+        dma = args.ep_exchange == "copy" and args.mode == "fwd"
         runner = ep.PipelinedExpertParallelMoE(t, TOP_K, dist.group.WORLD, n_tokens=wl["n_tokens"], chunks=args.ep_chunks,
-                                               comm_sms=args.comm_sms)
+                                               comm_sms=args.comm_sms, dma=dma, copy_streams=bool(args.copy_streams))
         step = lambda: runner.forward(t["x"])
         ws = None
         if args.mode == "fwdbwd":
@@ -276,7 +281,7 @@ def main():
     if world > 1:
         # token slices on separate streams: the copies of one slice run under the kernels of another
         e2e_runner = runner if args.e2e_chunks == args.ep_chunks else ep.PipelinedExpertParallelMoE(
-            t, TOP_K, dist.group.WORLD, n_tokens=wl["n_tokens"], chunks=args.e2e_chunks, comm_sms=args.comm_sms)
+            t, TOP_K, dist.group.WORLD, n_tokens=wl["n_tokens"], chunks=args.e2e_chunks, comm_sms=args.comm_sms, dma=dma, copy_streams=bool(args.copy_streams))
         e2e_step = lambda: e2e_runner.forward_host(x_host, out_host, x_dev, out_dev)
     else:
         if ws is not None:
@@ -299,11 +304,11 @@ def main():
     if world > 1 and args.mode == "fwd":      # one extra profiled step: when each phase of each token slice ended (ms from step start)
         for lane in runner.lanes:
             lane.profile = True
-        t_start = torch.cuda.Event(enable_timing=True)
         barrier()
-        t_start.record()
         step()
+        step()                                # the marks of the second of two back-to-back steps survive
         barrier()
+        t_start = min((lane.marks[0][1] for lane in runner.lanes), key=lambda ev: runner.lanes[0].marks[0][1].elapsed_time(ev))
         ep_phases = [{n: round(t_start.elapsed_time(ev), 3) for n, ev in lane.marks} for lane in runner.lanes]
         for lane in runner.lanes:
             lane.profile = False

@@ -43,7 +43,8 @@ class EpArgs(C.Structure):
 
 
 class EpDma(C.Structure):
-    _fields_ = [(n, _vp) for n in ("xp_send", "y_owner", "y_home_peers", "row_token", "cnt_host", "counts_ready")]
+    _fields_ = ([(n, _vp) for n in ("xp_send", "y_owner", "y_home_peers", "row_token", "cnt_host", "counts_ready")] +
+                [("n_aux", _i32)] + [(n, _vp) for n in ("aux_streams", "aux_events", "marks")])
 
 
 class EpBwdArgs(C.Structure):

@@ -55,12 +55,16 @@ ep_plan_kernel(const int32_t* __restrict__ cnt_all, int rank, int world, int n_e
   }
   __syncthreads();
   const bool over = s_over != 0;
+  // tiles of one local expert are paired across its source groups (two tiles of a pair only have to
+  // share the expert), so at most one pair per expert is left with a single tile
   if (tid == 0) {
     const int rows = over ? 0 : s_off[n_experts];
     int pacc = 0;
-    for (int g = 0; g < n_experts; ++g) {
-      s_pair_off[g] = pacc;
-      pacc += ((s_cnt[g] + BIBO_TILE_M - 1) / BIBO_TILE_M + 1) / 2;
+    for (int le = 0; le < el; ++le) {
+      int nt = 0;
+      for (int s = 0; s < world; ++s) nt += (s_cnt[le * world + s] + BIBO_TILE_M - 1) / BIBO_TILE_M;
+      s_pair_off[le] = pacc;
+      pacc += (nt + 1) / 2;
     }
     plan[PLAN_N_TILES] = rows / BIBO_TILE_M;
     plan[PLAN_ROWS_USED] = rows;
@@ -81,11 +85,21 @@ ep_plan_kernel(const int32_t* __restrict__ cnt_all, int rank, int world, int n_e
     if (!over) {
       const int row0 = s_off[tid], cnt = s_cnt[tid], le = tid / world, src = tid % world;
       const int t0 = row0 / BIBO_TILE_M, nt = (cnt + BIBO_TILE_M - 1) / BIBO_TILE_M;
-      for (int i = 0; i < nt; ++i) {
+      for (int i = 0; i < nt; ++i)
         tiles[t0 + i] = make_int4(le, row0 + i * BIBO_TILE_M, min(BIBO_TILE_M, cnt - i * BIBO_TILE_M), src);
-        if ((i & 1) == 0) pairs[s_pair_off[tid] + i / 2] = make_int2(t0 + i, i + 1 < nt ? t0 + i + 1 : -1);
+    }
+  }
+  if (tid < el && !over) {
+    int idx = 0, prev = -1;
+    for (int s = 0; s < world; ++s) {
+      const int g = tid * world + s;
+      const int t0 = s_off[g] / BIBO_TILE_M, nt = (s_cnt[g] + BIBO_TILE_M - 1) / BIBO_TILE_M;
+      for (int i = 0; i < nt; ++i, ++idx) {
+        if (idx & 1) pairs[s_pair_off[tid] + idx / 2] = make_int2(prev, t0 + i);
+        else prev = t0 + i;
       }
     }
+    if (idx & 1) pairs[s_pair_off[tid] + idx / 2] = make_int2(prev, -1);
   }
 }
 

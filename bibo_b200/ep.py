@@ -89,7 +89,7 @@ class ExpertParallelMoE:
 
     def __init__(self, weights, top_k: int, group=None, n_tokens: Optional[int] = None, norm_mode="sum",
                  scale: float = 1.0, capacity_factor: float = 2.0, max_ctas: int = 0, comm_ctas: int = 0,
-                 dma: bool = False):
+                 dma: bool = False, copy_streams: bool = False):
         os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")   # plain peer loads/stores only
         self.group = group if group is not None else dist.group.WORLD
         self.rank, self.world = dist.get_rank(self.group), dist.get_world_size(self.group)
@@ -98,6 +98,7 @@ class ExpertParallelMoE:
         # dma: rows travel by asynchronous peer copies (copy engines) instead of the dispatch / combine
         # kernels (bibo_moe_ep_forward_dma); inference forward only, training calls use the kernels
         self.dma = bool(dma)
+        self.copy_streams = bool(copy_streams)     # copies to different peers on separate streams (concurrent)
         w_r = weights["w_router"]
         self.device = w_r.device
         self.n_experts, self.hidden = w_r.shape
@@ -145,6 +146,13 @@ class ExpertParallelMoE:
             self.cnt_host = torch.zeros(self.world * e, dtype=torch.int32).pin_memory()
             self.counts_ready = torch.cuda.Event()
             self.counts_ready.record()          # creates the underlying event
+            n_aux = min(self.world, 8) if self.copy_streams else 0
+            self._aux_streams = [torch.cuda.Stream(device=dev) for _ in range(n_aux)]
+            self._aux_events = [torch.cuda.Event() for _ in range(18)]
+            for ev in self._aux_events:
+                ev.record()
+            self._aux_stream_ptrs = (C.c_void_p * max(n_aux, 1))(*[s_.cuda_stream for s_ in self._aux_streams])
+            self._aux_event_ptrs = (C.c_void_p * 18)(*[ev.cuda_event for ev in self._aux_events])
         self.flags = _Symmetric((64,), torch.int32, dev, self.group)
         self.flags.tensor.zero_()
         torch.cuda.synchronize(dev)
@@ -239,6 +247,19 @@ class ExpertParallelMoE:
         self._last_args = None
         return dx, d_wr, d_gu, d_dn, d_th
 
+    DMA_MARKS = ("start", "histograms", "sorted", "sent", "received", "experts", "returned", "all_returned", "combine")
+
+    def _mark_array(self):
+        """profile=True: nine timing events the copy-engine forward records (see ``marks``)."""
+        if not getattr(self, "profile", False):
+            return None
+        evs = [torch.cuda.Event(enable_timing=True) for _ in self.DMA_MARKS]
+        for e in evs:
+            e.record()                           # creates the underlying events
+        self.marks = list(zip(self.DMA_MARKS, evs))
+        self._mark_ptrs = (C.c_void_p * len(evs))(*[e.cuda_event for e in evs])
+        return C.cast(self._mark_ptrs, C.c_void_p)
+
     def finish(self) -> None:
         """Second half of a ``forward(..., phase=1)`` of the copy-engine path (same stream)."""
         a, d, st = self._dma_call
@@ -265,7 +286,9 @@ class ExpertParallelMoE:
         self._epoch += 3
         if self.dma and not training:
             d = _lib.EpDma(p(self.xp_send), p(self.y_owner), cast(self.y_home.ptr_array), p(self.row_token_dma),
-                           p(self.cnt_host), self.counts_ready.cuda_event)
+                           p(self.cnt_host), self.counts_ready.cuda_event, len(self._aux_streams),
+                           C.cast(self._aux_stream_ptrs, C.c_void_p), C.cast(self._aux_event_ptrs, C.c_void_p),
+                           self._mark_array())
             self._dma_call = (a, d, st)
             if phase != 2:
                 _lib.check(_lib.load().bibo_moe_ep_forward_dma(C.byref(a), C.byref(d), phase, st),

@@ -304,6 +304,13 @@ typedef struct {
   int32_t* row_token;          /* local [N*k + E*127 rounded] scratch                                       */
   int32_t* cnt_host;           /* pinned host int32 [world*E]                                               */
   void* counts_ready;          /* a cudaEvent_t of the caller, one per token slice                          */
+  int n_aux;                   /* 0, or the number of auxiliary streams (at most 8)                         */
+  void* const* aux_streams;    /* n_aux cudaStream_t of this token slice: the copies to different peers run on
+                                  them at the same time (forked from and joined into `stream`)              */
+  void* const* aux_events;     /* 18 cudaEvent_t (timing disabled) used for that fork / join                */
+  void* const* marks;          /* NULL, or 9 cudaEvent_t recorded on the stream: start, histograms exchanged,
+                                  rows sorted, rows sent, all rows received, experts done, results sent, all
+                                  results received, combined                                                 */
 } bibo_moe_ep_dma;
 /* phase 0 = the whole forward; 1 = up to the point where the host must read the table; 2 = the rest
  * (a caller with several token slices issues phase 1 of all slices, then phase 2 of each).          */
