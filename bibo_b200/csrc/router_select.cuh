@@ -37,22 +37,35 @@ __device__ __forceinline__ void select_and_rank(
   const bool active = tid < rows;
   if (active) {
     float* row = lg + tid * ld;
-    for (int e = 0; e < n_experts; ++e) row[e] = sigmoid_accurate(row[e]);
+    // One pass over the experts keeps the BIBO_MAX_TOP_K best (key, index) pairs in registers, ordered by
+    // key descending and, among equal keys, index ascending (a later expert never displaces an equal
+    // key: strict '>'), which is the order k successive arg-max passes would produce; the first top_k
+    // entries are the selection.
+    float best_v[BIBO_MAX_TOP_K], best_s[BIBO_MAX_TOP_K];
+    int best_i[BIBO_MAX_TOP_K];
+#pragma unroll
+    for (int j = 0; j < BIBO_MAX_TOP_K; ++j) { best_v[j] = -INFINITY; best_s[j] = 0.f; best_i[j] = -1; }
+    for (int e = 0; e < n_experts; ++e) {
+      const float s = sigmoid_accurate(row[e]);
+      row[e] = s;
+      const float v = s + bias_s[e];
+      if (v > best_v[BIBO_MAX_TOP_K - 1] || best_i[BIBO_MAX_TOP_K - 1] < 0) {
+        // shift down every entry that v beats (strictly, or an empty slot), then drop v into the gap
+#pragma unroll
+        for (int j = BIBO_MAX_TOP_K - 1; j >= 0; --j) {
+          const bool beats = v > best_v[j] || best_i[j] < 0;
+          const bool beats_prev = j > 0 && (v > best_v[j - 1] || best_i[j - 1] < 0);
+          if (beats) {
+            if (beats_prev) { best_v[j] = best_v[j - 1]; best_s[j] = best_s[j - 1]; best_i[j] = best_i[j - 1]; }
+            else { best_v[j] = v; best_s[j] = s; best_i[j] = e; }
+          }
+        }
+      }
+    }
 #pragma unroll
     for (int j = 0; j < BIBO_MAX_TOP_K; ++j) {
-      if (j < top_k) {
-        float best = -INFINITY;
-        int bi = -1;
-        for (int e = 0; e < n_experts; ++e) {
-          float s = row[e];
-          float v = s + bias_s[e];
-          // taken entries hold -inf; strict '>' keeps the lowest index among equal keys
-          if (s != -INFINITY && (bi < 0 || v > best)) { best = v; bi = e; }
-        }
-        sel_idx[j] = bi;
-        sel_s[j] = row[bi];
-        row[bi] = -INFINITY;
-      }
+      sel_idx[j] = best_i[j];
+      sel_s[j] = best_s[j];
     }
     // ascending expert index (insertion sort, k <= 8)
 #pragma unroll

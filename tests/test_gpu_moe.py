@@ -138,6 +138,36 @@ def test_host_buffer_call_equals_device_call(n):
         assert torch.equal(out_host, ref.cpu())
 
 
+def test_forward_is_cuda_graph_capturable():
+    """The single-GPU forward makes no host synchronisation and allocates nothing: after one warm-up
+    call it can be captured in a CUDA graph and replayed on new inputs."""
+    from bibo_b200 import functional as Fn
+    n, h, i, k = 3000, 1024, 512, 6
+    inp = orc.make_inputs(n, h, i, 64, seed=4, bias_mode="uniform", theta_std=0.5)
+    t = {kk: v.to(DEV) for kk, v in inp.items()}
+    for kk in ("x", "w_router", "gate_up_proj", "down_proj"):
+        t[kk] = t[kk].to(torch.bfloat16).contiguous()
+    args = (t["w_router"], t["bias"], t["gate_up_proj"], t["down_proj"], t["radial_theta"], k)
+    geo = Fn.Geometry(n, h, i, 64, 64, 0, k, torch.bfloat16)
+    ws = Fn.get_workspace(geo, t["x"].device, fresh=True)
+    x_static, out_static = t["x"].clone(), torch.empty_like(t["x"])
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+        Fn.moe_forward(x_static, *args, ws=ws, out=out_static)          # warm-up: attributes, tensor maps
+    torch.cuda.current_stream().wait_stream(side)
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        Fn.moe_forward(x_static, *args, ws=ws, out=out_static)
+    for seed in (1, 2):
+        x_new = torch.randn(n, h, generator=torch.Generator().manual_seed(seed)).to(torch.bfloat16).to(DEV)
+        x_static.copy_(x_new)
+        graph.replay()
+        torch.cuda.synchronize()
+        eager, _ = Fn.moe_forward(x_new, *args, ws=Fn.get_workspace(geo, t["x"].device, fresh=True))
+        assert torch.equal(out_static, eager)
+
+
 def test_forward_is_deterministic():
     inp = orc.make_inputs(1500, 256, 128, 64, seed=4, bias_mode="uniform", theta_std=0.5)
     a, _ = _run(inp, dtype=torch.bfloat16, top_k=6)
