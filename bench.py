@@ -340,12 +340,14 @@ def main():
             stages[nm] = {"ms": round(ms[nm], 4), "bound": "tensor" if tensor else "hbm", "achieved": round(ach, 2),
                           "unit": "TFLOP/s" if tensor else "GB/s", "frac": round(ach / peak, 4) if nm != "plan" else None}
         top = max(names, key=lambda nm: ms[nm])
-        ncu_traffic = {"gemm1_radial": None, "gemm2": None}
+        # DRAM bytes per launch of the c4 workload from ncu (dram__bytes_read.sum + dram__bytes_write.sum),
+        # profiles/c4_forward_gemm1_global_exchange.md; other workloads were not captured
+        ncu_traffic = {"gemm1_radial": 1.307e9, "gemm2": 1.110e9} if args.workload == "c4" else {}
         roof = {"kernel": top, "bound": stages[top]["bound"], "achieved": stages[top]["achieved"],
                 "peak": pk["tf"] if stages[top]["bound"] == "tensor" else pk["hbm"], "unit": stages[top]["unit"],
                 "frac": stages[top]["frac"], "traffic": ncu_traffic.get(top),
                 "peak_source": f"of {pk['src']} (burst figure)", "ms_per_launch": stages[top]["ms"]}
-    layer_flops = 36.0 * n * h * i + 2.0 * n * h * N_EXPERTS
+    layer_flops = (36.0 * n * h * i + 2.0 * n * h * N_EXPERTS) * (3.0 if args.mode == "fwdbwd" else 1.0)
     line = {
         "metric": METRIC if args.mode == "fwd" else "moe_layer_fwdbwd_tokens_per_s", "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
         "ms_per_step": ms_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
