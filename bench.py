@@ -231,7 +231,7 @@ def main():
         if args.mode == "fwdbwd":
             ws = None                       # no per-kernel events: the backward consumes its workspace
             dout = torch.randn_like(t["x"])
-            ws_b = Fn.MoEWorkspace(geo, dev, keep_gate_up=True)
+            ws_b = Fn.MoEWorkspace(geo, dev, keep_logits=True, keep_gate_up=True)
 
             def step():
                 o, w = Fn.moe_forward(t["x"], t["w_router"], t["bias"], t["gate_up_proj"], t["down_proj"],

@@ -420,7 +420,11 @@ static int backward_t(const bibo_moe_shape* s, const T* x, const T* w_router, co
       BIBO_CHECK_LAUNCH("grouped_gemm_dw_kernel");
     }
     dim3 rgrid((unsigned)((pv.rows_alloc + BW - 1) / BW));
-    if (vec)
+    if (vec && I == 32 * V16<T>::N)
+      radial_bwd_reg_kernel<T, 1><<<rgrid, 256, 0, st>>>(dh, gu, ws->rnorm, theta, pv.plan, pv.tiles_off, I, b->dtheta_row);
+    else if (vec && I == 64 * V16<T>::N)
+      radial_bwd_reg_kernel<T, 2><<<rgrid, 256, 0, st>>>(dh, gu, ws->rnorm, theta, pv.plan, pv.tiles_off, I, b->dtheta_row);
+    else if (vec)
       radial_bwd_vec_kernel<T><<<rgrid, 256, 0, st>>>(dh, gu, ws->rnorm, theta, pv.plan, pv.tiles_off, I, b->dtheta_row);
     else
       radial_bwd_kernel<T><<<rgrid, BW * 32, 0, st>>>(dh, gu, ws->rnorm, theta, pv.plan, pv.tiles_off, I, b->dtheta_row);
@@ -447,7 +451,7 @@ static int backward_t(const bibo_moe_shape* s, const T* x, const T* w_router, co
   case KK:                                                                                                          \
     gather_dx_vec_kernel<T, KK><<<tok_grid, 256, 0, st>>>(dxp, dout, x, w_router, ws->slot_row, ws->topk_idx,       \
                                                           ws->topk_w, b->dw, n, H, G, s->n_pos, s->norm_mode,       \
-                                                          s->scale, dx, b->dlogit, b->dlogit_row);                   \
+                                                          s->scale, dx, b->dlogit, b->dlogit_row, ws->logits, E);    \
     break;
     switch (k) {
       BIBO_GDX(1) BIBO_GDX(2) BIBO_GDX(3) BIBO_GDX(4) BIBO_GDX(5) BIBO_GDX(6) BIBO_GDX(7) BIBO_GDX(8)

@@ -148,6 +148,74 @@ radial_bwd_vec_kernel(const T* __restrict__ dh, T* __restrict__ gate_up, const f
   }
 }
 
+// sigmoid for the backward of the activation: exact form for fp32 tensors, one tanh.approx for bf16
+// tensors (absolute error about 5e-4, below the bf16 resolution of the results)
+template <typename T> __device__ __forceinline__ float bwd_sigmoid(float z) { return __fdiv_rn(1.0f, 1.0f + expf(-z)); }
+template <> __device__ __forceinline__ float bwd_sigmoid<__nv_bfloat16>(float z) {
+  float th;
+  asm("tanh.approx.f32 %0, %1;" : "=f"(th) : "f"(0.5f * z));
+  return fmaf(0.5f, th, 0.5f);
+}
+
+// Same backward with the row held in registers (CPL 16-byte chunks per lane, inter == CPL * 32 * VN): every
+// input is read once and the sigmoid evaluated once per element.
+template <typename T, int CPL>
+__global__ void __launch_bounds__(256)
+radial_bwd_reg_kernel(const T* __restrict__ dh, T* __restrict__ gate_up, const float* __restrict__ rnorm,
+                      const float* __restrict__ theta, const int32_t* __restrict__ plan, int64_t tiles_off, int inter,
+                      float* __restrict__ dtheta_row) {
+  constexpr int VN = V16<T>::N;
+  const int lane = threadIdx.x & 31;
+  const int64_t row = (int64_t)blockIdx.x * 8 + (threadIdx.x >> 5);
+  if (row >= plan[PLAN_ROWS_USED]) return;
+  const int4 tile = reinterpret_cast<const int4*>(plan + tiles_off)[row / BIBO_TILE_M];
+  if (row >= tile.y + tile.z) {
+    if (lane == 0) dtheta_row[row] = 0.f;
+    return;
+  }
+  T* g = gate_up + row * 2 * inter;
+  T* u = g + inter;
+  const T* dhr = dh + row * inter;
+  float gv[CPL][VN], uv[CPL][VN], dv[CPL][VN];
+#pragma unroll
+  for (int q = 0; q < CPL; ++q) {
+    const int c = q * 32 + lane;
+    V16<T>::load(g + c * VN, gv[q]); V16<T>::load(u + c * VN, uv[q]); V16<T>::load(dhr + c * VN, dv[q]);
+  }
+  const float r = rnorm[row];
+  const float p = sigmoid_accurate(theta[tile.x]);
+  const float gain = powf(r, p);
+  const float inv_r = __fdiv_rn(1.0f, r);
+  float s1 = 0.f, s2 = 0.f, s3 = 0.f;
+#pragma unroll
+  for (int q = 0; q < CPL; ++q)
+#pragma unroll
+    for (int i = 0; i < VN; ++i) {
+      const float z = gv[q][i] * inv_r;
+      const float sg = bwd_sigmoid<T>(z);
+      const float sl = z * sg;
+      const float dA = dv[q][i] * uv[q][i];
+      const float dz = dA * gain * (sg * (1.0f + z * (1.0f - sg)));
+      s1 = fmaf(dA, sl, s1);
+      s2 = fmaf(dz, gv[q][i], s2);
+      s3 = fmaf(dA, sl * gain, s3);
+      uv[q][i] = dv[q][i] * V16<T>::round(sl * gain);   // dUp
+      dv[q][i] = dz * inv_r;                             // dGate without the norm term
+    }
+  s1 = wsum(s1); s2 = wsum(s2); s3 = wsum(s3);
+  const float dr = s1 * p * powf(r, p - 1.0f) - s2 * inv_r * inv_r;
+  const float kg = dr * inv_r / (float)inter;
+  if (lane == 0) dtheta_row[row] = p * (1.0f - p) * logf(r) * s3;
+#pragma unroll
+  for (int q = 0; q < CPL; ++q) {
+    const int c = q * 32 + lane;
+#pragma unroll
+    for (int i = 0; i < VN; ++i) dv[q][i] = fmaf(kg, gv[q][i], dv[q][i]);
+    V16<T>::store(g + c * VN, dv[q]);
+    V16<T>::store(u + c * VN, uv[q]);
+  }
+}
+
 // dW_r[e, cols] = sum over the expert's rows of dlogit_row[row] * xp[row, cols].
 // grid = (E_glu, ceil(H / (32*VN))), 256 threads = 8 row lanes x 32 column groups of VN columns.
 template <typename T>
@@ -197,7 +265,8 @@ gather_dx_vec_kernel(const T* __restrict__ dxp, const T* __restrict__ dout, cons
                      const T* __restrict__ w_router, const int32_t* __restrict__ slot_row,
                      const int32_t* __restrict__ topk_idx, const float* __restrict__ topk_w,
                      const float* __restrict__ dw, int64_t n_tokens, int hidden, int n_glu, int n_pos, int norm_mode,
-                     float scale, T* __restrict__ dx, float* __restrict__ dlogit, float* __restrict__ dlogit_row) {
+                     float scale, T* __restrict__ dx, float* __restrict__ dlogit, float* __restrict__ dlogit_row,
+                     const float* __restrict__ logits, int n_experts) {
   constexpr int VN = V16<T>::N;
   const int lane = threadIdx.x & 31;
   const int64_t t = (int64_t)blockIdx.x * 8 + (threadIdx.x >> 5);
@@ -213,7 +282,8 @@ gather_dx_vec_kernel(const T* __restrict__ dxp, const T* __restrict__ dout, cons
     wj[j] = topk_w[t * K + j];
     dot[j] = 0.f;
   }
-  for (int c = lane; c < chunks; c += 32) {   // the K selected logits, x read once
+  // the K selected logits: taken from the forward's logits when it kept them, else recomputed (x read once)
+  for (int c = lane; logits == nullptr && c < chunks; c += 32) {
     float xv[VN];
     V16<T>::load(xr + c * VN, xv);
 #pragma unroll
@@ -227,7 +297,8 @@ gather_dx_vec_kernel(const T* __restrict__ dxp, const T* __restrict__ dout, cons
   float tot = 0.f, mx = -INFINITY;
 #pragma unroll
   for (int j = 0; j < K; ++j) {
-    s[j] = sigmoid_accurate(V16<T>::round(wsum(dot[j])));
+    s[j] = logits != nullptr ? sigmoid_accurate(logits[t * n_experts + ex[j]])
+                             : sigmoid_accurate(V16<T>::round(wsum(dot[j])));
     tot += s[j];
     mx = fmaxf(mx, s[j]);
   }

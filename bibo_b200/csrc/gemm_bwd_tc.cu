@@ -63,7 +63,7 @@ __device__ __forceinline__ BwdWork decode_work(int w, const int32_t* plan, const
     o.m0 = (rem / n_chunks) * BM; o.n0 = (rem % n_chunks) * XBN;
     o.krow0 = expert_off[o.e]; o.row0 = 0;
     o.k_blocks = (expert_off[o.e + 1] - expert_off[o.e]) / BK;
-    o.valid = counts[o.e] > 0;
+    o.valid = true;          // an expert without rows has k_blocks == 0: its gradient tile is written as zeros
   }
   return o;
 }
@@ -188,6 +188,10 @@ gemm_bwd_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
         tmem_ld32(ta, r0);
         tmem_ld32(ta + 32, r1);
         tmem_ld_wait();
+        if (wk.k_blocks == 0) {   // nothing was accumulated: the buffer holds stale values
+#pragma unroll
+          for (int i = 0; i < 32; ++i) r0[i] = r1[i] = 0u;
+        }
         if (g == XBN / 64 - 1) {
           tc_fence_before();
           __syncwarp();

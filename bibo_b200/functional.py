@@ -312,8 +312,8 @@ def moe_backward(dout: torch.Tensor, x: torch.Tensor, w_router: torch.Tensor, ga
     dtheta_row = torch.empty(rows, **f32)
     dx = torch.empty_like(x)
     d_wr = torch.zeros_like(w_router)
-    d_gu = torch.zeros_like(gate_up_proj)
-    d_dn = torch.zeros_like(down_proj)
+    d_gu = torch.empty_like(gate_up_proj)    # written in full by the weight-gradient kernels (zeros for unused experts)
+    d_dn = torch.empty_like(down_proj)
     d_theta = torch.zeros(geo.n_glu, **f32)
     p = _lib.ptr
     bws = _lib.BwdWorkspace(p(dy), p(dh), p(dw), p(dlogit), p(dlogit_row), p(dtheta_row))

@@ -156,7 +156,8 @@ class _MoEBlockFunction(torch.autograd.Function):
         geo = Fn.Geometry(n, hidden, gate_up_proj.shape[1] // 2, w_router.shape[0], gate_up_proj.shape[0], n_pos, top_k,
                           x.dtype)
         # a private workspace: its tensors are what the backward pass re-reads
-        ws = Fn.MoEWorkspace(geo, x.device, keep_logits=keep_logits, keep_gate_up=True)
+        # the fp32 logits are kept as well: the backward reads the selected ones instead of recomputing them
+        ws = Fn.MoEWorkspace(geo, x.device, keep_logits=True, keep_gate_up=True)
         out, ws = Fn.moe_forward(x, w_router, bias, gate_up_proj, down_proj, theta, top_k, norm, scale, n_pos=n_pos,
                                  n_neg=n_neg, ws=ws, zero_padding=True)
         ctx.save_for_backward(x, w_router, gate_up_proj, down_proj, theta)

@@ -90,6 +90,26 @@ def test_backward_matches_oracle_autograd(dtype, n, h, i, e, k):
             assert rel_err(got, r) < BF16_MAX and mean_rel_err(got, r) < BF16_MEAN, key
 
 
+def test_backward_with_unused_experts_writes_zero_gradients():
+    """Strongly skewed routing leaves experts without tokens: their weight gradients must come out as
+    exact zeros (the gradient buffers are not pre-zeroed) and the rest must match the oracle."""
+    n, h, i, k = 1500, 1024, 512, 6
+    inp = orc.make_inputs(n, h, i, 64, seed=77, bias_mode="zipf", theta_std=0.5, zipf_alpha=6.0)
+    dout = torch.randn(n, h, generator=torch.Generator().manual_seed(8))
+    layer = _layer(inp, k, "sum", 0, torch.bfloat16)
+    out, g = _grads(layer, inp["x"].to(torch.bfloat16).to(DEV), dout.to(torch.bfloat16).to(DEV))
+    idx, ref = _oracle_grads(inp, dout, k, torch.bfloat16)
+    counts = torch.bincount(idx.reshape(-1), minlength=64)
+    unused = counts == 0
+    assert int(unused.sum()) > 0, "the case must leave some experts unused"
+    assert bool((layer.last_workspace.topk_idx.cpu().long() == idx).all())
+    for key in ("d_gate_up_proj", "d_down_proj"):
+        got = g[key].float().cpu()
+        assert float(got[unused].abs().max()) == 0.0, key
+        assert rel_err(got, ref[key]) < BF16_MAX and mean_rel_err(got, ref[key]) < BF16_MEAN, key
+    assert rel_err(g["dx"].float().cpu(), ref["dx"]) < BF16_MAX
+
+
 def test_backward_is_deterministic_and_eval_forward_unchanged():
     inp = orc.make_inputs(600, 256, 128, 64, seed=3, bias_mode="uniform", theta_std=0.5)
     dout = torch.randn(600, 256, generator=torch.Generator().manual_seed(6)).to(torch.bfloat16).to(DEV)
