@@ -38,6 +38,23 @@ template <> struct V16<__nv_bfloat16> {
   static __device__ __forceinline__ float round(float v) { return __bfloat162float(__float2bfloat16_rn(v)); }
 };
 
+// acc[0..N) += w * (16 bytes of T)
+template <typename T> __device__ __forceinline__ void fma16(const uint4& v, float w, float* acc);
+template <> __device__ __forceinline__ void fma16<float>(const uint4& v, float w, float* acc) {
+  acc[0] = fmaf(__uint_as_float(v.x), w, acc[0]);
+  acc[1] = fmaf(__uint_as_float(v.y), w, acc[1]);
+  acc[2] = fmaf(__uint_as_float(v.z), w, acc[2]);
+  acc[3] = fmaf(__uint_as_float(v.w), w, acc[3]);
+}
+template <> __device__ __forceinline__ void fma16<__nv_bfloat16>(const uint4& v, float w, float* acc) {
+  const uint32_t u[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    acc[2 * i] = fmaf(__uint_as_float(u[i] << 16), w, acc[2 * i]);
+    acc[2 * i + 1] = fmaf(__uint_as_float(u[i] & 0xffff0000u), w, acc[2 * i + 1]);
+  }
+}
+
 __device__ __forceinline__ float wsum(float v) {
 #pragma unroll
   for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
@@ -331,28 +348,27 @@ gather_dx_vec_kernel(const T* __restrict__ dxp, const T* __restrict__ dout, cons
       if (rows[j] >= 0) dlogit_row[rows[j]] = dl[j];
     }
   }
+  // dx[t] = sum_j f_j * row_j + round(sum_j dl_j * W_r[e_j]); all 2K 16-byte loads of a chunk are issued
+  // before the first is used (raw registers, converted at accumulation) to keep HBM busy
   const T* go = dout + t * hidden;
+  const uint4* src[K];
+  const uint4* wsrc[K];
+  float f[K];
+#pragma unroll
+  for (int j = 0; j < K; ++j) {
+    src[j] = reinterpret_cast<const uint4*>(rows[j] >= 0 ? dxp + (int64_t)rows[j] * hidden : go);
+    wsrc[j] = reinterpret_cast<const uint4*>(w_router + (int64_t)ex[j] * hidden);
+    f[j] = rows[j] >= 0 ? 1.0f : (ex[j] >= n_glu + n_pos ? -wj[j] : wj[j]);
+  }
   for (int c = lane; c < chunks; c += 32) {
+    uint4 v[K], wv[K];
+#pragma unroll
+    for (int j = 0; j < K; ++j) { v[j] = __ldcs(src[j] + c); wv[j] = __ldg(wsrc[j] + c); }
     float acc[VN], racc[VN];
 #pragma unroll
     for (int i = 0; i < VN; ++i) acc[i] = racc[i] = 0.f;
-    float v[K][VN];
 #pragma unroll
-    for (int j = 0; j < K; ++j) {
-      const T* src = rows[j] >= 0 ? dxp + (int64_t)rows[j] * hidden : go;
-      V16<T>::load(src + c * VN, v[j]);
-    }
-#pragma unroll
-    for (int j = 0; j < K; ++j) {
-      const float f = rows[j] >= 0 ? 1.0f : (ex[j] >= n_glu + n_pos ? -wj[j] : wj[j]);
-      float wv[VN];
-      V16<T>::load(w_router + (int64_t)ex[j] * hidden + c * VN, wv);
-#pragma unroll
-      for (int i = 0; i < VN; ++i) {
-        acc[i] = fmaf(f, v[j][i], acc[i]);
-        racc[i] = fmaf(dl[j], wv[i], racc[i]);
-      }
-    }
+    for (int j = 0; j < K; ++j) { fma16<T>(v[j], f[j], acc); fma16<T>(wv[j], dl[j], racc); }
     float o[VN];
 #pragma unroll
     for (int i = 0; i < VN; ++i) o[i] = acc[i] + V16<T>::round(racc[i]);
