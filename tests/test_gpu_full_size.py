@@ -114,3 +114,46 @@ def test_sampled_tokens_match_the_cpu_oracle(run):
     assert float((ws.topk_w.cpu()[pick][same] - w[same]).abs().max()) < 1e-3
     o, r = out.float().cpu()[pick][same], ref[same]
     assert rel_err(o, r) < BF16_MAX and mean_rel_err(o, r) < BF16_MEAN
+
+
+def _fwd_bwd(t, x, dout):
+    from bibo_b200 import functional as Fn
+    geo = Fn.Geometry(x.shape[0], x.shape[1], t["gate_up_proj"].shape[1] // 2, E, E, 0, K, torch.bfloat16)
+    ws = Fn.MoEWorkspace(geo, x.device, keep_logits=True, keep_gate_up=True)
+    out, ws = Fn.moe_forward(x, t["w_router"], t["bias"], t["gate_up_proj"], t["down_proj"], t["radial_theta"], K,
+                             ws=ws, zero_padding=True)
+    grads = Fn.moe_backward(dout, x, t["w_router"], t["gate_up_proj"], t["down_proj"], t["radial_theta"], ws, "sum")
+    torch.cuda.synchronize()
+    assert Fn.plan_header(ws)[2] == 0, "device status word"
+    return out, grads
+
+
+def test_backward_at_configuration_4_size():
+    """Forward + backward on 32768 tokens (H=2048, I=512): deterministic; the weight gradients of the
+    whole batch equal the sum over two token slices (a gradient is a sum over tokens); dx of sampled
+    tokens against autograd through the CPU oracle on those tokens alone (dx of a token depends only
+    on that token)."""
+    cfg = CONFIGS["config4"]
+    inp, t = _inputs(cfg, seed=5)
+    n = cfg["n"]
+    dout = torch.randn(n, cfg["h"], generator=torch.Generator().manual_seed(11)).to(torch.bfloat16).to(DEV)
+    out, g = _fwd_bwd(t, t["x"], dout)
+    out2, g2 = _fwd_bwd(t, t["x"], dout)
+    for a, b in zip(g, g2):
+        assert torch.equal(a, b), "backward is not deterministic"
+    cut = n // 2 + 333
+    _, ga = _fwd_bwd(t, t["x"][:cut].contiguous(), dout[:cut].contiguous())
+    _, gb = _fwd_bwd(t, t["x"][cut:].contiguous(), dout[cut:].contiguous())
+    assert torch.equal(torch.cat([ga[0], gb[0]]), g[0]), "dx of a token depends on the other tokens"
+    for name, whole, pa, pb in zip(("d_w_router", "d_gate_up_proj", "d_down_proj", "d_theta"), g[1:], ga[1:], gb[1:]):
+        s = pa.float() + pb.float()                      # each part is rounded to bf16 once more than the whole
+        assert rel_err(whole.float(), s) < BF16_MAX and mean_rel_err(whole.float(), s) < BF16_MEAN, name
+    pick = torch.randperm(n, generator=torch.Generator().manual_seed(4))[:192].sort().values
+    c = {k: (v.to(torch.bfloat16).float() if k in ("x", "w_router", "gate_up_proj", "down_proj") else v.clone())
+         for k, v in inp.items()}
+    xs = c["x"][pick].clone().requires_grad_(True)
+    ref, logits, idx, w, _ = orc.moe_forward(xs, c["w_router"], c["bias"], c["gate_up_proj"], c["down_proj"],
+                                             c["radial_theta"], K, return_routing=True)
+    (ref * dout.cpu()[pick].float()).sum().backward()
+    got = g[0].float().cpu()[pick]
+    assert rel_err(got, xs.grad) < BF16_MAX and mean_rel_err(got, xs.grad) < BF16_MEAN
