@@ -274,9 +274,19 @@ extern "C" int bibo_moe_ep_backward(const bibo_moe_ep_args* a, const bibo_moe_ep
   if ((rc = gemm_dw_tc_launch(dy_local, a->h, b->d_down_proj, a->ep_plan, ep_off_le_span(E), ep_off_le_off(E), cap, EL,
                               H, I, st)))
     return rc;
-  radial_bwd_vec_kernel<bf16><<<(unsigned)((cap + 7) / 8), 256, 0, st>>>(
-      static_cast<const bf16*>(b->dh), static_cast<bf16*>(a->gate_up_recv), a->rnorm_recv, a->theta, a->ep_plan,
-      pv.tiles_off, I, b->dtheta_row);
+  const unsigned rgrid = (unsigned)((cap + 7) / 8);
+  if (I == 512)
+    radial_bwd_reg_kernel<bf16, 2><<<rgrid, 256, 0, st>>>(static_cast<const bf16*>(b->dh),
+                                                          static_cast<bf16*>(a->gate_up_recv), a->rnorm_recv, a->theta,
+                                                          a->ep_plan, pv.tiles_off, I, b->dtheta_row);
+  else if (I == 256)
+    radial_bwd_reg_kernel<bf16, 1><<<rgrid, 256, 0, st>>>(static_cast<const bf16*>(b->dh),
+                                                          static_cast<bf16*>(a->gate_up_recv), a->rnorm_recv, a->theta,
+                                                          a->ep_plan, pv.tiles_off, I, b->dtheta_row);
+  else
+    radial_bwd_vec_kernel<bf16><<<rgrid, 256, 0, st>>>(
+        static_cast<const bf16*>(b->dh), static_cast<bf16*>(a->gate_up_recv), a->rnorm_recv, a->theta, a->ep_plan,
+        pv.tiles_off, I, b->dtheta_row);
   BIBO_CHECK_LAUNCH("radial_bwd_vec_kernel");
   ep_dtheta_reduce_kernel<<<EL, 256, 0, st>>>(b->dtheta_row, a->ep_plan + ep_off_le_off(E), b->d_theta);
   BIBO_CHECK_LAUNCH("ep_dtheta_reduce_kernel");

@@ -237,7 +237,7 @@ class ExpertParallelMoE:
         dout = dout.contiguous()
         dx = torch.empty_like(dout)
         d_wr = torch.zeros_like(self.w_router)
-        d_gu, d_dn = torch.zeros_like(self.gate_up), torch.zeros_like(self.down)
+        d_gu, d_dn = torch.empty_like(self.gate_up), torch.empty_like(self.down)   # written in full by the kernels
         d_th = torch.zeros(self.el, dtype=torch.float32, device=dev)
         b = _lib.EpBwdArgs(p(dout), C.cast(self.dy.ptr_array, C.c_void_p), p(self.dh), p(self.dw), p(self.dlogit_row),
                            p(self.dtheta_row), p(dx), p(d_wr), p(d_gu), p(d_dn), p(d_th), self._epoch)
