@@ -24,7 +24,7 @@ _vp, _i32, _i64, _f32 = C.c_void_p, C.c_int, C.c_int64, C.c_float
 class Workspace(C.Structure):
     _fields_ = [(n, _vp) for n in (
         "topk_idx", "topk_w", "slot_rank", "block_counts", "plan", "slot_row", "row_token",
-        "xp", "h", "y", "gate_up", "rnorm", "logits", "stage_events")]
+        "xp", "h", "y", "gate_up", "rnorm", "logits", "stage_events", "addend")]
 
 
 class BwdWorkspace(C.Structure):
@@ -82,6 +82,8 @@ SIGNATURES = {
     "bibo_moe_gemm2_fwd": (_i32, [_vp, _vp, _vp, _i64, _i32, _i32, _i32, _i32, _i32, _i32, _vp, _vp]),
     "bibo_moe_combine_fwd": (_i32, [_vp, _vp, _vp, _vp, _vp, _i64, _i32, _i32, _i32, _i32, _i32,
                                     _vp, _vp]),
+    "bibo_moe_combine_add_fwd": (_i32, [_vp, _vp, _vp, _vp, _vp, _vp, _i64, _i32, _i32, _i32, _i32, _i32,
+                                        _vp, _vp]),
     "bibo_moe_forward": (_i32, [C.POINTER(Shape), _vp, _vp, _vp, _vp, _vp, _vp,
                                 C.POINTER(Workspace), _vp, _vp]),
     "bibo_moe_forward_host": (_i32, [C.POINTER(Shape), _vp, _vp, _vp, _vp, _vp, _vp, _vp,
@@ -93,6 +95,9 @@ SIGNATURES = {
     "bibo_moe_ep_plan": (_i32, [_vp, _i32, _i32, _i32, _i64, _vp, _vp]),
     "bibo_moe_ep_dispatch": (_i32, [_vp, _vp, _vp, _vp, _vp, _vp, _i64, _i32, _i32, _i32, _i32, _i32, _i64, _i32, _vp, _vp,
                                     _vp]),
+    "bibo_moe_mlp_plan_words": (_i64, [_i64]),
+    "bibo_moe_mlp_supported": (_i32, [_i32, _i32, _i32]),
+    "bibo_moe_mlp_forward": (_i32, [_vp, _vp, _vp, _vp, _i64, _i32, _i32, _i32, _vp, _vp, _vp, _vp]),
     "bibo_moe_ep_forward": (_i32, [C.POINTER(EpArgs), _vp]),
     "bibo_moe_ep_forward_dma": (_i32, [C.POINTER(EpArgs), C.POINTER(EpDma), _i32, _vp]),
     "bibo_moe_ep_plan_layout": (_i32, [_vp, _i32, _i32, _i32, _i64, _i32, _vp, _vp]),

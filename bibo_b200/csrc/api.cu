@@ -109,8 +109,8 @@ extern "C" int bibo_moe_forward(const bibo_moe_shape* s, const void* x, const vo
                           s->n_glu, s->top_k, s->dtype, ws->y, stream);
   if (rc) return rc;
   BIBO_STAGE(5);
-  rc = bibo_moe_combine_fwd(ws->y, x, ws->slot_row, ws->topk_idx, ws->topk_w, s->n_tokens, s->hidden,
-                            s->top_k, s->n_glu, s->n_pos, s->dtype, out, stream);
+  rc = bibo_moe_combine_add_fwd(ws->y, x, ws->slot_row, ws->topk_idx, ws->topk_w, ws->addend, s->n_tokens, s->hidden,
+                                s->top_k, s->n_glu, s->n_pos, s->dtype, out, stream);
   if (rc) return rc;
   BIBO_STAGE(6);
 #undef BIBO_STAGE

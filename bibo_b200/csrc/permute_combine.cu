@@ -115,6 +115,21 @@ template <> struct Acc16<__nv_bfloat16> {
   }
 };
 
+// acc[i] = T(acc[i]) + v[i]: the sum is rounded to T before the second term is added
+template <typename T> __device__ __forceinline__ void add_rounded(float* acc, const uint4& v);
+template <> __device__ __forceinline__ void add_rounded<float>(float* acc, const uint4& v) {
+  acc[0] += __uint_as_float(v.x); acc[1] += __uint_as_float(v.y);
+  acc[2] += __uint_as_float(v.z); acc[3] += __uint_as_float(v.w);
+}
+template <> __device__ __forceinline__ void add_rounded<__nv_bfloat16>(float* acc, const uint4& v) {
+  const uint32_t u[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    acc[2 * i] = __bfloat162float(__float2bfloat16_rn(acc[2 * i])) + __uint_as_float(u[i] << 16);
+    acc[2 * i + 1] = __bfloat162float(__float2bfloat16_rn(acc[2 * i + 1])) + __uint_as_float(u[i] & 0xffff0000u);
+  }
+}
+
 // One warp per token; the k rows are summed in slot order (= ascending expert index), fp32.
 // All k 16-byte loads of a chunk are issued before the first is used (raw registers, converted
 // only at accumulation), and two chunks are in flight per lane, to keep HBM busy.
@@ -122,7 +137,8 @@ template <typename T, int K>
 __global__ void __launch_bounds__(PW * 32, 4)
 combine_kernel(const T* __restrict__ y, const T* __restrict__ x, const int32_t* __restrict__ slot_row,
                const int32_t* __restrict__ topk_idx, const float* __restrict__ topk_w,
-               int64_t n_tokens, int hidden, int n_glu, int n_pos, T* __restrict__ out) {
+               int64_t n_tokens, int hidden, int n_glu, int n_pos, T* __restrict__ out,
+               const T* __restrict__ addend) {
   constexpr int VN = Acc16<T>::N;
   const int lane = threadIdx.x & 31;
   const int64_t t = (int64_t)blockIdx.x * PW + (threadIdx.x >> 5);
@@ -146,6 +162,8 @@ combine_kernel(const T* __restrict__ y, const T* __restrict__ x, const int32_t* 
     src[j] = reinterpret_cast<const uint4*>(r >= 0 ? y + (int64_t)r * hidden : x + t * hidden);
   }
   uint4* dst = reinterpret_cast<uint4*>(out + t * hidden);
+  // optional second term (the shared expert's output): out = T(T(sum) + addend), the reference's two roundings
+  const uint4* add = addend ? reinterpret_cast<const uint4*>(addend + t * hidden) : nullptr;
   const int chunks = hidden / VN;
   int c = lane;
   for (; c + 32 < chunks; c += 64) {
@@ -157,6 +175,7 @@ combine_kernel(const T* __restrict__ y, const T* __restrict__ x, const int32_t* 
     for (int i = 0; i < VN; ++i) a0[i] = a1[i] = 0.f;
 #pragma unroll
     for (int j = 0; j < K; ++j) { Acc16<T>::fma(v0[j], ws[j], a0); Acc16<T>::fma(v1[j], ws[j], a1); }
+    if (add != nullptr) { add_rounded<T>(a0, __ldcs(add + c)); add_rounded<T>(a1, __ldcs(add + c + 32)); }
     Vec16<T>::store(dst + c, a0);
     Vec16<T>::store(dst + c + 32, a1);
   }
@@ -169,6 +188,7 @@ combine_kernel(const T* __restrict__ y, const T* __restrict__ x, const int32_t* 
     for (int i = 0; i < VN; ++i) a0[i] = 0.f;
 #pragma unroll
     for (int j = 0; j < K; ++j) Acc16<T>::fma(v0[j], ws[j], a0);
+    if (add != nullptr) add_rounded<T>(a0, __ldcs(add + c));
     Vec16<T>::store(dst + c, a0);
   }
 }
@@ -176,12 +196,12 @@ combine_kernel(const T* __restrict__ y, const T* __restrict__ x, const int32_t* 
 template <typename T>
 static int combine_launch(const void* y, const void* x, const int32_t* slot_row, const int32_t* topk_idx,
                           const float* topk_w, int64_t n_tokens, int hidden, int top_k, int n_glu, int n_pos,
-                          void* out, cudaStream_t st) {
+                          void* out, const void* addend, cudaStream_t st) {
   dim3 grid((unsigned)((n_tokens + PW - 1) / PW));
 #define BIBO_COMBINE_CASE(KK)                                                                                   \
   case KK:                                                                                                       \
     combine_kernel<T, KK><<<grid, PW * 32, 0, st>>>((const T*)y, (const T*)x, slot_row, topk_idx, topk_w,        \
-                                                    n_tokens, hidden, n_glu, n_pos, (T*)out);                    \
+                                                    n_tokens, hidden, n_glu, n_pos, (T*)out, (const T*)addend);  \
     break;
   switch (top_k) {
     BIBO_COMBINE_CASE(1) BIBO_COMBINE_CASE(2) BIBO_COMBINE_CASE(3) BIBO_COMBINE_CASE(4)
@@ -219,10 +239,10 @@ extern "C" int bibo_moe_permute_fwd(const void* x, const int32_t* topk_idx, cons
   return BIBO_OK;
 }
 
-extern "C" int bibo_moe_combine_fwd(const void* y, const void* x, const int32_t* slot_row,
-                                    const int32_t* topk_idx, const float* topk_w, int64_t n_tokens,
-                                    int hidden, int top_k, int n_glu, int n_pos, int dtype, void* out,
-                                    void* stream) {
+extern "C" int bibo_moe_combine_add_fwd(const void* y, const void* x, const int32_t* slot_row,
+                                        const int32_t* topk_idx, const float* topk_w, const void* addend,
+                                        int64_t n_tokens, int hidden, int top_k, int n_glu, int n_pos, int dtype,
+                                        void* out, void* stream) {
   if (n_tokens <= 0) return BIBO_OK;
   if (!y || !x || !slot_row || !topk_idx || !topk_w || !out)
     return fail(BIBO_ERR_ARG, "combine_fwd: null pointer");
@@ -231,10 +251,19 @@ extern "C" int bibo_moe_combine_fwd(const void* y, const void* x, const int32_t*
   const int row_bytes = hidden * (dtype == BIBO_F32 ? 4 : 2);
   if (row_bytes % 16 != 0)
     return fail(BIBO_ERR_UNSUPPORTED, "combine_fwd: row of %d bytes is not a multiple of 16", row_bytes);
-  if (!aligned16(y) || !aligned16(x) || !aligned16(out))
-    return fail(BIBO_ERR_ALIGN, "combine_fwd: y / x / out not 16-byte aligned");
+  if (!aligned16(y) || !aligned16(x) || !aligned16(out) || !aligned16(addend))
+    return fail(BIBO_ERR_ALIGN, "combine_fwd: y / x / out / addend not 16-byte aligned");
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   if (dtype == BIBO_F32)
-    return combine_launch<float>(y, x, slot_row, topk_idx, topk_w, n_tokens, hidden, top_k, n_glu, n_pos, out, st);
-  return combine_launch<__nv_bfloat16>(y, x, slot_row, topk_idx, topk_w, n_tokens, hidden, top_k, n_glu, n_pos, out, st);
+    return combine_launch<float>(y, x, slot_row, topk_idx, topk_w, n_tokens, hidden, top_k, n_glu, n_pos, out, addend, st);
+  return combine_launch<__nv_bfloat16>(y, x, slot_row, topk_idx, topk_w, n_tokens, hidden, top_k, n_glu, n_pos, out,
+                                       addend, st);
+}
+
+extern "C" int bibo_moe_combine_fwd(const void* y, const void* x, const int32_t* slot_row,
+                                    const int32_t* topk_idx, const float* topk_w, int64_t n_tokens,
+                                    int hidden, int top_k, int n_glu, int n_pos, int dtype, void* out,
+                                    void* stream) {
+  return bibo_moe_combine_add_fwd(y, x, slot_row, topk_idx, topk_w, nullptr, n_tokens, hidden, top_k, n_glu, n_pos,
+                                  dtype, out, stream);
 }

@@ -107,7 +107,8 @@ class MoEWorkspace:
             ev = C.cast(self._stage_event_array, C.c_void_p)
         return _lib.Workspace(p(self.topk_idx), p(self.topk_w), p(self.slot_rank), p(self.block_counts),
                               p(self.plan), p(self.slot_row), p(self.row_token), p(self.xp), p(self.h),
-                              p(self.y), p(self.gate_up), p(self.rnorm), p(self.logits), ev)
+                              p(self.y), p(self.gate_up), p(self.rnorm), p(self.logits), ev,
+                              p(getattr(self, "addend", None)))
 
     def enable_stage_timing(self) -> None:
         """Ask bibo_moe_forward to record an event around every stage (see stage_ms)."""
@@ -198,8 +199,10 @@ def launch_count() -> int:
 def moe_forward(x: torch.Tensor, w_router: torch.Tensor, bias: torch.Tensor, gate_up_proj: torch.Tensor,
                 down_proj: torch.Tensor, theta: torch.Tensor, top_k: int, norm_mode="sum", scale: float = 1.0,
                 n_pos: int = 0, n_neg: int = 0, ws: Optional[MoEWorkspace] = None, out: Optional[torch.Tensor] = None,
-                zero_padding: bool = False, keep_logits: bool = False) -> Tuple[torch.Tensor, MoEWorkspace]:
-    """The whole block on flat tokens x [N,H]: one call of bibo_moe_forward.  Returns (out, workspace)."""
+                zero_padding: bool = False, keep_logits: bool = False,
+                addend: Optional[torch.Tensor] = None) -> Tuple[torch.Tensor, MoEWorkspace]:
+    """The whole block on flat tokens x [N,H]: one call of bibo_moe_forward.  Returns (out, workspace).
+    ``addend`` [N,H] (the shared expert's output) is added in the combine kernel."""
     lib = _lib.load()
     for name, t in (("x", x), ("w_router", w_router), ("bias", bias), ("gate_up_proj", gate_up_proj),
                     ("down_proj", down_proj), ("radial_theta", theta)):
@@ -221,7 +224,11 @@ def moe_forward(x: torch.Tensor, w_router: torch.Tensor, bias: torch.Tensor, gat
     bias32 = bias if bias.dtype == torch.float32 else bias.float()
     theta32 = theta if theta.dtype == torch.float32 else theta.float()
     shape = _shape(geo, norm_mode, scale, zero_padding)
+    if addend is not None and (addend.shape != x.shape or addend.dtype != x.dtype or not addend.is_contiguous()):
+        raise RuntimeError("addend must be a contiguous tensor of the activations' shape and dtype")
+    ws.addend = addend
     cws = ws.c_struct()
+    ws.addend = None
     rc = lib.bibo_moe_forward(C.byref(shape), _lib.ptr(x), _lib.ptr(w_router), _lib.ptr(bias32),
                               _lib.ptr(gate_up_proj), _lib.ptr(down_proj), _lib.ptr(theta32), C.byref(cws),
                               _lib.ptr(out), _stream(x.device))
@@ -288,6 +295,33 @@ def experts_forward(x: torch.Tensor, topk_idx: torch.Tensor, topk_w: torch.Tenso
     ws.topk_idx_external = idx32  # keep alive until the stream has consumed it
     ws.topk_w_external = w32
     return out, ws
+
+
+def mlp_forward(x: torch.Tensor, gate_proj: torch.Tensor, up_proj: torch.Tensor, down_proj: torch.Tensor,
+                out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Dense SwiGLU MLP ``down(silu(gate(x)) * up(x))`` on flat tokens x [N,H] (bibo_moe_mlp_forward);
+    weights are the ``nn.Linear`` weights as stored: gate/up [I,H], down [H,I].  bf16, forward only."""
+    lib = _lib.load()
+    for name, t in (("x", x), ("gate_proj", gate_proj), ("up_proj", up_proj), ("down_proj", down_proj)):
+        _need_cuda(t, name)
+        if t.dtype != x.dtype:
+            raise RuntimeError(f"{name} dtype {t.dtype} != activation dtype {x.dtype}")
+    n, hidden = x.shape
+    inter = gate_proj.shape[0]
+    dt = dtype_code(x.dtype)
+    if not lib.bibo_moe_mlp_supported(hidden, inter, dt):
+        raise RuntimeError(f"bibo_b200: the dense MLP kernels take bf16 with hidden % 256 == 0 and intermediate % 256 "
+                           f"== 0 (got {x.dtype}, {hidden}, {inter})")
+    if out is None:
+        out = torch.empty_like(x)
+    if n == 0:
+        return out
+    plan = torch.empty(int(lib.bibo_moe_mlp_plan_words(n)), dtype=torch.int32, device=x.device)
+    h = torch.empty(n, inter, dtype=x.dtype, device=x.device)
+    p = _lib.ptr
+    _lib.check(lib.bibo_moe_mlp_forward(p(x), p(gate_proj), p(up_proj), p(down_proj), n, hidden, inter, dt, p(plan),
+                                        p(h), p(out), _stream(x.device)), "bibo_moe_mlp_forward")
+    return out
 
 
 def moe_backward(dout: torch.Tensor, x: torch.Tensor, w_router: torch.Tensor, gate_up_proj: torch.Tensor,

@@ -1,0 +1,44 @@
+"""Dense SwiGLU MLP with the reference's module interface (src/modeling/ffn/mlp.py:9-34).
+
+``BiBoMLP(config, is_expert=False, intermediate_size=None)`` owns ``gate_proj``, ``up_proj`` and
+``down_proj`` as bias-free ``nn.Linear`` modules (state-dict compatible with the reference) and runs
+``down_proj(silu(gate_proj(x)) * up_proj(x))`` on the tensor-core kernels of the MoE block
+(``bibo_moe_mlp_forward``).  It serves as the shared expert of ``BiBoMoELayer`` and as a dense
+feed-forward layer.  bf16 on a CUDA device, forward only: anything else raises.
+"""
+from __future__ import annotations
+
+import torch
+import torch.nn as nn
+
+from . import functional as Fn
+
+__all__ = ["BiBoMLP", "mlp_module_forward"]
+
+
+def mlp_module_forward(mlp, x: torch.Tensor) -> torch.Tensor:
+    """``BiBoMLP.forward`` written against the reference's attribute names only (works on an instance of
+    the reference's own class)."""
+    act = getattr(getattr(mlp, "config", None), "hidden_act", "silu")
+    if act not in ("silu", "swish"):
+        raise NotImplementedError(f"bibo_b200.BiBoMLP: hidden_act={act!r} (the kernels implement SiLU)")
+    weights = (mlp.gate_proj.weight, mlp.up_proj.weight, mlp.down_proj.weight)
+    if torch.is_grad_enabled() and (x.requires_grad or any(w.requires_grad for w in weights)):
+        raise NotImplementedError("bibo_b200.BiBoMLP is forward-only: call it under torch.no_grad()")
+    flat = x.reshape(-1, x.shape[-1]).contiguous()
+    return Fn.mlp_forward(flat, *weights).view(x.shape)
+
+
+class BiBoMLP(nn.Module):
+    def __init__(self, config, is_expert: bool = False, intermediate_size=None):
+        super().__init__()
+        self.config = config
+        self.hidden_size = config.hidden_size
+        self.intermediate_size = intermediate_size if intermediate_size is not None else (
+            config.moe_intermediate_size if is_expert else config.intermediate_size)
+        self.gate_proj = nn.Linear(self.hidden_size, self.intermediate_size, bias=False)
+        self.up_proj = nn.Linear(self.hidden_size, self.intermediate_size, bias=False)
+        self.down_proj = nn.Linear(self.intermediate_size, self.hidden_size, bias=False)
+
+    def forward(self, x: torch.Tensor) -> torch.Tensor:
+        return mlp_module_forward(self, x)

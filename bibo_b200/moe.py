@@ -11,9 +11,11 @@ Parameter / buffer names and shapes are the reference's: ``gate.gate_proj.weight
 ``gate.bias [E]`` (a Parameter with requires_grad=False), ``experts.gate_up_proj [E_glu,2I,H]``,
 ``experts.down_proj [E_glu,H,I]``, ``experts.radial_theta [E_glu]``, buffer ``accumulated_tpe [E]``.
 
-Every forward runs CUDA kernels; CPU tensors raise.  Configurations outside the kernels' coverage
-(shared expert, float16) raise at construction or call time instead of silently taking another
-path.
+Every forward runs CUDA kernels; CPU tensors raise.  ``use_shared_expert=True`` adds the reference's
+shared SwiGLU expert (``shared_experts_list.0`` = ``bibo_b200.BiBoMLP``, src/modeling/ffn/moe.py:120-127),
+forward only (bf16).  Configurations outside the kernels' coverage (convolutional shared expert,
+float16, training with a shared expert) raise at construction or call time instead of silently
+taking another path.
 """
 from __future__ import annotations
 
@@ -42,6 +44,9 @@ class MoEConfig:
     bias_update_threshold: int = 8000
     initializer_range: float = 0.02
     use_shared_expert: bool = False
+    shared_expert_type: str = "mlp"
+    num_shared_experts: int = 1
+    hidden_act: str = "silu"
     routed_scaling_factor: float = 1.0
 
     @property
@@ -193,9 +198,14 @@ class BiBoMoELayer(nn.Module):
         self.use_shared_expert = bool(_cfg(config, "use_shared_expert", False))
         self.shared_experts_list = nn.ModuleList()
         if self.use_shared_expert:
-            raise NotImplementedError(
-                "bibo_b200.BiBoMoELayer: use_shared_expert=True is outside the kernels' coverage "
-                "(the reference's default and every benchmark configuration have it off)")
+            # moe.py:120-127: one SwiGLU MLP of width moe_intermediate_size * num_shared_experts
+            if _cfg(config, "shared_expert_type", "mlp") == "conv":
+                raise NotImplementedError("bibo_b200.BiBoMoELayer: shared_expert_type='conv' is outside the kernels' "
+                                          "coverage")
+            from .mlp import BiBoMLP
+            n_sh = int(_cfg(config, "num_shared_experts", 1))
+            self.shared_experts_list.append(BiBoMLP(config, is_expert=True,
+                                                    intermediate_size=config.moe_intermediate_size * n_sh))
         self.gate = BiBoMoERouter(config)
         self.last_workspace: Optional[Fn.MoEWorkspace] = None
 
@@ -243,9 +253,18 @@ def layer_forward(layer, hidden_states: torch.Tensor) -> torch.Tensor:
     """
     bsz, seq_len, hidden = hidden_states.shape
     n = bsz * seq_len
-    if getattr(layer, "use_shared_expert", False):
-        raise NotImplementedError("bibo_b200: use_shared_expert=True is outside the kernels' coverage")
     flat = hidden_states.reshape(n, hidden).contiguous()
+    shared_out = None
+    if getattr(layer, "use_shared_expert", False):
+        # moe.py:174-176: final = routed + shared(hidden_states); the sum happens in the combine kernel
+        from .mlp import mlp_module_forward
+        shared = layer.shared_experts_list[0]
+        if not hasattr(shared, "gate_proj"):
+            raise NotImplementedError("bibo_b200: only the MLP shared expert is covered by the kernels")
+        if torch.is_grad_enabled() and (flat.requires_grad or any(p.requires_grad for p in layer.parameters())):
+            raise NotImplementedError("bibo_b200: the shared expert is forward-only; run the layer under "
+                                      "torch.no_grad() or with use_shared_expert=False")
+        shared_out = mlp_module_forward(shared, flat)
     gate, ex = layer.gate, layer.experts
     n_pos, n_neg = ex.pos_end - ex.pos_start, ex.neg_end - ex.neg_start
     want_gap = gate._probe_gap and gate.top_k < gate.num_routed_experts
@@ -259,7 +278,7 @@ def layer_forward(layer, hidden_states: torch.Tensor) -> torch.Tensor:
     else:
         out, ws = Fn.moe_forward(flat, gate.gate_proj.weight, gate.bias, ex.gate_up_proj, ex.down_proj,
                                  ex.radial_theta, gate.top_k, gate.norm_topk_prob, scale,
-                                 n_pos=n_pos, n_neg=n_neg, keep_logits=want_gap)
+                                 n_pos=n_pos, n_neg=n_neg, keep_logits=want_gap, addend=shared_out)
     layer.last_workspace = ws
     if want_gap:
         with torch.no_grad():

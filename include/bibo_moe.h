@@ -147,6 +147,11 @@ int bibo_moe_combine_fwd(const void* y, const void* x, const int32_t* slot_row,
                          const int32_t* topk_idx, const float* topk_w, int64_t n_tokens,
                          int hidden, int top_k, int n_glu, int n_pos, int dtype, void* out,
                          void* stream);
+/* The same with a second term: out[t] = T(T(sum over slots) + addend[t]) (addend may be NULL).      */
+int bibo_moe_combine_add_fwd(const void* y, const void* x, const int32_t* slot_row,
+                             const int32_t* topk_idx, const float* topk_w, const void* addend,
+                             int64_t n_tokens, int hidden, int top_k, int n_glu, int n_pos, int dtype,
+                             void* out, void* stream);
 
 /* ---- whole block -------------------------------------------------------------------------------
  * Replaces BiBoMoELayer.forward in eval mode without shared expert
@@ -170,6 +175,8 @@ typedef struct {
                                 before stage i (router, plan, permute, gate/up, down, combine) and
                                 [6] after the last; lets a caller time each kernel without extra
                                 launches or synchronisation                                        */
+  const void* addend;     /* optional [N,H] dtype: added to the combined output (the shared expert's
+                             result, src/modeling/ffn/moe.py:174-176): out = T(T(sum) + addend)        */
 } bibo_moe_workspace;
 
 typedef struct {
@@ -334,6 +341,19 @@ typedef struct {
   int epoch_base;
 } bibo_moe_ep_bwd_args;
 int bibo_moe_ep_backward(const bibo_moe_ep_args* fwd, const bibo_moe_ep_bwd_args* bwd, void* stream);
+
+/* ---- dense SwiGLU MLP -----------------------------------------------------------------------------
+ * Replaces BiBoMLP.forward, `down_proj(act_fn(gate_proj(x)) * up_proj(x))` with act = SiLU
+ * (src/modeling/ffn/mlp.py:33-34): the shared expert of the MoE layer (src/modeling/ffn/moe.py:120-127,
+ * 174-176) and the dense feed-forward layers.  x [N,H], gate_proj / up_proj [I,H], down_proj [H,I]
+ * (the nn.Linear weights as stored) -> y [N,H]; h [N,I] and plan (bibo_moe_mlp_plan_words(N) int32) are
+ * scratch.  bf16 with H % 256 == 0 and I % 256 == 0 (bibo_moe_mlp_supported), forward only.  Rounding
+ * points as in the reference run in bf16: gate and up outputs, the activation, their product.      */
+int64_t bibo_moe_mlp_plan_words(int64_t n_tokens);
+int bibo_moe_mlp_supported(int hidden, int inter, int dtype);
+int bibo_moe_mlp_forward(const void* x, const void* gate_proj, const void* up_proj, const void* down_proj,
+                     int64_t n_tokens, int hidden, int inter, int dtype, int32_t* plan, void* h, void* y,
+                     void* stream);
 
 /* ---- routing without any allocation -------------------------------------------------------------
  * No counterpart in the reference: added for callers that cannot allocate device memory (a runtime

@@ -235,6 +235,21 @@ def moe_forward(
     return out
 
 
+def mlp_forward(x: torch.Tensor, gate_proj: torch.Tensor, up_proj: torch.Tensor, down_proj: torch.Tensor):
+    """Dense SwiGLU MLP, BiBoMLP.forward with hidden_act = "silu" (src/modeling/ffn/mlp.py:33-34):
+    down_proj(silu(gate_proj(x)) * up_proj(x)); weights as nn.Linear stores them ([I,H], [I,H], [H,I])."""
+    return F.linear(F.silu(F.linear(x, gate_proj)) * F.linear(x, up_proj), down_proj)
+
+
+def make_mlp_weights(hidden: int, inter: int, seed: int = 0):
+    """Seeded N(0, 0.02) weights of a dense MLP (own generators, like make_inputs)."""
+    def gen(i):
+        return torch.Generator().manual_seed(seed * 1000 + 20 + i)
+    return dict(gate_proj=torch.randn(inter, hidden, generator=gen(1)) * 0.02,
+                up_proj=torch.randn(inter, hidden, generator=gen(2)) * 0.02,
+                down_proj=torch.randn(hidden, inter, generator=gen(3)) * 0.02)
+
+
 # --------------------------------------------------------------------------------------------
 # seeded synthetic workloads (shapes and distributions of the benchmark configurations)
 # --------------------------------------------------------------------------------------------

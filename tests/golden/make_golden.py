@@ -97,6 +97,51 @@ def run_case(ref_root, name, n_tokens, hidden, inter, n_experts, top_k, pairs=0,
           f"{int(rec['counts'].min())}/{int(rec['counts'].max())}  {sz:.0f} KiB")
 
 
+def run_mlp_case(ref_root, name, n_tokens, hidden, inter, seed, shared_in_layer=False, n_experts=64, top_k=6,
+                 moe_inter=64, n_shared=2):
+    """The reference's dense SwiGLU MLP (src/modeling/ffn/mlp.py) alone, or as the shared expert of the
+    MoE layer (use_shared_expert=True, width moe_inter * n_shared); fp32 on CPU."""
+    if ref_root not in sys.path:
+        sys.path.insert(0, ref_root)
+    from src.configuration_bibo import BiBoConfig
+    from src.modeling.ffn.mlp import BiBoMLP
+    from src.modeling.ffn.moe import BiBoMoELayer
+    rec = dict(name=name, n_tokens=n_tokens, hidden=hidden, inter=inter, seed=seed, shared_in_layer=shared_in_layer)
+    w = orc.make_mlp_weights(hidden, inter, seed)
+    if not shared_in_layer:
+        cfg = BiBoConfig(vocab_size=512, hidden_size=hidden, num_hidden_layers=4, num_attention_heads=4,
+                         num_key_value_heads=2, intermediate_size=inter, moe_intermediate_size=moe_inter,
+                         num_routed_experts=n_experts, special_expert_pairs=0, num_experts_per_tok=top_k)
+        mlp = BiBoMLP(cfg).eval()
+        x = torch.randn(n_tokens, hidden, generator=torch.Generator().manual_seed(seed * 1000 + 1))
+    else:
+        assert inter == moe_inter * n_shared
+        cfg = BiBoConfig(vocab_size=512, hidden_size=hidden, num_hidden_layers=4, num_attention_heads=4,
+                         num_key_value_heads=2, intermediate_size=4 * hidden, moe_intermediate_size=moe_inter,
+                         num_routed_experts=n_experts, special_expert_pairs=0, num_experts_per_tok=top_k,
+                         use_shared_expert=True, shared_expert_type="mlp", num_shared_experts=n_shared,
+                         bias_update_factor=0.4)
+        layer = BiBoMoELayer(cfg).eval()
+        inp = orc.make_inputs(n_tokens, hidden, moe_inter, n_experts, seed=seed, bias_mode="uniform", theta_std=0.5)
+        with torch.no_grad():
+            layer.gate.gate_proj.weight.copy_(inp["w_router"])
+            layer.gate.bias.copy_(inp["bias"])
+            layer.experts.gate_up_proj.copy_(inp["gate_up_proj"])
+            layer.experts.down_proj.copy_(inp["down_proj"])
+            layer.experts.radial_theta.copy_(inp["radial_theta"])
+        mlp = layer.shared_experts_list[0]
+        x = inp["x"]
+        rec.update(n_experts=n_experts, top_k=top_k, moe_inter=moe_inter, n_shared=n_shared)
+    with torch.no_grad():
+        mlp.gate_proj.weight.copy_(w["gate_proj"])
+        mlp.up_proj.weight.copy_(w["up_proj"])
+        mlp.down_proj.weight.copy_(w["down_proj"])
+        out = layer(x.reshape(1, n_tokens, hidden))[0] if shared_in_layer else mlp(x)
+    rec["out"] = out.clone()
+    torch.save(rec, HERE / f"{name}.pt")
+    print(f"{name}: out abs-mean {out.abs().mean():.4e}  {os.path.getsize(HERE / f'{name}.pt') / 1024:.0f} KiB")
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--reference", required=True)
@@ -116,6 +161,9 @@ def main():
     # by oracle.moe_oracle.make_inputs and are not stored.
     run_case(r, "config1", 2048, 512, 128, 64, 6, bias_mode="zero", theta_std=0.0, seed=0,
              backward=False, keep_rows=64)
+    # dense SwiGLU MLP alone and as the shared expert of the layer (shapes the tensor-core kernels accept)
+    run_mlp_case(r, "mlp_dense", 300, 256, 512, seed=7)
+    run_mlp_case(r, "layer_shared_expert", 300, 256, 512, seed=8, shared_in_layer=True, moe_inter=256, n_shared=2)
 
 
 if __name__ == "__main__":

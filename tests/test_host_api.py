@@ -53,8 +53,16 @@ def test_module_mirrors_reference_names_and_shapes():
     assert layer.gate.bias.requires_grad is False
     e = layer.experts
     assert (e.pos_start, e.pos_end, e.neg_start, e.neg_end) == (6, 7, 7, 8)
+    # shared expert: one SwiGLU MLP of width moe_intermediate_size * num_shared_experts (moe.py:120-127)
+    shared = BiBoMoELayer(MoEConfig(use_shared_expert=True, num_shared_experts=2, hidden_size=64,
+                                    moe_intermediate_size=32, num_routed_experts=8))
+    sd = shared.state_dict()
+    assert sd["shared_experts_list.0.gate_proj.weight"].shape == (64, 64)
+    assert sd["shared_experts_list.0.up_proj.weight"].shape == (64, 64)
+    assert sd["shared_experts_list.0.down_proj.weight"].shape == (64, 64)
     with pytest.raises(NotImplementedError):
-        BiBoMoELayer(MoEConfig(use_shared_expert=True, hidden_size=64, moe_intermediate_size=32, num_routed_experts=8))
+        BiBoMoELayer(MoEConfig(use_shared_expert=True, shared_expert_type="conv", hidden_size=64,
+                               moe_intermediate_size=32, num_routed_experts=8))
 
 
 def test_balancer_host_logic_matches_reference_tests():

@@ -2,7 +2,7 @@
 import pytest
 import torch
 
-from conftest import GOLDEN_CASES, digest_close, grad_digest, load_golden, rel_err, upstream_grad
+from conftest import GOLDEN, GOLDEN_CASES, digest_close, grad_digest, load_golden, rel_err, upstream_grad
 from oracle import moe_oracle as orc
 
 
@@ -109,3 +109,24 @@ def test_balancer_interval_and_direction():
     tpe[0] = 100.0
     orc.update_bias(bias, tpe, 0.4)
     assert bias[0] < 0 and (bias[1:] > 0).all() and abs(float(bias.mean())) < 1e-6
+
+
+def test_dense_mlp_oracle_matches_the_reference_fixture():
+    """oracle.mlp_forward against the reference's BiBoMLP (src/modeling/ffn/mlp.py), fp32."""
+    rec = torch.load(GOLDEN / "mlp_dense.pt")
+    w = orc.make_mlp_weights(rec["hidden"], rec["inter"], rec["seed"])
+    x = torch.randn(rec["n_tokens"], rec["hidden"], generator=torch.Generator().manual_seed(rec["seed"] * 1000 + 1))
+    out = orc.mlp_forward(x, w["gate_proj"], w["up_proj"], w["down_proj"])
+    assert rel_err(out, rec["out"]) < 1e-6
+
+
+def test_layer_with_shared_expert_oracle_matches_the_reference_fixture():
+    """Routed experts + shared SwiGLU expert (src/modeling/ffn/moe.py:120-127,174-176), fp32."""
+    rec = torch.load(GOLDEN / "layer_shared_expert.pt")
+    inp = orc.make_inputs(rec["n_tokens"], rec["hidden"], rec["moe_inter"], rec["n_experts"], seed=rec["seed"],
+                          bias_mode="uniform", theta_std=0.5)
+    w = orc.make_mlp_weights(rec["hidden"], rec["inter"], rec["seed"])
+    routed = orc.moe_forward(inp["x"], inp["w_router"], inp["bias"], inp["gate_up_proj"], inp["down_proj"],
+                             inp["radial_theta"], rec["top_k"])
+    out = routed + orc.mlp_forward(inp["x"], w["gate_proj"], w["up_proj"], w["down_proj"])
+    assert rel_err(out, rec["out"]) < 1e-6
