@@ -97,7 +97,9 @@ SIGNATURES = {
                                     _vp]),
     "bibo_moe_mlp_plan_words": (_i64, [_i64]),
     "bibo_moe_mlp_supported": (_i32, [_i32, _i32, _i32]),
-    "bibo_moe_mlp_forward": (_i32, [_vp, _vp, _vp, _vp, _i64, _i32, _i32, _i32, _vp, _vp, _vp, _vp]),
+    "bibo_moe_mlp_forward": (_i32, [_vp, _vp, _vp, _vp, _i64, _i32, _i32, _i32, _vp, _vp, _vp, _vp, _vp]),
+    "bibo_moe_mlp_backward": (_i32, [_vp, _vp, _vp, _vp, _vp, _vp, _i64, _i32, _i32, _i32, _vp, _vp, _vp, _vp, _vp,
+                                     _vp]),
     "bibo_moe_ep_forward": (_i32, [C.POINTER(EpArgs), _vp]),
     "bibo_moe_ep_forward_dma": (_i32, [C.POINTER(EpArgs), C.POINTER(EpDma), _i32, _vp]),
     "bibo_moe_ep_plan_layout": (_i32, [_vp, _i32, _i32, _i32, _i64, _i32, _vp, _vp]),

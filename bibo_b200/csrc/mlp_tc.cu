@@ -44,6 +44,9 @@ __global__ void mlp_plan_kernel(int64_t n_tokens, int32_t* __restrict__ plan) {
     plan[PLAN_N_TILES] = n_tiles;
     plan[PLAN_ROWS_USED] = n_tiles * BM;
     plan[PLAN_N_PAIRS] = (n_tiles + 1) / 2;
+    // one-"expert" row range for the weight-gradient reductions of the backward: counts[0], expert_off[0..1]
+    int32_t* range = plan + mlp_off_pairs(n_tokens) + 2 * ((n_tiles + 1) / 2);
+    range[0] = (int32_t)n_tokens; range[1] = 0; range[2] = n_tiles * BM;
   }
   if (i < n_tiles) {
     tiles[i] = make_int4(0, i * BM, (int)min((int64_t)BM, n_tokens - (int64_t)i * BM), 0);
@@ -55,7 +58,8 @@ __global__ void mlp_plan_kernel(int64_t n_tokens, int32_t* __restrict__ plan) {
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 mlp_gemm1_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmG,
                       const __grid_constant__ CUtensorMap tmU, const __grid_constant__ CUtensorMap tmH,
-                      int32_t* __restrict__ plan, int64_t tiles_off, int64_t pairs_off, int k_blocks, int n_cblocks) {
+                      int32_t* __restrict__ plan, int64_t tiles_off, int64_t pairs_off, int k_blocks, int n_cblocks,
+                      __nv_bfloat16* __restrict__ gate_up_out, int64_t n_rows) {
   constexpr int NC = M_NC, STAGES = M_STAGES;
   extern __shared__ unsigned char smem_dyn[];
   unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_dyn) + 1023) & ~uintptr_t(1023));
@@ -183,6 +187,10 @@ mlp_gemm1_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
       if (lane == 0) mbar_arrive_cluster_addr(map_to_cta(gempty, leader));
       if (!mbar_wait(ufull, it & 1, abort_flag)) break;
       tc_fence_after();
+      // training: the raw gate | up rows [N, 2I] are kept for the backward pass
+      const int inter = n_cblocks * NC;
+      __nv_bfloat16* gu_row = (gate_up_out && !twin && t.y + row < n_rows)
+                                  ? gate_up_out + (int64_t)(t.y + row) * 2 * inter + cb * NC : nullptr;
 #pragma unroll 1
       for (int c2 = 0; c2 < NC / 64; ++c2) {       // h = bf16(silu(gate)) * bf16(up), in place in the stash
         uint32_t rr0[32], rr1[32];
@@ -197,11 +205,13 @@ mlp_gemm1_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
           uint4* slot = reinterpret_cast<uint4*>(sub + swz(row, jj));
           const uint4 gv = *slot;
           const uint32_t* pg = reinterpret_cast<const uint32_t*>(&gv);
-          uint4 hv;
+          uint4 hv, uv;
           uint32_t* ph = reinterpret_cast<uint32_t*>(&hv);
+          uint32_t* pu = reinterpret_cast<uint32_t*>(&uv);
 #pragma unroll
           for (int i = 0; i < 4; ++i) {
             const uint32_t upk = pack_bf16(__uint_as_float(r[8 * j + 2 * i]), __uint_as_float(r[8 * j + 2 * i + 1]));
+            pu[i] = upk;
             float hval[2];
 #pragma unroll
             for (int s = 0; s < 2; ++s) {
@@ -216,6 +226,11 @@ mlp_gemm1_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
             ph[i] = pack_bf16(hval[0], hval[1]);
           }
           *slot = hv;
+          if (gu_row != nullptr) {
+            const int col = c2 * 64 + (jj >> 2) * 32 + j * 8;
+            *reinterpret_cast<uint4*>(gu_row + col) = gv;
+            *reinterpret_cast<uint4*>(gu_row + inter + col) = uv;
+          }
         }
       }
       tc_fence_before();
@@ -252,8 +267,8 @@ extern "C" int bibo_moe_mlp_supported(int hidden, int inter, int dtype) {
 }
 
 extern "C" int bibo_moe_mlp_forward(const void* x, const void* gate_proj, const void* up_proj, const void* down_proj,
-                                int64_t n_tokens, int hidden, int inter, int dtype, int32_t* plan, void* h, void* y,
-                                void* stream) {
+                                    int64_t n_tokens, int hidden, int inter, int dtype, int32_t* plan, void* h, void* y,
+                                    void* gate_up_out, void* stream) {
   if (n_tokens <= 0) return BIBO_OK;
   if (!x || !gate_proj || !up_proj || !down_proj || !plan || !h || !y)
     return fail(BIBO_ERR_ARG, "mlp_forward: null pointer");
@@ -261,7 +276,7 @@ extern "C" int bibo_moe_mlp_forward(const void* x, const void* gate_proj, const 
     return fail(BIBO_ERR_UNSUPPORTED, "mlp_forward: needs bf16, hidden %% 256 == 0, intermediate %% 256 == 0 (got %d, %d)",
                 hidden, inter);
   if (!aligned16(x) || !aligned16(gate_proj) || !aligned16(up_proj) || !aligned16(down_proj) || !aligned16(h) ||
-      !aligned16(y))
+      !aligned16(y) || !aligned16(gate_up_out))
     return fail(BIBO_ERR_ALIGN, "mlp_forward: pointers must be 16-byte aligned");
   if (n_tokens > 0x7fffff00LL) return fail(BIBO_ERR_UNSUPPORTED, "mlp_forward: n_tokens=%lld", (long long)n_tokens);
   cudaStream_t st = static_cast<cudaStream_t>(stream);
@@ -311,7 +326,98 @@ extern "C" int bibo_moe_mlp_forward(const void* x, const void* gate_proj, const 
   const int clusters = (int)std::max<int64_t>(1, std::min<int64_t>(std::min(max_clusters, sms / 2), n_work));
   cfg.gridDim = dim3(clusters * 2);
   BIBO_CUDA(cudaLaunchKernelEx(&cfg, mlp_gemm1_pair_kernel, tmA, tmG, tmU, tmH, plan, pv.tiles_off, pv.pairs_off,
-                               hidden / BK, inter / M_NC));
+                               hidden / BK, inter / M_NC, static_cast<__nv_bfloat16*>(gate_up_out), n_tokens));
   launch_counter().fetch_add(1, std::memory_order_relaxed);
   return gemm2_tc_launch(h, down_proj, pv, hidden, inter, 1, y, st);
+}
+
+// ---- backward -------------------------------------------------------------------------------------------
+namespace bibo {
+// gemm_bwd_tc.cu
+int gemm_dx_tc_supported(int k_dim, int n_out);
+int gemm_dx_tc_launch(const void* A, const void* W, void* C, const PlanView& pv, int k_dim, int n_out,
+                      int n_weight_experts, cudaStream_t st);
+int gemm_dw_tc_supported(int m_dim, int n_dim);
+int gemm_dw_tc_launch(const void* A, const void* B, void* C, const int32_t* plan, int64_t counts_off,
+                      int64_t expert_off_off, int64_t rows_alloc, int n_experts, int m_dim, int n_dim, cudaStream_t st);
+
+// [gate | up] rows -> [dGate | dUp] in place: a = bf16(silu(g)), dUp = dh * a, dGate = dh * up * silu'(g).
+// One warp per row, 16-byte accesses; the sigmoid is one tanh.approx (error below the bf16 resolution).
+__global__ void __launch_bounds__(256)
+swiglu_bwd_kernel(const __nv_bfloat16* __restrict__ dh, __nv_bfloat16* __restrict__ gate_up, int64_t n_rows, int inter) {
+  const int lane = threadIdx.x & 31;
+  const int64_t row = (int64_t)blockIdx.x * 8 + (threadIdx.x >> 5);
+  if (row >= n_rows) return;
+  uint4* g = reinterpret_cast<uint4*>(gate_up + row * 2 * inter);
+  uint4* u = g + inter / 8;
+  const uint4* d = reinterpret_cast<const uint4*>(dh + row * inter);
+  for (int c = lane; c < inter / 8; c += 32) {
+    const uint4 gv = g[c], uv = u[c], dv = __ldcs(d + c);
+    const uint32_t* pg = reinterpret_cast<const uint32_t*>(&gv);
+    const uint32_t* pu = reinterpret_cast<const uint32_t*>(&uv);
+    const uint32_t* pd = reinterpret_cast<const uint32_t*>(&dv);
+    uint4 og, ou;
+    uint32_t* qg = reinterpret_cast<uint32_t*>(&og);
+    uint32_t* qu = reinterpret_cast<uint32_t*>(&ou);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      float dg2[2], du2[2];
+#pragma unroll
+      for (int s = 0; s < 2; ++s) {
+        const float gg = s ? tc::bf16_hi(pg[i]) : tc::bf16_lo(pg[i]);
+        const float uu = s ? tc::bf16_hi(pu[i]) : tc::bf16_lo(pu[i]);
+        const float dd = s ? tc::bf16_hi(pd[i]) : tc::bf16_lo(pd[i]);
+        float th;
+        asm("tanh.approx.f32 %0, %1;" : "=f"(th) : "f"(0.5f * gg));
+        const float sg = fmaf(0.5f, th, 0.5f);
+        du2[s] = dd * tc::round_bf16(gg * sg);
+        dg2[s] = dd * uu * (sg * (1.0f + gg * (1.0f - sg)));
+      }
+      qg[i] = tc::pack_bf16(dg2[0], dg2[1]);
+      qu[i] = tc::pack_bf16(du2[0], du2[1]);
+    }
+    g[c] = og;
+    u[c] = ou;
+  }
+}
+}  // namespace bibo
+
+extern "C" int bibo_moe_mlp_backward(const void* x, const void* gate_up_weight, const void* down_proj, void* gate_up,
+                                     const void* h, const void* dout, int64_t n_tokens, int hidden, int inter, int dtype,
+                                     int32_t* plan, void* dh, void* dx, void* d_gate_up_weight, void* d_down_proj,
+                                     void* stream) {
+  if (n_tokens <= 0) return BIBO_OK;
+  if (!x || !gate_up_weight || !down_proj || !gate_up || !h || !dout || !plan || !dh || !dx || !d_gate_up_weight ||
+      !d_down_proj)
+    return fail(BIBO_ERR_ARG, "mlp_backward: null pointer");
+  if (!bibo_moe_mlp_supported(hidden, inter, dtype) || !gemm_dx_tc_supported(hidden, inter) ||
+      !gemm_dx_tc_supported(2 * inter, hidden) || !gemm_dw_tc_supported(hidden, inter) ||
+      !gemm_dw_tc_supported(2 * inter, hidden))
+    return fail(BIBO_ERR_UNSUPPORTED, "mlp_backward: hidden=%d intermediate=%d is outside the tensor-core kernels",
+                hidden, inter);
+  if (!aligned16(x) || !aligned16(gate_up_weight) || !aligned16(down_proj) || !aligned16(gate_up) || !aligned16(h) ||
+      !aligned16(dout) || !aligned16(dh) || !aligned16(dx) || !aligned16(d_gate_up_weight) || !aligned16(d_down_proj))
+    return fail(BIBO_ERR_ALIGN, "mlp_backward: pointers must be 16-byte aligned");
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const int n_tiles = (int)mlp_tiles(n_tokens);
+  // the forward's plan (tiles, pairs) plus a one-expert row range for the weight-gradient reductions; rows past N
+  // read as zeros through the tensor maps, so the padded range needs no zero-filled buffers
+  const int64_t extra = mlp_off_pairs(n_tokens) + 2 * ((mlp_tiles(n_tokens) + 1) / 2);
+  // (written by the forward's plan kernel: counts[0], expert_off[0..1])
+  PlanView pv = {};
+  pv.plan = plan;
+  pv.tiles_off = mlp_off_tiles();
+  pv.pairs_off = mlp_off_pairs(n_tokens);
+  pv.tiles_cap = n_tiles;
+  pv.rows_alloc = n_tokens;
+  int rc;
+  // dH = dOut W_d ; dW_d = dOut^T h
+  if ((rc = gemm_dx_tc_launch(dout, down_proj, dh, pv, hidden, inter, 1, st))) return rc;
+  if ((rc = gemm_dw_tc_launch(dout, h, d_down_proj, plan, extra, extra + 1, n_tokens, 1, hidden, inter, st))) return rc;
+  swiglu_bwd_kernel<<<(unsigned)((n_tokens + 7) / 8), 256, 0, st>>>(static_cast<const __nv_bfloat16*>(dh),
+                                                                   static_cast<__nv_bfloat16*>(gate_up), n_tokens, inter);
+  BIBO_CHECK_LAUNCH("swiglu_bwd_kernel");
+  // dX = [dGate | dUp] [W_g ; W_u] ; d[W_g ; W_u] = [dGate | dUp]^T x
+  if ((rc = gemm_dx_tc_launch(gate_up, gate_up_weight, dx, pv, 2 * inter, hidden, 1, st))) return rc;
+  return gemm_dw_tc_launch(gate_up, x, d_gate_up_weight, plan, extra, extra + 1, n_tokens, 1, 2 * inter, hidden, st);
 }

@@ -298,9 +298,10 @@ def experts_forward(x: torch.Tensor, topk_idx: torch.Tensor, topk_w: torch.Tenso
 
 
 def mlp_forward(x: torch.Tensor, gate_proj: torch.Tensor, up_proj: torch.Tensor, down_proj: torch.Tensor,
-                out: Optional[torch.Tensor] = None) -> torch.Tensor:
+                out: Optional[torch.Tensor] = None, keep: bool = False):
     """Dense SwiGLU MLP ``down(silu(gate(x)) * up(x))`` on flat tokens x [N,H] (bibo_moe_mlp_forward);
-    weights are the ``nn.Linear`` weights as stored: gate/up [I,H], down [H,I].  bf16, forward only."""
+    weights are the ``nn.Linear`` weights as stored: gate/up [I,H], down [H,I].  bf16.
+    ``keep=True`` returns ``(out, saved)`` with the tensors ``mlp_backward`` needs."""
     lib = _lib.load()
     for name, t in (("x", x), ("gate_proj", gate_proj), ("up_proj", up_proj), ("down_proj", down_proj)):
         _need_cuda(t, name)
@@ -315,13 +316,34 @@ def mlp_forward(x: torch.Tensor, gate_proj: torch.Tensor, up_proj: torch.Tensor,
     if out is None:
         out = torch.empty_like(x)
     if n == 0:
-        return out
+        return (out, None) if keep else out
     plan = torch.empty(int(lib.bibo_moe_mlp_plan_words(n)), dtype=torch.int32, device=x.device)
     h = torch.empty(n, inter, dtype=x.dtype, device=x.device)
+    gate_up = torch.empty(n, 2 * inter, dtype=x.dtype, device=x.device) if keep else None
     p = _lib.ptr
     _lib.check(lib.bibo_moe_mlp_forward(p(x), p(gate_proj), p(up_proj), p(down_proj), n, hidden, inter, dt, p(plan),
-                                        p(h), p(out), _stream(x.device)), "bibo_moe_mlp_forward")
-    return out
+                                        p(h), p(out), p(gate_up), _stream(x.device)), "bibo_moe_mlp_forward")
+    return (out, (plan, h, gate_up)) if keep else out
+
+
+def mlp_backward(dout: torch.Tensor, x: torch.Tensor, gate_proj: torch.Tensor, up_proj: torch.Tensor,
+                 down_proj: torch.Tensor, saved):
+    """Gradients of ``mlp_forward(..., keep=True)`` (bibo_moe_mlp_backward); ``saved`` is consumed.
+    Returns (dx, d_gate_proj, d_up_proj, d_down_proj)."""
+    lib = _lib.load()
+    plan, h, gate_up = saved
+    n, hidden = x.shape
+    inter = gate_proj.shape[0]
+    w_gu = torch.cat([gate_proj, up_proj])                      # [2I, H]: one K-stacked operand for dX
+    dh = torch.empty(n, inter, dtype=x.dtype, device=x.device)
+    dx = torch.empty_like(x)
+    d_gu = torch.empty_like(w_gu)
+    d_dn = torch.empty_like(down_proj)
+    p = _lib.ptr
+    _lib.check(lib.bibo_moe_mlp_backward(p(x), p(w_gu), p(down_proj), p(gate_up), p(h), p(dout), n, hidden, inter,
+                                         dtype_code(x.dtype), p(plan), p(dh), p(dx), p(d_gu), p(d_dn),
+                                         _stream(x.device)), "bibo_moe_mlp_backward")
+    return dx, d_gu[:inter], d_gu[inter:], d_dn
 
 
 def moe_backward(dout: torch.Tensor, x: torch.Tensor, w_router: torch.Tensor, gate_up_proj: torch.Tensor,

@@ -4,7 +4,7 @@
 ``down_proj`` as bias-free ``nn.Linear`` modules (state-dict compatible with the reference) and runs
 ``down_proj(silu(gate_proj(x)) * up_proj(x))`` on the tensor-core kernels of the MoE block
 (``bibo_moe_mlp_forward``).  It serves as the shared expert of ``BiBoMoELayer`` and as a dense
-feed-forward layer.  bf16 on a CUDA device, forward only: anything else raises.
+feed-forward layer.  bf16 on a CUDA device (forward and backward): anything else raises.
 """
 from __future__ import annotations
 
@@ -16,6 +16,27 @@ from . import functional as Fn
 __all__ = ["BiBoMLP", "mlp_module_forward"]
 
 
+class _MLPFunction(torch.autograd.Function):
+    """Forward and backward of the dense MLP as single C-ABI calls (the reference relies on autograd over
+    three nn.Linear modules and the activation)."""
+
+    @staticmethod
+    def forward(ctx, x, gate_w, up_w, down_w):
+        out, saved = Fn.mlp_forward(x, gate_w, up_w, down_w, keep=True)
+        ctx.save_for_backward(x, gate_w, up_w, down_w)
+        ctx.saved = saved
+        return out
+
+    @staticmethod
+    def backward(ctx, dout):
+        x, gate_w, up_w, down_w = ctx.saved_tensors
+        if ctx.saved is None:
+            raise RuntimeError("bibo_b200: the MLP's backward ran twice (its saved tensors are consumed)")
+        grads = Fn.mlp_backward(dout.contiguous(), x, gate_w, up_w, down_w, ctx.saved)
+        ctx.saved = None
+        return grads
+
+
 def mlp_module_forward(mlp, x: torch.Tensor) -> torch.Tensor:
     """``BiBoMLP.forward`` written against the reference's attribute names only (works on an instance of
     the reference's own class)."""
@@ -23,9 +44,9 @@ def mlp_module_forward(mlp, x: torch.Tensor) -> torch.Tensor:
     if act not in ("silu", "swish"):
         raise NotImplementedError(f"bibo_b200.BiBoMLP: hidden_act={act!r} (the kernels implement SiLU)")
     weights = (mlp.gate_proj.weight, mlp.up_proj.weight, mlp.down_proj.weight)
-    if torch.is_grad_enabled() and (x.requires_grad or any(w.requires_grad for w in weights)):
-        raise NotImplementedError("bibo_b200.BiBoMLP is forward-only: call it under torch.no_grad()")
     flat = x.reshape(-1, x.shape[-1]).contiguous()
+    if torch.is_grad_enabled() and (x.requires_grad or any(w.requires_grad for w in weights)):
+        return _MLPFunction.apply(flat, *weights).view(x.shape)
     return Fn.mlp_forward(flat, *weights).view(x.shape)
 
 

@@ -13,9 +13,8 @@ Parameter / buffer names and shapes are the reference's: ``gate.gate_proj.weight
 
 Every forward runs CUDA kernels; CPU tensors raise.  ``use_shared_expert=True`` adds the reference's
 shared SwiGLU expert (``shared_experts_list.0`` = ``bibo_b200.BiBoMLP``, src/modeling/ffn/moe.py:120-127),
-forward only (bf16).  Configurations outside the kernels' coverage (convolutional shared expert,
-float16, training with a shared expert) raise at construction or call time instead of silently
-taking another path.
+bf16.  Configurations outside the kernels' coverage (convolutional shared expert, float16) raise at
+construction or call time instead of silently taking another path.
 """
 from __future__ import annotations
 
@@ -155,7 +154,7 @@ class _MoEBlockFunction(torch.autograd.Function):
     eager ops per layer; here both directions are single C-ABI calls)."""
 
     @staticmethod
-    def forward(ctx, x, w_router, gate_up_proj, down_proj, theta, bias, cfg, holder):
+    def forward(ctx, x, w_router, gate_up_proj, down_proj, theta, bias, cfg, holder, addend=None):
         top_k, norm, scale, n_pos, n_neg, keep_logits = cfg
         n, hidden = x.shape
         geo = Fn.Geometry(n, hidden, gate_up_proj.shape[1] // 2, w_router.shape[0], gate_up_proj.shape[0], n_pos, top_k,
@@ -164,9 +163,10 @@ class _MoEBlockFunction(torch.autograd.Function):
         # the fp32 logits are kept as well: the backward reads the selected ones instead of recomputing them
         ws = Fn.MoEWorkspace(geo, x.device, keep_logits=True, keep_gate_up=True)
         out, ws = Fn.moe_forward(x, w_router, bias, gate_up_proj, down_proj, theta, top_k, norm, scale, n_pos=n_pos,
-                                 n_neg=n_neg, ws=ws, zero_padding=True)
+                                 n_neg=n_neg, ws=ws, zero_padding=True, addend=addend)
         ctx.save_for_backward(x, w_router, gate_up_proj, down_proj, theta)
         ctx.ws, ctx.norm, ctx.scale = ws, norm, scale
+        ctx.has_addend = addend is not None
         holder["ws"] = ws
         return out
 
@@ -178,7 +178,8 @@ class _MoEBlockFunction(torch.autograd.Function):
         dx, d_wr, d_gu, d_dn, d_th = Fn.moe_backward(dout.contiguous(), x, w_router, gate_up_proj, down_proj, theta,
                                                      ctx.ws, ctx.norm, ctx.scale)
         ctx.ws = None
-        return dx, d_wr, d_gu, d_dn, d_th.to(theta.dtype), None, None, None
+        # the addend (shared expert output) enters the result by a plain sum: its gradient is dout
+        return dx, d_wr, d_gu, d_dn, d_th.to(theta.dtype), None, None, None, (dout if ctx.has_addend else None)
 
 
 class BiBoMoELayer(nn.Module):
@@ -261,10 +262,7 @@ def layer_forward(layer, hidden_states: torch.Tensor) -> torch.Tensor:
         shared = layer.shared_experts_list[0]
         if not hasattr(shared, "gate_proj"):
             raise NotImplementedError("bibo_b200: only the MLP shared expert is covered by the kernels")
-        if torch.is_grad_enabled() and (flat.requires_grad or any(p.requires_grad for p in layer.parameters())):
-            raise NotImplementedError("bibo_b200: the shared expert is forward-only; run the layer under "
-                                      "torch.no_grad() or with use_shared_expert=False")
-        shared_out = mlp_module_forward(shared, flat)
+        shared_out = mlp_module_forward(shared, flat)          # its own autograd node when gradients are on
     gate, ex = layer.gate, layer.experts
     n_pos, n_neg = ex.pos_end - ex.pos_start, ex.neg_end - ex.neg_start
     want_gap = gate._probe_gap and gate.top_k < gate.num_routed_experts
@@ -273,7 +271,8 @@ def layer_forward(layer, hidden_states: torch.Tensor) -> torch.Tensor:
     if torch.is_grad_enabled() and (flat.requires_grad or any(p.requires_grad for p in params)):
         holder = {}
         out = _MoEBlockFunction.apply(flat, *params, gate.bias.detach(),
-                                      (gate.top_k, gate.norm_topk_prob, scale, n_pos, n_neg, want_gap), holder)
+                                      (gate.top_k, gate.norm_topk_prob, scale, n_pos, n_neg, want_gap), holder,
+                                      shared_out)
         ws = holder["ws"]
     else:
         out, ws = Fn.moe_forward(flat, gate.gate_proj.weight, gate.bias, ex.gate_up_proj, ex.down_proj,

@@ -351,9 +351,18 @@ int bibo_moe_ep_backward(const bibo_moe_ep_args* fwd, const bibo_moe_ep_bwd_args
  * points as in the reference run in bf16: gate and up outputs, the activation, their product.      */
 int64_t bibo_moe_mlp_plan_words(int64_t n_tokens);
 int bibo_moe_mlp_supported(int hidden, int inter, int dtype);
+/* gate_up_out: NULL, or [N, 2I] receiving the raw gate | up rows (what the backward re-reads).      */
 int bibo_moe_mlp_forward(const void* x, const void* gate_proj, const void* up_proj, const void* down_proj,
-                     int64_t n_tokens, int hidden, int inter, int dtype, int32_t* plan, void* h, void* y,
-                     void* stream);
+                         int64_t n_tokens, int hidden, int inter, int dtype, int32_t* plan, void* h, void* y,
+                         void* gate_up_out, void* stream);
+/* Backward of bibo_moe_mlp_forward (autograd through BiBoMLP.forward in the reference).  plan, h and
+ * gate_up are the forward's (gate_up is overwritten with [dGate | dUp]); gate_up_weight is
+ * [gate_proj ; up_proj] stacked [2I, H] and d_gate_up_weight [2I, H] receives their gradients in the
+ * same order; dh [N, I] is scratch.  Every output is written in full.                               */
+int bibo_moe_mlp_backward(const void* x, const void* gate_up_weight, const void* down_proj, void* gate_up,
+                          const void* h, const void* dout, int64_t n_tokens, int hidden, int inter, int dtype,
+                          int32_t* plan, void* dh, void* dx, void* d_gate_up_weight, void* d_down_proj,
+                          void* stream);
 
 /* ---- routing without any allocation -------------------------------------------------------------
  * No counterpart in the reference: added for callers that cannot allocate device memory (a runtime

@@ -136,8 +136,16 @@ def run_mlp_case(ref_root, name, n_tokens, hidden, inter, seed, shared_in_layer=
         mlp.gate_proj.weight.copy_(w["gate_proj"])
         mlp.up_proj.weight.copy_(w["up_proj"])
         mlp.down_proj.weight.copy_(w["down_proj"])
-        out = layer(x.reshape(1, n_tokens, hidden))[0] if shared_in_layer else mlp(x)
-    rec["out"] = out.clone()
+    # forward and autograd gradients (upstream gradient = the seeded dOut of the other fixtures)
+    xg = x.clone().requires_grad_(True)
+    out = layer(xg.reshape(1, n_tokens, hidden))[0] if shared_in_layer else mlp(xg)
+    (out * upstream_grad(n_tokens, hidden, seed)[0]).sum().backward()
+    rec["out"] = out.detach().clone()
+    rec["dx"] = xg.grad.clone()
+    for key, prm in (("d_gate_proj", mlp.gate_proj.weight), ("d_up_proj", mlp.up_proj.weight),
+                     ("d_down_proj", mlp.down_proj.weight)):
+        rec[key + "_digest"] = grad_digest(prm.grad.float(), seed)      # per row: L2 norm, probe inner product
+        rec[key + "_head"] = prm.grad[:8].clone()
     torch.save(rec, HERE / f"{name}.pt")
     print(f"{name}: out abs-mean {out.abs().mean():.4e}  {os.path.getsize(HERE / f'{name}.pt') / 1024:.0f} KiB")
 

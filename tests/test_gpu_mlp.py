@@ -5,7 +5,7 @@ import pathlib
 import pytest
 import torch
 
-from conftest import mean_rel_err, rel_err
+from conftest import digest_close, grad_digest, mean_rel_err, rel_err, upstream_grad
 from oracle import moe_oracle as orc
 
 pytestmark = pytest.mark.gpu
@@ -80,8 +80,97 @@ def test_layer_with_shared_expert_matches_the_reference_fixture():
     assert float(same.float().mean()) > 0.95
     o, r = out.float().cpu()[same], rec["out"][same]
     assert rel_err(o, r) < BF16_MAX and mean_rel_err(o, r) < BF16_MEAN
-    with pytest.raises(NotImplementedError):                   # the shared expert has no backward kernels
-        layer.train()(x.clone().requires_grad_(True))
+
+
+def _bf16_close(got, ref, name=""):
+    got = got.float().cpu()
+    assert rel_err(got, ref) < BF16_MAX and mean_rel_err(got, ref) < BF16_MEAN, name
+
+
+def test_dense_mlp_backward_matches_the_reference_fixture():
+    """Gradients of BiBoMLP against the reference's autograd (fp32 fixture), bf16 bars."""
+    from bibo_b200 import BiBoMLP, MoEConfig
+    rec = torch.load(GOLDEN / "mlp_dense.pt")
+    w = orc.make_mlp_weights(rec["hidden"], rec["inter"], rec["seed"])
+    cfg = MoEConfig(hidden_size=rec["hidden"], moe_intermediate_size=rec["inter"])
+    mlp = BiBoMLP(cfg, is_expert=True)
+    with torch.no_grad():
+        mlp.gate_proj.weight.copy_(w["gate_proj"]); mlp.up_proj.weight.copy_(w["up_proj"]); mlp.down_proj.weight.copy_(w["down_proj"])
+    mlp = mlp.to(DEV).to(torch.bfloat16)
+    x = torch.randn(rec["n_tokens"], rec["hidden"], generator=torch.Generator().manual_seed(rec["seed"] * 1000 + 1))
+    xg = x.to(torch.bfloat16).to(DEV).requires_grad_(True)
+    out = mlp(xg)
+    (out * upstream_grad(rec).to(torch.bfloat16).to(DEV)).sum().backward()
+    _bf16_close(out.detach(), rec["out"], "out")
+    _bf16_close(xg.grad, rec["dx"], "dx")
+    for key, prm in (("gate_proj", mlp.gate_proj.weight), ("up_proj", mlp.up_proj.weight), ("down_proj", mlp.down_proj.weight)):
+        _bf16_close(prm.grad[:8], rec[f"d_{key}_head"], key)
+        assert digest_close(grad_digest(prm.grad.float().cpu(), rec["seed"]), rec[f"d_{key}_digest"], BF16_MAX), key
+
+
+@pytest.mark.parametrize("n,h,i", [(130, 256, 256), (1000, 1024, 2048), (2050, 512, 768)])
+def test_dense_mlp_backward_matches_oracle_autograd(n, h, i):
+    from bibo_b200 import functional as Fn
+    w = orc.make_mlp_weights(h, i, seed=n)
+    x = torch.randn(n, h, generator=torch.Generator().manual_seed(n))
+    dout = torch.randn(n, h, generator=torch.Generator().manual_seed(n + 1))
+    r = lambda t: t.to(torch.bfloat16).float()
+    cx = r(x).requires_grad_(True)
+    cw = {k: r(v).requires_grad_(True) for k, v in w.items()}
+    (orc.mlp_forward(cx, cw["gate_proj"], cw["up_proj"], cw["down_proj"]) * r(dout)).sum().backward()
+    wd = _dev(w)
+    xd = x.to(torch.bfloat16).to(DEV)
+    out, saved = Fn.mlp_forward(xd, wd["gate_proj"], wd["up_proj"], wd["down_proj"], keep=True)
+    plain = Fn.mlp_forward(xd, wd["gate_proj"], wd["up_proj"], wd["down_proj"])
+    assert torch.equal(out, plain), "keeping the gate/up rows changes the result"
+    dx, dg, du, dd = Fn.mlp_backward(dout.to(torch.bfloat16).to(DEV), xd, wd["gate_proj"], wd["up_proj"], wd["down_proj"], saved)
+    torch.cuda.synchronize()
+    _bf16_close(dx, cx.grad, "dx")
+    _bf16_close(dg, cw["gate_proj"].grad, "d_gate_proj")
+    _bf16_close(du, cw["up_proj"].grad, "d_up_proj")
+    _bf16_close(dd, cw["down_proj"].grad, "d_down_proj")
+
+
+def test_layer_with_shared_expert_trains():
+    """Gradients through BiBoMoELayer(use_shared_expert=True) against autograd through the CPU oracle
+    (routed block + shared MLP, inputs rounded to bf16, fp32 math)."""
+    from bibo_b200 import BiBoMoELayer, MoEConfig
+    n, h, i, n_sh, k = 700, 256, 256, 2, 6
+    cfg = MoEConfig(hidden_size=h, moe_intermediate_size=i, num_routed_experts=64, num_experts_per_tok=k,
+                    use_shared_expert=True, num_shared_experts=n_sh, bias_update_factor=0.0)
+    inp = orc.make_inputs(n, h, i, 64, seed=12, bias_mode="uniform", theta_std=0.5)
+    w = orc.make_mlp_weights(h, i * n_sh, seed=12)
+    dout = torch.randn(n, h, generator=torch.Generator().manual_seed(13))
+    layer = BiBoMoELayer(cfg)
+    sh = layer.shared_experts_list[0]
+    with torch.no_grad():
+        layer.gate.gate_proj.weight.copy_(inp["w_router"]); layer.gate.bias.copy_(inp["bias"])
+        layer.experts.gate_up_proj.copy_(inp["gate_up_proj"]); layer.experts.down_proj.copy_(inp["down_proj"])
+        layer.experts.radial_theta.copy_(inp["radial_theta"])
+        sh.gate_proj.weight.copy_(w["gate_proj"]); sh.up_proj.weight.copy_(w["up_proj"]); sh.down_proj.weight.copy_(w["down_proj"])
+    layer = layer.to(DEV).to(torch.bfloat16).train()
+    layer.gate.bias.data = inp["bias"].to(DEV)
+    layer.experts.radial_theta.data = inp["radial_theta"].to(DEV)
+    xg = inp["x"].to(torch.bfloat16).to(DEV).requires_grad_(True)
+    out = layer(xg.unsqueeze(0))[0]
+    (out * dout.to(torch.bfloat16).to(DEV)).sum().backward()
+    r = lambda t: t.to(torch.bfloat16).float()
+    c = {kk: (r(v) if kk in ("x", "w_router", "gate_up_proj", "down_proj") else v.clone()) for kk, v in inp.items()}
+    cw = {kk: r(v).requires_grad_(True) for kk, v in w.items()}
+    for kk in ("x", "w_router", "gate_up_proj", "down_proj", "radial_theta"):
+        c[kk].requires_grad_(True)
+    routed, _, idx, _, _ = orc.moe_forward(c["x"], c["w_router"], c["bias"], c["gate_up_proj"], c["down_proj"],
+                                           c["radial_theta"], k, return_routing=True)
+    ref = routed + orc.mlp_forward(c["x"], cw["gate_proj"], cw["up_proj"], cw["down_proj"])
+    (ref * r(dout)).sum().backward()
+    assert bool((layer.last_workspace.topk_idx.cpu().long() == idx).all()), "routing differs: gradients not comparable"
+    _bf16_close(out.detach(), ref.detach(), "out")
+    _bf16_close(xg.grad, c["x"].grad, "dx")
+    _bf16_close(sh.gate_proj.weight.grad, cw["gate_proj"].grad, "shared d_gate_proj")
+    _bf16_close(sh.up_proj.weight.grad, cw["up_proj"].grad, "shared d_up_proj")
+    _bf16_close(sh.down_proj.weight.grad, cw["down_proj"].grad, "shared d_down_proj")
+    _bf16_close(layer.experts.gate_up_proj.grad, c["gate_up_proj"].grad, "d_gate_up_proj")
+    _bf16_close(layer.gate.gate_proj.weight.grad, c["w_router"].grad, "d_w_router")
 
 
 def test_unsupported_mlp_inputs_are_refused():

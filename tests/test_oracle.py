@@ -116,8 +116,16 @@ def test_dense_mlp_oracle_matches_the_reference_fixture():
     rec = torch.load(GOLDEN / "mlp_dense.pt")
     w = orc.make_mlp_weights(rec["hidden"], rec["inter"], rec["seed"])
     x = torch.randn(rec["n_tokens"], rec["hidden"], generator=torch.Generator().manual_seed(rec["seed"] * 1000 + 1))
+    x.requires_grad_(True)
+    for v in w.values():
+        v.requires_grad_(True)
     out = orc.mlp_forward(x, w["gate_proj"], w["up_proj"], w["down_proj"])
-    assert rel_err(out, rec["out"]) < 1e-6
+    assert rel_err(out.detach(), rec["out"]) < 1e-6
+    (out * upstream_grad(rec)).sum().backward()
+    assert rel_err(x.grad, rec["dx"]) < 1e-5
+    for key in ("gate_proj", "up_proj", "down_proj"):
+        assert rel_err(w[key].grad[:8], rec[f"d_{key}_head"]) < 1e-5
+        assert digest_close(grad_digest(w[key].grad, rec["seed"]), rec[f"d_{key}_digest"], 1e-5)
 
 
 def test_layer_with_shared_expert_oracle_matches_the_reference_fixture():
