@@ -5,6 +5,7 @@ itself: class-level assignment wrapped in ``torch.compiler.disable``
     import bibo_b200
     bibo_b200.install()                      # BiBoMoELayer.forward -> kernel chain
     bibo_b200.install(seam="experts")        # only BiBoFusedExperts.forward(x, idx, w)
+    bibo_b200.install(seam="mlp")            # BiBoMLP.forward (dense layers, shared expert) -> SwiGLU kernels
     bibo_b200.uninstall()
 
 ``ref_moe_module`` is the reference's ``src.modeling.ffn.moe`` module (imported by default; pass it
@@ -15,6 +16,7 @@ from __future__ import annotations
 
 import torch
 
+from . import mlp as _mlp
 from . import moe as _moe
 
 _saved = {}
@@ -35,8 +37,15 @@ def install(ref_moe_module=None, seam: str = "layer") -> None:
         cls = ref_moe_module.BiBoFusedExperts
         _saved.setdefault((cls, "forward"), cls.forward)
         cls.forward = _nc(_moe.experts_forward_seam)
+    elif seam == "mlp":
+        # the MLP class lives next to the MoE module (src/modeling/ffn/mlp.py); the MoE module imports it
+        cls = getattr(ref_moe_module, "BiBoMLP", None)
+        if cls is None:
+            from src.modeling.ffn.mlp import BiBoMLP as cls
+        _saved.setdefault((cls, "forward"), cls.forward)
+        cls.forward = _nc(_mlp.mlp_module_forward)
     else:
-        raise ValueError(f"seam must be 'layer' or 'experts', got {seam!r}")
+        raise ValueError(f"seam must be 'layer', 'experts' or 'mlp', got {seam!r}")
 
 
 def uninstall() -> None:

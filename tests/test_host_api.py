@@ -105,3 +105,32 @@ def test_install_patches_reference_classes_and_state_dict_is_compatible():
     finally:
         bibo_b200.uninstall()
     assert ref.BiBoMoELayer.forward is orig
+
+
+@pytest.mark.skipif(not REF.exists(), reason="needs the reference checkout")
+def test_install_mlp_seam_and_shared_expert_state_dict():
+    sys.path.insert(0, str(REF))
+    sys.dont_write_bytecode = True
+    from src.configuration_bibo import BiBoConfig
+    from src.modeling.ffn import moe as ref
+    from src.modeling.ffn.mlp import BiBoMLP as RefMLP
+    import bibo_b200
+    cfg = BiBoConfig(vocab_size=512, hidden_size=64, num_hidden_layers=4, num_attention_heads=4, num_key_value_heads=2,
+                     intermediate_size=256, moe_intermediate_size=32, num_routed_experts=8, special_expert_pairs=0,
+                     num_experts_per_tok=2, use_shared_expert=True, shared_expert_type="mlp", num_shared_experts=2)
+    ref_layer = ref.BiBoMoELayer(cfg)
+    mine = bibo_b200.BiBoMoELayer(cfg)
+    mine.load_state_dict(ref_layer.state_dict())       # shared_experts_list.0.{gate,up,down}_proj.weight included
+    assert mine.shared_experts_list[0].intermediate_size == 64
+    dense = bibo_b200.BiBoMLP(cfg)                      # dense layer form: intermediate_size of the config
+    dense.load_state_dict(RefMLP(cfg).state_dict())
+    assert dense.gate_proj.weight.shape == (256, 64)
+    orig = RefMLP.forward
+    bibo_b200.install(ref, seam="mlp")
+    try:
+        assert RefMLP.forward is not orig
+        with torch.no_grad(), pytest.raises(RuntimeError, match="no CPU implementation"):
+            RefMLP(cfg)(torch.randn(4, 64))
+    finally:
+        bibo_b200.uninstall()
+    assert RefMLP.forward is orig
