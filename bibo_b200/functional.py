@@ -297,6 +297,20 @@ def experts_forward(x: torch.Tensor, topk_idx: torch.Tensor, topk_w: torch.Tenso
     return out, ws
 
 
+def rmsnorm_forward(h: torch.Tensor, weight: torch.Tensor, eps: float) -> torch.Tensor:
+    """BiBoRMSNorm.forward on flat rows h [N,H] (bibo_moe_rmsnorm_fwd)."""
+    lib = _lib.load()
+    _need_cuda(h, "hidden_states")
+    _need_cuda(weight, "norm weight")
+    if weight.dtype != h.dtype:
+        weight = weight.to(h.dtype)
+    out = torch.empty_like(h)
+    n, hidden = h.shape
+    _lib.check(lib.bibo_moe_rmsnorm_fwd(_lib.ptr(h), _lib.ptr(weight.contiguous()), float(eps), n, hidden,
+                                        dtype_code(h.dtype), _lib.ptr(out), _stream(h.device)), "bibo_moe_rmsnorm_fwd")
+    return out
+
+
 def mlp_forward(x: torch.Tensor, gate_proj: torch.Tensor, up_proj: torch.Tensor, down_proj: torch.Tensor,
                 out: Optional[torch.Tensor] = None, keep: bool = False):
     """Dense SwiGLU MLP ``down(silu(gate(x)) * up(x))`` on flat tokens x [N,H] (bibo_moe_mlp_forward);

@@ -6,6 +6,8 @@ itself: class-level assignment wrapped in ``torch.compiler.disable``
     bibo_b200.install()                      # BiBoMoELayer.forward -> kernel chain
     bibo_b200.install(seam="experts")        # only BiBoFusedExperts.forward(x, idx, w)
     bibo_b200.install(seam="mlp")            # BiBoMLP.forward (dense layers, shared expert) -> SwiGLU kernels
+    bibo_b200.install(seam="ffn")            # BiBoDecoderLayer._ffn_forward: norm + block + residual (the
+                                             # reference's own "megakernel" seam, patches.py:184-199,290)
     bibo_b200.uninstall()
 
 ``ref_moe_module`` is the reference's ``src.modeling.ffn.moe`` module (imported by default; pass it
@@ -44,8 +46,12 @@ def install(ref_moe_module=None, seam: str = "layer") -> None:
             from src.modeling.ffn.mlp import BiBoMLP as cls
         _saved.setdefault((cls, "forward"), cls.forward)
         cls.forward = _nc(_mlp.mlp_module_forward)
+    elif seam == "ffn":
+        from src.modeling.layers import BiBoDecoderLayer as cls
+        _saved.setdefault((cls, "_ffn_forward"), cls._ffn_forward)
+        cls._ffn_forward = _nc(_moe.ffn_forward)
     else:
-        raise ValueError(f"seam must be 'layer', 'experts' or 'mlp', got {seam!r}")
+        raise ValueError(f"seam must be 'layer', 'experts', 'mlp' or 'ffn', got {seam!r}")
 
 
 def uninstall() -> None:

@@ -246,11 +246,13 @@ def _balance_from_counts(layer, counts: torch.Tensor, num_tokens: int):
     return None
 
 
-def layer_forward(layer, hidden_states: torch.Tensor) -> torch.Tensor:
+def layer_forward(layer, hidden_states: torch.Tensor, residual: Optional[torch.Tensor] = None) -> torch.Tensor:
     """``BiBoMoELayer.forward`` (src/modeling/ffn/moe.py:157-183) on the CUDA kernel chain.
 
     Written against the REFERENCE's attribute names only, so it serves both this package's layer
     and, through ``bibo_b200.install``, an instance of the reference's own class.
+    ``residual`` (same shape; used by ``ffn_forward``) is added to the result, inside the combine
+    kernel when the layer has no shared expert.
     """
     bsz, seq_len, hidden = hidden_states.shape
     n = bsz * seq_len
@@ -263,6 +265,12 @@ def layer_forward(layer, hidden_states: torch.Tensor) -> torch.Tensor:
         if not hasattr(shared, "gate_proj"):
             raise NotImplementedError("bibo_b200: only the MLP shared expert is covered by the kernels")
         shared_out = mlp_module_forward(shared, flat)          # its own autograd node when gradients are on
+    late_residual = None
+    if residual is not None:
+        if shared_out is None:
+            shared_out = residual.reshape(n, hidden).contiguous()   # the combine kernel's second term
+        else:
+            late_residual = residual
     gate, ex = layer.gate, layer.experts
     n_pos, n_neg = ex.pos_end - ex.pos_start, ex.neg_end - ex.neg_start
     want_gap = gate._probe_gap and gate.top_k < gate.num_routed_experts
@@ -295,7 +303,37 @@ def layer_forward(layer, hidden_states: torch.Tensor) -> torch.Tensor:
         tpe = _balance_from_counts(layer, ws.counts(), n)
         if tpe is not None:
             layer.update_bias(tpe)
-    return out.view(bsz, seq_len, hidden)
+    out = out.view(bsz, seq_len, hidden)
+    return out if late_residual is None else late_residual + out
+
+
+def ffn_forward(decoder_layer, hidden_states: torch.Tensor) -> torch.Tensor:
+    """``BiBoDecoderLayer._ffn_forward`` (src/modeling/layers.py:57-67): post-attention RMSNorm, the
+    feed-forward block and the residual add.  Inference runs the norm kernel and folds the residual add
+    into the combine kernel; with gradients on, the norm stays the module's own (autograd provides its
+    backward) and the block runs through its autograd node.  Written against the reference's attribute
+    names (``post_attention_layernorm``, ``mlp``, ``_bf16_moe_out``, ``_bf16_stream``)."""
+    from .mlp import mlp_module_forward
+    mlp, norm = decoder_layer.mlp, decoder_layer.post_attention_layernorm
+    is_moe = hasattr(mlp, "gate") and hasattr(mlp, "experts")
+    block = (lambda x, res=None: layer_forward(mlp, x, res)) if is_moe else (lambda x, res=None: mlp_module_forward(mlp, x))
+    bf16_out = bool(getattr(decoder_layer, "_bf16_moe_out", False))
+    bf16_stream = bool(getattr(decoder_layer, "_bf16_stream", False))
+    needs_grad = torch.is_grad_enabled() and (hidden_states.requires_grad or
+                                              any(p.requires_grad for p in decoder_layer.parameters()))
+    plain = hidden_states.dtype == torch.bfloat16 or not (bf16_out or bf16_stream)   # the casts are no-ops
+    if needs_grad or not plain:
+        out = block(norm(hidden_states))
+        if bf16_out:
+            out = out.to(torch.bfloat16)
+        hidden_states = hidden_states + out
+        return hidden_states.to(torch.bfloat16) if bf16_stream else hidden_states
+    shape = hidden_states.shape
+    flat = hidden_states.reshape(-1, shape[-1]).contiguous()
+    x = Fn.rmsnorm_forward(flat, norm.weight, norm.variance_epsilon).view(shape)
+    if is_moe:
+        return block(x, hidden_states)
+    return hidden_states + block(x)
 
 
 def experts_forward_seam(experts, hidden_states: torch.Tensor, top_k_indices: torch.Tensor,

@@ -342,6 +342,14 @@ typedef struct {
 } bibo_moe_ep_bwd_args;
 int bibo_moe_ep_backward(const bibo_moe_ep_args* fwd, const bibo_moe_ep_bwd_args* bwd, void* stream);
 
+/* ---- RMSNorm in front of the block -------------------------------------------------------------------
+ * Replaces BiBoRMSNorm.forward (src/modeling/norm.py:19-24) where BiBoDecoderLayer._ffn_forward
+ * applies post_attention_layernorm before the feed-forward block (src/modeling/layers.py:57-67):
+ * out = weight * T(float(h) * rsqrt(mean(float(h)^2) + eps)), h / out [N,H], weight [H], all in dtype.
+ * The residual add of the same function is the `addend` of the combine kernel.                      */
+int bibo_moe_rmsnorm_fwd(const void* h, const void* weight, float eps, int64_t n_rows, int hidden, int dtype,
+                         void* out, void* stream);
+
 /* ---- dense SwiGLU MLP -----------------------------------------------------------------------------
  * Replaces BiBoMLP.forward, `down_proj(act_fn(gate_proj(x)) * up_proj(x))` with act = SiLU
  * (src/modeling/ffn/mlp.py:33-34): the shared expert of the MoE layer (src/modeling/ffn/moe.py:120-127,

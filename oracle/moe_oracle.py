@@ -235,6 +235,14 @@ def moe_forward(
     return out
 
 
+def rmsnorm(h: torch.Tensor, weight: torch.Tensor, eps: float = 1e-6):
+    """BiBoRMSNorm.forward (src/modeling/norm.py:19-24): fp32 statistics, the normalised value cast back to
+    the input dtype, then multiplied by the weight."""
+    v = h.to(torch.float32)
+    v = v * torch.rsqrt(v.pow(2).mean(-1, keepdim=True) + eps)
+    return weight * v.to(h.dtype)
+
+
 def mlp_forward(x: torch.Tensor, gate_proj: torch.Tensor, up_proj: torch.Tensor, down_proj: torch.Tensor):
     """Dense SwiGLU MLP, BiBoMLP.forward with hidden_act = "silu" (src/modeling/ffn/mlp.py:33-34):
     down_proj(silu(gate_proj(x)) * up_proj(x)); weights as nn.Linear stores them ([I,H], [I,H], [H,I])."""

@@ -150,6 +150,35 @@ def run_mlp_case(ref_root, name, n_tokens, hidden, inter, seed, shared_in_layer=
     print(f"{name}: out abs-mean {out.abs().mean():.4e}  {os.path.getsize(HERE / f'{name}.pt') / 1024:.0f} KiB")
 
 
+def run_ffn_case(ref_root, name, n_tokens, hidden, inter, n_experts, top_k, seed):
+    """BiBoDecoderLayer._ffn_forward of a MoE layer (src/modeling/layers.py:57-67): post-attention RMSNorm,
+    MoE block, residual add; fp32 on CPU.  The norm weight is 1 + 0.1 N(0,1) from its own generator."""
+    if ref_root not in sys.path:
+        sys.path.insert(0, ref_root)
+    from src.configuration_bibo import BiBoConfig
+    from src.modeling.layers import BiBoDecoderLayer
+    cfg = BiBoConfig(vocab_size=512, hidden_size=hidden, num_hidden_layers=4, num_attention_heads=4,
+                     num_key_value_heads=2, intermediate_size=4 * hidden, moe_intermediate_size=inter,
+                     num_routed_experts=n_experts, special_expert_pairs=0, num_experts_per_tok=top_k)
+    layer_idx = next(i for i in range(cfg.num_hidden_layers) if i not in cfg.mlp_only_layers)
+    dl = BiBoDecoderLayer(cfg, layer_idx=layer_idx).eval()
+    inp = orc.make_inputs(n_tokens, hidden, inter, n_experts, seed=seed, bias_mode="uniform", theta_std=0.5)
+    norm_w = 1.0 + 0.1 * torch.randn(hidden, generator=torch.Generator().manual_seed(seed * 1000 + 31))
+    with torch.no_grad():
+        dl.post_attention_layernorm.weight.copy_(norm_w)
+        dl.mlp.gate.gate_proj.weight.copy_(inp["w_router"])
+        dl.mlp.gate.bias.copy_(inp["bias"])
+        dl.mlp.experts.gate_up_proj.copy_(inp["gate_up_proj"])
+        dl.mlp.experts.down_proj.copy_(inp["down_proj"])
+        dl.mlp.experts.radial_theta.copy_(inp["radial_theta"])
+        out = dl._ffn_forward(inp["x"].reshape(1, n_tokens, hidden))[0]
+        normed = dl.post_attention_layernorm(inp["x"])
+    rec = dict(name=name, n_tokens=n_tokens, hidden=hidden, inter=inter, n_experts=n_experts, top_k=top_k, seed=seed,
+               eps=float(dl.post_attention_layernorm.variance_epsilon), out=out.clone(), normed=normed.clone())
+    torch.save(rec, HERE / f"{name}.pt")
+    print(f"{name}: out abs-mean {out.abs().mean():.4e}  {os.path.getsize(HERE / f'{name}.pt') / 1024:.0f} KiB")
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--reference", required=True)
@@ -172,6 +201,8 @@ def main():
     # dense SwiGLU MLP alone and as the shared expert of the layer (shapes the tensor-core kernels accept)
     run_mlp_case(r, "mlp_dense", 300, 256, 512, seed=7)
     run_mlp_case(r, "layer_shared_expert", 300, 256, 512, seed=8, shared_in_layer=True, moe_inter=256, n_shared=2)
+    # the decoder layer's feed-forward half: RMSNorm + MoE block + residual
+    run_ffn_case(r, "ffn_moe", 300, 256, 256, 64, 6, seed=9)
 
 
 if __name__ == "__main__":

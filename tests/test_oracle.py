@@ -138,3 +138,16 @@ def test_layer_with_shared_expert_oracle_matches_the_reference_fixture():
                              inp["radial_theta"], rec["top_k"])
     out = routed + orc.mlp_forward(inp["x"], w["gate_proj"], w["up_proj"], w["down_proj"])
     assert rel_err(out, rec["out"]) < 1e-6
+
+
+def test_ffn_half_of_the_decoder_layer_oracle_matches_the_reference_fixture():
+    """RMSNorm + MoE block + residual (BiBoDecoderLayer._ffn_forward, src/modeling/layers.py:57-67), fp32."""
+    rec = torch.load(GOLDEN / "ffn_moe.pt")
+    inp = orc.make_inputs(rec["n_tokens"], rec["hidden"], rec["inter"], rec["n_experts"], seed=rec["seed"],
+                          bias_mode="uniform", theta_std=0.5)
+    norm_w = 1.0 + 0.1 * torch.randn(rec["hidden"], generator=torch.Generator().manual_seed(rec["seed"] * 1000 + 31))
+    x = orc.rmsnorm(inp["x"], norm_w, rec["eps"])
+    assert rel_err(x, rec["normed"]) < 1e-6
+    out = inp["x"] + orc.moe_forward(x, inp["w_router"], inp["bias"], inp["gate_up_proj"], inp["down_proj"],
+                                     inp["radial_theta"], rec["top_k"])
+    assert rel_err(out, rec["out"]) < 1e-6
