@@ -134,3 +134,13 @@ def test_install_mlp_seam_and_shared_expert_state_dict():
     finally:
         bibo_b200.uninstall()
     assert RefMLP.forward is orig
+    from src.modeling.layers import BiBoDecoderLayer
+    orig_ffn = BiBoDecoderLayer._ffn_forward
+    bibo_b200.install(ref, seam="ffn")
+    try:
+        assert BiBoDecoderLayer._ffn_forward is not orig_ffn
+    finally:
+        bibo_b200.uninstall()
+    assert BiBoDecoderLayer._ffn_forward is orig_ffn
+    with pytest.raises(ValueError):
+        bibo_b200.install(ref, seam="attention")
