@@ -71,6 +71,26 @@ def synth(wl, device, seed, rank=0, dtype=torch.bfloat16):
     return t
 
 
+def bind_to_gpu_cpus(index):
+    """Pin this process to the CPUs NVML reports as local to GPU `index` (read-only query), so that the
+    pinned host buffers of the end-to-end path are allocated on the GPU's own NUMA node.  Several ranks
+    copying over PCIe at once otherwise all pull from one socket's memory.  Returns the CPU count or None."""
+    try:
+        import pynvml
+        pynvml.nvmlInit()
+        h = pynvml.nvmlDeviceGetHandleByIndex(index)
+        words = (os.cpu_count() + 63) // 64
+        mask = pynvml.nvmlDeviceGetCpuAffinity(h, words)
+        cpus = {w * 64 + b for w, m in enumerate(mask) for b in range(64) if (m >> b) & 1}
+        cpus &= os.sched_getaffinity(0)
+        if cpus:
+            os.sched_setaffinity(0, cpus)
+            return len(cpus)
+    except Exception:
+        pass
+    return None
+
+
 class ClockSampler(threading.Thread):
     """Samples SM clock and throttle reasons through NVML while the timed region runs (read-only)."""
     BITS = {0x8: "hw_slowdown", 0x40: "hw_thermal_slowdown", 0x20: "sw_thermal_slowdown", 0x4: "sw_power_cap"}
@@ -185,6 +205,8 @@ def main():
     ap.add_argument("--ep-exchange", default="kernel", choices=["copy", "kernel"],
                     help="N>1: rows travel by peer copies on the copy engines, or by the dispatch/combine kernels")
     ap.add_argument("--copy-streams", type=int, default=0, help="copy exchange: 1 = one stream per peer, 0 = one stream")
+    ap.add_argument("--no-numa-bind", action="store_true",
+                    help="N>1: do not pin each rank to the CPUs local to its GPU (pinned host buffers then land anywhere)")
     ap.add_argument("--e2e-chunks", type=int, default=4, help="token slices of the host-buffer (e2e) forward (N>1)")
     ap.add_argument("--comm-sms", type=int, default=20, help="SMs left to the exchange kernels (N>1)")
     ap.add_argument("--mode", default="fwd", choices=["fwd", "fwdbwd"],
@@ -204,6 +226,8 @@ def main():
     dev = torch.device("cuda", local)
     if world > 1:
         dist.init_process_group("nccl", device_id=dev)
+        if not args.no_numa_bind:
+            bind_to_gpu_cpus(local)
     t = synth(wl, dev, seed=1234, rank=rank)
     n, h, i = wl["n_tokens"], wl["hidden"], wl["inter"]
     dtype = torch.bfloat16
