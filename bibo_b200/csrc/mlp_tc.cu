@@ -22,6 +22,8 @@ int gemm2_tc_launch(const void* h, const void* down_proj, const PlanView& pv, in
 namespace tc {
 
 constexpr int M_NC = 256, M_STAGES = 5;
+constexpr int M_EG = 2;                                  // epilogue groups of four warps; group e drains 64-column
+constexpr int M_THREADS = 64 + EPI_THREADS * M_EG;       // sub-blocks 2e and 2e+1 of both accumulators
 constexpr int M_BH_BYTES = (M_NC / 2) * BK * 2;
 constexpr int M_OFF_A = 0;
 constexpr int M_OFF_B = M_OFF_A + M_STAGES * A_BYTES;
@@ -55,7 +57,7 @@ __global__ void mlp_plan_kernel(int64_t n_tokens, int32_t* __restrict__ plan) {
 }
 
 // Work item w = pair * n_cblocks + column block.  Cluster of two CTAs = one MMA pair.
-__global__ void __launch_bounds__(NUM_THREADS, 1)
+__global__ void __launch_bounds__(M_THREADS, 1)
 mlp_gemm1_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmG,
                       const __grid_constant__ CUtensorMap tmU, const __grid_constant__ CUtensorMap tmH,
                       int32_t* __restrict__ plan, int64_t tiles_off, int64_t pairs_off, int k_blocks, int n_cblocks,
@@ -81,7 +83,7 @@ mlp_gemm1_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1); }
     mbar_init(gfull, 1); mbar_init(ufull, 1);
-    mbar_init(gempty, 8); mbar_init(uempty, 8);
+    mbar_init(gempty, 8 * M_EG); mbar_init(uempty, 8 * M_EG);   // 4 warps x groups x 2 CTAs
     *abort_flag = 0;
     fence_barrier_init();
     prefetch_tmap(&tmA); prefetch_tmap(&tmG); prefetch_tmap(&tmU); prefetch_tmap(&tmH);
@@ -148,7 +150,10 @@ mlp_gemm1_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
   } else {
     const int q = warp & 3;
     const int row = q * 32 + lane;
-    const bool issuer = (threadIdx.x == 64);
+    const int eg = (warp - 2) >> 2;                         // epilogue group
+    constexpr int SUBS = (M_NC / 64) / M_EG;               // sub-blocks per group
+    const int c_lo = eg * SUBS, c_hi = c_lo + SUBS;
+    const bool issuer = (threadIdx.x == 64 + eg * EPI_THREADS);
     const uint32_t lane_addr = tmem_base + ((uint32_t)(q * 32) << 16);
     unsigned char* stash = smem + M_OFF_STASH;
     uint32_t it = 0;
@@ -157,12 +162,12 @@ mlp_gemm1_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
       const int cb = w % n_cblocks;
       const bool twin = (pr == 1 && pp.y < 0);     // duplicate of the leader's tile: compute, write nothing
       const int4 t = tiles[(pr == 1 && pp.y >= 0) ? pp.y : pp.x];
-      if (issuer) tma_store_wait_read();           // the previous item's stores are done with the stash
-      named_bar_sync(1, EPI_THREADS);
+      if (issuer) tma_store_wait_read();           // this group's previous stores are done with its sub-blocks
+      named_bar_sync(1 + eg, EPI_THREADS);
       if (!mbar_wait(gfull, it & 1, abort_flag)) break;
       tc_fence_after();
 #pragma unroll 1
-      for (int c = 0; c < NC / 64; ++c) {          // gate -> bf16 -> stash
+      for (int c = c_lo; c < c_hi; ++c) {          // gate -> bf16 -> stash
         uint32_t r0[32], r1[32];
         tmem_ld32(lane_addr + c * 64, r0);
         tmem_ld32(lane_addr + c * 64 + 32, r1);
@@ -192,7 +197,7 @@ mlp_gemm1_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
       __nv_bfloat16* gu_row = (gate_up_out && !twin && t.y + row < n_rows)
                                   ? gate_up_out + (int64_t)(t.y + row) * 2 * inter + cb * NC : nullptr;
 #pragma unroll 1
-      for (int c2 = 0; c2 < NC / 64; ++c2) {       // h = bf16(silu(gate)) * bf16(up), in place in the stash
+      for (int c2 = c_lo; c2 < c_hi; ++c2) {       // h = bf16(silu(gate)) * bf16(up), in place in the stash
         uint32_t rr0[32], rr1[32];
         tmem_ld32(lane_addr + NC + c2 * 64, rr0);
         tmem_ld32(lane_addr + NC + c2 * 64 + 32, rr1);
@@ -237,10 +242,9 @@ mlp_gemm1_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
       __syncwarp();
       if (lane == 0) mbar_arrive_cluster_addr(map_to_cta(uempty, leader));
       fence_proxy_async_smem();
-      named_bar_sync(1, EPI_THREADS);
+      named_bar_sync(1 + eg, EPI_THREADS);
       if (issuer && !twin) {
-#pragma unroll
-        for (int s = 0; s < NC / 64; ++s) tma_store_2d(&tmH, stash + s * C_SUB, cb * NC + s * 64, t.y);
+        for (int s = c_lo; s < c_hi; ++s) tma_store_2d(&tmH, stash + s * C_SUB, cb * NC + s * 64, t.y);
         tma_store_commit();
       }
     }
@@ -302,7 +306,7 @@ extern "C" int bibo_moe_mlp_forward(const void* x, const void* gate_proj, const 
   static int max_clusters = 0;
   static int sms = 0;
   cudaLaunchConfig_t cfg = {};
-  cfg.blockDim = dim3(NUM_THREADS);
+  cfg.blockDim = dim3(M_THREADS);
   cfg.dynamicSmemBytes = M_SMEM;
   cfg.stream = st;
   cudaLaunchAttribute attr[1];
