@@ -170,7 +170,7 @@ extern "C" int bibo_moe_forward_host(const bibo_moe_shape* s, const void* x_host
                                      const void* down_proj, const float* theta,
                                      const bibo_moe_workspace* ws, void* out_dev, void* out_host,
                                      void* stream) {
-  if (!s || !x_host || !x_dev || !out_dev || !out_host) return fail(BIBO_ERR_ARG, "forward_host: null pointer");
+  if (!s || !ws || !x_host || !x_dev || !out_dev || !out_host) return fail(BIBO_ERR_ARG, "forward_host: null pointer");
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   const size_t row_bytes = (size_t)s->hidden * (s->dtype == BIBO_F32 ? 4 : 2);
   int64_t lens[HOST_MAX_SLICES];
@@ -202,9 +202,11 @@ extern "C" int bibo_moe_forward_host(const bibo_moe_shape* s, const void* x_host
     const int64_t nt = lens[i];
     bibo_moe_shape part = *s;
     part.n_tokens = nt;                               // the workspace of the whole batch is large enough for a slice
+    bibo_moe_workspace wpart = *ws;
+    if (wpart.addend) wpart.addend = static_cast<const char*>(ws->addend) + t0 * row_bytes;   // per-token tensor
     BIBO_CUDA(cudaStreamWaitEvent(st, hp->copied[i], 0));
     rc = bibo_moe_forward(&part, static_cast<const char*>(x_dev) + t0 * row_bytes, w_router, bias, gate_up_proj,
-                          down_proj, theta, ws, static_cast<char*>(out_dev) + t0 * row_bytes, stream);
+                          down_proj, theta, &wpart, static_cast<char*>(out_dev) + t0 * row_bytes, stream);
     if (rc) return rc;
     BIBO_CUDA(cudaEventRecord(hp->computed[i], st));
     BIBO_CUDA(cudaStreamWaitEvent(hp->out, hp->computed[i], 0));
