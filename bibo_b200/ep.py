@@ -409,3 +409,121 @@ class PipelinedExpertParallelMoE:
 
     def status(self) -> int:
         return max(lane.status() for lane in self.lanes)
+
+
+# ---- module interface --------------------------------------------------------------------------------
+class _EPBlockFunction(torch.autograd.Function):
+    """Expert-parallel forward / backward as one autograd node (bibo_moe_ep_forward / _backward)."""
+
+    @staticmethod
+    def forward(ctx, x, w_router, gate_up, down, theta, layer):
+        runner = layer._runner
+        out = runner.forward(x, training=True)
+        ctx.layer = layer
+        return out
+
+    @staticmethod
+    def backward(ctx, dout):
+        layer = ctx.layer
+        dx, d_wr, d_gu, d_dn, d_th = layer._runner.backward(dout.contiguous())
+        if layer.reduce_router_grad and layer._runner.world > 1:
+            # the router is replicated and the tokens are data-parallel: its gradient is the sum over ranks
+            acc = d_wr.float()
+            dist.all_reduce(acc, group=layer.group)
+            d_wr = acc.to(d_wr.dtype)
+        return dx, d_wr, d_gu, d_dn, d_th.to(layer.radial_theta.dtype), None
+
+
+class ExpertParallelMoELayer(torch.nn.Module):
+    """``BiBoMoELayer`` with the experts sharded over a process group (one rank per GPU of one box).
+
+    Same ``forward([B,S,H]) -> [B,S,H]`` and balancer semantics as the single-GPU layer
+    (src/modeling/ffn/moe.py:104-183); the reference itself has no expert parallelism.  Every rank keeps the
+    full router (``gate``, replicated) and the E/world experts ``[rank*E/world, (rank+1)*E/world)`` as
+    ``gate_up_proj [E/world, 2I, H]``, ``down_proj [E/world, H, I]``, ``radial_theta [E/world]``; tokens stay
+    on their rank.  Training runs through one autograd node; the router weight gradient is all-reduced over
+    the group (``reduce_router_grad``), expert gradients stay with their owner.  bf16, no ±Identity
+    experts, no shared expert.
+    """
+
+    def __init__(self, config, group=None, capacity_factor: float = 2.0, reduce_router_grad: bool = True):
+        super().__init__()
+        from .moe import BiBoMoERouter, _cfg
+        self.group = group if group is not None else dist.group.WORLD
+        self.rank, self.world = dist.get_rank(self.group), dist.get_world_size(self.group)
+        e = config.num_routed_experts
+        n_special = int(_cfg(config, "num_pos_identity_experts", 0)) + int(_cfg(config, "num_neg_identity_experts", 0))
+        if n_special == 0 and _cfg(config, "special_expert_pairs", 0):
+            n_special = 2 * int(config.special_expert_pairs)
+        if n_special or _cfg(config, "use_shared_expert", False):
+            raise NotImplementedError("ExpertParallelMoELayer: identity and shared experts are not sharded")
+        if e % self.world:
+            raise RuntimeError(f"{e} experts do not shard evenly over {self.world} ranks")
+        self.num_routed_experts, self.el = e, e // self.world
+        h, i = config.hidden_size, config.moe_intermediate_size
+        std = float(_cfg(config, "initializer_range", 0.02))
+        self.gate = BiBoMoERouter(config)
+        self.gate_up_proj = torch.nn.Parameter(torch.randn(self.el, 2 * i, h) * std)
+        self.down_proj = torch.nn.Parameter(torch.randn(self.el, h, i) * std)
+        self.radial_theta = torch.nn.Parameter(torch.zeros(self.el))
+        self.register_buffer("accumulated_tpe", torch.zeros(e, dtype=torch.float))
+        self.bias_update_factor = _cfg(config, "bias_update_factor", 0.4)
+        self.bias_update_threshold = _cfg(config, "bias_update_threshold", 8000)
+        self._fwd_step, self._update_every = 0, None
+        self.capacity_factor, self.reduce_router_grad = capacity_factor, reduce_router_grad
+        self._runner, self._runner_key = None, None
+
+    @classmethod
+    def from_full_layer(cls, layer, config, group=None, **kw):
+        """Shard a single-GPU ``BiBoMoELayer`` (or the reference's) into this rank's slice."""
+        ep = cls(config, group, **kw)
+        lo, hi = ep.rank * ep.el, (ep.rank + 1) * ep.el
+        with torch.no_grad():
+            ep.gate.gate_proj.weight.copy_(layer.gate.gate_proj.weight)
+            ep.gate.bias.copy_(layer.gate.bias)
+            ep.gate_up_proj.copy_(layer.experts.gate_up_proj[lo:hi])
+            ep.down_proj.copy_(layer.experts.down_proj[lo:hi])
+            ep.radial_theta.copy_(layer.experts.radial_theta[lo:hi])
+        return ep
+
+    @torch.no_grad()
+    def update_bias(self, tokens_per_expert: torch.Tensor):
+        """src/modeling/ffn/moe.py:131-137 (proportional bias update)."""
+        if self.bias_update_factor <= 0:
+            return
+        share = tokens_per_expert.detach().float()
+        share = share / share.sum().clamp_min(1.0)
+        self.gate.bias.add_(self.bias_update_factor * (share.mean() - share))
+
+    def _get_runner(self) -> ExpertParallelMoE:
+        w = dict(w_router=self.gate.gate_proj.weight.data, bias=self.gate.bias.data, gate_up_proj=self.gate_up_proj.data,
+                 down_proj=self.down_proj.data, radial_theta=self.radial_theta.data)
+        key = tuple(t.data_ptr() for t in w.values())
+        if self._runner is None or key != self._runner_key:     # first call, or the parameters were moved / cast
+            self._runner = ExpertParallelMoE(w, self.gate.top_k, self.group, norm_mode=self.gate.norm_topk_prob,
+                                             scale=float(getattr(self.gate, "routed_scaling_factor", 1.0)),
+                                             capacity_factor=self.capacity_factor)
+            self._runner_key = key
+        # the runner keeps fp32 copies of bias / theta when the parameters are not fp32: refresh them
+        r = self._runner
+        if r.bias.data_ptr() != self.gate.bias.data_ptr():
+            r.bias.copy_(self.gate.bias.data)
+        if r.theta.data_ptr() != self.radial_theta.data_ptr():
+            r.theta.copy_(self.radial_theta.data)
+        return r
+
+    def forward(self, hidden_states: torch.Tensor) -> torch.Tensor:
+        from .moe import _balance_from_counts
+        bsz, seq_len, hidden = hidden_states.shape
+        flat = hidden_states.reshape(-1, hidden).contiguous()
+        runner = self._get_runner()
+        params = (self.gate.gate_proj.weight, self.gate_up_proj, self.down_proj, self.radial_theta)
+        if torch.is_grad_enabled() and (flat.requires_grad or any(p.requires_grad for p in params)):
+            out = _EPBlockFunction.apply(flat, *params, self)
+        else:
+            out = runner.forward(flat)
+        if self.training and self.bias_update_factor > 0:
+            tpe = _balance_from_counts(self, runner._counts, flat.shape[0])   # all-reduces accumulated_tpe
+            if tpe is not None:
+                self.update_bias(tpe)
+        return out.view(bsz, seq_len, hidden)

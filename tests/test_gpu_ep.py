@@ -34,3 +34,11 @@ def test_expert_parallel_backward_matches_oracle_autograd(args):
     world = 2 if torch.cuda.device_count() < 4 else 4
     r = _run(world, args, port=29547, worker="ep_bwd_worker.py")
     assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs at least 2 GPUs")
+def test_expert_parallel_module_trains_like_the_single_gpu_layer():
+    world = 2 if torch.cuda.device_count() < 4 else 4
+    r = _run(world, (1200, 512, 256, 64, 6), port=29553, worker="ep_module_worker.py")
+    assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]
+    assert "forward identical True" in r.stdout
