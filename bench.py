@@ -36,6 +36,8 @@ WORKLOADS = {
     "c2": dict(n_tokens=16384, hidden=1024, inter=256, bias="uniform", zipf_alpha=0.0),
     "c3": dict(n_tokens=65536, hidden=2048, inter=512, bias="zipf", zipf_alpha=1.0),
     "c3a": dict(n_tokens=65536, hidden=2048, inter=512, bias="zipf", zipf_alpha=0.07),
+    # one MoE layer of benchmark configuration 5 (batch 8 x 4096 tokens, hidden 1024, intermediate 256)
+    "c5layer": dict(n_tokens=32768, hidden=1024, inter=256, bias="uniform", zipf_alpha=0.0),
 }
 N_EXPERTS, TOP_K = 64, 6
 METRIC, UNIT = "moe_layer_fwd_tokens_per_s", "tokens/s"
