@@ -8,7 +8,7 @@
 namespace bibo {
 // gemm_simt.cu
 int gemm_simt_launch(const void* A, const void* B, void* C, const PlanView& pv, int k_dim, int n_out, int dtype,
-                     cudaStream_t st);
+                     cudaStream_t st, int ldc = 0, int64_t row_limit = INT64_MAX);
 int radial_rows_launch(const void* gate_up, const float* theta, const PlanView& pv, int inter, int dtype, void* h,
                        float* rnorm_out, cudaStream_t st);
 // gemm_tc.cu

@@ -8,11 +8,13 @@ namespace bibo {
 constexpr int GM = BIBO_TILE_M, GN = 64, GK = 16;
 
 // C[row, n] = sum_k A[row, k] * B[e][n, k] over the row tiles of the plan.
-// grid = (tiles_cap, ceil(n_out / GN)); tile t belongs to expert tiles[t].x.
+// grid = (tiles_cap, ceil(n_out / GN)); tile t belongs to expert tiles[t].x.  ldc = row pitch of C in
+// elements; rows >= row_limit are neither read nor written (buffers without padding rows).
 template <typename T>
 __global__ void __launch_bounds__(256)
 grouped_gemm_simt_kernel(const T* __restrict__ A, const T* __restrict__ B, T* __restrict__ C,
-                         const int32_t* __restrict__ plan, int64_t tiles_off, int k_dim, int n_out) {
+                         const int32_t* __restrict__ plan, int64_t tiles_off, int k_dim, int n_out, int ldc,
+                         int64_t row_limit) {
   if ((int)blockIdx.x >= plan[PLAN_N_TILES]) return;
   const int4 tile = reinterpret_cast<const int4*>(plan + tiles_off)[blockIdx.x];
   const int e = tile.x, row0 = tile.y;
@@ -30,7 +32,7 @@ grouped_gemm_simt_kernel(const T* __restrict__ A, const T* __restrict__ B, T* __
   for (int k0 = 0; k0 < k_dim; k0 += GK) {
     for (int i = tid; i < GM * GK; i += 256) {
       int r = i / GK, c = i % GK;
-      As[c][r] = (k0 + c < k_dim) ? to_f32<T>(Ab[(int64_t)r * k_dim + k0 + c]) : 0.f;
+      As[c][r] = (k0 + c < k_dim && row0 + r < row_limit) ? to_f32<T>(Ab[(int64_t)r * k_dim + k0 + c]) : 0.f;
     }
     for (int i = tid; i < GN * GK; i += 256) {
       int r = i / GK, c = i % GK;
@@ -56,7 +58,7 @@ grouped_gemm_simt_kernel(const T* __restrict__ A, const T* __restrict__ B, T* __
 #pragma unroll
     for (int j = 0; j < 4; ++j) {
       int n = n0 + tx * 4 + j;
-      if (n < n_out) C[(int64_t)(row0 + ty * 8 + i) * n_out + n] = from_f32<T>(acc[i][j]);
+      if (n < n_out && row0 + ty * 8 + i < row_limit) C[(int64_t)(row0 + ty * 8 + i) * ldc + n] = from_f32<T>(acc[i][j]);
     }
 }
 
@@ -93,15 +95,42 @@ radial_rows_kernel(const T* __restrict__ gate_up, const float* __restrict__ thet
 }
 
 int gemm_simt_launch(const void* A, const void* B, void* C, const PlanView& pv, int k_dim, int n_out, int dtype,
-                     cudaStream_t st) {
+                     cudaStream_t st, int ldc, int64_t row_limit) {
+  if (ldc <= 0) ldc = n_out;
   dim3 grid((unsigned)pv.tiles_cap, (unsigned)((n_out + GN - 1) / GN));
   if (dtype == BIBO_F32)
     grouped_gemm_simt_kernel<float><<<grid, 256, 0, st>>>((const float*)A, (const float*)B, (float*)C, pv.plan,
-                                                          pv.tiles_off, k_dim, n_out);
+                                                          pv.tiles_off, k_dim, n_out, ldc, row_limit);
   else
     grouped_gemm_simt_kernel<__nv_bfloat16><<<grid, 256, 0, st>>>(
-        (const __nv_bfloat16*)A, (const __nv_bfloat16*)B, (__nv_bfloat16*)C, pv.plan, pv.tiles_off, k_dim, n_out);
+        (const __nv_bfloat16*)A, (const __nv_bfloat16*)B, (__nv_bfloat16*)C, pv.plan, pv.tiles_off, k_dim, n_out, ldc,
+        row_limit);
   BIBO_CHECK_LAUNCH("grouped_gemm_simt_kernel");
+  return BIBO_OK;
+}
+
+// h[r, i] = T(T(silu(g)) * u) on gate | up rows [rows, 2I]   (dense SwiGLU MLP, src/modeling/ffn/mlp.py:33-34)
+template <typename T>
+__global__ void __launch_bounds__(256)
+swiglu_rows_kernel(const T* __restrict__ gate_up, int64_t n_rows, int inter, T* __restrict__ h) {
+  const int64_t i = (int64_t)blockIdx.x * 256 + threadIdx.x;
+  if (i >= n_rows * inter) return;
+  const int64_t r = i / inter;
+  const int c = (int)(i % inter);
+  const float g = to_f32<T>(gate_up[r * 2 * inter + c]);
+  const float u = to_f32<T>(gate_up[r * 2 * inter + inter + c]);
+  const T a = from_f32<T>(__fdiv_rn(g, 1.0f + expf(-g)));
+  h[i] = from_f32<T>(to_f32<T>(a) * u);
+}
+
+int swiglu_rows_launch(const void* gate_up, int64_t n_rows, int inter, int dtype, void* h, cudaStream_t st) {
+  const unsigned grid = (unsigned)((n_rows * inter + 255) / 256);
+  if (dtype == BIBO_F32)
+    swiglu_rows_kernel<float><<<grid, 256, 0, st>>>((const float*)gate_up, n_rows, inter, (float*)h);
+  else
+    swiglu_rows_kernel<__nv_bfloat16><<<grid, 256, 0, st>>>((const __nv_bfloat16*)gate_up, n_rows, inter,
+                                                           (__nv_bfloat16*)h);
+  BIBO_CHECK_LAUNCH("swiglu_rows_kernel");
   return BIBO_OK;
 }
 

@@ -14,6 +14,10 @@
 #include "tc_common.cuh"
 
 namespace bibo {
+// gemm_simt.cu
+int gemm_simt_launch(const void* A, const void* B, void* C, const PlanView& pv, int k_dim, int n_out, int dtype,
+                     cudaStream_t st, int ldc, int64_t row_limit);
+int swiglu_rows_launch(const void* gate_up, int64_t n_rows, int inter, int dtype, void* h, cudaStream_t st);
 // gemm_tc.cu
 int gemm2_tc_supported(int hidden, int inter, int dtype);
 int gemm2_tc_launch(const void* h, const void* down_proj, const PlanView& pv, int hidden, int inter,
@@ -276,13 +280,36 @@ extern "C" int bibo_moe_mlp_forward(const void* x, const void* gate_proj, const 
   if (n_tokens <= 0) return BIBO_OK;
   if (!x || !gate_proj || !up_proj || !down_proj || !plan || !h || !y)
     return fail(BIBO_ERR_ARG, "mlp_forward: null pointer");
-  if (!bibo_moe_mlp_supported(hidden, inter, dtype))
-    return fail(BIBO_ERR_UNSUPPORTED, "mlp_forward: needs bf16, hidden %% 256 == 0, intermediate %% 256 == 0 (got %d, %d)",
-                hidden, inter);
+  if (dtype != BIBO_F32 && dtype != BIBO_BF16) return fail(BIBO_ERR_ARG, "mlp_forward: dtype=%d", dtype);
+  if (n_tokens > 0x7fffff00LL) return fail(BIBO_ERR_UNSUPPORTED, "mlp_forward: n_tokens=%lld", (long long)n_tokens);
+  if (!bibo_moe_mlp_supported(hidden, inter, dtype)) {
+    // float32 (the 1e-4 parity bar rules out tensor cores) and shapes outside the tensor-core kernels:
+    // CUDA-core GEMMs into the gate | up buffer, an elementwise SwiGLU, a CUDA-core down GEMM
+    if (!gate_up_out)
+      return fail(BIBO_ERR_ARG, "mlp_forward: this dtype/shape runs the CUDA-core path and needs the gate_up buffer");
+    cudaStream_t st0 = static_cast<cudaStream_t>(stream);
+    const int nt = (int)mlp_tiles(n_tokens);
+    BIBO_CUDA(cudaMemsetAsync(plan, 0, 4 * sizeof(int32_t), st0));
+    mlp_plan_kernel<<<(nt + 255) / 256, 256, 0, st0>>>(n_tokens, plan);
+    BIBO_CHECK_LAUNCH("mlp_plan_kernel");
+    PlanView pv0 = {};
+    pv0.plan = plan;
+    pv0.tiles_off = mlp_off_tiles();
+    pv0.pairs_off = mlp_off_pairs(n_tokens);
+    pv0.tiles_cap = nt;
+    pv0.rows_alloc = n_tokens;
+    const size_t es = dtype == BIBO_F32 ? 4 : 2;
+    int rc0;
+    if ((rc0 = gemm_simt_launch(x, gate_proj, gate_up_out, pv0, hidden, inter, dtype, st0, 2 * inter, n_tokens))) return rc0;
+    if ((rc0 = gemm_simt_launch(x, up_proj, static_cast<char*>(gate_up_out) + (size_t)inter * es, pv0, hidden, inter, dtype,
+                                st0, 2 * inter, n_tokens)))
+      return rc0;
+    if ((rc0 = swiglu_rows_launch(gate_up_out, n_tokens, inter, dtype, h, st0))) return rc0;
+    return gemm_simt_launch(h, down_proj, y, pv0, inter, hidden, dtype, st0, hidden, n_tokens);
+  }
   if (!aligned16(x) || !aligned16(gate_proj) || !aligned16(up_proj) || !aligned16(down_proj) || !aligned16(h) ||
       !aligned16(y) || !aligned16(gate_up_out))
     return fail(BIBO_ERR_ALIGN, "mlp_forward: pointers must be 16-byte aligned");
-  if (n_tokens > 0x7fffff00LL) return fail(BIBO_ERR_UNSUPPORTED, "mlp_forward: n_tokens=%lld", (long long)n_tokens);
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   const int n_tiles = (int)mlp_tiles(n_tokens);
   BIBO_CUDA(cudaMemsetAsync(plan, 0, 4 * sizeof(int32_t), st));

@@ -324,8 +324,11 @@ def mlp_forward(x: torch.Tensor, gate_proj: torch.Tensor, up_proj: torch.Tensor,
     n, hidden = x.shape
     inter = gate_proj.shape[0]
     dt = dtype_code(x.dtype)
-    if not lib.bibo_moe_mlp_supported(hidden, inter, dt):
-        raise RuntimeError(f"bibo_b200: the dense MLP kernels take bf16 with hidden % 256 == 0 and intermediate % 256 "
+    # bf16 with hidden % 256 == 0 and intermediate % 256 == 0 runs on tensor cores; float32 and other shapes run
+    # the CUDA-core kernels (forward only), which stage gate | up in a buffer
+    tensor_cores = bool(lib.bibo_moe_mlp_supported(hidden, inter, dt))
+    if keep and not tensor_cores:
+        raise RuntimeError(f"bibo_b200: the dense MLP backward needs bf16 with hidden % 256 == 0 and intermediate % 256 "
                            f"== 0 (got {x.dtype}, {hidden}, {inter})")
     if out is None:
         out = torch.empty_like(x)
@@ -333,7 +336,7 @@ def mlp_forward(x: torch.Tensor, gate_proj: torch.Tensor, up_proj: torch.Tensor,
         return (out, None) if keep else out
     plan = torch.empty(int(lib.bibo_moe_mlp_plan_words(n)), dtype=torch.int32, device=x.device)
     h = torch.empty(n, inter, dtype=x.dtype, device=x.device)
-    gate_up = torch.empty(n, 2 * inter, dtype=x.dtype, device=x.device) if keep else None
+    gate_up = torch.empty(n, 2 * inter, dtype=x.dtype, device=x.device) if (keep or not tensor_cores) else None
     p = _lib.ptr
     _lib.check(lib.bibo_moe_mlp_forward(p(x), p(gate_proj), p(up_proj), p(down_proj), n, hidden, inter, dt, p(plan),
                                         p(h), p(out), p(gate_up), _stream(x.device)), "bibo_moe_mlp_forward")

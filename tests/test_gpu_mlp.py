@@ -173,6 +173,32 @@ def test_layer_with_shared_expert_trains():
     _bf16_close(layer.gate.gate_proj.weight.grad, c["w_router"].grad, "d_w_router")
 
 
+def test_dense_mlp_fp32_matches_the_reference_fixture():
+    """float32 runs the CUDA-core kernels: 1e-4 against the reference's own fp32 output."""
+    from bibo_b200 import functional as Fn
+    rec = torch.load(GOLDEN / "mlp_dense.pt")
+    w = {k: v.to(DEV) for k, v in orc.make_mlp_weights(rec["hidden"], rec["inter"], rec["seed"]).items()}
+    x = torch.randn(rec["n_tokens"], rec["hidden"], generator=torch.Generator().manual_seed(rec["seed"] * 1000 + 1))
+    out = Fn.mlp_forward(x.to(DEV), w["gate_proj"], w["up_proj"], w["down_proj"])
+    torch.cuda.synchronize()
+    assert rel_err(out.cpu(), rec["out"]) < 1e-4
+
+
+@pytest.mark.parametrize("dtype,n,h,i", [(torch.float32, 77, 96, 80), (torch.bfloat16, 130, 192, 96)])
+def test_dense_mlp_on_cuda_cores_for_other_shapes(dtype, n, h, i):
+    from bibo_b200 import functional as Fn
+    w = orc.make_mlp_weights(h, i, seed=3)
+    x = torch.randn(n, h, generator=torch.Generator().manual_seed(3))
+    r = lambda t: t.to(dtype).float()
+    ref = orc.mlp_forward(r(x), r(w["gate_proj"]), r(w["up_proj"]), r(w["down_proj"]))
+    wd = {k: v.to(dtype).to(DEV) for k, v in w.items()}
+    out = Fn.mlp_forward(x.to(dtype).to(DEV), wd["gate_proj"], wd["up_proj"], wd["down_proj"]).float().cpu()
+    if dtype == torch.float32:
+        assert rel_err(out, ref) < 1e-4
+    else:
+        assert rel_err(out, ref) < BF16_MAX and mean_rel_err(out, ref) < BF16_MEAN
+
+
 def test_unsupported_mlp_inputs_are_refused():
     from bibo_b200 import functional as Fn
     w = _dev(orc.make_mlp_weights(256, 256, seed=1))
@@ -180,7 +206,6 @@ def test_unsupported_mlp_inputs_are_refused():
     with pytest.raises(RuntimeError):
         Fn.mlp_forward(x.to(torch.bfloat16), w["gate_proj"], w["up_proj"], w["down_proj"])      # CPU tensor
     with pytest.raises(RuntimeError):
-        Fn.mlp_forward(x.to(DEV), w["gate_proj"].float(), w["up_proj"].float(), w["down_proj"].float())   # fp32
-    w2 = _dev(orc.make_mlp_weights(256, 192, seed=1))
-    with pytest.raises(RuntimeError):
-        Fn.mlp_forward(x.to(torch.bfloat16).to(DEV), w2["gate_proj"], w2["up_proj"], w2["down_proj"])     # I % 256
+        Fn.mlp_forward(x.to(DEV), w["gate_proj"], w["up_proj"], w["down_proj"])                   # dtype mismatch
+    with pytest.raises(RuntimeError):                                                             # no fp32 backward
+        Fn.mlp_forward(x.to(DEV), w["gate_proj"].float(), w["up_proj"].float(), w["down_proj"].float(), keep=True)
