@@ -68,7 +68,8 @@ combine_bwd_kernel(const T* __restrict__ dout, const T* __restrict__ y, const T*
 template <typename T>
 __global__ void __launch_bounds__(256)
 grouped_gemm_bkn_kernel(const T* __restrict__ A, const T* __restrict__ B, T* __restrict__ C,
-                        const int32_t* __restrict__ plan, int64_t tiles_off, int k_dim, int n_out) {
+                        const int32_t* __restrict__ plan, int64_t tiles_off, int k_dim, int n_out,
+                        int64_t row_limit = INT64_MAX) {   // rows >= row_limit are neither read nor written
   if ((int)blockIdx.x >= plan[PLAN_N_TILES]) return;
   const int4 tile = reinterpret_cast<const int4*>(plan + tiles_off)[blockIdx.x];
   const int e = tile.x, row0 = tile.y, n0 = blockIdx.y * 64;
@@ -85,7 +86,7 @@ grouped_gemm_bkn_kernel(const T* __restrict__ A, const T* __restrict__ B, T* __r
   for (int k0 = 0; k0 < k_dim; k0 += 16) {
     for (int i = tid; i < BIBO_TILE_M * 16; i += 256) {
       const int r = i / 16, c = i % 16;
-      As[c][r] = (k0 + c < k_dim) ? to_f32<T>(Ab[(int64_t)r * k_dim + k0 + c]) : 0.f;
+      As[c][r] = (k0 + c < k_dim && row0 + r < row_limit) ? to_f32<T>(Ab[(int64_t)r * k_dim + k0 + c]) : 0.f;
     }
     for (int i = tid; i < 16 * 64; i += 256) {
       const int c = i / 64, n = i % 64;
@@ -111,7 +112,7 @@ grouped_gemm_bkn_kernel(const T* __restrict__ A, const T* __restrict__ B, T* __r
 #pragma unroll
     for (int j = 0; j < 4; ++j) {
       const int n = n0 + tx * 4 + j;
-      if (n < n_out) C[(int64_t)(row0 + ty * 8 + i) * n_out + n] = from_f32<T>(acc[i][j]);
+      if (n < n_out && row0 + ty * 8 + i < row_limit) C[(int64_t)(row0 + ty * 8 + i) * n_out + n] = from_f32<T>(acc[i][j]);
     }
 }
 
@@ -482,6 +483,52 @@ static int backward_t(const bibo_moe_shape* s, const T* x, const T* w_router, co
     router_dw_scan_kernel<T><<<g6, 256, 0, st>>>(b->dlogit, ws->topk_idx, x, n, H, k, G, d_w_router);
     BIBO_CHECK_LAUNCH("router_dw_scan_kernel");
   }
+  return BIBO_OK;
+}
+
+// ---- CUDA-core pieces of the dense MLP backward (float32 and shapes outside the tensor-core kernels) -----
+// [gate | up] rows -> [dGate | dUp] in place: a = T(silu(g)), dUp = dh * a, dGate = dh * up * silu'(g)
+template <typename T>
+__global__ void __launch_bounds__(256)
+swiglu_bwd_rows_kernel(const T* __restrict__ dh, T* __restrict__ gate_up, int64_t n_rows, int inter) {
+  const int64_t i = (int64_t)blockIdx.x * 256 + threadIdx.x;
+  if (i >= n_rows * inter) return;
+  const int64_t r = i / inter;
+  const int c = (int)(i % inter);
+  T* g = gate_up + r * 2 * inter + c;
+  T* u = g + inter;
+  const float gg = to_f32<T>(*g), uu = to_f32<T>(*u), dd = to_f32<T>(dh[i]);
+  const float sg = __fdiv_rn(1.0f, 1.0f + expf(-gg));
+  const float a = to_f32<T>(from_f32<T>(gg * sg));
+  *u = from_f32<T>(dd * a);
+  *g = from_f32<T>(dd * uu * (sg * (1.0f + gg * (1.0f - sg))));
+}
+
+int mlp_backward_simt(const void* x, const void* w_gu, const void* down_proj, void* gate_up, const void* h,
+                      const void* dout, int64_t n, int hidden, int inter, int dtype, const PlanView& pv,
+                      const int32_t* counts, const int32_t* expert_off, void* dh, void* dx, void* d_w_gu, void* d_down,
+                      cudaStream_t st) {
+  auto run = [&](auto tag) {
+    using T = decltype(tag);
+    const T* X = static_cast<const T*>(x);
+    const T* DO = static_cast<const T*>(dout);
+    T* GU = static_cast<T*>(gate_up);
+    dim3 g1((unsigned)pv.tiles_cap, (unsigned)((inter + 63) / 64));
+    grouped_gemm_bkn_kernel<T><<<g1, 256, 0, st>>>(DO, static_cast<const T*>(down_proj), static_cast<T*>(dh), pv.plan,
+                                                   pv.tiles_off, hidden, inter, n);
+    dim3 g2((unsigned)((hidden + 63) / 64), (unsigned)((inter + 63) / 64), 1);
+    grouped_gemm_dw_kernel<T><<<g2, 256, 0, st>>>(DO, static_cast<const T*>(h), static_cast<T*>(d_down), counts,
+                                                  expert_off, hidden, inter);
+    swiglu_bwd_rows_kernel<T><<<(unsigned)((n * inter + 255) / 256), 256, 0, st>>>(static_cast<const T*>(dh), GU, n, inter);
+    dim3 g3((unsigned)pv.tiles_cap, (unsigned)((hidden + 63) / 64));
+    grouped_gemm_bkn_kernel<T><<<g3, 256, 0, st>>>(GU, static_cast<const T*>(w_gu), static_cast<T*>(dx), pv.plan,
+                                                   pv.tiles_off, 2 * inter, hidden, n);
+    dim3 g4((unsigned)((2 * inter + 63) / 64), (unsigned)((hidden + 63) / 64), 1);
+    grouped_gemm_dw_kernel<T><<<g4, 256, 0, st>>>(GU, X, static_cast<T*>(d_w_gu), counts, expert_off, 2 * inter, hidden);
+  };
+  if (dtype == BIBO_F32) run(float{});
+  else run(__nv_bfloat16{});
+  BIBO_CHECK_LAUNCH("mlp_backward_simt");
   return BIBO_OK;
 }
 

@@ -372,6 +372,12 @@ int gemm_dw_tc_supported(int m_dim, int n_dim);
 int gemm_dw_tc_launch(const void* A, const void* B, void* C, const int32_t* plan, int64_t counts_off,
                       int64_t expert_off_off, int64_t rows_alloc, int n_experts, int m_dim, int n_dim, cudaStream_t st);
 
+// backward.cu: the same backward on CUDA cores
+int mlp_backward_simt(const void* x, const void* w_gu, const void* down_proj, void* gate_up, const void* h,
+                      const void* dout, int64_t n, int hidden, int inter, int dtype, const PlanView& pv,
+                      const int32_t* counts, const int32_t* expert_off, void* dh, void* dx, void* d_w_gu, void* d_down,
+                      cudaStream_t st);
+
 // [gate | up] rows -> [dGate | dUp] in place: a = bf16(silu(g)), dUp = dh * a, dGate = dh * up * silu'(g).
 // One warp per row, 16-byte accesses; the sigmoid is one tanh.approx (error below the bf16 resolution).
 __global__ void __launch_bounds__(256)
@@ -421,11 +427,22 @@ extern "C" int bibo_moe_mlp_backward(const void* x, const void* gate_up_weight, 
   if (!x || !gate_up_weight || !down_proj || !gate_up || !h || !dout || !plan || !dh || !dx || !d_gate_up_weight ||
       !d_down_proj)
     return fail(BIBO_ERR_ARG, "mlp_backward: null pointer");
-  if (!bibo_moe_mlp_supported(hidden, inter, dtype) || !gemm_dx_tc_supported(hidden, inter) ||
-      !gemm_dx_tc_supported(2 * inter, hidden) || !gemm_dw_tc_supported(hidden, inter) ||
-      !gemm_dw_tc_supported(2 * inter, hidden))
-    return fail(BIBO_ERR_UNSUPPORTED, "mlp_backward: hidden=%d intermediate=%d is outside the tensor-core kernels",
-                hidden, inter);
+  if (dtype != BIBO_F32 && dtype != BIBO_BF16) return fail(BIBO_ERR_ARG, "mlp_backward: dtype=%d", dtype);
+  const bool tensor_cores = bibo_moe_mlp_supported(hidden, inter, dtype) && gemm_dx_tc_supported(hidden, inter) &&
+                            gemm_dx_tc_supported(2 * inter, hidden) && gemm_dw_tc_supported(hidden, inter) &&
+                            gemm_dw_tc_supported(2 * inter, hidden);
+  if (!tensor_cores) {   // float32 and other shapes: CUDA-core kernels, same order of operations
+    const int64_t ex = mlp_off_pairs(n_tokens) + 2 * ((mlp_tiles(n_tokens) + 1) / 2);
+    PlanView pv0 = {};
+    pv0.plan = plan;
+    pv0.tiles_off = mlp_off_tiles();
+    pv0.pairs_off = mlp_off_pairs(n_tokens);
+    pv0.tiles_cap = (int)mlp_tiles(n_tokens);
+    pv0.rows_alloc = n_tokens;
+    return mlp_backward_simt(x, gate_up_weight, down_proj, gate_up, h, dout, n_tokens, hidden, inter, dtype, pv0,
+                             plan + ex, plan + ex + 1, dh, dx, d_gate_up_weight, d_down_proj,
+                             static_cast<cudaStream_t>(stream));
+  }
   if (!aligned16(x) || !aligned16(gate_up_weight) || !aligned16(down_proj) || !aligned16(gate_up) || !aligned16(h) ||
       !aligned16(dout) || !aligned16(dh) || !aligned16(dx) || !aligned16(d_gate_up_weight) || !aligned16(d_down_proj))
     return fail(BIBO_ERR_ALIGN, "mlp_backward: pointers must be 16-byte aligned");

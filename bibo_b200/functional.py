@@ -325,11 +325,8 @@ def mlp_forward(x: torch.Tensor, gate_proj: torch.Tensor, up_proj: torch.Tensor,
     inter = gate_proj.shape[0]
     dt = dtype_code(x.dtype)
     # bf16 with hidden % 256 == 0 and intermediate % 256 == 0 runs on tensor cores; float32 and other shapes run
-    # the CUDA-core kernels (forward only), which stage gate | up in a buffer
+    # the CUDA-core kernels, which stage gate | up in a buffer
     tensor_cores = bool(lib.bibo_moe_mlp_supported(hidden, inter, dt))
-    if keep and not tensor_cores:
-        raise RuntimeError(f"bibo_b200: the dense MLP backward needs bf16 with hidden % 256 == 0 and intermediate % 256 "
-                           f"== 0 (got {x.dtype}, {hidden}, {inter})")
     if out is None:
         out = torch.empty_like(x)
     if n == 0:

@@ -5,7 +5,7 @@
 ``down_proj(silu(gate_proj(x)) * up_proj(x))`` on the tensor-core kernels of the MoE block
 (``bibo_moe_mlp_forward``).  It serves as the shared expert of ``BiBoMoELayer`` and as a dense
 feed-forward layer.  On a CUDA device: bf16 at tile-friendly shapes on tensor cores (forward and backward),
-float32 and other shapes on CUDA cores (forward only); anything else raises.
+float32 and other shapes on CUDA cores (forward and backward); anything else raises.
 """
 from __future__ import annotations
 

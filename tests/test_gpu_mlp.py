@@ -184,6 +184,26 @@ def test_dense_mlp_fp32_matches_the_reference_fixture():
     assert rel_err(out.cpu(), rec["out"]) < 1e-4
 
 
+def test_dense_mlp_fp32_backward_matches_the_reference_fixture():
+    """float32 gradients (CUDA-core kernels) against the reference's autograd at 1e-4."""
+    from bibo_b200 import BiBoMLP, MoEConfig
+    rec = torch.load(GOLDEN / "mlp_dense.pt")
+    w = orc.make_mlp_weights(rec["hidden"], rec["inter"], rec["seed"])
+    mlp = BiBoMLP(MoEConfig(hidden_size=rec["hidden"], moe_intermediate_size=rec["inter"]), is_expert=True)
+    with torch.no_grad():
+        mlp.gate_proj.weight.copy_(w["gate_proj"]); mlp.up_proj.weight.copy_(w["up_proj"]); mlp.down_proj.weight.copy_(w["down_proj"])
+    mlp = mlp.to(DEV)
+    x = torch.randn(rec["n_tokens"], rec["hidden"], generator=torch.Generator().manual_seed(rec["seed"] * 1000 + 1))
+    xg = x.to(DEV).requires_grad_(True)
+    out = mlp(xg)
+    (out * upstream_grad(rec).to(DEV)).sum().backward()
+    assert rel_err(out.detach().cpu(), rec["out"]) < 1e-4
+    assert rel_err(xg.grad.cpu(), rec["dx"]) < 1e-4
+    for key, prm in (("gate_proj", mlp.gate_proj.weight), ("up_proj", mlp.up_proj.weight), ("down_proj", mlp.down_proj.weight)):
+        assert rel_err(prm.grad[:8].cpu(), rec[f"d_{key}_head"]) < 1e-4, key
+        assert digest_close(grad_digest(prm.grad.cpu(), rec["seed"]), rec[f"d_{key}_digest"], 1e-4), key
+
+
 @pytest.mark.parametrize("dtype,n,h,i", [(torch.float32, 77, 96, 80), (torch.bfloat16, 130, 192, 96)])
 def test_dense_mlp_on_cuda_cores_for_other_shapes(dtype, n, h, i):
     from bibo_b200 import functional as Fn
@@ -207,5 +227,4 @@ def test_unsupported_mlp_inputs_are_refused():
         Fn.mlp_forward(x.to(torch.bfloat16), w["gate_proj"], w["up_proj"], w["down_proj"])      # CPU tensor
     with pytest.raises(RuntimeError):
         Fn.mlp_forward(x.to(DEV), w["gate_proj"], w["up_proj"], w["down_proj"])                   # dtype mismatch
-    with pytest.raises(RuntimeError):                                                             # no fp32 backward
-        Fn.mlp_forward(x.to(DEV), w["gate_proj"].float(), w["up_proj"].float(), w["down_proj"].float(), keep=True)
+
