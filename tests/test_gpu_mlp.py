@@ -228,3 +228,32 @@ def test_unsupported_mlp_inputs_are_refused():
     with pytest.raises(RuntimeError):
         Fn.mlp_forward(x.to(DEV), w["gate_proj"], w["up_proj"], w["down_proj"])                   # dtype mismatch
 
+
+
+def test_layer_with_shared_expert_fp32_forward_and_backward_match_the_reference_fixture():
+    """float32: routed block (CUDA-core kernels) + shared MLP against the reference's own forward and
+    autograd gradients at 1e-4."""
+    from bibo_b200 import BiBoMoELayer, MoEConfig
+    rec = torch.load(GOLDEN / "layer_shared_expert.pt")
+    cfg = MoEConfig(hidden_size=rec["hidden"], moe_intermediate_size=rec["moe_inter"], num_routed_experts=rec["n_experts"],
+                    num_experts_per_tok=rec["top_k"], use_shared_expert=True, num_shared_experts=rec["n_shared"],
+                    bias_update_factor=0.0)
+    layer = BiBoMoELayer(cfg)
+    inp = orc.make_inputs(rec["n_tokens"], rec["hidden"], rec["moe_inter"], rec["n_experts"], seed=rec["seed"],
+                          bias_mode="uniform", theta_std=0.5)
+    w = orc.make_mlp_weights(rec["hidden"], rec["inter"], rec["seed"])
+    sh = layer.shared_experts_list[0]
+    with torch.no_grad():
+        layer.gate.gate_proj.weight.copy_(inp["w_router"]); layer.gate.bias.copy_(inp["bias"])
+        layer.experts.gate_up_proj.copy_(inp["gate_up_proj"]); layer.experts.down_proj.copy_(inp["down_proj"])
+        layer.experts.radial_theta.copy_(inp["radial_theta"])
+        sh.gate_proj.weight.copy_(w["gate_proj"]); sh.up_proj.weight.copy_(w["up_proj"]); sh.down_proj.weight.copy_(w["down_proj"])
+    layer = layer.to(DEV).train()
+    xg = inp["x"].to(DEV).requires_grad_(True)
+    out = layer(xg.unsqueeze(0))[0]
+    (out * upstream_grad(rec).to(DEV)).sum().backward()
+    assert rel_err(out.detach().cpu(), rec["out"]) < 1e-4
+    assert rel_err(xg.grad.cpu(), rec["dx"]) < 1e-4
+    for key, prm in (("gate_proj", sh.gate_proj.weight), ("up_proj", sh.up_proj.weight), ("down_proj", sh.down_proj.weight)):
+        assert rel_err(prm.grad[:8].cpu(), rec[f"d_{key}_head"]) < 1e-4, key
+        assert digest_close(grad_digest(prm.grad.cpu(), rec["seed"]), rec[f"d_{key}_digest"], 1e-4), key
