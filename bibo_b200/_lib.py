@@ -96,6 +96,8 @@ SIGNATURES = {
     "bibo_moe_ep_dispatch": (_i32, [_vp, _vp, _vp, _vp, _vp, _vp, _i64, _i32, _i32, _i32, _i32, _i32, _i64, _i32, _vp, _vp,
                                     _vp]),
     "bibo_moe_rmsnorm_fwd": (_i32, [_vp, _vp, _f32, _i64, _i32, _i32, _vp, _vp]),
+    "bibo_moe_rmsnorm_bwd_parts": (_i64, [_i64]),
+    "bibo_moe_rmsnorm_bwd": (_i32, [_vp, _vp, _vp, _f32, _i64, _i32, _i32, _vp, _vp, _vp, _vp]),
     "bibo_moe_mlp_plan_words": (_i64, [_i64]),
     "bibo_moe_mlp_supported": (_i32, [_i32, _i32, _i32]),
     "bibo_moe_mlp_forward": (_i32, [_vp, _vp, _vp, _vp, _i64, _i32, _i32, _i32, _vp, _vp, _vp, _vp, _vp]),

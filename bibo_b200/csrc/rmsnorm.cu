@@ -120,3 +120,102 @@ extern "C" int bibo_moe_rmsnorm_fwd(const void* h, const void* weight, float eps
   BIBO_CHECK_LAUNCH("rmsnorm_kernel");
   return BIBO_OK;
 }
+
+// ---- backward ---------------------------------------------------------------------------------------------
+// With v = float(h), rs = rsqrt(mean(v^2) + eps), xhat = v * rs, out = weight * T(xhat):
+//   g      = float(T(dy * weight))                       (the reference multiplies in T)
+//   dh     = T(rs * (g - xhat * mean(g * xhat)))
+//   dweight[c] = sum over rows of dy[r,c] * T(xhat[r,c])
+// Kernel 1: one warp per row writes dh and adds its dy * T(xhat) into the block's shared partial
+// (RB rows per block, fixed order), blocks write partial[block][H] fp32.  Kernel 2 sums the partials of
+// a column in block order.  No float atomics: results are deterministic.
+namespace bibo {
+
+constexpr int RB_WARPS = 8, RB_ROWS = 64;   // rows per block in the backward (8 warps x 8 rows each)
+
+template <typename T>
+__global__ void __launch_bounds__(RB_WARPS * 32)
+rmsnorm_bwd_kernel(const T* __restrict__ h, const T* __restrict__ weight, const T* __restrict__ dy, float eps,
+                   int64_t n_rows, int hidden, T* __restrict__ dh, float* __restrict__ partial) {
+  extern __shared__ float acc_s[];                    // [RB_WARPS][hidden]
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  float* mine = acc_s + (size_t)warp * hidden;
+  for (int c = lane; c < hidden; c += 32) mine[c] = 0.f;
+  const int64_t row0 = (int64_t)blockIdx.x * RB_ROWS;
+  for (int i = 0; i < RB_ROWS / RB_WARPS; ++i) {
+    const int64_t row = row0 + warp + (int64_t)i * RB_WARPS;
+    if (row >= n_rows) break;
+    const T* hr = h + row * hidden;
+    const T* gr = dy + row * hidden;
+    float ss = 0.f;
+    for (int c = lane; c < hidden; c += 32) { const float v = to_f32<T>(hr[c]); ss = fmaf(v, v, ss); }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+    const float rs = rsqrtf(ss / (float)hidden + eps);
+    float dot = 0.f;
+    for (int c = lane; c < hidden; c += 32) {
+      const float xhat = to_f32<T>(hr[c]) * rs;
+      const float g = to_f32<T>(from_f32<T>(to_f32<T>(gr[c]) * to_f32<T>(weight[c])));
+      dot = fmaf(g, xhat, dot);
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) dot += __shfl_xor_sync(0xffffffffu, dot, o);
+    const float m = dot / (float)hidden;
+    for (int c = lane; c < hidden; c += 32) {
+      const float xhat = to_f32<T>(hr[c]) * rs;
+      const float gy = to_f32<T>(gr[c]);
+      const float g = to_f32<T>(from_f32<T>(gy * to_f32<T>(weight[c])));
+      dh[row * hidden + c] = from_f32<T>(rs * (g - xhat * m));
+      mine[c] = fmaf(gy, to_f32<T>(from_f32<T>(xhat)), mine[c]);
+    }
+  }
+  __syncthreads();
+  for (int c = threadIdx.x; c < hidden; c += RB_WARPS * 32) {
+    float s = 0.f;
+#pragma unroll
+    for (int w = 0; w < RB_WARPS; ++w) s += acc_s[(size_t)w * hidden + c];   // fixed order
+    partial[(int64_t)blockIdx.x * hidden + c] = s;
+  }
+}
+
+template <typename T>
+__global__ void __launch_bounds__(256)
+rmsnorm_dweight_kernel(const float* __restrict__ partial, int n_parts, int hidden, T* __restrict__ dweight) {
+  const int c = blockIdx.x * 256 + threadIdx.x;
+  if (c >= hidden) return;
+  float s = 0.f;
+  for (int p = 0; p < n_parts; ++p) s += partial[(int64_t)p * hidden + c];
+  dweight[c] = from_f32<T>(s);
+}
+
+}  // namespace bibo
+
+extern "C" int64_t bibo_moe_rmsnorm_bwd_parts(int64_t n_rows) { return (n_rows + RB_ROWS - 1) / RB_ROWS; }
+
+extern "C" int bibo_moe_rmsnorm_bwd(const void* h, const void* weight, const void* dy, float eps, int64_t n_rows,
+                                    int hidden, int dtype, void* dh, float* partial, void* dweight, void* stream) {
+  if (n_rows <= 0) return BIBO_OK;
+  if (!h || !weight || !dy || !dh || !partial || !dweight) return fail(BIBO_ERR_ARG, "rmsnorm_bwd: null pointer");
+  if (dtype != BIBO_F32 && dtype != BIBO_BF16) return fail(BIBO_ERR_ARG, "rmsnorm_bwd: dtype=%d", dtype);
+  const size_t smem = sizeof(float) * RB_WARPS * (size_t)hidden;
+  if (hidden < 1 || smem > 200 * 1024) return fail(BIBO_ERR_UNSUPPORTED, "rmsnorm_bwd: hidden=%d", hidden);
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const int n_parts = (int)bibo_moe_rmsnorm_bwd_parts(n_rows);
+  if (dtype == BIBO_F32) {
+    BIBO_CUDA(cudaFuncSetAttribute(rmsnorm_bwd_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    rmsnorm_bwd_kernel<float><<<n_parts, RB_WARPS * 32, smem, st>>>(
+        static_cast<const float*>(h), static_cast<const float*>(weight), static_cast<const float*>(dy), eps, n_rows, hidden,
+        static_cast<float*>(dh), partial);
+    rmsnorm_dweight_kernel<float><<<(hidden + 255) / 256, 256, 0, st>>>(partial, n_parts, hidden,
+                                                                        static_cast<float*>(dweight));
+  } else {
+    BIBO_CUDA(cudaFuncSetAttribute(rmsnorm_bwd_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    rmsnorm_bwd_kernel<__nv_bfloat16><<<n_parts, RB_WARPS * 32, smem, st>>>(
+        static_cast<const __nv_bfloat16*>(h), static_cast<const __nv_bfloat16*>(weight),
+        static_cast<const __nv_bfloat16*>(dy), eps, n_rows, hidden, static_cast<__nv_bfloat16*>(dh), partial);
+    rmsnorm_dweight_kernel<__nv_bfloat16><<<(hidden + 255) / 256, 256, 0, st>>>(partial, n_parts, hidden,
+                                                                                static_cast<__nv_bfloat16*>(dweight));
+  }
+  BIBO_CHECK_LAUNCH("rmsnorm_bwd_kernel");
+  return BIBO_OK;
+}

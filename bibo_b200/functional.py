@@ -311,6 +311,23 @@ def rmsnorm_forward(h: torch.Tensor, weight: torch.Tensor, eps: float) -> torch.
     return out
 
 
+def rmsnorm_backward(dy: torch.Tensor, h: torch.Tensor, weight: torch.Tensor, eps: float):
+    """Gradients of ``rmsnorm_forward``: (dh [N,H], dweight [H]) (bibo_moe_rmsnorm_bwd)."""
+    lib = _lib.load()
+    _need_cuda(dy, "dy")
+    if weight.dtype != h.dtype:
+        weight = weight.to(h.dtype)
+    n, hidden = h.shape
+    dh = torch.empty_like(h)
+    dweight = torch.empty(hidden, dtype=h.dtype, device=h.device)
+    partial = torch.empty(int(lib.bibo_moe_rmsnorm_bwd_parts(n)), hidden, dtype=torch.float32, device=h.device)
+    p = _lib.ptr
+    _lib.check(lib.bibo_moe_rmsnorm_bwd(p(h), p(weight.contiguous()), p(dy.contiguous()), float(eps), n, hidden,
+                                        dtype_code(h.dtype), p(dh), p(partial), p(dweight), _stream(h.device)),
+               "bibo_moe_rmsnorm_bwd")
+    return dh, dweight
+
+
 def mlp_forward(x: torch.Tensor, gate_proj: torch.Tensor, up_proj: torch.Tensor, down_proj: torch.Tensor,
                 out: Optional[torch.Tensor] = None, keep: bool = False):
     """Dense SwiGLU MLP ``down(silu(gate(x)) * up(x))`` on flat tokens x [N,H] (bibo_moe_mlp_forward);

@@ -307,11 +307,27 @@ def layer_forward(layer, hidden_states: torch.Tensor, residual: Optional[torch.T
     return out if late_residual is None else late_residual + out
 
 
+class _RMSNormFunction(torch.autograd.Function):
+    """BiBoRMSNorm forward / backward as single C-ABI calls (src/modeling/norm.py:19-24)."""
+
+    @staticmethod
+    def forward(ctx, h, weight, eps):
+        ctx.save_for_backward(h, weight)
+        ctx.eps = eps
+        return Fn.rmsnorm_forward(h, weight, eps)
+
+    @staticmethod
+    def backward(ctx, dy):
+        h, weight = ctx.saved_tensors
+        dh, dw = Fn.rmsnorm_backward(dy, h, weight, ctx.eps)
+        return dh, dw.to(weight.dtype), None
+
+
 def ffn_forward(decoder_layer, hidden_states: torch.Tensor) -> torch.Tensor:
     """``BiBoDecoderLayer._ffn_forward`` (src/modeling/layers.py:57-67): post-attention RMSNorm, the
     feed-forward block and the residual add.  Inference runs the norm kernel and folds the residual add
-    into the combine kernel; with gradients on, the norm stays the module's own (autograd provides its
-    backward) and the block runs through its autograd node.  Written against the reference's attribute
+    into the combine kernel; with gradients on, norm and block run through their autograd nodes (kernels
+    in both directions) and the residual add is torch's.  Written against the reference's attribute
     names (``post_attention_layernorm``, ``mlp``, ``_bf16_moe_out``, ``_bf16_stream``)."""
     from .mlp import mlp_module_forward
     mlp, norm = decoder_layer.mlp, decoder_layer.post_attention_layernorm
@@ -323,7 +339,13 @@ def ffn_forward(decoder_layer, hidden_states: torch.Tensor) -> torch.Tensor:
                                               any(p.requires_grad for p in decoder_layer.parameters()))
     plain = hidden_states.dtype == torch.bfloat16 or not (bf16_out or bf16_stream)   # the casts are no-ops
     if needs_grad or not plain:
-        out = block(norm(hidden_states))
+        shape = hidden_states.shape
+        if hidden_states.is_cuda and norm.weight.dtype == hidden_states.dtype:
+            x = _RMSNormFunction.apply(hidden_states.reshape(-1, shape[-1]).contiguous(), norm.weight,
+                                       norm.variance_epsilon).view(shape)
+        else:
+            x = norm(hidden_states)
+        out = block(x)
         if bf16_out:
             out = out.to(torch.bfloat16)
         hidden_states = hidden_states + out

@@ -349,6 +349,11 @@ int bibo_moe_ep_backward(const bibo_moe_ep_args* fwd, const bibo_moe_ep_bwd_args
  * The residual add of the same function is the `addend` of the combine kernel.                      */
 int bibo_moe_rmsnorm_fwd(const void* h, const void* weight, float eps, int64_t n_rows, int hidden, int dtype,
                          void* out, void* stream);
+/* Backward (autograd through BiBoRMSNorm.forward in the reference): dh [N,H] and dweight [H] from dy [N,H];
+ * partial is fp32 scratch [bibo_moe_rmsnorm_bwd_parts(N), H].  Deterministic (no float atomics).       */
+int64_t bibo_moe_rmsnorm_bwd_parts(int64_t n_rows);
+int bibo_moe_rmsnorm_bwd(const void* h, const void* weight, const void* dy, float eps, int64_t n_rows,
+                         int hidden, int dtype, void* dh, float* partial, void* dweight, void* stream);
 
 /* ---- dense SwiGLU MLP -----------------------------------------------------------------------------
  * Replaces BiBoMLP.forward, `down_proj(act_fn(gate_proj(x)) * up_proj(x))` with act = SiLU

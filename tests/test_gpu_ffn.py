@@ -89,6 +89,43 @@ def test_ffn_forward_bf16_and_training_path():
     assert rel_err(o, r) < BF16_MAX and mean_rel_err(o, r) < BF16_MEAN
     hg = h.clone().requires_grad_(True)
     out_t = ffn_forward(dl.train(), hg)[0]
-    out_t.float().sum().backward()
-    assert hg.grad is not None and bool(torch.isfinite(hg.grad.float()).all())
+    dout = torch.randn(out_t.shape, generator=torch.Generator().manual_seed(3)).to(torch.bfloat16).to(DEV)
+    (out_t * dout).sum().backward()
     assert rel_err(out_t.detach().float().cpu()[same], o) < 8e-3      # same math, one rounding order differs
+    # gradients against autograd through the CPU oracle (norm + block + residual), bf16-rounded inputs
+    r = lambda t: t.to(torch.bfloat16).float()
+    ch = r(inp["x"]).requires_grad_(True)
+    nw = r(dl.post_attention_layernorm.weight.detach().cpu()).requires_grad_(True)
+    c = {k: (r(v) if k in ("w_router", "gate_up_proj", "down_proj") else v.clone()) for k, v in inp.items()}
+    routed, _, idx2, _, _ = orc.moe_forward(orc.rmsnorm(ch, nw, rec["eps"]), c["w_router"], c["bias"], c["gate_up_proj"],
+                                            c["down_proj"], c["radial_theta"], rec["top_k"], return_routing=True)
+    ((ch + routed) * dout.float().cpu()).sum().backward()
+    # a token at a near-tie may route differently (the oracle normalises in fp32, the kernel rounds x to bf16 first):
+    # per-token gradients are compared on the other tokens, the norm weight gradient (a sum over all tokens) loosely
+    same2 = (dl.mlp.last_workspace.topk_idx.cpu().long() == idx2).all(-1)
+    assert float(same2.float().mean()) > 0.97
+    got = hg.grad[0].float().cpu()
+    assert rel_err(got[same2], ch.grad[same2]) < BF16_MAX and mean_rel_err(got[same2], ch.grad[same2]) < BF16_MEAN
+    gw = dl.post_attention_layernorm.weight.grad.float().cpu()
+    cos = float(torch.nn.functional.cosine_similarity(gw, nw.grad, dim=0))
+    assert cos > 0.99, cos      # the few differently-routed tokens enter this sum; the kernel itself is checked above
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("n,h", [(1, 64), (333, 256), (2100, 2048)])
+def test_rmsnorm_backward_matches_oracle_autograd(dtype, n, h):
+    from bibo_b200 import functional as Fn
+    g = torch.Generator().manual_seed(n * 7 + h)
+    x = (torch.randn(n, h, generator=g) * 2).to(dtype)
+    w = (1.0 + 0.1 * torch.randn(h, generator=g)).to(dtype)
+    dy = torch.randn(n, h, generator=g).to(dtype)
+    cx, cw = x.clone().requires_grad_(True), w.clone().requires_grad_(True)
+    (orc.rmsnorm(cx, cw, 1e-6).float() * dy.float()).sum().backward()
+    dh, dw = Fn.rmsnorm_backward(dy.to(DEV), x.to(DEV), w.to(DEV), 1e-6)
+    dh2, dw2 = Fn.rmsnorm_backward(dy.to(DEV), x.to(DEV), w.to(DEV), 1e-6)
+    assert torch.equal(dh, dh2) and torch.equal(dw, dw2)
+    if dtype == torch.float32:
+        assert rel_err(dh.cpu(), cx.grad) < 1e-4 and rel_err(dw.cpu(), cw.grad) < 1e-4
+    else:
+        assert rel_err(dh.float().cpu(), cx.grad.float()) < BF16_MAX
+        assert rel_err(dw.float().cpu(), cw.grad.float()) < BF16_MAX
