@@ -84,3 +84,47 @@ def test_source_major_layout_makes_each_exchange_one_block():
                 assert int(lays[s]["send_base"][d * el + le]) == run
                 run += int(pad[s, d * el + le])
         assert int(lays[d]["rows"][d]) == run
+
+
+def _module_worker(rank, world, path):
+    import bibo_b200
+    from bibo_b200 import ep
+    dist.init_process_group("gloo", init_method=f"file://{path}", rank=rank, world_size=world)
+    cfg = bibo_b200.MoEConfig(hidden_size=64, moe_intermediate_size=32, num_routed_experts=8, num_experts_per_tok=2)
+    torch.manual_seed(0)                                  # the same full layer on every rank
+    full = bibo_b200.BiBoMoELayer(cfg)
+    shard = ep.ExpertParallelMoELayer.from_full_layer(full, cfg)
+    el = 8 // world
+    lo, hi = rank * el, (rank + 1) * el
+    assert shard.gate_up_proj.shape == (el, 64, 64) and shard.down_proj.shape == (el, 64, 32)
+    assert torch.equal(shard.gate_up_proj, full.experts.gate_up_proj[lo:hi])
+    assert torch.equal(shard.down_proj, full.experts.down_proj[lo:hi])
+    assert torch.equal(shard.radial_theta, full.experts.radial_theta[lo:hi])
+    assert torch.equal(shard.gate.gate_proj.weight, full.gate.gate_proj.weight)      # router replicated
+    sd = shard.state_dict()
+    assert set(sd) == {"gate.bias", "gate.gate_proj.weight", "gate_up_proj", "down_proj", "radial_theta", "accumulated_tpe"}
+    # the balancer all-reduces the token counts: every rank applies the same bias update
+    counts = torch.zeros(8)
+    counts[rank] = 100.0
+    from bibo_b200.moe import _balance_from_counts
+    shard.bias_update_threshold = 50
+    tpe = _balance_from_counts(shard, counts, 50)
+    assert tpe is not None and float(tpe.sum()) == 100.0 * world
+    shard.update_bias(tpe)
+    biases = [torch.zeros(8) for _ in range(world)]
+    dist.all_gather(biases, shard.gate.bias.data)
+    assert all(torch.equal(b, biases[0]) for b in biases) and float(biases[0].abs().max()) > 0
+    for bad in (dict(num_pos_identity_experts=1, num_neg_identity_experts=1), dict(use_shared_expert=True)):
+        try:
+            ep.ExpertParallelMoELayer(bibo_b200.MoEConfig(hidden_size=64, moe_intermediate_size=32,
+                                                          num_routed_experts=8 + 2 * ("num_pos_identity_experts" in bad),
+                                                          num_experts_per_tok=2, **bad))
+            raise AssertionError("identity / shared experts must be refused")
+        except NotImplementedError:
+            pass
+    dist.destroy_process_group()
+
+
+def test_expert_parallel_module_shards_and_balances_on_cpu_ranks():
+    with tempfile.TemporaryDirectory() as d:
+        mp.spawn(_module_worker, args=(2, os.path.join(d, "store")), nprocs=2, join=True)
