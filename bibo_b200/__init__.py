@@ -2,7 +2,8 @@
 the reference's PyTorch module API.  See include/bibo_moe.h for the C ABI underneath."""
 from .moe import BiBoFusedExperts, BiBoMoELayer, BiBoMoERouter, MoEConfig  # noqa: F401
 from .mlp import BiBoMLP  # noqa: F401
+from .trace import RouterTrace  # noqa: F401
 from . import functional  # noqa: F401
 from .install import install, uninstall  # noqa: F401
 
-__all__ = ["BiBoMoELayer", "BiBoMoERouter", "BiBoFusedExperts", "BiBoMLP", "MoEConfig", "functional", "install", "uninstall"]
+__all__ = ["BiBoMoELayer", "BiBoMoERouter", "BiBoFusedExperts", "BiBoMLP", "MoEConfig", "RouterTrace", "functional", "install", "uninstall"]

@@ -24,7 +24,14 @@ _vp, _i32, _i64, _f32 = C.c_void_p, C.c_int, C.c_int64, C.c_float
 class Workspace(C.Structure):
     _fields_ = [(n, _vp) for n in (
         "topk_idx", "topk_w", "slot_rank", "block_counts", "plan", "slot_row", "row_token",
-        "xp", "h", "y", "gate_up", "rnorm", "logits", "stage_events", "addend")]
+        "xp", "h", "y", "gate_up", "rnorm", "logits", "stage_events", "addend", "trace")]
+
+
+class RouterTrace(C.Structure):
+    _fields_ = [(n, _vp) for n in ("block_sums", "acc", "counts", "gap")]
+
+
+TRACE_WORDS = 8
 
 
 class BwdWorkspace(C.Structure):
@@ -68,8 +75,11 @@ SIGNATURES = {
     "bibo_moe_plan_words": (_i64, [_i64, _i32, _i32, _i32]),
     "bibo_moe_router_fwd": (_i32, [_vp, _vp, _vp, _vp, _i64, _i32, _i32, _i32, _i32, _f32, _i32,
                                    _vp, _vp, _vp, _vp, _vp, _vp, _vp]),
+    "bibo_moe_router_fwd_trace": (_i32, [_vp, _vp, _vp, _vp, _i64, _i32, _i32, _i32, _i32, _f32, _i32,
+                                         _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp]),
     "bibo_moe_route_from_indices": (_i32, [_vp, _i64, _i32, _i32, _vp, _vp, _vp, _vp]),
     "bibo_moe_plan": (_i32, [_vp, _i64, _i32, _i32, _i32, _vp, _vp]),
+    "bibo_moe_plan_trace": (_i32, [_vp, _i64, _i32, _i32, _i32, _vp, _vp, _vp]),
     "bibo_moe_plan_off_counts": (_i64, []),
     "bibo_moe_plan_off_expert_off": (_i64, [_i32]),
     "bibo_moe_plan_off_block_base": (_i64, [_i32, _i32]),

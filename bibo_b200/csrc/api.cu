@@ -87,12 +87,15 @@ extern "C" int bibo_moe_forward(const bibo_moe_shape* s, const void* x, const vo
     if (ev) BIBO_CUDA(cudaEventRecord(static_cast<cudaEvent_t>(ev[i]), st_));      \
   } while (0)
   BIBO_STAGE(0);
-  int rc = bibo_moe_router_fwd(x, w_router, bias, nullptr, s->n_tokens, s->hidden, s->n_experts, s->top_k,
-                               s->norm_mode, s->scale, s->dtype, ws->logits, ws->topk_idx, ws->topk_w,
-                               ws->slot_rank, ws->block_counts, ws->plan ? ws->plan + PLAN_STATUS : nullptr, stream);
+  const bibo_moe_router_trace* tr = ws->trace;
+  if (tr && !tr->block_sums) return fail(BIBO_ERR_ARG, "forward: trace without block_sums");
+  int rc = bibo_moe_router_fwd_trace(x, w_router, bias, nullptr, s->n_tokens, s->hidden, s->n_experts, s->top_k,
+                                     s->norm_mode, s->scale, s->dtype, ws->logits, ws->topk_idx, ws->topk_w,
+                                     ws->slot_rank, ws->block_counts, ws->plan ? ws->plan + PLAN_STATUS : nullptr,
+                                     tr ? tr->block_sums : nullptr, stream);
   if (rc) return rc;
   BIBO_STAGE(1);
-  rc = bibo_moe_plan(ws->block_counts, s->n_tokens, s->top_k, s->n_experts, s->n_glu, ws->plan, stream);
+  rc = bibo_moe_plan_trace(ws->block_counts, s->n_tokens, s->top_k, s->n_experts, s->n_glu, ws->plan, tr, stream);
   if (rc) return rc;
   BIBO_STAGE(2);
   rc = bibo_moe_permute_fwd(x, ws->topk_idx, ws->slot_rank, ws->plan, s->n_tokens, s->hidden, s->n_experts,

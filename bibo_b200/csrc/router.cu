@@ -20,7 +20,7 @@ router_simt_kernel(const T* __restrict__ x, const T* __restrict__ w_router,
                    int64_t n_tokens, int hidden, int n_experts, int top_k, int norm_mode,
                    float scale, float* __restrict__ logits_out, int32_t* __restrict__ topk_idx,
                    float* __restrict__ topk_w, int32_t* __restrict__ slot_rank,
-                   int32_t* __restrict__ block_counts) {
+                   int32_t* __restrict__ block_counts, float* __restrict__ trace_blocks) {
   extern __shared__ __align__(16) unsigned char smem_raw[];
   const int ld = n_experts | 1;  // odd leading dimension -> conflict-free column walks
   float* lg = reinterpret_cast<float*>(smem_raw);                 // [RB][ld]
@@ -92,7 +92,8 @@ router_simt_kernel(const T* __restrict__ x, const T* __restrict__ w_router,
     __syncthreads();
   }
   select_and_rank(lg, ld, mask, bias, t0, rows, n_experts, top_k, norm_mode, scale, topk_idx,
-                  topk_w, slot_rank, block_counts + (int64_t)blockIdx.x * n_experts);
+                  topk_w, slot_rank, block_counts + (int64_t)blockIdx.x * n_experts,
+                  trace_blocks ? trace_blocks + (int64_t)blockIdx.x * BIBO_TRACE_WORDS : nullptr);
 }
 
 // ---- ranks for routing decided elsewhere ------------------------------------------------------------
@@ -151,7 +152,8 @@ rank_kernel(const int32_t* __restrict__ topk_idx, int64_t n_tokens, int n_expert
 constexpr int PLAN_THREADS = 1024;
 __global__ void __launch_bounds__(PLAN_THREADS)
 plan_kernel(const int32_t* __restrict__ block_counts, int64_t n_tokens, int top_k, int n_experts,
-            int n_glu, int ep, int32_t* __restrict__ plan) {
+            int n_glu, int ep, int32_t* __restrict__ plan, const float* __restrict__ trace_blocks,
+            float* __restrict__ trace_acc, float* __restrict__ trace_counts, float* __restrict__ trace_gap) {
   __shared__ int s_part[PLAN_THREADS];
   __shared__ int s_padded[BIBO_MAX_EXPERTS + 1];
   __shared__ int s_count[BIBO_MAX_EXPERTS];
@@ -222,6 +224,27 @@ plan_kernel(const int32_t* __restrict__ block_counts, int64_t n_tokens, int top_
       if ((i & 1) == 0) pairs[s_pair_off[e] + i / 2] = make_int2(t0 + i, i + 1 < nt ? t0 + i + 1 : -1);
     }
   }
+  // router diagnostics: warp j adds up word j of the router blocks' sums (lanes stride over the blocks,
+  // then a fixed shuffle tree: the same bits every run) and folds it into the caller's accumulators
+  // the way RouterTrace._hook / _router_hook do (ablate/common/router_trace.py:106-130)
+  if (trace_blocks != nullptr) {
+    const int w = tid >> 5, lane = tid & 31;
+    if (w < BIBO_TRACE_WORDS) {
+      float s = 0.f;
+      for (int b = lane; b < nb; b += 32) s += trace_blocks[(int64_t)b * BIBO_TRACE_WORDS + w];
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
+      if (lane == 0) {
+        if (w == 6) {                          // mean boundary gap of this forward
+          s = s / (float)n_tokens;
+          if (trace_gap != nullptr) *trace_gap = s;
+        }
+        if (w == 7) s = 1.f;                   // router forwards seen
+        if (trace_acc != nullptr) trace_acc[w] += s;
+      }
+    }
+    if (trace_counts != nullptr && tid < n_experts) trace_counts[tid] += (float)s_count[tid];
+  }
 }
 
 }  // namespace bibo
@@ -240,7 +263,7 @@ int router_tc_supported(int hidden, int n_experts, int dtype);
 int router_tc_launch(const void* x, const void* w_router, const float* bias, int64_t n_tokens,
                      int hidden, int n_experts, int top_k, int norm_mode, float scale,
                      float* logits_out, int32_t* topk_idx, float* topk_w, int32_t* slot_rank,
-                     int32_t* block_counts, int32_t* status, cudaStream_t st);
+                     int32_t* block_counts, int32_t* status, float* trace_blocks, cudaStream_t st);
 }
 
 int bibo_moe_router_fwd(const void* x, const void* w_router, const float* bias,
@@ -248,6 +271,16 @@ int bibo_moe_router_fwd(const void* x, const void* w_router, const float* bias,
                         int top_k, int norm_mode, float scale, int dtype, float* logits_out,
                         int32_t* topk_idx, float* topk_w, int32_t* slot_rank,
                         int32_t* block_counts, int32_t* status, void* stream) {
+  return bibo_moe_router_fwd_trace(x, w_router, bias, logits_in, n_tokens, hidden, n_experts, top_k, norm_mode, scale,
+                                   dtype, logits_out, topk_idx, topk_w, slot_rank, block_counts, status, nullptr, stream);
+}
+
+extern "C" int bibo_moe_router_fwd_trace(const void* x, const void* w_router, const float* bias,
+                                         const float* logits_in, int64_t n_tokens, int hidden, int n_experts,
+                                         int top_k, int norm_mode, float scale, int dtype, float* logits_out,
+                                         int32_t* topk_idx, float* topk_w, int32_t* slot_rank,
+                                         int32_t* block_counts, int32_t* status, float* trace_blocks,
+                                         void* stream) {
   if (n_tokens <= 0) return BIBO_OK;
   if (!bias || !topk_idx || !topk_w || !slot_rank || !block_counts)
     return fail(BIBO_ERR_ARG, "router_fwd: null output or bias pointer");
@@ -264,7 +297,7 @@ int bibo_moe_router_fwd(const void* x, const void* w_router, const float* bias,
 
   if (!logits_in && router_tc_supported(hidden, n_experts, dtype) && aligned16(x) && aligned16(w_router))
     return router_tc_launch(x, w_router, bias, n_tokens, hidden, n_experts, top_k, norm_mode,
-                            scale, logits_out, topk_idx, topk_w, slot_rank, block_counts, status, st);
+                            scale, logits_out, topk_idx, topk_w, slot_rank, block_counts, status, trace_blocks, st);
 
   const int ld = n_experts | 1;
   size_t smem = sizeof(float) * ((size_t)RB * ld + RK * (RB + 1) + RK * (RE + 1)) +
@@ -275,13 +308,13 @@ int bibo_moe_router_fwd(const void* x, const void* w_router, const float* bias,
     BIBO_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
     kern<<<grid, 256, smem, st>>>((const float*)x, (const float*)w_router, bias, logits_in,
                                   n_tokens, hidden, n_experts, top_k, norm_mode, scale, logits_out,
-                                  topk_idx, topk_w, slot_rank, block_counts);
+                                  topk_idx, topk_w, slot_rank, block_counts, trace_blocks);
   } else {
     auto kern = router_simt_kernel<__nv_bfloat16>;
     BIBO_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
     kern<<<grid, 256, smem, st>>>((const __nv_bfloat16*)x, (const __nv_bfloat16*)w_router, bias,
                                   logits_in, n_tokens, hidden, n_experts, top_k, norm_mode, scale,
-                                  logits_out, topk_idx, topk_w, slot_rank, block_counts);
+                                  logits_out, topk_idx, topk_w, slot_rank, block_counts, trace_blocks);
   }
   BIBO_CHECK_LAUNCH("router_simt_kernel");
   return BIBO_OK;
@@ -303,6 +336,12 @@ extern "C" int bibo_moe_route_from_indices(const int32_t* topk_idx, int64_t n_to
 
 extern "C" int bibo_moe_plan(const int32_t* block_counts, int64_t n_tokens, int top_k,
                              int n_experts, int n_glu, int32_t* plan, void* stream) {
+  return bibo_moe_plan_trace(block_counts, n_tokens, top_k, n_experts, n_glu, plan, nullptr, stream);
+}
+
+extern "C" int bibo_moe_plan_trace(const int32_t* block_counts, int64_t n_tokens, int top_k, int n_experts,
+                                   int n_glu, int32_t* plan, const bibo_moe_router_trace* trace, void* stream) {
+  if (trace && !trace->block_sums) return fail(BIBO_ERR_ARG, "plan: trace without block_sums");
   if (!block_counts || !plan) return fail(BIBO_ERR_ARG, "plan: null pointer");
   if (n_experts < 1 || n_experts > BIBO_MAX_EXPERTS || n_glu < 0 || n_glu > n_experts)
     return fail(BIBO_ERR_UNSUPPORTED, "plan: n_experts=%d n_glu=%d", n_experts, n_glu);
@@ -315,7 +354,11 @@ extern "C" int bibo_moe_plan(const int32_t* block_counts, int64_t n_tokens, int 
   int ep = 1;
   while (ep < n_experts) ep <<= 1;
   plan_kernel<<<1, PLAN_THREADS, 0, static_cast<cudaStream_t>(stream)>>>(block_counts, n_tokens, top_k, n_experts,
-                                                                       n_glu, ep, plan);
+                                                                       n_glu, ep, plan,
+                                                                       trace ? trace->block_sums : nullptr,
+                                                                       trace ? trace->acc : nullptr,
+                                                                       trace ? trace->counts : nullptr,
+                                                                       trace ? trace->gap : nullptr);
   BIBO_CHECK_LAUNCH("plan_kernel");
   return BIBO_OK;
 }

@@ -5,6 +5,13 @@
 // selection on score + bias; weights gathered from the un-biased scores; "sum" normalisation
 // divides by (sum + 1e-20).  Ties go to the lower expert index, and the k experts are written in
 // ascending expert index.
+//
+// Optional diagnostics (trace_row != nullptr): the block's sums of the per-token quantities that the
+// boundary-gap probe (src/modeling/ffn/router.py:33-36) and RouterTrace._hook
+// (ablate/common/router_trace.py:113-130) compute with extra launches:
+//   [0] max_j p_j   [1] -sum_j |p_j| log |p_j|   [2] 1   [3] max_j w_j   [4] sum_j w_j   [5] min_j w_j
+//   [6] score of rank k minus score of rank k+1 (raw scores, no bias)   [7] unused
+// with w the weights as written and p = w / max(sum |w|, 1e-9).
 #pragma once
 #include "common.cuh"
 
@@ -23,8 +30,12 @@ __device__ __forceinline__ void select_and_rank(
     float* lg, int ld, uint32_t* scratch, const float* __restrict__ bias, int64_t t0, int rows,
     int n_experts, int top_k, int norm_mode, float scale, int32_t* __restrict__ topk_idx,
     float* __restrict__ topk_w, int32_t* __restrict__ slot_rank,
-    int32_t* __restrict__ block_counts_row) {
+    int32_t* __restrict__ block_counts_row, float* __restrict__ trace_row = nullptr) {
   constexpr int WORDS = BIBO_ROUTER_BLOCK_TOKENS / 32;
+  __shared__ float s_trace[BIBO_ROUTER_BLOCK_TOKENS / 32][BIBO_TRACE_WORDS];
+  float tr[BIBO_TRACE_WORDS];
+#pragma unroll
+  for (int j = 0; j < BIBO_TRACE_WORDS; ++j) tr[j] = 0.f;
   uint32_t* mask = scratch;                                            // [n_experts][WORDS]
   float* bias_s = reinterpret_cast<float*>(scratch + n_experts * WORDS);  // [n_experts]
   const int tid = threadIdx.x;
@@ -105,12 +116,61 @@ __device__ __forceinline__ void select_and_rank(
     for (int j = 0; j < BIBO_MAX_TOP_K; ++j) {
       if (j < top_k) {
         topk_idx[base + j] = sel_idx[j];
-        topk_w[base + j] = (scale == 1.0f) ? w[j] : w[j] * scale;
+        w[j] = (scale == 1.0f) ? w[j] : w[j] * scale;
+        topk_w[base + j] = w[j];
         atomicOr(&mask[sel_idx[j] * WORDS + (tid >> 5)], 1u << (tid & 31));
       }
     }
+    if (trace_row != nullptr) {
+      float w_max = -INFINITY, w_min = INFINITY, w_sum = 0.f, l1 = 0.f;
+#pragma unroll
+      for (int j = 0; j < BIBO_MAX_TOP_K; ++j)
+        if (j < top_k) { w_max = fmaxf(w_max, w[j]); w_min = fminf(w_min, w[j]); w_sum += w[j]; l1 += fabsf(w[j]); }
+      l1 = fmaxf(l1, 1e-9f);
+      float ent = 0.f;
+#pragma unroll
+      for (int j = 0; j < BIBO_MAX_TOP_K; ++j)
+        if (j < top_k) { const float a = fabsf(__fdiv_rn(w[j], l1)); ent -= a * logf(fmaxf(a, 1e-12f)); }
+      tr[0] = __fdiv_rn(w_max, l1); tr[1] = ent; tr[2] = 1.f; tr[3] = w_max; tr[4] = w_sum; tr[5] = w_min;
+      if (top_k < n_experts) {
+        // the top_k + 1 largest raw scores (the row now holds scores), descending; values only
+        float tv[BIBO_MAX_TOP_K + 1];
+#pragma unroll
+        for (int j = 0; j <= BIBO_MAX_TOP_K; ++j) tv[j] = -INFINITY;
+        for (int e = 0; e < n_experts; ++e) {
+          const float s = row[e];
+          if (s > tv[BIBO_MAX_TOP_K]) {
+#pragma unroll
+            for (int j = BIBO_MAX_TOP_K; j >= 0; --j) {
+              const bool beats = s > tv[j];
+              const bool beats_prev = j > 0 && s > tv[j - 1];
+              if (beats) tv[j] = beats_prev ? tv[j - 1] : s;
+            }
+          }
+        }
+        float hi = 0.f, lo = 0.f;
+#pragma unroll
+        for (int j = 0; j <= BIBO_MAX_TOP_K; ++j) { if (j == top_k - 1) hi = tv[j]; if (j == top_k) lo = tv[j]; }
+        tr[6] = hi - lo;
+      }
+    }
+  }
+  if (trace_row != nullptr) {   // fixed-order block sum: shuffle tree per warp, then the warps in order
+#pragma unroll
+    for (int j = 0; j < BIBO_TRACE_WORDS; ++j) {
+      float v = tr[j];
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+      if ((tid & 31) == 0 && tid < BIBO_ROUTER_BLOCK_TOKENS) s_trace[tid >> 5][j] = v;
+    }
   }
   __syncthreads();
+  if (trace_row != nullptr && tid < BIBO_TRACE_WORDS) {
+    float v = 0.f;
+#pragma unroll
+    for (int q = 0; q < BIBO_ROUTER_BLOCK_TOKENS / 32; ++q) v += s_trace[q][tid];
+    trace_row[tid] = v;
+  }
   if (active) {
     const int64_t base = (t0 + tid) * top_k;
     const int wq = tid >> 5;

@@ -24,7 +24,7 @@ router_tc_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant_
                  const float* __restrict__ bias, int64_t n_tokens, int k_blocks, int top_k, int norm_mode,
                  float scale, float* __restrict__ logits_out, int32_t* __restrict__ topk_idx,
                  float* __restrict__ topk_w, int32_t* __restrict__ slot_rank, int32_t* __restrict__ block_counts,
-                 int32_t* __restrict__ status) {
+                 int32_t* __restrict__ status, float* __restrict__ trace_blocks) {
   extern __shared__ unsigned char smem_dyn[];
   unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_dyn) + 1023) & ~uintptr_t(1023));
   uint64_t* full = reinterpret_cast<uint64_t*>(smem + R_OFF_BAR);
@@ -109,7 +109,8 @@ router_tc_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant_
     __syncthreads();
   }
   select_and_rank(lg, R_LD, reinterpret_cast<uint32_t*>(smem + R_OFF_SEL), bias, t0, rows, R_BN, top_k, norm_mode,
-                  scale, topk_idx, topk_w, slot_rank, block_counts + (int64_t)blockIdx.x * R_BN);
+                  scale, topk_idx, topk_w, slot_rank, block_counts + (int64_t)blockIdx.x * R_BN,
+                  trace_blocks ? trace_blocks + (int64_t)blockIdx.x * BIBO_TRACE_WORDS : nullptr);
 }
 
 }  // namespace tc
@@ -120,7 +121,8 @@ int router_tc_supported(int hidden, int n_experts, int dtype) {
 
 int router_tc_launch(const void* x, const void* w_router, const float* bias, int64_t n_tokens, int hidden,
                      int n_experts, int top_k, int norm_mode, float scale, float* logits_out, int32_t* topk_idx,
-                     float* topk_w, int32_t* slot_rank, int32_t* block_counts, int32_t* status, cudaStream_t st) {
+                     float* topk_w, int32_t* slot_rank, int32_t* block_counts, int32_t* status, float* trace_blocks,
+                     cudaStream_t st) {
   using namespace tc;
   CUtensorMap tmX, tmW;
   int rc;
@@ -136,7 +138,7 @@ int router_tc_launch(const void* x, const void* w_router, const float* bias, int
   }
   router_tc_kernel<<<(unsigned)router_blocks(n_tokens), 128, R_SMEM, st>>>(
       tmX, tmW, bias, n_tokens, hidden / R_BK, top_k, norm_mode, scale, logits_out, topk_idx, topk_w, slot_rank,
-      block_counts, status);
+      block_counts, status, trace_blocks);
   BIBO_CHECK_LAUNCH("router_tc_kernel");
   return BIBO_OK;
 }

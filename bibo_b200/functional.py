@@ -94,6 +94,8 @@ class MoEWorkspace:
         self.status = torch.zeros(1, **i32)
         self.stage_events = None      # optional list of 7 torch.cuda.Event(enable_timing=True)
         self._stage_event_array = None
+        self.trace_blocks = None      # [router_blocks, 8] fp32 scratch of the router diagnostics, on first use
+        self._trace_struct = None
 
     def c_struct(self) -> _lib.Workspace:
         p = _lib.ptr
@@ -105,10 +107,18 @@ class MoEWorkspace:
                     e.record()
             self._stage_event_array = (C.c_void_p * 7)(*[e.cuda_event for e in self.stage_events])
             ev = C.cast(self._stage_event_array, C.c_void_p)
+        tr = None
+        trace = getattr(self, "trace", None)       # (acc, counts, gap) tensors or None each, for this call only
+        if trace is not None:
+            if self.trace_blocks is None:
+                self.trace_blocks = torch.empty(self.geo.router_blocks, _lib.TRACE_WORDS, dtype=torch.float32,
+                                                device=self.plan.device)
+            self._trace_struct = _lib.RouterTrace(p(self.trace_blocks), *[p(t) for t in trace])
+            tr = C.cast(C.pointer(self._trace_struct), C.c_void_p)
         return _lib.Workspace(p(self.topk_idx), p(self.topk_w), p(self.slot_rank), p(self.block_counts),
                               p(self.plan), p(self.slot_row), p(self.row_token), p(self.xp), p(self.h),
                               p(self.y), p(self.gate_up), p(self.rnorm), p(self.logits), ev,
-                              p(getattr(self, "addend", None)))
+                              p(getattr(self, "addend", None)), tr)
 
     def enable_stage_timing(self) -> None:
         """Ask bibo_moe_forward to record an event around every stage (see stage_ms)."""
@@ -200,9 +210,13 @@ def moe_forward(x: torch.Tensor, w_router: torch.Tensor, bias: torch.Tensor, gat
                 down_proj: torch.Tensor, theta: torch.Tensor, top_k: int, norm_mode="sum", scale: float = 1.0,
                 n_pos: int = 0, n_neg: int = 0, ws: Optional[MoEWorkspace] = None, out: Optional[torch.Tensor] = None,
                 zero_padding: bool = False, keep_logits: bool = False,
-                addend: Optional[torch.Tensor] = None) -> Tuple[torch.Tensor, MoEWorkspace]:
+                addend: Optional[torch.Tensor] = None,
+                trace: Optional[Tuple[Optional[torch.Tensor], Optional[torch.Tensor], Optional[torch.Tensor]]] = None,
+                ) -> Tuple[torch.Tensor, MoEWorkspace]:
     """The whole block on flat tokens x [N,H]: one call of bibo_moe_forward.  Returns (out, workspace).
-    ``addend`` [N,H] (the shared expert's output) is added in the combine kernel."""
+    ``addend`` [N,H] (the shared expert's output) is added in the combine kernel.
+    ``trace`` = (acc [8], counts [E], gap [1]) fp32 device tensors, each optional: the router and plan
+    kernels fold this call's routing diagnostics into them (see bibo_moe_router_trace in the header)."""
     lib = _lib.load()
     for name, t in (("x", x), ("w_router", w_router), ("bias", bias), ("gate_up_proj", gate_up_proj),
                     ("down_proj", down_proj), ("radial_theta", theta)):
@@ -226,9 +240,14 @@ def moe_forward(x: torch.Tensor, w_router: torch.Tensor, bias: torch.Tensor, gat
     shape = _shape(geo, norm_mode, scale, zero_padding)
     if addend is not None and (addend.shape != x.shape or addend.dtype != x.dtype or not addend.is_contiguous()):
         raise RuntimeError("addend must be a contiguous tensor of the activations' shape and dtype")
-    ws.addend = addend
+    if trace is not None:
+        for t, words in zip(trace, (_lib.TRACE_WORDS, geo.n_experts, 1)):
+            if t is not None and (t.dtype != torch.float32 or t.numel() != words or t.device != x.device
+                                  or not t.is_contiguous()):
+                raise RuntimeError("trace tensors must be contiguous fp32 device tensors of 8 / n_experts / 1 elements")
+    ws.addend, ws.trace = addend, trace
     cws = ws.c_struct()
-    ws.addend = None
+    ws.addend = ws.trace = None
     rc = lib.bibo_moe_forward(C.byref(shape), _lib.ptr(x), _lib.ptr(w_router), _lib.ptr(bias32),
                               _lib.ptr(gate_up_proj), _lib.ptr(down_proj), _lib.ptr(theta32), C.byref(cws),
                               _lib.ptr(out), _stream(x.device))

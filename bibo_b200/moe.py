@@ -155,7 +155,7 @@ class _MoEBlockFunction(torch.autograd.Function):
 
     @staticmethod
     def forward(ctx, x, w_router, gate_up_proj, down_proj, theta, bias, cfg, holder, addend=None):
-        top_k, norm, scale, n_pos, n_neg, keep_logits = cfg
+        top_k, norm, scale, n_pos, n_neg, trace = cfg
         n, hidden = x.shape
         geo = Fn.Geometry(n, hidden, gate_up_proj.shape[1] // 2, w_router.shape[0], gate_up_proj.shape[0], n_pos, top_k,
                           x.dtype)
@@ -163,7 +163,7 @@ class _MoEBlockFunction(torch.autograd.Function):
         # the fp32 logits are kept as well: the backward reads the selected ones instead of recomputing them
         ws = Fn.MoEWorkspace(geo, x.device, keep_logits=True, keep_gate_up=True)
         out, ws = Fn.moe_forward(x, w_router, bias, gate_up_proj, down_proj, theta, top_k, norm, scale, n_pos=n_pos,
-                                 n_neg=n_neg, ws=ws, zero_padding=True, addend=addend)
+                                 n_neg=n_neg, ws=ws, zero_padding=True, addend=addend, trace=trace)
         ctx.save_for_backward(x, w_router, gate_up_proj, down_proj, theta)
         ctx.ws, ctx.norm, ctx.scale = ws, norm, scale
         ctx.has_addend = addend is not None
@@ -275,22 +275,27 @@ def layer_forward(layer, hidden_states: torch.Tensor, residual: Optional[torch.T
     n_pos, n_neg = ex.pos_end - ex.pos_start, ex.neg_end - ex.neg_start
     want_gap = gate._probe_gap and gate.top_k < gate.num_routed_experts
     scale = float(getattr(gate, "routed_scaling_factor", 1.0))
+    # routing diagnostics come out of the router / plan kernels themselves (no extra launches): the sums
+    # of an attached bibo_b200.RouterTrace, and the boundary gap of router.py:33-36 when it is probed
+    tracer = getattr(layer, "_router_trace", None)
+    trace = tracer.buffers(layer) if tracer is not None else None
+    if want_gap:
+        gap = torch.empty(1, dtype=torch.float32, device=flat.device)
+        trace = (trace[0], trace[1], gap) if trace is not None else (None, None, gap)
     params = (gate.gate_proj.weight, ex.gate_up_proj, ex.down_proj, ex.radial_theta)
     if torch.is_grad_enabled() and (flat.requires_grad or any(p.requires_grad for p in params)):
         holder = {}
         out = _MoEBlockFunction.apply(flat, *params, gate.bias.detach(),
-                                      (gate.top_k, gate.norm_topk_prob, scale, n_pos, n_neg, want_gap), holder,
+                                      (gate.top_k, gate.norm_topk_prob, scale, n_pos, n_neg, trace), holder,
                                       shared_out)
         ws = holder["ws"]
     else:
         out, ws = Fn.moe_forward(flat, gate.gate_proj.weight, gate.bias, ex.gate_up_proj, ex.down_proj,
                                  ex.radial_theta, gate.top_k, gate.norm_topk_prob, scale,
-                                 n_pos=n_pos, n_neg=n_neg, keep_logits=want_gap, addend=shared_out)
+                                 n_pos=n_pos, n_neg=n_neg, addend=shared_out, trace=trace)
     layer.last_workspace = ws
     if want_gap:
-        with torch.no_grad():
-            tk = torch.sigmoid(ws.logits).topk(gate.top_k + 1, dim=-1).values
-            gate.boundary_gap = (tk[..., gate.top_k - 1] - tk[..., gate.top_k]).mean()
+        gate.boundary_gap = gap[0]
     # replay the reference's diagnostic hook points only when someone is listening
     if ex._forward_pre_hooks:
         for hook in ex._forward_pre_hooks.values():

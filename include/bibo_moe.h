@@ -83,6 +83,34 @@ int bibo_moe_router_fwd(const void* x, const void* w_router, const float* bias,
                         float* logits_out, int32_t* topk_idx, float* topk_w,
                         int32_t* slot_rank, int32_t* block_counts, int32_t* status, void* stream);
 
+/* ---- router diagnostics without extra launches -------------------------------------------------
+ * Replaces the boundary-gap probe of BiBoMoERouter.forward (src/modeling/ffn/router.py:33-36: mean over
+ * tokens of the raw score of rank k minus that of rank k+1) and the device-side sums of
+ * RouterTrace._hook / _router_hook (ablate/common/router_trace.py:106-130), which the reference
+ * computes with a second top-k and about twenty small launches per layer.  The router kernel
+ * writes per-block sums (block_sums [router_blocks, BIBO_TRACE_WORDS] fp32, see router_select.cuh
+ * for the words); the plan kernel adds them up in a fixed order and folds them into the caller's
+ * accumulators:
+ *   acc[0] += sum_t max_j p   acc[1] += sum_t entropy(p)   acc[2] += N   acc[3] += sum_t max_j w
+ *   acc[4] += sum_t sum_j w   acc[5] += sum_t min_j w      acc[6] += mean gap   acc[7] += 1
+ *   counts[e] += tokens routed to expert e (as float)      gap[0] = mean gap of this call
+ * with w the weights as written to topk_w and p = w / max(sum_j |w_j|, 1e-9).  acc, counts and gap
+ * are optional device pointers; the struct itself lives in HOST memory.                           */
+#define BIBO_TRACE_WORDS 8
+typedef struct {
+  float* block_sums;      /* scratch [router_blocks, BIBO_TRACE_WORDS] */
+  float* acc;             /* optional [BIBO_TRACE_WORDS], accumulated  */
+  float* counts;          /* optional [E], accumulated                 */
+  float* gap;             /* optional [1], overwritten                 */
+} bibo_moe_router_trace;
+/* bibo_moe_router_fwd that also writes block_sums (NULL = off).                                    */
+int bibo_moe_router_fwd_trace(const void* x, const void* w_router, const float* bias,
+                              const float* logits_in, int64_t n_tokens, int hidden, int n_experts,
+                              int top_k, int norm_mode, float scale, int dtype,
+                              float* logits_out, int32_t* topk_idx, float* topk_w,
+                              int32_t* slot_rank, int32_t* block_counts, int32_t* status,
+                              float* block_sums, void* stream);
+
 /* Histogram and ranks for routing decided by the caller: the BiBoFusedExperts.forward(x, idx, w)
  * seam (src/modeling/ffn/moe.py:47-52).  topk_idx [N,k] int32 in any order.  status (optional
  * device int32, zeroed by the caller) is set to 2 for an index outside [0,E) (treated as expert 0)
@@ -101,6 +129,9 @@ int bibo_moe_route_from_indices(const int32_t* topk_idx, int64_t n_tokens, int n
  * blocks), tiles[tiles_cap*4].  Accessors below return the word offsets.                         */
 int bibo_moe_plan(const int32_t* block_counts, int64_t n_tokens, int top_k, int n_experts,
                   int n_glu, int32_t* plan, void* stream);
+/* bibo_moe_plan that also reduces the router's diagnostic sums (trace NULL = off).                */
+int bibo_moe_plan_trace(const int32_t* block_counts, int64_t n_tokens, int top_k, int n_experts,
+                        int n_glu, int32_t* plan, const bibo_moe_router_trace* trace, void* stream);
 int64_t bibo_moe_plan_off_counts(void);
 int64_t bibo_moe_plan_off_expert_off(int n_experts);
 int64_t bibo_moe_plan_off_block_base(int n_experts, int n_glu);
@@ -177,6 +208,7 @@ typedef struct {
                                 launches or synchronisation                                        */
   const void* addend;     /* optional [N,H] dtype: added to the combined output (the shared expert's
                              result, src/modeling/ffn/moe.py:174-176): out = T(T(sum) + addend)        */
+  const bibo_moe_router_trace* trace; /* optional HOST struct: router diagnostics of this call       */
 } bibo_moe_workspace;
 
 typedef struct {

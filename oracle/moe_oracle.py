@@ -96,8 +96,21 @@ def boundary_gap(logits: torch.Tensor, bias: torch.Tensor, top_k: int) -> torch.
 
 def probe_gap(logits: torch.Tensor, top_k: int) -> torch.Tensor:
     """Mean un-biased score gap the reference exposes as ``boundary_gap`` (router.py:33-36)."""
-    tk = torch.sigmoid(logits.float()).topk(top_k + 1, dim=-1).values
+    tk = torch.sigmoid(logits if logits.dtype == torch.float64 else logits.float()).topk(top_k + 1, dim=-1).values
     return (tk[..., top_k - 1] - tk[..., top_k]).mean()
+
+
+def router_trace_sums(logits: torch.Tensor, idx: torch.Tensor, w: torch.Tensor, top_k: int) -> torch.Tensor:
+    """What one training forward adds to the reference's RouterTrace accumulator
+    (ablate/common/router_trace.py:106-130): [sum max p, sum entropy(p), tokens, sum max w, sum sum w,
+    sum min w, mean boundary gap, 1] with p = w / max(sum |w|, 1e-9), in fp64."""
+    wr = w.double()
+    p = wr / wr.abs().sum(-1, keepdim=True).clamp_min(1e-9)
+    ent = -(p.abs() * p.abs().clamp_min(1e-12).log()).sum(-1)
+    gap = probe_gap(logits.double(), top_k) if top_k < logits.shape[-1] else torch.zeros(())
+    return torch.stack([p.max(-1).values.sum(), ent.sum(), torch.tensor(float(w.shape[0]), dtype=torch.float64),
+                        wr.max(-1).values.sum(), wr.sum(), wr.min(-1).values.sum(), gap.double(),
+                        torch.tensor(1.0, dtype=torch.float64)])
 
 
 # --------------------------------------------------------------------------------------------

@@ -179,6 +179,39 @@ def run_ffn_case(ref_root, name, n_tokens, hidden, inter, n_experts, top_k, seed
     print(f"{name}: out abs-mean {out.abs().mean():.4e}  {os.path.getsize(HERE / f'{name}.pt') / 1024:.0f} KiB")
 
 
+def run_trace_case(ref_root, name, n_tokens, hidden, inter, n_experts, top_k, pairs, norm, seeds):
+    """The reference's RouterTrace (ablate/common/router_trace.py) hooked onto its own layer in training
+    mode: its accumulator and expert counts after each forward, and what flush() reports."""
+    if ref_root not in sys.path:
+        sys.path.insert(0, ref_root)
+    from ablate.common.router_trace import RouterTrace
+    n_glu = n_experts - 2 * pairs
+    layer = build_layer(ref_root, hidden, inter, n_experts, top_k, pairs, norm, torch.float32).train()
+    layer.bias_update_factor = 0.0           # keep the bias fixed between the forwards
+    model = torch.nn.ModuleDict({"mlp": layer})
+    trace = RouterTrace(model, n_experts, "cpu")
+    rec = dict(name=name, n_tokens=n_tokens, hidden=hidden, inter=inter, n_experts=n_experts, n_glu=n_glu,
+               pairs=pairs, top_k=top_k, norm=norm, seeds=list(seeds), acc=[], counts=[], gap=[])
+    for seed in seeds:
+        inp = orc.make_inputs(n_tokens, hidden, inter, n_experts, seed=seed, bias_mode="uniform", theta_std=0.5)
+        if seed == seeds[0]:                 # weights of the first seed; later seeds only change x
+            with torch.no_grad():
+                layer.gate.gate_proj.weight.copy_(inp["w_router"])
+                layer.gate.bias.copy_(inp["bias"])
+                layer.experts.gate_up_proj.copy_(inp["gate_up_proj"][:n_glu])
+                layer.experts.down_proj.copy_(inp["down_proj"][:n_glu])
+                layer.experts.radial_theta.copy_(inp["radial_theta"][:n_glu])
+        with torch.no_grad():
+            layer(inp["x"].reshape(1, n_tokens, hidden))
+        rec["acc"].append(trace.acc.clone())
+        rec["counts"].append(trace.counts.clone())
+        rec["gap"].append(layer.gate.boundary_gap.clone())
+    rec["flush"] = trace.flush()
+    trace.close()
+    torch.save(rec, HERE / f"{name}.pt")
+    print(f"{name}: " + ", ".join(f"{k.split('/')[-1]} {v:.4f}" for k, v in rec["flush"].items()))
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--reference", required=True)
@@ -203,6 +236,10 @@ def main():
     run_mlp_case(r, "layer_shared_expert", 300, 256, 512, seed=8, shared_in_layer=True, moe_inter=256, n_shared=2)
     # the decoder layer's feed-forward half: RMSNorm + MoE block + residual
     run_ffn_case(r, "ffn_moe", 300, 256, 256, 64, 6, seed=9)
+    # RouterTrace of the reference over two training forwards: sum-normalised top-6 of 64, and raw weights
+    # with one +/-Identity pair
+    run_trace_case(r, "router_trace_sum", 320, 128, 64, 64, 6, pairs=0, norm="sum", seeds=(11, 12))
+    run_trace_case(r, "router_trace_raw", 320, 128, 64, 64, 6, pairs=1, norm=False, seeds=(13, 14))
 
 
 if __name__ == "__main__":

@@ -151,3 +151,29 @@ def test_ffn_half_of_the_decoder_layer_oracle_matches_the_reference_fixture():
     out = inp["x"] + orc.moe_forward(x, inp["w_router"], inp["bias"], inp["gate_up_proj"], inp["down_proj"],
                                      inp["radial_theta"], rec["top_k"])
     assert rel_err(out, rec["out"]) < 1e-6
+
+
+def _trace_forwards(rec):
+    """The routing of the trace fixture's forwards through the oracle: (logits, idx, w, counts) per seed."""
+    n_glu, first = rec["n_glu"], None
+    for seed in rec["seeds"]:
+        inp = orc.make_inputs(rec["n_tokens"], rec["hidden"], rec["inter"], rec["n_experts"], seed=seed,
+                              bias_mode="uniform", theta_std=0.5)
+        first = first or inp
+        logits = orc.router_logits(inp["x"], first["w_router"])
+        idx, w, counts = orc.router_select(logits, first["bias"], rec["top_k"], rec["norm"])
+        yield logits, idx, w, counts
+
+
+@pytest.mark.parametrize("name", ["router_trace_sum", "router_trace_raw"])
+def test_router_trace_sums_match_the_reference_trace(name):
+    """oracle.router_trace_sums against the accumulator of the reference's RouterTrace, hooked onto the
+    reference layer for two training forwards (fixture: tests/golden/make_golden.py run_trace_case)."""
+    rec = torch.load(GOLDEN / f"{name}.pt", weights_only=True)
+    acc, counts = torch.zeros(8, dtype=torch.float64), torch.zeros(rec["n_experts"], dtype=torch.float64)
+    for i, (logits, idx, w, c) in enumerate(_trace_forwards(rec)):
+        acc += orc.router_trace_sums(logits, idx, w, rec["top_k"])
+        counts += c
+        assert torch.allclose(acc, rec["acc"][i].double(), rtol=2e-6, atol=1e-7), (i, acc, rec["acc"][i])
+        assert torch.equal(counts.float(), rec["counts"][i])
+        assert abs(float(orc.probe_gap(logits, rec["top_k"])) - float(rec["gap"][i])) < 1e-7
