@@ -211,8 +211,10 @@ def main():
                     help="N>1: do not pin each rank to the CPUs local to its GPU (pinned host buffers then land anywhere)")
     ap.add_argument("--e2e-chunks", type=int, default=4, help="token slices of the host-buffer (e2e) forward (N>1)")
     ap.add_argument("--comm-sms", type=int, default=20, help="SMs left to the exchange kernels (N>1)")
-    ap.add_argument("--mode", default="fwd", choices=["fwd", "fwdbwd"],
-                    help="fwd = the headline metric; fwdbwd = forward + backward of the block (1 GPU)")
+    ap.add_argument("--mode", default="fwd", choices=["fwd", "fwdbwd", "ffn", "ffn_separate"],
+                    help="fwd = the headline metric; fwdbwd = forward + backward of the block (1 GPU); ffn = the decoder "
+                         "layer's feed-forward half (RMSNorm + block + residual) with the norm folded into the router's and "
+                         "the permute's loads; ffn_separate = the same with the norm as a kernel of its own (1 GPU)")
     args = ap.parse_args()
     wl = WORKLOADS[args.workload]
     rank, world = int(os.environ.get("RANK", 0)), int(os.environ.get("WORLD_SIZE", 1))
@@ -254,6 +256,16 @@ def main():
         out = torch.empty_like(t["x"])
         step = lambda: Fn.moe_forward(t["x"], t["w_router"], t["bias"], t["gate_up_proj"], t["down_proj"],
                                       t["radial_theta"], TOP_K, "sum", ws=ws, out=out)
+        if args.mode in ("ffn", "ffn_separate"):
+            norm_w = (1.0 + 0.1 * torch.randn(h, generator=torch.Generator().manual_seed(99))).to(dtype).to(dev)
+            if args.mode == "ffn":
+                step = lambda: Fn.ffn_forward(t["x"], norm_w, 1e-6, t["w_router"], t["bias"], t["gate_up_proj"],
+                                              t["down_proj"], t["radial_theta"], TOP_K, "sum", ws=ws, out=out)
+            else:
+                def step():
+                    xn = Fn.rmsnorm_forward(t["x"], norm_w, 1e-6)
+                    return Fn.moe_forward(xn, t["w_router"], t["bias"], t["gate_up_proj"], t["down_proj"],
+                                          t["radial_theta"], TOP_K, "sum", ws=ws, out=out, addend=t["x"])
         if args.mode == "fwdbwd":
             ws = None                       # no per-kernel events: the backward consumes its workspace
             dout = torch.randn_like(t["x"])
@@ -375,7 +387,7 @@ def main():
                 "peak_source": f"of {pk['src']} (burst figure)", "ms_per_launch": stages[top]["ms"]}
     layer_flops = (36.0 * n * h * i + 2.0 * n * h * N_EXPERTS) * (3.0 if args.mode == "fwdbwd" else 1.0)
     line = {
-        "metric": METRIC if args.mode == "fwd" else "moe_layer_fwdbwd_tokens_per_s", "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+        "metric": {"fwd": METRIC, "fwdbwd": "moe_layer_fwdbwd_tokens_per_s"}.get(args.mode, "ffn_half_fwd_tokens_per_s"), "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
         "ms_per_step": ms_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
         "data": "synthetic", "config": workload_config(args, wl, world),
         "layer_tflops": round(layer_flops * world / (ms_step * 1e-3) / 1e12, 2),

@@ -76,9 +76,12 @@ extern "C" int bibo_moe_gemm2_fwd(const void* h, const void* down_proj, const in
   return gemm_simt_launch(h, down_proj, y, pv, inter, hidden, dtype, st);
 }
 
-extern "C" int bibo_moe_forward(const bibo_moe_shape* s, const void* x, const void* w_router,
-                                const float* bias, const void* gate_up_proj, const void* down_proj,
-                                const float* theta, const bibo_moe_workspace* ws, void* out, void* stream) {
+// The kernel chain.  With norm_w the input is the raw residual stream: the RMSNorm is folded into the
+// router's and the permute's loads, and the residual add into the combine (out = h + block(norm(h))).
+static int forward_chain(const bibo_moe_shape* s, const void* x, const void* w_router, const float* bias,
+                         const void* gate_up_proj, const void* down_proj, const float* theta,
+                         const bibo_moe_workspace* ws, void* out, void* stream, const void* norm_w, float eps,
+                         float* rstd, void* w_fold, int refold) {
   if (!s || !ws) return fail(BIBO_ERR_ARG, "forward: null shape / workspace");
   cudaStream_t st_ = static_cast<cudaStream_t>(stream);
   void* const* ev = ws->stage_events;
@@ -89,18 +92,29 @@ extern "C" int bibo_moe_forward(const bibo_moe_shape* s, const void* x, const vo
   BIBO_STAGE(0);
   const bibo_moe_router_trace* tr = ws->trace;
   if (tr && !tr->block_sums) return fail(BIBO_ERR_ARG, "forward: trace without block_sums");
-  int rc = bibo_moe_router_fwd_trace(x, w_router, bias, nullptr, s->n_tokens, s->hidden, s->n_experts, s->top_k,
-                                     s->norm_mode, s->scale, s->dtype, ws->logits, ws->topk_idx, ws->topk_w,
-                                     ws->slot_rank, ws->block_counts, ws->plan ? ws->plan + PLAN_STATUS : nullptr,
-                                     tr ? tr->block_sums : nullptr, stream);
+  int32_t* status = ws->plan ? ws->plan + PLAN_STATUS : nullptr;
+  int rc = BIBO_OK;
+  if (norm_w && refold) rc = bibo_moe_fold_norm_weight(w_router, norm_w, s->n_experts, s->hidden, w_fold, stream);
+  if (rc) return rc;
+  rc = norm_w
+      ? bibo_moe_router_norm_fwd(x, w_fold, eps, bias, s->n_tokens, s->hidden, s->n_experts, s->top_k,
+                                 s->norm_mode, s->scale, ws->logits, ws->topk_idx, ws->topk_w, ws->slot_rank,
+                                 ws->block_counts, status, tr ? tr->block_sums : nullptr, rstd, stream)
+      : bibo_moe_router_fwd_trace(x, w_router, bias, nullptr, s->n_tokens, s->hidden, s->n_experts, s->top_k,
+                                  s->norm_mode, s->scale, s->dtype, ws->logits, ws->topk_idx, ws->topk_w,
+                                  ws->slot_rank, ws->block_counts, status, tr ? tr->block_sums : nullptr, stream);
   if (rc) return rc;
   BIBO_STAGE(1);
   rc = bibo_moe_plan_trace(ws->block_counts, s->n_tokens, s->top_k, s->n_experts, s->n_glu, ws->plan, tr, stream);
   if (rc) return rc;
   BIBO_STAGE(2);
-  rc = bibo_moe_permute_fwd(x, ws->topk_idx, ws->slot_rank, ws->plan, s->n_tokens, s->hidden, s->n_experts,
-                            s->n_glu, s->top_k, s->dtype, s->zero_padding, ws->xp, ws->slot_row,
-                            ws->row_token, stream);
+  rc = norm_w
+      ? bibo_moe_permute_norm_fwd(x, rstd, norm_w, ws->topk_idx, ws->slot_rank, ws->plan, s->n_tokens, s->hidden,
+                                  s->n_experts, s->n_glu, s->top_k, s->zero_padding, ws->xp, ws->slot_row,
+                                  ws->row_token, stream)
+      : bibo_moe_permute_fwd(x, ws->topk_idx, ws->slot_rank, ws->plan, s->n_tokens, s->hidden, s->n_experts,
+                             s->n_glu, s->top_k, s->dtype, s->zero_padding, ws->xp, ws->slot_row,
+                             ws->row_token, stream);
   if (rc) return rc;
   BIBO_STAGE(3);
   rc = bibo_moe_gemm1_radial_fwd(ws->xp, gate_up_proj, theta, ws->plan, s->n_tokens, s->hidden, s->inter,
@@ -112,12 +126,37 @@ extern "C" int bibo_moe_forward(const bibo_moe_shape* s, const void* x, const vo
                           s->n_glu, s->top_k, s->dtype, ws->y, stream);
   if (rc) return rc;
   BIBO_STAGE(5);
-  rc = bibo_moe_combine_add_fwd(ws->y, x, ws->slot_row, ws->topk_idx, ws->topk_w, ws->addend, s->n_tokens, s->hidden,
-                                s->top_k, s->n_glu, s->n_pos, s->dtype, out, stream);
+  rc = bibo_moe_combine_add_fwd(ws->y, x, ws->slot_row, ws->topk_idx, ws->topk_w, norm_w ? x : ws->addend, s->n_tokens,
+                                s->hidden, s->top_k, s->n_glu, s->n_pos, s->dtype, out, stream);
   if (rc) return rc;
   BIBO_STAGE(6);
 #undef BIBO_STAGE
   return BIBO_OK;
+}
+
+extern "C" int bibo_moe_forward(const bibo_moe_shape* s, const void* x, const void* w_router,
+                                const float* bias, const void* gate_up_proj, const void* down_proj,
+                                const float* theta, const bibo_moe_workspace* ws, void* out, void* stream) {
+  return forward_chain(s, x, w_router, bias, gate_up_proj, down_proj, theta, ws, out, stream, nullptr, 0.f, nullptr,
+                       nullptr, 0);
+}
+
+extern "C" int bibo_moe_ffn_supported(const bibo_moe_shape* s) {
+  return s && s->dtype == BIBO_BF16 && s->n_glu == s->n_experts &&
+         bibo_moe_router_norm_supported(s->hidden, s->n_experts, s->dtype);
+}
+
+extern "C" int bibo_moe_ffn_forward(const bibo_moe_shape* s, const void* h, const void* norm_weight, float eps,
+                                    const void* w_router, const float* bias, const void* gate_up_proj,
+                                    const void* down_proj, const float* theta, const bibo_moe_workspace* ws,
+                                    float* rstd, void* w_fold, int refold, void* out, void* stream) {
+  if (!s || !ws || !h || !norm_weight || !rstd || !w_fold) return fail(BIBO_ERR_ARG, "ffn_forward: null pointer");
+  if (!bibo_moe_ffn_supported(s))
+    return fail(BIBO_ERR_UNSUPPORTED, "ffn_forward: bf16, 64 GLU experts without identity experts and hidden %% 64 == 0 "
+                "only");
+  if (ws->addend) return fail(BIBO_ERR_ARG, "ffn_forward: the addend slot is taken by the residual");
+  return forward_chain(s, h, w_router, bias, gate_up_proj, down_proj, theta, ws, out, stream, norm_weight, eps, rstd,
+                       w_fold, refold);
 }
 
 // ---- host-buffer call: copies overlapped with the kernels --------------------------------------------

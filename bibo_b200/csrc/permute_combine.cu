@@ -10,13 +10,17 @@ constexpr int PW = 8;  // warps per block
 // Warps [0, n_tokens): lane j < k computes the destination row of slot j; the rows are broadcast by
 // shuffle and every lane copies its 16-byte chunks of x[t] to all k rows (x is read once).
 // Warps [n_tokens, n_tokens + n_glu*(TILE_M-1)): mark (and optionally zero) one padding row each.
+// With rstd / norm_w (bf16 rows only) x holds the raw residual stream and the copies are the RMSNorm
+// of the row, rounded where BiBoRMSNorm.forward rounds (src/modeling/norm.py:19-24):
+// bf16(w * bf16(h * rstd)).
 template <int VEC_BYTES>
 __global__ void __launch_bounds__(PW * 32)
 permute_kernel(const uint8_t* __restrict__ x, const int32_t* __restrict__ topk_idx,
                const int32_t* __restrict__ slot_rank, const int32_t* __restrict__ plan,
                int64_t n_tokens, int row_bytes, int n_experts, int n_glu, int top_k,
                int zero_padding, uint8_t* __restrict__ xp, int32_t* __restrict__ slot_row,
-               int32_t* __restrict__ row_token) {
+               int32_t* __restrict__ row_token, const float* __restrict__ rstd = nullptr,
+               const uint8_t* __restrict__ norm_w = nullptr) {
   const int lane = threadIdx.x & 31;
   const int64_t w = (int64_t)blockIdx.x * PW + (threadIdx.x >> 5);
   const int32_t* counts = plan + plan_off_counts();
@@ -39,8 +43,22 @@ permute_kernel(const uint8_t* __restrict__ x, const int32_t* __restrict__ topk_i
 #pragma unroll
     for (int j = 0; j < BIBO_MAX_TOP_K; ++j) rows[j] = __shfl_sync(0xffffffffu, my_row, j);
     const uint4* src = reinterpret_cast<const uint4*>(x + w * row_bytes);
+    const float rs = rstd != nullptr ? rstd[w] : 0.f;
     for (int c = lane; c < chunks; c += 32) {
-      const uint4 v = __ldg(src + c);
+      uint4 v = __ldg(src + c);
+      if (rstd != nullptr) {
+        const uint4 wv = __ldg(reinterpret_cast<const uint4*>(norm_w) + c);
+        uint32_t* hv = reinterpret_cast<uint32_t*>(&v);
+        const uint32_t* ww = reinterpret_cast<const uint32_t*>(&wv);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          const float a = __uint_as_float(hv[i] << 16), b = __uint_as_float(hv[i] & 0xffff0000u);
+          const float na = __bfloat162float(__float2bfloat16_rn(a * rs)), nb = __bfloat162float(__float2bfloat16_rn(b * rs));
+          const __nv_bfloat162 o = __floats2bfloat162_rn(na * __uint_as_float(ww[i] << 16),
+                                                         nb * __uint_as_float(ww[i] & 0xffff0000u));
+          hv[i] = *reinterpret_cast<const uint32_t*>(&o);
+        }
+      }
 #pragma unroll
       for (int j = 0; j < BIBO_MAX_TOP_K; ++j)
         if (j < top_k && rows[j] >= 0)
@@ -235,6 +253,29 @@ extern "C" int bibo_moe_permute_fwd(const void* x, const int32_t* topk_idx, cons
   permute_kernel<16><<<grid, PW * 32, 0, static_cast<cudaStream_t>(stream)>>>(
       (const uint8_t*)x, topk_idx, slot_rank, plan, n_tokens, row_bytes, n_experts, n_glu, top_k,
       zero_padding, (uint8_t*)xp, slot_row, row_token);
+  BIBO_CHECK_LAUNCH("permute_kernel");
+  return BIBO_OK;
+}
+
+extern "C" int bibo_moe_permute_norm_fwd(const void* h, const float* rstd, const void* norm_weight,
+                                         const int32_t* topk_idx, const int32_t* slot_rank, const int32_t* plan,
+                                         int64_t n_tokens, int hidden, int n_experts, int n_glu, int top_k,
+                                         int zero_padding, void* xp, int32_t* slot_row, int32_t* row_token,
+                                         void* stream) {
+  if (n_tokens <= 0) return BIBO_OK;
+  if (!h || !rstd || !norm_weight || !topk_idx || !slot_rank || !plan || !xp || !slot_row || !row_token)
+    return fail(BIBO_ERR_ARG, "permute_norm_fwd: null pointer");
+  if (top_k < 1 || top_k > BIBO_MAX_TOP_K) return fail(BIBO_ERR_UNSUPPORTED, "permute_norm_fwd: top_k=%d", top_k);
+  const int row_bytes = hidden * 2;
+  if (row_bytes % 16 != 0)
+    return fail(BIBO_ERR_UNSUPPORTED, "permute_norm_fwd: row of %d bytes is not a multiple of 16", row_bytes);
+  if (!aligned16(h) || !aligned16(xp) || !aligned16(norm_weight))
+    return fail(BIBO_ERR_ALIGN, "permute_norm_fwd: h / xp / norm_weight not 16-byte aligned");
+  const int64_t warps = n_tokens + (int64_t)n_glu * (BIBO_TILE_M - 1);
+  dim3 grid((unsigned)((warps + PW - 1) / PW));
+  permute_kernel<16><<<grid, PW * 32, 0, static_cast<cudaStream_t>(stream)>>>(
+      (const uint8_t*)h, topk_idx, slot_rank, plan, n_tokens, row_bytes, n_experts, n_glu, top_k, zero_padding,
+      (uint8_t*)xp, slot_row, row_token, rstd, (const uint8_t*)norm_weight);
   BIBO_CHECK_LAUNCH("permute_kernel");
   return BIBO_OK;
 }

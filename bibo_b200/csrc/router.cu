@@ -263,7 +263,10 @@ int router_tc_supported(int hidden, int n_experts, int dtype);
 int router_tc_launch(const void* x, const void* w_router, const float* bias, int64_t n_tokens,
                      int hidden, int n_experts, int top_k, int norm_mode, float scale,
                      float* logits_out, int32_t* topk_idx, float* topk_w, int32_t* slot_rank,
-                     int32_t* block_counts, int32_t* status, float* trace_blocks, cudaStream_t st);
+                     int32_t* block_counts, int32_t* status, float* trace_blocks, float eps, float* rstd_out,
+                     cudaStream_t st);
+int fold_norm_weight_launch(const void* w_router, const void* norm_w, int n_experts, int hidden, void* w_fold,
+                            cudaStream_t st);
 }
 
 int bibo_moe_router_fwd(const void* x, const void* w_router, const float* bias,
@@ -297,7 +300,8 @@ extern "C" int bibo_moe_router_fwd_trace(const void* x, const void* w_router, co
 
   if (!logits_in && router_tc_supported(hidden, n_experts, dtype) && aligned16(x) && aligned16(w_router))
     return router_tc_launch(x, w_router, bias, n_tokens, hidden, n_experts, top_k, norm_mode,
-                            scale, logits_out, topk_idx, topk_w, slot_rank, block_counts, status, trace_blocks, st);
+                            scale, logits_out, topk_idx, topk_w, slot_rank, block_counts, status, trace_blocks, 0.f,
+                            nullptr, st);
 
   const int ld = n_experts | 1;
   size_t smem = sizeof(float) * ((size_t)RB * ld + RK * (RB + 1) + RK * (RE + 1)) +
@@ -318,6 +322,41 @@ extern "C" int bibo_moe_router_fwd_trace(const void* x, const void* w_router, co
   }
   BIBO_CHECK_LAUNCH("router_simt_kernel");
   return BIBO_OK;
+}
+
+extern "C" int bibo_moe_router_norm_supported(int hidden, int n_experts, int dtype) {
+  return router_tc_supported(hidden, n_experts, dtype);
+}
+
+extern "C" int bibo_moe_fold_norm_weight(const void* w_router, const void* norm_weight, int n_experts, int hidden,
+                                         void* w_fold, void* stream) {
+  if (!w_router || !norm_weight || !w_fold) return fail(BIBO_ERR_ARG, "fold_norm_weight: null pointer");
+  if (n_experts < 1 || hidden < 8 || hidden % 8 != 0)
+    return fail(BIBO_ERR_UNSUPPORTED, "fold_norm_weight: n_experts=%d hidden=%d", n_experts, hidden);
+  if (!aligned16(w_router) || !aligned16(norm_weight) || !aligned16(w_fold))
+    return fail(BIBO_ERR_ALIGN, "fold_norm_weight: pointers not 16-byte aligned");
+  return fold_norm_weight_launch(w_router, norm_weight, n_experts, hidden, w_fold, static_cast<cudaStream_t>(stream));
+}
+
+extern "C" int bibo_moe_router_norm_fwd(const void* h, const void* w_fold, float eps, const float* bias,
+                                        int64_t n_tokens, int hidden, int n_experts, int top_k, int norm_mode,
+                                        float scale, float* logits_out, int32_t* topk_idx, float* topk_w,
+                                        int32_t* slot_rank, int32_t* block_counts, int32_t* status,
+                                        float* block_sums, float* rstd_out, void* stream) {
+  if (n_tokens <= 0) return BIBO_OK;
+  if (!h || !w_fold || !bias || !topk_idx || !topk_w || !slot_rank || !block_counts || !rstd_out)
+    return fail(BIBO_ERR_ARG, "router_norm_fwd: null pointer");
+  if (!bibo_moe_router_norm_supported(hidden, n_experts, BIBO_BF16))
+    return fail(BIBO_ERR_UNSUPPORTED, "router_norm_fwd: bf16, 64 experts and hidden %% 64 == 0 only (hidden=%d, "
+                "n_experts=%d)", hidden, n_experts);
+  if (top_k < 1 || top_k > BIBO_MAX_TOP_K || top_k > n_experts)
+    return fail(BIBO_ERR_UNSUPPORTED, "router_norm_fwd: top_k=%d", top_k);
+  if (norm_mode < BIBO_NORM_RAW || norm_mode > BIBO_NORM_SOFTMAX)
+    return fail(BIBO_ERR_ARG, "router_norm_fwd: norm_mode=%d", norm_mode);
+  if (!aligned16(h) || !aligned16(w_fold)) return fail(BIBO_ERR_ALIGN, "router_norm_fwd: h / w_fold not 16-byte aligned");
+  return router_tc_launch(h, w_fold, bias, n_tokens, hidden, n_experts, top_k, norm_mode, scale, logits_out, topk_idx,
+                          topk_w, slot_rank, block_counts, status, block_sums, eps, rstd_out,
+                          static_cast<cudaStream_t>(stream));
 }
 
 extern "C" int bibo_moe_route_from_indices(const int32_t* topk_idx, int64_t n_tokens, int n_experts,

@@ -255,6 +255,59 @@ def moe_forward(x: torch.Tensor, w_router: torch.Tensor, bias: torch.Tensor, gat
     return out, ws
 
 
+def ffn_supported(hidden: int, inter: int, n_experts: int, top_k: int) -> bool:
+    geo = Geometry(1, hidden, inter, n_experts, n_experts, 0, top_k, torch.bfloat16)
+    shape = _shape(geo, "sum", 1.0, False)
+    return bool(_lib.load().bibo_moe_ffn_supported(C.byref(shape)))
+
+
+def ffn_forward(h: torch.Tensor, norm_weight: torch.Tensor, eps: float, w_router: torch.Tensor, bias: torch.Tensor,
+                gate_up_proj: torch.Tensor, down_proj: torch.Tensor, theta: torch.Tensor, top_k: int, norm_mode="sum",
+                scale: float = 1.0, ws: Optional[MoEWorkspace] = None, out: Optional[torch.Tensor] = None,
+                keep_logits: bool = False, trace=None) -> Tuple[torch.Tensor, MoEWorkspace]:
+    """out = h + block(rmsnorm(h)) on flat bf16 rows h [N,H] with the norm folded into the router's and the
+    permute's loads (bibo_moe_ffn_forward).  The per-row rstd is left in ``ws.rstd``.  The router weight with
+    the norm weight folded in lives in ``ws.w_fold`` and is recomputed only when one of the two tensors
+    changed (another tensor, or an in-place update: torch's version counter)."""
+    lib = _lib.load()
+    for name, t in (("hidden_states", h), ("norm weight", norm_weight), ("w_router", w_router), ("bias", bias),
+                    ("gate_up_proj", gate_up_proj), ("down_proj", down_proj), ("radial_theta", theta)):
+        _need_cuda(t, name)
+    n, hidden = h.shape
+    n_glu, two_i, _ = gate_up_proj.shape
+    geo = Geometry(n, hidden, two_i // 2, w_router.shape[0], n_glu, 0, top_k, h.dtype)
+    for name, t in (("norm weight", norm_weight), ("w_router", w_router), ("gate_up_proj", gate_up_proj),
+                    ("down_proj", down_proj)):
+        if t.dtype != torch.bfloat16 or h.dtype != torch.bfloat16:
+            raise RuntimeError(f"ffn_forward is bf16 only ({name} is {t.dtype}, activations {h.dtype})")
+    if not h.is_contiguous() or not norm_weight.is_contiguous():
+        raise RuntimeError("ffn_forward: hidden_states and the norm weight must be contiguous")
+    if ws is None:
+        ws = get_workspace(geo, h.device, keep_logits=keep_logits)
+    if out is None:
+        out = torch.empty_like(h)
+    if n == 0:
+        return out, ws
+    if getattr(ws, "rstd", None) is None:
+        ws.rstd = torch.empty(n, dtype=torch.float32, device=h.device)
+        ws.w_fold, ws.w_fold_key = torch.empty_like(w_router), None
+    key = (w_router.data_ptr(), w_router._version, norm_weight.data_ptr(), norm_weight._version)
+    refold = int(ws.w_fold_key != key)
+    ws.w_fold_key = key
+    bias32 = bias if bias.dtype == torch.float32 else bias.float()
+    theta32 = theta if theta.dtype == torch.float32 else theta.float()
+    shape = _shape(geo, norm_mode, scale, False)
+    ws.addend, ws.trace = None, trace
+    cws = ws.c_struct()
+    ws.trace = None
+    rc = lib.bibo_moe_ffn_forward(C.byref(shape), _lib.ptr(h), _lib.ptr(norm_weight), float(eps), _lib.ptr(w_router),
+                                  _lib.ptr(bias32), _lib.ptr(gate_up_proj), _lib.ptr(down_proj), _lib.ptr(theta32),
+                                  C.byref(cws), _lib.ptr(ws.rstd), _lib.ptr(ws.w_fold), refold, _lib.ptr(out),
+                                  _stream(h.device))
+    _lib.check(rc, "bibo_moe_ffn_forward")
+    return out, ws
+
+
 def moe_forward_host(x_host: torch.Tensor, out_host: torch.Tensor, x_dev: torch.Tensor, out_dev: torch.Tensor,
                      w_router, bias, gate_up_proj, down_proj, theta, top_k: int, norm_mode="sum",
                      scale: float = 1.0, ws: Optional[MoEWorkspace] = None) -> torch.Tensor:

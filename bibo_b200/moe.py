@@ -246,13 +246,17 @@ def _balance_from_counts(layer, counts: torch.Tensor, num_tokens: int):
     return None
 
 
-def layer_forward(layer, hidden_states: torch.Tensor, residual: Optional[torch.Tensor] = None) -> torch.Tensor:
+def layer_forward(layer, hidden_states: torch.Tensor, residual: Optional[torch.Tensor] = None,
+                  fused_norm=None) -> torch.Tensor:
     """``BiBoMoELayer.forward`` (src/modeling/ffn/moe.py:157-183) on the CUDA kernel chain.
 
     Written against the REFERENCE's attribute names only, so it serves both this package's layer
     and, through ``bibo_b200.install``, an instance of the reference's own class.
     ``residual`` (same shape; used by ``ffn_forward``) is added to the result, inside the combine
-    kernel when the layer has no shared expert.
+    kernel when the layer has no shared expert.  ``fused_norm`` = (norm weight, eps), inference only and
+    only where ``fused_ffn_applies`` says so: ``hidden_states`` is then the raw residual stream, the
+    RMSNorm happens inside the router's and the permute's loads and the stream itself is added to the
+    result (``bibo_moe_ffn_forward``).
     """
     bsz, seq_len, hidden = hidden_states.shape
     n = bsz * seq_len
@@ -284,11 +288,16 @@ def layer_forward(layer, hidden_states: torch.Tensor, residual: Optional[torch.T
         trace = (trace[0], trace[1], gap) if trace is not None else (None, None, gap)
     params = (gate.gate_proj.weight, ex.gate_up_proj, ex.down_proj, ex.radial_theta)
     if torch.is_grad_enabled() and (flat.requires_grad or any(p.requires_grad for p in params)):
+        if fused_norm is not None:
+            raise RuntimeError("bibo_b200: the fused norm path has no backward; call it under torch.no_grad()")
         holder = {}
         out = _MoEBlockFunction.apply(flat, *params, gate.bias.detach(),
                                       (gate.top_k, gate.norm_topk_prob, scale, n_pos, n_neg, trace), holder,
                                       shared_out)
         ws = holder["ws"]
+    elif fused_norm is not None:
+        out, ws = Fn.ffn_forward(flat, fused_norm[0], fused_norm[1], gate.gate_proj.weight, gate.bias, ex.gate_up_proj,
+                                 ex.down_proj, ex.radial_theta, gate.top_k, gate.norm_topk_prob, scale, trace=trace)
     else:
         out, ws = Fn.moe_forward(flat, gate.gate_proj.weight, gate.bias, ex.gate_up_proj, ex.down_proj,
                                  ex.radial_theta, gate.top_k, gate.norm_topk_prob, scale,
@@ -356,11 +365,27 @@ def ffn_forward(decoder_layer, hidden_states: torch.Tensor) -> torch.Tensor:
         hidden_states = hidden_states + out
         return hidden_states.to(torch.bfloat16) if bf16_stream else hidden_states
     shape = hidden_states.shape
+    if is_moe and fused_ffn_applies(mlp, hidden_states, norm):
+        return layer_forward(mlp, hidden_states, fused_norm=(norm.weight, float(norm.variance_epsilon)))
     flat = hidden_states.reshape(-1, shape[-1]).contiguous()
     x = Fn.rmsnorm_forward(flat, norm.weight, norm.variance_epsilon).view(shape)
     if is_moe:
         return block(x, hidden_states)
     return hidden_states + block(x)
+
+
+def fused_ffn_applies(layer, hidden_states: torch.Tensor, norm) -> bool:
+    """Whether ``bibo_moe_ffn_forward`` covers this layer and input: bf16 on a CUDA device, 64 GLU experts
+    and nothing else (the +/-Identity experts and the shared expert read the normalised activations, which
+    the fused path never writes), and nobody listening on the hooks that hand those activations out."""
+    gate, ex = layer.gate, layer.experts
+    if not hidden_states.is_cuda or hidden_states.dtype != torch.bfloat16 or norm.weight.dtype != torch.bfloat16:
+        return False
+    if getattr(layer, "use_shared_expert", False) or ex.pos_end != ex.pos_start or ex.neg_end != ex.neg_start:
+        return False
+    if ex._forward_pre_hooks or gate._forward_hooks:
+        return False
+    return Fn.ffn_supported(hidden_states.shape[-1], ex.gate_up_proj.shape[1] // 2, gate.num_routed_experts, gate.top_k)
 
 
 def experts_forward_seam(experts, hidden_states: torch.Tensor, top_k_indices: torch.Tensor,
