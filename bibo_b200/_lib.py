@@ -46,7 +46,7 @@ class EpArgs(C.Structure):
                 [(n, _vp) for n in ("x", "w_router", "bias", "gate_up_proj", "down_proj", "theta", "topk_idx", "topk_w",
                                     "slot_rank", "block_counts", "local_plan", "ep_plan", "slot_row", "h", "xp_peers",
                                     "y_peers", "flags_peers", "cnt_peers", "out", "gate_up_recv", "rnorm_recv",
-                                    "row_token")])
+                                    "row_token", "trace")])
 
 
 class EpDma(C.Structure):

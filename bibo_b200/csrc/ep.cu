@@ -466,11 +466,14 @@ extern "C" int bibo_moe_ep_forward(const bibo_moe_ep_args* a, void* stream) {
   ep_set_carveouts();
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   int32_t* status = a->ep_plan + PLAN_STATUS;
-  rc = bibo_moe_router_fwd(a->x, a->w_router, a->bias, nullptr, a->n_tokens, a->hidden, a->n_experts, a->top_k,
-                           a->norm_mode, a->scale, BIBO_BF16, nullptr, a->topk_idx, a->topk_w, a->slot_rank,
-                           a->block_counts, a->local_plan + PLAN_STATUS, stream);
+  if (a->trace && !a->trace->block_sums) return fail(BIBO_ERR_ARG, "ep_forward: trace without block_sums");
+  rc = bibo_moe_router_fwd_trace(a->x, a->w_router, a->bias, nullptr, a->n_tokens, a->hidden, a->n_experts, a->top_k,
+                                 a->norm_mode, a->scale, BIBO_BF16, nullptr, a->topk_idx, a->topk_w, a->slot_rank,
+                                 a->block_counts, a->local_plan + PLAN_STATUS, a->trace ? a->trace->block_sums : nullptr,
+                                 stream);
   if (rc) return rc;
-  rc = bibo_moe_plan(a->block_counts, a->n_tokens, a->top_k, a->n_experts, a->n_experts, a->local_plan, stream);
+  rc = bibo_moe_plan_trace(a->block_counts, a->n_tokens, a->top_k, a->n_experts, a->n_experts, a->local_plan, a->trace,
+                           stream);
   if (rc) return rc;
   rc = ep_share_counts_launch(a->local_plan + plan_off_counts(), a->cnt_peers, a->rank, a->world, a->n_experts, st);
   if (rc) return rc;

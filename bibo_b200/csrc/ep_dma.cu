@@ -81,11 +81,12 @@ extern "C" int bibo_moe_ep_forward_dma(const bibo_moe_ep_args* a, const bibo_moe
   } while (0)
   if (phase != 2) {
   EP_MARK(0);
-  rc = bibo_moe_router_fwd(a->x, a->w_router, a->bias, nullptr, a->n_tokens, a->hidden, E, a->top_k, a->norm_mode,
-                               a->scale, BIBO_BF16, nullptr, a->topk_idx, a->topk_w, a->slot_rank, a->block_counts,
-                               a->local_plan + PLAN_STATUS, stream);
+  if (a->trace && !a->trace->block_sums) return fail(BIBO_ERR_ARG, "ep_forward_dma: trace without block_sums");
+  rc = bibo_moe_router_fwd_trace(a->x, a->w_router, a->bias, nullptr, a->n_tokens, a->hidden, E, a->top_k, a->norm_mode,
+                                 a->scale, BIBO_BF16, nullptr, a->topk_idx, a->topk_w, a->slot_rank, a->block_counts,
+                                 a->local_plan + PLAN_STATUS, a->trace ? a->trace->block_sums : nullptr, stream);
   if (rc) return rc;
-  rc = bibo_moe_plan(a->block_counts, a->n_tokens, a->top_k, E, E, a->local_plan, stream);
+  rc = bibo_moe_plan_trace(a->block_counts, a->n_tokens, a->top_k, E, E, a->local_plan, a->trace, stream);
   if (rc) return rc;
   for (int i = 0; i < R; ++i)
     if (!a->cnt_peers[i] || !a->xp_peers[i] || !d->y_home_peers[i])

@@ -282,7 +282,7 @@ class ExpertParallelMoE:
             p(self.ep_plan), p(self.slot_row), p(self.h), cast(self.xp.ptr_array), cast(self.y.ptr_array),
             cast(self.flags.ptr_array), cast(self.cnt.ptr_array), p(out),
             p(self.gate_up_recv) if training else None, p(self.rnorm_recv) if training else None,
-            p(self.row_token) if training else None)
+            p(self.row_token) if training else None, self._trace_struct())
         self._epoch += 3
         if self.dma and not training:
             d = _lib.EpDma(p(self.xp_send), p(self.y_owner), cast(self.y_home.ptr_array), p(self.row_token_dma),
@@ -297,6 +297,18 @@ class ExpertParallelMoE:
         _lib.check(_lib.load().bibo_moe_ep_forward(C.byref(a), st), "bibo_moe_ep_forward")
         self._last_args, self._last_x = (a, x) if training else (None, None)
         return out
+
+    def _trace_struct(self):
+        """Pointer to a bibo_moe_router_trace for this call when ``self.trace`` = (acc, counts, gap) is set
+        (the router and plan kernels then fold this rank's routing diagnostics into those tensors)."""
+        trace = getattr(self, "trace", None)
+        if trace is None:
+            return None
+        blocks = _lib.load().bibo_moe_router_blocks(self._n)
+        if getattr(self, "_trace_blocks", None) is None or self._trace_blocks.shape[0] != blocks:
+            self._trace_blocks = torch.empty(blocks, _lib.TRACE_WORDS, dtype=torch.float32, device=self.device)
+        self._trace_c = _lib.RouterTrace(_lib.ptr(self._trace_blocks), *[_lib.ptr(t) for t in trace])
+        return C.cast(C.pointer(self._trace_c), C.c_void_p)
 
     def _mark(self, name: str) -> None:
         """profile=True: record a timing event after each phase of the current forward."""
@@ -518,10 +530,22 @@ class ExpertParallelMoELayer(torch.nn.Module):
         flat = hidden_states.reshape(-1, hidden).contiguous()
         runner = self._get_runner()
         params = (self.gate.gate_proj.weight, self.gate_up_proj, self.down_proj, self.radial_theta)
+        # routing diagnostics of this rank's tokens, produced by the router / plan kernels (bibo_b200.RouterTrace,
+        # gate._probe_gap), as in the single-GPU layer
+        tracer = getattr(self, "_router_trace", None)
+        trace = tracer.buffers(self) if tracer is not None else None
+        want_gap = self.gate._probe_gap and self.gate.top_k < self.gate.num_routed_experts
+        if want_gap:
+            gap = torch.empty(1, dtype=torch.float32, device=flat.device)
+            trace = (trace[0], trace[1], gap) if trace is not None else (None, None, gap)
+        runner.trace = trace
         if torch.is_grad_enabled() and (flat.requires_grad or any(p.requires_grad for p in params)):
             out = _EPBlockFunction.apply(flat, *params, self)
         else:
             out = runner.forward(flat)
+        runner.trace = None
+        if want_gap:
+            self.gate.boundary_gap = gap[0]
         if self.training and self.bias_update_factor > 0:
             tpe = _balance_from_counts(self, runner._counts, flat.shape[0])   # all-reduces accumulated_tpe
             if tpe is not None:

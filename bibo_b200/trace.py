@@ -9,8 +9,10 @@ folds them into this object's device buffers (``bibo_moe_router_trace`` in inclu
 traced training forward launches exactly the kernels an untraced one does.  ``flush()`` makes the one
 device-to-host transfer of an interval, as the reference's does.
 
-Layers served: this package's ``BiBoMoELayer`` and any layer of the reference's class whose forward was
-replaced by ``bibo_b200.install`` (``moe.layer_forward`` reads ``layer._router_trace``).
+Layers served: this package's ``BiBoMoELayer``, any layer of the reference's class whose forward was
+replaced by ``bibo_b200.install`` (``moe.layer_forward`` reads ``layer._router_trace``) and the
+expert-parallel ``ExpertParallelMoELayer`` (every rank traces its own tokens, as the reference's hooks
+would).
 """
 import math
 
@@ -26,8 +28,8 @@ class RouterTrace:
         self.counts = torch.zeros(self.E, dtype=torch.float32, device=device)
         self.acc = torch.zeros(8, dtype=torch.float32, device=device)
         self._layers = [m for m in model.modules()
-                        if m.__class__.__name__ == "BiBoMoELayer" and hasattr(m, "gate") and hasattr(m, "experts")]
-        first = self._layers[0].experts if self._layers else None
+                        if m.__class__.__name__ in ("BiBoMoELayer", "ExpertParallelMoELayer") and hasattr(m, "gate")]
+        first = getattr(self._layers[0], "experts", None) if self._layers else None
         # boundaries of the +Identity / -Identity experts, for the two special-load channels
         self.n_glu = int(getattr(first, "num_glu_experts", self.E))
         self.pos_end = int(getattr(first, "pos_end", self.E))

@@ -355,6 +355,7 @@ typedef struct {
    * [rows_cap_recv] of the received rows, and the token of every row of the local expert-sorted
    * order [N*k + E*127]; with these set the padding rows of the receive buffer are zeroed.       */
   void* gate_up_recv; float* rnorm_recv; int32_t* row_token;
+  const bibo_moe_router_trace* trace; /* optional HOST struct: diagnostics of this rank's own tokens */
 } bibo_moe_ep_args;
 int bibo_moe_ep_forward(const bibo_moe_ep_args* args, void* stream);
 

@@ -4,7 +4,8 @@ Every rank builds the same single-GPU BiBoMoELayer (seeded weights), shards it i
 ExpertParallelMoELayer and trains one step on its own tokens; results are compared with the
 single-GPU layer run on the concatenated batch of all ranks: forward bit-identical, gradients at the
 bf16 bars (the two paths sum the same bf16 values in a different order), and the balancer's bias
-update identical."""
+update identical.  A RouterTrace on each layer: the sharded layer's sums over this rank's tokens against
+the single-GPU layer's trace of the same tokens."""
 import os
 import pathlib
 import sys
@@ -26,7 +27,7 @@ def main():
     torch.cuda.set_device(local)
     dev = torch.device("cuda", local)
     dist.init_process_group("nccl", device_id=dev)
-    from bibo_b200 import BiBoMoELayer, MoEConfig, ep
+    from bibo_b200 import BiBoMoELayer, MoEConfig, RouterTrace, ep
     from oracle import moe_oracle as orc
 
     # the balancer updates every round(threshold / tokens of this rank's forward) forwards: with these thresholds both
@@ -53,6 +54,18 @@ def main():
 
     x_all = inp["x"].to(torch.bfloat16).to(dev)
     xs = x_all[rank * n:(rank + 1) * n].clone().requires_grad_(True)
+    # routing diagnostics of this rank's tokens: the single-GPU layer on the same tokens (bias not yet updated)
+    full.bias_update_factor, keep = 0.0, full.bias_update_factor
+    trace_full = RouterTrace(torch.nn.ModuleDict({"m": full}), n_exp, dev)
+    full.gate._probe_gap = True
+    with torch.no_grad():
+        full(xs.detach().unsqueeze(0))
+    want_acc, want_counts, want_gap = trace_full.acc.clone(), trace_full.counts.clone(), full.gate.boundary_gap.clone()
+    trace_full.close()
+    full.gate._probe_gap = False
+    full.bias_update_factor = keep
+    trace_shard = RouterTrace(torch.nn.ModuleDict({"m": shard}), n_exp, dev)
+    shard.gate._probe_gap = True
     out = shard(xs.unsqueeze(0))[0]
     (out * dout[rank * n:(rank + 1) * n]).sum().backward()
     xf = x_all.clone().requires_grad_(True)
@@ -76,6 +89,10 @@ def main():
         r = rel(got.float(), want.float())
         msgs.append(f"{name} {r:.2e}")
         ok &= r < 2e-2
+    trace_same = (torch.equal(trace_shard.acc, want_acc) and torch.equal(trace_shard.counts, want_counts)
+                  and torch.equal(shard.gate.boundary_gap, want_gap) and float(want_acc[2]) == n)
+    msgs.append(f"router trace identical {trace_same}")
+    ok &= trace_same
     bias_same = torch.allclose(shard.gate.bias.data, full.gate.bias.data, rtol=0, atol=1e-7)
     moved = float((full.gate.bias.data - inp["bias"].to(dev)).abs().max()) > 0
     msgs.append(f"bias update identical {bias_same} (moved {moved})")
