@@ -144,3 +144,34 @@ def test_install_mlp_seam_and_shared_expert_state_dict():
     assert BiBoDecoderLayer._ffn_forward is orig_ffn
     with pytest.raises(ValueError):
         bibo_b200.install(ref, seam="attention")
+
+
+@pytest.mark.parametrize("name", ["router_trace_sum", "router_trace_raw"])
+def test_router_trace_flush_matches_the_reference_flush(name):
+    """bibo_b200.RouterTrace on CPU buffers: attach / detach, eval forwards skipped, and flush() on the
+    accumulator the reference's RouterTrace held after two forwards gives the reference's metrics
+    (fixture: tests/golden/make_golden.py run_trace_case)."""
+    import torch
+    from conftest import GOLDEN
+    from bibo_b200 import BiBoMoELayer, MoEConfig, RouterTrace
+    rec = torch.load(GOLDEN / f"{name}.pt", weights_only=True)
+    cfg = MoEConfig(hidden_size=rec["hidden"], moe_intermediate_size=rec["inter"], num_routed_experts=rec["n_experts"],
+                    num_experts_per_tok=rec["top_k"], num_pos_identity_experts=rec["pairs"],
+                    num_neg_identity_experts=rec["pairs"], norm_topk_prob=rec["norm"])
+    model = torch.nn.ModuleDict({"a": BiBoMoELayer(cfg), "b": BiBoMoELayer(cfg), "other": torch.nn.Linear(4, 4)})
+    trace = RouterTrace(model, rec["n_experts"], "cpu")
+    assert model["a"]._router_trace is trace and model["b"]._router_trace is trace
+    assert trace.n_glu == rec["n_glu"] and trace.pos_end == rec["n_glu"] + rec["pairs"]
+    bufs = trace.buffers(model["a"].train())
+    assert bufs[0] is trace.acc and bufs[1] is trace.counts and bufs[2] is None
+    assert trace.buffers(model["a"].eval()) is None
+    assert trace.flush() == {}, "nothing accumulated yet"
+    trace.acc.copy_(rec["acc"][-1])
+    trace.counts.copy_(rec["counts"][-1])
+    got = trace.flush()
+    assert list(got) == list(rec["flush"])
+    for k, v in rec["flush"].items():
+        assert abs(got[k] - v) <= 1e-6 * max(1.0, abs(v)), (k, got[k], v)
+    assert float(trace.acc.abs().sum()) == 0 and float(trace.counts.sum()) == 0
+    trace.close()
+    assert model["a"]._router_trace is None and model["b"]._router_trace is None
