@@ -82,9 +82,9 @@ SIGNATURES = {
     "bibo_moe_router_norm_fwd": (_i32, [_vp, _vp, _f32, _vp, _i64, _i32, _i32, _i32, _i32, _f32,
                                         _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp]),
     "bibo_moe_permute_norm_fwd": (_i32, [_vp, _vp, _vp, _vp, _vp, _vp, _i64, _i32, _i32, _i32, _i32, _i32,
-                                         _vp, _vp, _vp, _vp]),
+                                         _vp, _vp, _vp, _vp, _vp]),
     "bibo_moe_ffn_supported": (_i32, [_vp]),
-    "bibo_moe_ffn_forward": (_i32, [_vp, _vp, _vp, _f32, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i32, _vp, _vp]),
+    "bibo_moe_ffn_forward": (_i32, [_vp, _vp, _vp, _f32, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i32, _vp, _vp, _vp]),
     "bibo_moe_route_from_indices": (_i32, [_vp, _i64, _i32, _i32, _vp, _vp, _vp, _vp]),
     "bibo_moe_plan": (_i32, [_vp, _i64, _i32, _i32, _i32, _vp, _vp]),
     "bibo_moe_plan_trace": (_i32, [_vp, _i64, _i32, _i32, _i32, _vp, _vp, _vp]),

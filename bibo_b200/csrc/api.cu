@@ -81,7 +81,7 @@ extern "C" int bibo_moe_gemm2_fwd(const void* h, const void* down_proj, const in
 static int forward_chain(const bibo_moe_shape* s, const void* x, const void* w_router, const float* bias,
                          const void* gate_up_proj, const void* down_proj, const float* theta,
                          const bibo_moe_workspace* ws, void* out, void* stream, const void* norm_w, float eps,
-                         float* rstd, void* w_fold, int refold) {
+                         float* rstd, void* w_fold, int refold, void* xn) {
   if (!s || !ws) return fail(BIBO_ERR_ARG, "forward: null shape / workspace");
   cudaStream_t st_ = static_cast<cudaStream_t>(stream);
   void* const* ev = ws->stage_events;
@@ -111,7 +111,7 @@ static int forward_chain(const bibo_moe_shape* s, const void* x, const void* w_r
   rc = norm_w
       ? bibo_moe_permute_norm_fwd(x, rstd, norm_w, ws->topk_idx, ws->slot_rank, ws->plan, s->n_tokens, s->hidden,
                                   s->n_experts, s->n_glu, s->top_k, s->zero_padding, ws->xp, ws->slot_row,
-                                  ws->row_token, stream)
+                                  ws->row_token, xn, stream)
       : bibo_moe_permute_fwd(x, ws->topk_idx, ws->slot_rank, ws->plan, s->n_tokens, s->hidden, s->n_experts,
                              s->n_glu, s->top_k, s->dtype, s->zero_padding, ws->xp, ws->slot_row,
                              ws->row_token, stream);
@@ -126,8 +126,9 @@ static int forward_chain(const bibo_moe_shape* s, const void* x, const void* w_r
                           s->n_glu, s->top_k, s->dtype, ws->y, stream);
   if (rc) return rc;
   BIBO_STAGE(5);
-  rc = bibo_moe_combine_add_fwd(ws->y, x, ws->slot_row, ws->topk_idx, ws->topk_w, norm_w ? x : ws->addend, s->n_tokens,
-                                s->hidden, s->top_k, s->n_glu, s->n_pos, s->dtype, out, stream);
+  // with the norm folded in, x is the raw stream: it is the residual, and the identity experts (if any) read xn
+  rc = bibo_moe_combine_add_fwd(ws->y, (norm_w && xn) ? xn : x, ws->slot_row, ws->topk_idx, ws->topk_w, norm_w ? x : ws->addend,
+                                s->n_tokens, s->hidden, s->top_k, s->n_glu, s->n_pos, s->dtype, out, stream);
   if (rc) return rc;
   BIBO_STAGE(6);
 #undef BIBO_STAGE
@@ -138,25 +139,24 @@ extern "C" int bibo_moe_forward(const bibo_moe_shape* s, const void* x, const vo
                                 const float* bias, const void* gate_up_proj, const void* down_proj,
                                 const float* theta, const bibo_moe_workspace* ws, void* out, void* stream) {
   return forward_chain(s, x, w_router, bias, gate_up_proj, down_proj, theta, ws, out, stream, nullptr, 0.f, nullptr,
-                       nullptr, 0);
+                       nullptr, 0, nullptr);
 }
 
 extern "C" int bibo_moe_ffn_supported(const bibo_moe_shape* s) {
-  return s && s->dtype == BIBO_BF16 && s->n_glu == s->n_experts &&
-         bibo_moe_router_norm_supported(s->hidden, s->n_experts, s->dtype);
+  return s && s->dtype == BIBO_BF16 && bibo_moe_router_norm_supported(s->hidden, s->n_experts, s->dtype);
 }
 
 extern "C" int bibo_moe_ffn_forward(const bibo_moe_shape* s, const void* h, const void* norm_weight, float eps,
                                     const void* w_router, const float* bias, const void* gate_up_proj,
                                     const void* down_proj, const float* theta, const bibo_moe_workspace* ws,
-                                    float* rstd, void* w_fold, int refold, void* out, void* stream) {
+                                    float* rstd, void* w_fold, int refold, void* xn, void* out, void* stream) {
   if (!s || !ws || !h || !norm_weight || !rstd || !w_fold) return fail(BIBO_ERR_ARG, "ffn_forward: null pointer");
   if (!bibo_moe_ffn_supported(s))
-    return fail(BIBO_ERR_UNSUPPORTED, "ffn_forward: bf16, 64 GLU experts without identity experts and hidden %% 64 == 0 "
-                "only");
+    return fail(BIBO_ERR_UNSUPPORTED, "ffn_forward: bf16, 64 routed experts and hidden %% 64 == 0 only");
+  if (s->n_glu < s->n_experts && !xn) return fail(BIBO_ERR_ARG, "ffn_forward: identity experts need the xn buffer");
   if (ws->addend) return fail(BIBO_ERR_ARG, "ffn_forward: the addend slot is taken by the residual");
   return forward_chain(s, h, w_router, bias, gate_up_proj, down_proj, theta, ws, out, stream, norm_weight, eps, rstd,
-                       w_fold, refold);
+                       w_fold, refold, xn);
 }
 
 // ---- host-buffer call: copies overlapped with the kernels --------------------------------------------

@@ -12,7 +12,8 @@ constexpr int PW = 8;  // warps per block
 // Warps [n_tokens, n_tokens + n_glu*(TILE_M-1)): mark (and optionally zero) one padding row each.
 // With rstd / norm_w (bf16 rows only) x holds the raw residual stream and the copies are the RMSNorm
 // of the row, rounded where BiBoRMSNorm.forward rounds (src/modeling/norm.py:19-24):
-// bf16(w * bf16(h * rstd)).
+// bf16(w * bf16(h * rstd)).  A token with a slot on a +/-Identity expert also leaves its normalised row
+// in xn[t] (the only rows of xn ever written), where the combine kernel finds it.
 template <int VEC_BYTES>
 __global__ void __launch_bounds__(PW * 32)
 permute_kernel(const uint8_t* __restrict__ x, const int32_t* __restrict__ topk_idx,
@@ -20,7 +21,7 @@ permute_kernel(const uint8_t* __restrict__ x, const int32_t* __restrict__ topk_i
                int64_t n_tokens, int row_bytes, int n_experts, int n_glu, int top_k,
                int zero_padding, uint8_t* __restrict__ xp, int32_t* __restrict__ slot_row,
                int32_t* __restrict__ row_token, const float* __restrict__ rstd = nullptr,
-               const uint8_t* __restrict__ norm_w = nullptr) {
+               const uint8_t* __restrict__ norm_w = nullptr, uint8_t* __restrict__ xn = nullptr) {
   const int lane = threadIdx.x & 31;
   const int64_t w = (int64_t)blockIdx.x * PW + (threadIdx.x >> 5);
   const int32_t* counts = plan + plan_off_counts();
@@ -30,8 +31,10 @@ permute_kernel(const uint8_t* __restrict__ x, const int32_t* __restrict__ topk_i
 
   if (w < n_tokens) {
     int my_row = -1;
+    bool identity = false;       // a slot on a +/-Identity expert: the combine kernel reads the normalised row itself
     if (lane < top_k) {
       const int e = topk_idx[w * top_k + lane];
+      identity = e >= n_glu;
       if (e < n_glu) {
         const int64_t b = w / BIBO_ROUTER_BLOCK_TOKENS;
         my_row = expert_off[e] + block_base[b * n_experts + e] + slot_rank[w * top_k + lane];
@@ -44,6 +47,8 @@ permute_kernel(const uint8_t* __restrict__ x, const int32_t* __restrict__ topk_i
     for (int j = 0; j < BIBO_MAX_TOP_K; ++j) rows[j] = __shfl_sync(0xffffffffu, my_row, j);
     const uint4* src = reinterpret_cast<const uint4*>(x + w * row_bytes);
     const float rs = rstd != nullptr ? rstd[w] : 0.f;
+    uint4* keep = (xn != nullptr && __any_sync(0xffffffffu, identity)) ? reinterpret_cast<uint4*>(xn + w * row_bytes)
+                                                                      : nullptr;
     for (int c = lane; c < chunks; c += 32) {
       uint4 v = __ldg(src + c);
       if (rstd != nullptr) {
@@ -58,6 +63,7 @@ permute_kernel(const uint8_t* __restrict__ x, const int32_t* __restrict__ topk_i
                                                          nb * __uint_as_float(ww[i] & 0xffff0000u));
           hv[i] = *reinterpret_cast<const uint32_t*>(&o);
         }
+        if (keep != nullptr) keep[c] = v;
       }
 #pragma unroll
       for (int j = 0; j < BIBO_MAX_TOP_K; ++j)
@@ -261,10 +267,12 @@ extern "C" int bibo_moe_permute_norm_fwd(const void* h, const float* rstd, const
                                          const int32_t* topk_idx, const int32_t* slot_rank, const int32_t* plan,
                                          int64_t n_tokens, int hidden, int n_experts, int n_glu, int top_k,
                                          int zero_padding, void* xp, int32_t* slot_row, int32_t* row_token,
-                                         void* stream) {
+                                         void* xn, void* stream) {
   if (n_tokens <= 0) return BIBO_OK;
   if (!h || !rstd || !norm_weight || !topk_idx || !slot_rank || !plan || !xp || !slot_row || !row_token)
     return fail(BIBO_ERR_ARG, "permute_norm_fwd: null pointer");
+  if (n_glu < n_experts && (!xn || !aligned16(xn)))
+    return fail(BIBO_ERR_ARG, "permute_norm_fwd: identity experts need the xn buffer (16-byte aligned)");
   if (top_k < 1 || top_k > BIBO_MAX_TOP_K) return fail(BIBO_ERR_UNSUPPORTED, "permute_norm_fwd: top_k=%d", top_k);
   const int row_bytes = hidden * 2;
   if (row_bytes % 16 != 0)
@@ -275,7 +283,7 @@ extern "C" int bibo_moe_permute_norm_fwd(const void* h, const float* rstd, const
   dim3 grid((unsigned)((warps + PW - 1) / PW));
   permute_kernel<16><<<grid, PW * 32, 0, static_cast<cudaStream_t>(stream)>>>(
       (const uint8_t*)h, topk_idx, slot_rank, plan, n_tokens, row_bytes, n_experts, n_glu, top_k, zero_padding,
-      (uint8_t*)xp, slot_row, row_token, rstd, (const uint8_t*)norm_weight);
+      (uint8_t*)xp, slot_row, row_token, rstd, (const uint8_t*)norm_weight, n_glu < n_experts ? (uint8_t*)xn : nullptr);
   BIBO_CHECK_LAUNCH("permute_kernel");
   return BIBO_OK;
 }

@@ -264,7 +264,8 @@ def ffn_supported(hidden: int, inter: int, n_experts: int, top_k: int) -> bool:
 def ffn_forward(h: torch.Tensor, norm_weight: torch.Tensor, eps: float, w_router: torch.Tensor, bias: torch.Tensor,
                 gate_up_proj: torch.Tensor, down_proj: torch.Tensor, theta: torch.Tensor, top_k: int, norm_mode="sum",
                 scale: float = 1.0, ws: Optional[MoEWorkspace] = None, out: Optional[torch.Tensor] = None,
-                keep_logits: bool = False, trace=None) -> Tuple[torch.Tensor, MoEWorkspace]:
+                keep_logits: bool = False, trace=None, n_pos: int = 0, n_neg: int = 0,
+                ) -> Tuple[torch.Tensor, MoEWorkspace]:
     """out = h + block(rmsnorm(h)) on flat bf16 rows h [N,H] with the norm folded into the router's and the
     permute's loads (bibo_moe_ffn_forward).  The per-row rstd is left in ``ws.rstd``.  The router weight with
     the norm weight folded in lives in ``ws.w_fold`` and is recomputed only when one of the two tensors
@@ -275,7 +276,9 @@ def ffn_forward(h: torch.Tensor, norm_weight: torch.Tensor, eps: float, w_router
         _need_cuda(t, name)
     n, hidden = h.shape
     n_glu, two_i, _ = gate_up_proj.shape
-    geo = Geometry(n, hidden, two_i // 2, w_router.shape[0], n_glu, 0, top_k, h.dtype)
+    geo = Geometry(n, hidden, two_i // 2, w_router.shape[0], n_glu, n_pos, top_k, h.dtype)
+    if geo.n_experts != n_glu + n_pos + n_neg:
+        raise RuntimeError(f"{geo.n_experts} routed experts != {n_glu} GLU + {n_pos} + {n_neg} identity experts")
     for name, t in (("norm weight", norm_weight), ("w_router", w_router), ("gate_up_proj", gate_up_proj),
                     ("down_proj", down_proj)):
         if t.dtype != torch.bfloat16 or h.dtype != torch.bfloat16:
@@ -291,6 +294,8 @@ def ffn_forward(h: torch.Tensor, norm_weight: torch.Tensor, eps: float, w_router
     if getattr(ws, "rstd", None) is None:
         ws.rstd = torch.empty(n, dtype=torch.float32, device=h.device)
         ws.w_fold, ws.w_fold_key = torch.empty_like(w_router), None
+        # normalised rows of the tokens that pick a +/-Identity expert (only those rows are ever touched)
+        ws.xn = torch.empty_like(h) if n_glu < geo.n_experts else None
     key = (w_router.data_ptr(), w_router._version, norm_weight.data_ptr(), norm_weight._version)
     refold = int(ws.w_fold_key != key)
     ws.w_fold_key = key
@@ -302,8 +307,8 @@ def ffn_forward(h: torch.Tensor, norm_weight: torch.Tensor, eps: float, w_router
     ws.trace = None
     rc = lib.bibo_moe_ffn_forward(C.byref(shape), _lib.ptr(h), _lib.ptr(norm_weight), float(eps), _lib.ptr(w_router),
                                   _lib.ptr(bias32), _lib.ptr(gate_up_proj), _lib.ptr(down_proj), _lib.ptr(theta32),
-                                  C.byref(cws), _lib.ptr(ws.rstd), _lib.ptr(ws.w_fold), refold, _lib.ptr(out),
-                                  _stream(h.device))
+                                  C.byref(cws), _lib.ptr(ws.rstd), _lib.ptr(ws.w_fold), refold, _lib.ptr(ws.xn),
+                                  _lib.ptr(out), _stream(h.device))
     _lib.check(rc, "bibo_moe_ffn_forward")
     return out, ws
 

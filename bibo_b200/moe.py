@@ -297,7 +297,8 @@ def layer_forward(layer, hidden_states: torch.Tensor, residual: Optional[torch.T
         ws = holder["ws"]
     elif fused_norm is not None:
         out, ws = Fn.ffn_forward(flat, fused_norm[0], fused_norm[1], gate.gate_proj.weight, gate.bias, ex.gate_up_proj,
-                                 ex.down_proj, ex.radial_theta, gate.top_k, gate.norm_topk_prob, scale, trace=trace)
+                                 ex.down_proj, ex.radial_theta, gate.top_k, gate.norm_topk_prob, scale, trace=trace,
+                                 n_pos=n_pos, n_neg=n_neg)
     else:
         out, ws = Fn.moe_forward(flat, gate.gate_proj.weight, gate.bias, ex.gate_up_proj, ex.down_proj,
                                  ex.radial_theta, gate.top_k, gate.norm_topk_prob, scale,
@@ -375,13 +376,13 @@ def ffn_forward(decoder_layer, hidden_states: torch.Tensor) -> torch.Tensor:
 
 
 def fused_ffn_applies(layer, hidden_states: torch.Tensor, norm) -> bool:
-    """Whether ``bibo_moe_ffn_forward`` covers this layer and input: bf16 on a CUDA device, 64 GLU experts
-    and nothing else (the +/-Identity experts and the shared expert read the normalised activations, which
-    the fused path never writes), and nobody listening on the hooks that hand those activations out."""
+    """Whether ``bibo_moe_ffn_forward`` covers this layer and input: bf16 on a CUDA device, 64 routed experts,
+    no shared expert (it reads the normalised activations, which the fused path never writes), and nobody
+    listening on the hooks that hand those activations out."""
     gate, ex = layer.gate, layer.experts
     if not hidden_states.is_cuda or hidden_states.dtype != torch.bfloat16 or norm.weight.dtype != torch.bfloat16:
         return False
-    if getattr(layer, "use_shared_expert", False) or ex.pos_end != ex.pos_start or ex.neg_end != ex.neg_start:
+    if getattr(layer, "use_shared_expert", False):
         return False
     if ex._forward_pre_hooks or gate._forward_hooks:
         return False

@@ -230,14 +230,17 @@ int bibo_moe_forward(const bibo_moe_shape* shape, const void* x, const void* w_r
  * and scales its accumulators by rstd = rsqrt(mean h^2 + eps) (rstd [N] fp32 is an output); the
  * permute kernel writes bf16(w * bf16(h * rstd)), BiBoRMSNorm.forward's rounding
  * (src/modeling/norm.py:19-24), into the expert rows; the combine kernel adds h.
- * bf16, 64 experts, no identity experts, hidden % 64 == 0 (bibo_moe_ffn_supported); ws->addend must be
- * NULL.  w_fold [E,H] bf16 is caller-owned scratch: refold != 0 recomputes it first (one small extra
- * launch); refold == 0 reuses what an earlier call left there for the same weights.                 */
+ * bf16, 64 routed experts, hidden % 64 == 0 (bibo_moe_ffn_supported); ws->addend must be NULL.
+ * w_fold [E,H] bf16 is caller-owned scratch: refold != 0 recomputes it first (one small extra
+ * launch); refold == 0 reuses what an earlier call left there for the same weights.
+ * xn [N,H] bf16 is needed only with +/-Identity experts (n_glu < n_experts; NULL otherwise): the
+ * permute kernel leaves there the normalised row of every token that picked such an expert (no other
+ * row is written or read), which the combine kernel adds as +w*x / -w*x.                            */
 int bibo_moe_ffn_supported(const bibo_moe_shape* shape);
 int bibo_moe_ffn_forward(const bibo_moe_shape* shape, const void* h, const void* norm_weight, float eps,
                          const void* w_router, const float* bias, const void* gate_up_proj,
                          const void* down_proj, const float* theta, const bibo_moe_workspace* ws,
-                         float* rstd, void* w_fold, int refold, void* out, void* stream);
+                         float* rstd, void* w_fold, int refold, void* xn, void* out, void* stream);
 /* The pieces on their own.                                                                          */
 int bibo_moe_router_norm_supported(int hidden, int n_experts, int dtype);
 int bibo_moe_fold_norm_weight(const void* w_router, const void* norm_weight, int n_experts, int hidden,
@@ -251,7 +254,7 @@ int bibo_moe_permute_norm_fwd(const void* h, const float* rstd, const void* norm
                               const int32_t* topk_idx, const int32_t* slot_rank, const int32_t* plan,
                               int64_t n_tokens, int hidden, int n_experts, int n_glu, int top_k,
                               int zero_padding, void* xp, int32_t* slot_row, int32_t* row_token,
-                              void* stream);
+                              void* xn, void* stream);
 
 /* Same block with HOST input and output: copies x_host to x_dev, runs the block, copies the result
  * into out_host and waits for it.  x_dev / out_dev are caller-allocated device staging buffers

@@ -135,8 +135,9 @@ def test_rmsnorm_backward_matches_oracle_autograd(dtype, n, h):
         assert rel_err(dw.float().cpu(), cw.grad.float()) < BF16_MAX
 
 
-@pytest.mark.parametrize("n,h,i", [(4096 + 37, 1024, 256), (2048, 2048, 512), (130, 4096, 128)])
-def test_fused_norm_chain_against_the_separate_norm_kernel(n, h, i):
+@pytest.mark.parametrize("n,h,i,pairs", [(4096 + 37, 1024, 256, 0), (2048, 2048, 512, 0), (130, 4096, 128, 0),
+                                         (3000, 1024, 256, 1), (777, 512, 128, 3)])
+def test_fused_norm_chain_against_the_separate_norm_kernel(n, h, i, pairs):
     """bibo_moe_ffn_forward (norm inside the router's and the permute's loads) against rmsnorm kernel ->
     block -> residual in the combine: rstd against torch, the normalised expert rows bit for bit where
     rstd has the same bits, the routing equal except at near-ties, the outputs equal on equally routed tokens."""
@@ -146,17 +147,20 @@ def test_fused_norm_chain_against_the_separate_norm_kernel(n, h, i):
     t = {k: v.to(DEV) for k, v in inp.items()}
     for k in ("w_router", "gate_up_proj", "down_proj"):
         t[k] = t[k].to(torch.bfloat16).contiguous()
+    g_ = 64 - 2 * pairs        # with pairs > 0 the last experts are +Identity / -Identity (no weights)
+    for k in ("gate_up_proj", "down_proj", "radial_theta"):
+        t[k] = t[k][:g_].contiguous()
     # a residual stream whose rows have different scales, as after a few layers
     hs = (torch.randn(n, h, generator=g) * (0.5 + 3 * torch.rand(n, 1, generator=g))).to(torch.bfloat16).to(DEV)
     nw = (1.0 + 0.1 * torch.randn(h, generator=g)).to(torch.bfloat16).to(DEV)
     eps = 1e-6
-    geo = Fn.Geometry(n, h, i, 64, 64, 0, 6, torch.bfloat16)
+    geo = Fn.Geometry(n, h, i, 64, g_, pairs, 6, torch.bfloat16)
     ws_a, ws_b = Fn.MoEWorkspace(geo, DEV, keep_logits=True), Fn.MoEWorkspace(geo, DEV, keep_logits=True)
     x = Fn.rmsnorm_forward(hs, nw, eps)
     ref, ws_a = Fn.moe_forward(x, t["w_router"], t["bias"], t["gate_up_proj"], t["down_proj"], t["radial_theta"], 6,
-                               ws=ws_a, addend=hs)
+                               ws=ws_a, addend=hs, n_pos=pairs, n_neg=pairs)
     out, ws_b = Fn.ffn_forward(hs, nw, eps, t["w_router"], t["bias"], t["gate_up_proj"], t["down_proj"],
-                               t["radial_theta"], 6, ws=ws_b)
+                               t["radial_theta"], 6, ws=ws_b, n_pos=pairs, n_neg=pairs)
     torch.cuda.synchronize()
     assert Fn.plan_header(ws_a)[2] == 0 and Fn.plan_header(ws_b)[2] == 0
     rstd = torch.rsqrt(hs.double().pow(2).mean(-1) + eps)
@@ -173,18 +177,23 @@ def test_fused_norm_chain_against_the_separate_norm_kernel(n, h, i):
         assert bool((gap <= 2 * err.double() + 1e-7).all())
     o, r = out.float()[same], ref.float()[same]
     assert rel_err(o.cpu(), r.cpu()) < 8e-3, rel_err(o.cpu(), r.cpu())
+    if pairs:
+        special = (ws_b.topk_idx >= g_).any(-1)
+        assert int((special & same).sum()) > 0, "no equally routed token picked an identity expert"
+        o2, r2 = out.float()[special & same], ref.float()[special & same]
+        assert rel_err(o2.cpu(), r2.cpu()) < 8e-3
     # the expert rows of an equally routed token are the separate kernel's normalised row
-    tok = int(same.nonzero()[0])
+    tok = int((same & (ws_b.slot_row[:, 0] >= 0)).nonzero()[0])
     row_a, row_b = int(ws_a.slot_row[tok, 0]), int(ws_b.slot_row[tok, 0])
     assert float((ws_a.xp[row_a].float() - ws_b.xp[row_b].float()).abs().max()) <= 2 ** -7 * float(x[tok].float().abs().max())
     again, _ = Fn.ffn_forward(hs, nw, eps, t["w_router"], t["bias"], t["gate_up_proj"], t["down_proj"],
-                              t["radial_theta"], 6, ws=ws_b)       # reuses the folded router weight
+                              t["radial_theta"], 6, ws=ws_b, n_pos=pairs, n_neg=pairs)   # reuses the folded router weight
     assert torch.equal(again, out), "the fused chain is not deterministic"
     fold = (t["w_router"].float() * nw.float()).to(torch.bfloat16)
     assert torch.equal(ws_b.w_fold, fold)
     nw.mul_(2.0)                                                    # an in-place update must be seen
     twice, _ = Fn.ffn_forward(hs, nw, eps, t["w_router"], t["bias"], t["gate_up_proj"], t["down_proj"],
-                              t["radial_theta"], 6, ws=ws_b)
+                              t["radial_theta"], 6, ws=ws_b, n_pos=pairs, n_neg=pairs)
     assert torch.equal(ws_b.w_fold, (t["w_router"].float() * nw.float()).to(torch.bfloat16))
     assert not torch.equal(twice, out)
 
