@@ -119,6 +119,8 @@ SIGNATURES = {
     "bibo_moe_mlp_plan_words": (_i64, [_i64]),
     "bibo_moe_mlp_supported": (_i32, [_i32, _i32, _i32]),
     "bibo_moe_mlp_forward": (_i32, [_vp, _vp, _vp, _vp, _i64, _i32, _i32, _i32, _vp, _vp, _vp, _vp, _vp]),
+    "bibo_moe_mlp_forward_residual": (_i32, [_vp, _vp, _vp, _vp, _i64, _i32, _i32, _i32, _vp, _vp, _vp, _vp, _vp,
+                                             _vp]),
     "bibo_moe_mlp_backward": (_i32, [_vp, _vp, _vp, _vp, _vp, _vp, _i64, _i32, _i32, _i32, _vp, _vp, _vp, _vp, _vp,
                                      _vp]),
     "bibo_moe_ep_forward": (_i32, [C.POINTER(EpArgs), _vp]),

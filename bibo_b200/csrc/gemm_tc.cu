@@ -32,11 +32,14 @@ struct G2Layout {
   static constexpr int BYTES = OFF_BAR + 256 + 1024;  // barriers + alignment slack
 };
 
-template <int BN, int STAGES>
+// RES: the epilogue adds residual[row][col] (same shape and pitch as y) to the rounded product,
+// y = bf16(bf16(acc) + residual): the decoder layer's `hidden_states + mlp(...)` (src/modeling/layers.py:61-66)
+// for the dense layers, without a pass of its own over the activations.
+template <int BN, int STAGES, bool RES = false>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 gemm2_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                 const __grid_constant__ CUtensorMap tmC, int32_t* __restrict__ plan, int64_t tiles_off,
-                int n_chunks, int k_blocks, int n_out) {
+                int n_chunks, int k_blocks, int n_out, const __nv_bfloat16* __restrict__ residual = nullptr) {
   using L = G2Layout<BN, STAGES>;
   extern __shared__ unsigned char smem_dyn[];
   unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_dyn) + 1023) & ~uintptr_t(1023));
@@ -128,15 +131,32 @@ gemm2_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
 #pragma unroll
         for (int hh = 0; hh < 2; ++hh) {
           uint32_t r[32];
+          uint4 res[4];
+          if (RES) {   // issued before the accumulator is read, so the loads fly under the tensor-memory load
+            const bool live = row < t.z;
+            const uint4* rp = reinterpret_cast<const uint4*>(residual + (int64_t)(t.y + row) * n_out + n0 + g * 64 + hh * 32);
+#pragma unroll
+            for (int j = 0; j < 4; ++j) res[j] = live ? __ldg(rp + j) : make_uint4(0, 0, 0, 0);
+          }
           tmem_ld32(tmem_base + ((uint32_t)(q * 32) << 16) + acc * BN + g * 64 + hh * 32, r);
           tmem_ld_wait();
 #pragma unroll
           for (int j = 0; j < 4; ++j) {
             uint4 v;
-            v.x = pack_bf16(__uint_as_float(r[8 * j + 0]), __uint_as_float(r[8 * j + 1]));
-            v.y = pack_bf16(__uint_as_float(r[8 * j + 2]), __uint_as_float(r[8 * j + 3]));
-            v.z = pack_bf16(__uint_as_float(r[8 * j + 4]), __uint_as_float(r[8 * j + 5]));
-            v.w = pack_bf16(__uint_as_float(r[8 * j + 6]), __uint_as_float(r[8 * j + 7]));
+            if (RES) {
+              const uint32_t* rv = reinterpret_cast<const uint32_t*>(&res[j]);
+              uint32_t o[4];
+#pragma unroll
+              for (int i = 0; i < 4; ++i)
+                o[i] = pack_bf16(round_bf16(__uint_as_float(r[8 * j + 2 * i])) + bf16_lo(rv[i]),
+                                 round_bf16(__uint_as_float(r[8 * j + 2 * i + 1])) + bf16_hi(rv[i]));
+              v = make_uint4(o[0], o[1], o[2], o[3]);
+            } else {
+              v.x = pack_bf16(__uint_as_float(r[8 * j + 0]), __uint_as_float(r[8 * j + 1]));
+              v.y = pack_bf16(__uint_as_float(r[8 * j + 2]), __uint_as_float(r[8 * j + 3]));
+              v.z = pack_bf16(__uint_as_float(r[8 * j + 4]), __uint_as_float(r[8 * j + 5]));
+              v.w = pack_bf16(__uint_as_float(r[8 * j + 6]), __uint_as_float(r[8 * j + 7]));
+            }
             *reinterpret_cast<uint4*>(cbuf + swz(row, hh * 4 + j)) = v;
           }
         }
@@ -716,23 +736,23 @@ int gemm2_tc_supported(int hidden, int inter, int dtype) {
   return dtype == BIBO_BF16 && hidden % 256 == 0 && inter % 64 == 0 && inter >= 64;
 }
 
-template <int BN, int STAGES>
+template <int BN, int STAGES, bool RES = false>
 static int gemm2_launch_t(const void* h, const void* down_proj, const PlanView& pv, int hidden, int inter,
-                          int n_weight_experts, void* y, cudaStream_t st) {
+                          int n_weight_experts, void* y, cudaStream_t st, const void* residual = nullptr) {
   using L = G2Layout<BN, STAGES>;
   CUtensorMap tmA, tmB, tmC;
   int rc;
   if ((rc = make_tmap_bf16_2d(&tmA, h, pv.rows_alloc, inter, inter, BM))) return rc;
   if ((rc = make_tmap_bf16_2d(&tmB, down_proj, (uint64_t)n_weight_experts * hidden, inter, inter, BN))) return rc;
   if ((rc = make_tmap_bf16_2d(&tmC, y, pv.rows_alloc, hidden, hidden, BM))) return rc;
-  auto kern = gemm2_tc_kernel<BN, STAGES>;
+  auto kern = gemm2_tc_kernel<BN, STAGES, RES>;
   static bool attr_done = false;
   if (!attr_done) { if ((rc = set_smem(kern, L::BYTES))) return rc; attr_done = true; }
   const int64_t work_cap = pv.tiles_cap * (hidden / BN);
   const int sms = pv.max_ctas > 0 ? std::min(pv.max_ctas, sm_count()) : sm_count();
   const int grid = (int)std::min<int64_t>(sms, work_cap);
   kern<<<grid, NUM_THREADS, L::BYTES, st>>>(tmA, tmB, tmC, const_cast<int32_t*>(pv.plan), pv.tiles_off, hidden / BN,
-                                           inter / BK, hidden);
+                                           inter / BK, hidden, static_cast<const __nv_bfloat16*>(residual));
   BIBO_CHECK_LAUNCH("gemm2_tc_kernel");
   return BIBO_OK;
 }
@@ -740,6 +760,12 @@ static int gemm2_launch_t(const void* h, const void* down_proj, const PlanView& 
 int gemm2_tc_launch(const void* h, const void* down_proj, const PlanView& pv, int hidden, int inter,
                     int n_weight_experts, void* y, cudaStream_t st) {
   return gemm2_launch_t<256, 4>(h, down_proj, pv, hidden, inter, n_weight_experts, y, st);
+}
+
+// y = bf16(bf16(h x down_proj^T) + residual); residual has y's shape and pitch
+int gemm2_tc_residual_launch(const void* h, const void* down_proj, const PlanView& pv, int hidden, int inter,
+                             int n_weight_experts, void* y, const void* residual, cudaStream_t st) {
+  return gemm2_launch_t<256, 4, true>(h, down_proj, pv, hidden, inter, n_weight_experts, y, st, residual);
 }
 
 int gemm1_tc_supported(int hidden, int inter, int dtype) {

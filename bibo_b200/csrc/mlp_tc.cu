@@ -22,6 +22,8 @@ int swiglu_rows_launch(const void* gate_up, int64_t n_rows, int inter, int dtype
 int gemm2_tc_supported(int hidden, int inter, int dtype);
 int gemm2_tc_launch(const void* h, const void* down_proj, const PlanView& pv, int hidden, int inter,
                     int n_weight_experts, void* y, cudaStream_t st);
+int gemm2_tc_residual_launch(const void* h, const void* down_proj, const PlanView& pv, int hidden, int inter,
+                             int n_weight_experts, void* y, const void* residual, cudaStream_t st);
 
 namespace tc {
 
@@ -277,7 +279,18 @@ extern "C" int bibo_moe_mlp_supported(int hidden, int inter, int dtype) {
 extern "C" int bibo_moe_mlp_forward(const void* x, const void* gate_proj, const void* up_proj, const void* down_proj,
                                     int64_t n_tokens, int hidden, int inter, int dtype, int32_t* plan, void* h, void* y,
                                     void* gate_up_out, void* stream) {
+  return bibo_moe_mlp_forward_residual(x, gate_proj, up_proj, down_proj, n_tokens, hidden, inter, dtype, plan, h, y,
+                                       gate_up_out, nullptr, stream);
+}
+
+extern "C" int bibo_moe_mlp_forward_residual(const void* x, const void* gate_proj, const void* up_proj,
+                                             const void* down_proj, int64_t n_tokens, int hidden, int inter, int dtype,
+                                             int32_t* plan, void* h, void* y, void* gate_up_out, const void* residual,
+                                             void* stream) {
   if (n_tokens <= 0) return BIBO_OK;
+  if (residual && (!bibo_moe_mlp_supported(hidden, inter, dtype) || !aligned16(residual)))
+    return fail(BIBO_ERR_UNSUPPORTED, "mlp_forward_residual: the residual add lives in the tensor-core down kernel "
+                "(bf16 shapes of bibo_moe_mlp_supported, 16-byte aligned residual)");
   if (!x || !gate_proj || !up_proj || !down_proj || !plan || !h || !y)
     return fail(BIBO_ERR_ARG, "mlp_forward: null pointer");
   if (dtype != BIBO_F32 && dtype != BIBO_BF16) return fail(BIBO_ERR_ARG, "mlp_forward: dtype=%d", dtype);
@@ -359,6 +372,7 @@ extern "C" int bibo_moe_mlp_forward(const void* x, const void* gate_proj, const 
   BIBO_CUDA(cudaLaunchKernelEx(&cfg, mlp_gemm1_pair_kernel, tmA, tmG, tmU, tmH, plan, pv.tiles_off, pv.pairs_off,
                                hidden / BK, inter / M_NC, static_cast<__nv_bfloat16*>(gate_up_out), n_tokens));
   launch_counter().fetch_add(1, std::memory_order_relaxed);
+  if (residual) return gemm2_tc_residual_launch(h, down_proj, pv, hidden, inter, 1, y, residual, st);
   return gemm2_tc_launch(h, down_proj, pv, hidden, inter, 1, y, st);
 }
 

@@ -406,10 +406,11 @@ def rmsnorm_backward(dy: torch.Tensor, h: torch.Tensor, weight: torch.Tensor, ep
 
 
 def mlp_forward(x: torch.Tensor, gate_proj: torch.Tensor, up_proj: torch.Tensor, down_proj: torch.Tensor,
-                out: Optional[torch.Tensor] = None, keep: bool = False):
+                out: Optional[torch.Tensor] = None, keep: bool = False, residual: Optional[torch.Tensor] = None):
     """Dense SwiGLU MLP ``down(silu(gate(x)) * up(x))`` on flat tokens x [N,H] (bibo_moe_mlp_forward);
     weights are the ``nn.Linear`` weights as stored: gate/up [I,H], down [H,I].  bf16.
-    ``keep=True`` returns ``(out, saved)`` with the tensors ``mlp_backward`` needs."""
+    ``keep=True`` returns ``(out, saved)`` with the tensors ``mlp_backward`` needs.
+    ``residual`` [N,H] is added in the down kernel's epilogue (tensor-core shapes only: ``mlp_residual_supported``)."""
     lib = _lib.load()
     for name, t in (("x", x), ("gate_proj", gate_proj), ("up_proj", up_proj), ("down_proj", down_proj)):
         _need_cuda(t, name)
@@ -429,9 +430,21 @@ def mlp_forward(x: torch.Tensor, gate_proj: torch.Tensor, up_proj: torch.Tensor,
     h = torch.empty(n, inter, dtype=x.dtype, device=x.device)
     gate_up = torch.empty(n, 2 * inter, dtype=x.dtype, device=x.device) if (keep or not tensor_cores) else None
     p = _lib.ptr
+    if residual is not None:
+        if residual.shape != x.shape or residual.dtype != x.dtype or not residual.is_contiguous() or not residual.is_cuda:
+            raise RuntimeError("residual must be a contiguous CUDA tensor of the activations' shape and dtype")
+        _lib.check(lib.bibo_moe_mlp_forward_residual(p(x), p(gate_proj), p(up_proj), p(down_proj), n, hidden, inter, dt,
+                                                     p(plan), p(h), p(out), p(gate_up), p(residual), _stream(x.device)),
+                   "bibo_moe_mlp_forward_residual")
+        return (out, (plan, h, gate_up)) if keep else out
     _lib.check(lib.bibo_moe_mlp_forward(p(x), p(gate_proj), p(up_proj), p(down_proj), n, hidden, inter, dt, p(plan),
                                         p(h), p(out), p(gate_up), _stream(x.device)), "bibo_moe_mlp_forward")
     return (out, (plan, h, gate_up)) if keep else out
+
+
+def mlp_residual_supported(hidden: int, inter: int, dtype) -> bool:
+    """Whether ``mlp_forward(residual=...)`` can add the residual inside the down kernel for these sizes."""
+    return bool(_lib.load().bibo_moe_mlp_supported(hidden, inter, dtype_code(dtype)))
 
 
 def mlp_backward(dout: torch.Tensor, x: torch.Tensor, gate_proj: torch.Tensor, up_proj: torch.Tensor,

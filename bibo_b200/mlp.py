@@ -38,16 +38,23 @@ class _MLPFunction(torch.autograd.Function):
         return grads
 
 
-def mlp_module_forward(mlp, x: torch.Tensor) -> torch.Tensor:
+def mlp_module_forward(mlp, x: torch.Tensor, residual=None) -> torch.Tensor:
     """``BiBoMLP.forward`` written against the reference's attribute names only (works on an instance of
-    the reference's own class)."""
+    the reference's own class).  ``residual`` (inference, x's shape): returns ``residual + mlp(x)`` with the
+    add inside the down kernel where the shapes allow it, by torch otherwise."""
     act = getattr(getattr(mlp, "config", None), "hidden_act", "silu")
     if act not in ("silu", "swish"):
         raise NotImplementedError(f"bibo_b200.BiBoMLP: hidden_act={act!r} (the kernels implement SiLU)")
     weights = (mlp.gate_proj.weight, mlp.up_proj.weight, mlp.down_proj.weight)
     flat = x.reshape(-1, x.shape[-1]).contiguous()
     if torch.is_grad_enabled() and (x.requires_grad or any(w.requires_grad for w in weights)):
-        return _MLPFunction.apply(flat, *weights).view(x.shape)
+        out = _MLPFunction.apply(flat, *weights).view(x.shape)
+        return out if residual is None else residual + out
+    if residual is not None:
+        if flat.is_cuda and Fn.mlp_residual_supported(flat.shape[1], weights[0].shape[0], flat.dtype):
+            res = residual.reshape(-1, x.shape[-1]).contiguous()
+            return Fn.mlp_forward(flat, *weights, residual=res).view(x.shape)
+        return residual + Fn.mlp_forward(flat, *weights).view(x.shape)
     return Fn.mlp_forward(flat, *weights).view(x.shape)
 
 

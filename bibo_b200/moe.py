@@ -372,7 +372,7 @@ def ffn_forward(decoder_layer, hidden_states: torch.Tensor) -> torch.Tensor:
     x = Fn.rmsnorm_forward(flat, norm.weight, norm.variance_epsilon).view(shape)
     if is_moe:
         return block(x, hidden_states)
-    return hidden_states + block(x)
+    return mlp_module_forward(mlp, x, residual=hidden_states)     # the add happens in the down kernel's epilogue
 
 
 def fused_ffn_applies(layer, hidden_states: torch.Tensor, norm) -> bool:

@@ -435,6 +435,13 @@ int bibo_moe_mlp_supported(int hidden, int inter, int dtype);
 int bibo_moe_mlp_forward(const void* x, const void* gate_proj, const void* up_proj, const void* down_proj,
                          int64_t n_tokens, int hidden, int inter, int dtype, int32_t* plan, void* h, void* y,
                          void* gate_up_out, void* stream);
+/* The same with the decoder layer's residual add (src/modeling/layers.py:61-66) in the down kernel's
+ * epilogue: y = T(T(mlp(x)) + residual), residual [N,H] (may alias nothing written here; NULL = plain
+ * forward).  Tensor-core shapes only (bibo_moe_mlp_supported).                                      */
+int bibo_moe_mlp_forward_residual(const void* x, const void* gate_proj, const void* up_proj,
+                                  const void* down_proj, int64_t n_tokens, int hidden, int inter, int dtype,
+                                  int32_t* plan, void* h, void* y, void* gate_up_out, const void* residual,
+                                  void* stream);
 /* Backward of bibo_moe_mlp_forward (autograd through BiBoMLP.forward in the reference).  plan, h and
  * gate_up are the forward's (gate_up is overwritten with [dGate | dUp]); gate_up_weight is
  * [gate_proj ; up_proj] stacked [2I, H] and d_gate_up_weight [2I, H] receives their gradients in the

@@ -221,3 +221,34 @@ def test_fused_norm_is_refused_or_bypassed_where_it_does_not_apply():
     with pytest.raises(RuntimeError, match="bf16 only"):
         Fn.ffn_forward(h[0].float(), dl.post_attention_layernorm.weight.float(), 1e-6, t["w_router"], t["bias"],
                        t["gate_up_proj"], t["down_proj"], t["radial_theta"], 6)
+
+
+def test_ffn_forward_of_a_dense_layer_adds_the_residual_in_the_down_kernel():
+    """A decoder layer whose feed-forward block is the dense BiBoMLP (layers 0 and N-1 of the reference model):
+    norm kernel, MLP with the residual added by the down kernel's epilogue; against the separate calls bit for
+    bit and against the oracle at the bf16 bars."""
+    from bibo_b200 import BiBoMLP, MoEConfig, functional as Fn
+    from bibo_b200.moe import ffn_forward
+    n, h, i = 700, 512, 1024
+    cfg = MoEConfig(hidden_size=h)
+    cfg.intermediate_size = i
+    w = orc.make_mlp_weights(h, i, seed=5)
+    mlp = BiBoMLP(cfg)
+    with torch.no_grad():
+        mlp.gate_proj.weight.copy_(w["gate_proj"]); mlp.up_proj.weight.copy_(w["up_proj"])
+        mlp.down_proj.weight.copy_(w["down_proj"])
+    g = torch.Generator().manual_seed(12)
+    norm_w = (1.0 + 0.1 * torch.randn(h, generator=g)).to(torch.bfloat16)
+    dl = torch.nn.Module()
+    dl.mlp = mlp.to(DEV).to(torch.bfloat16)
+    dl.post_attention_layernorm = _Norm(norm_w, 1e-6).to(DEV)
+    hs = (2 * torch.randn(1, n, h, generator=g)).to(torch.bfloat16).to(DEV)
+    with torch.no_grad():
+        out = ffn_forward(dl.eval(), hs)
+        x = Fn.rmsnorm_forward(hs[0], dl.post_attention_layernorm.weight, 1e-6)
+        sep = hs[0] + Fn.mlp_forward(x, dl.mlp.gate_proj.weight, dl.mlp.up_proj.weight, dl.mlp.down_proj.weight)
+    assert out.shape == hs.shape and torch.equal(out[0], sep)
+    r = lambda t: t.to(torch.bfloat16).float()
+    ref = hs[0].float().cpu() + orc.mlp_forward(orc.rmsnorm(hs[0].float().cpu(), norm_w.float(), 1e-6),
+                                                r(w["gate_proj"]), r(w["up_proj"]), r(w["down_proj"]))
+    assert rel_err(out[0].float().cpu(), ref) < BF16_MAX and mean_rel_err(out[0].float().cpu(), ref) < BF16_MEAN
