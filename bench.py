@@ -396,6 +396,8 @@ def main():
         "e2e": {"value": e2e_val, "unit": UNIT, "h2d_bytes_per_step": x_host.numel() * 2 * world,
                 "d2h_bytes_per_step": out_host.numel() * 2 * world},
     }
+    if args.mode != "fwd":      # the host-buffer call is the block's forward: it says nothing about the other modes
+        line["e2e"]["note"] = "host-buffer forward of the block alone (mode fwd), not of mode " + args.mode
     if world == 1 and not args.no_cpu_baseline:
         line["cpu_baseline"] = cpu_oracle_rate(wl)
     print(json.dumps(line))
