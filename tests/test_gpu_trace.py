@@ -126,3 +126,45 @@ def test_trace_pieces_are_optional_and_checked():
         Fn.moe_forward(*args, ws=ws, trace=(torch.zeros(7, device=DEV), None, None))
     with pytest.raises(RuntimeError, match="trace tensors"):
         Fn.moe_forward(*args, ws=ws, trace=(None, torch.zeros(64), None))
+
+
+def test_traced_and_fused_forwards_replay_from_a_cuda_graph():
+    """The traced block and the fused feed-forward half are plain stream work (no host synchronisation): both
+    are captured in one CUDA graph; every replay adds one forward to the trace accumulators and reproduces the
+    eager results on new inputs."""
+    from bibo_b200 import functional as Fn
+    n, h, i = 2048, 512, 128
+    t = _bf16_block(n=n, h=h, i=i)
+    args = (t["w_router"], t["bias"], t["gate_up_proj"], t["down_proj"], t["radial_theta"], 6)
+    geo = Fn.Geometry(n, h, i, 64, 64, 0, 6, torch.bfloat16)
+    ws, ws_f = Fn.MoEWorkspace(geo, DEV), Fn.MoEWorkspace(geo, DEV)
+    nw = (1.0 + 0.1 * torch.randn(h, generator=torch.Generator().manual_seed(3))).to(torch.bfloat16).to(DEV)
+    bufs = (torch.zeros(8, device=DEV), torch.zeros(64, device=DEV), torch.zeros(1, device=DEV))
+    x_static, out_a, out_b = t["x"].clone(), torch.empty_like(t["x"]), torch.empty_like(t["x"])
+
+    def both():
+        Fn.moe_forward(x_static, *args, ws=ws, out=out_a, trace=bufs)
+        Fn.ffn_forward(x_static, nw, 1e-6, *args, ws=ws_f, out=out_b)
+
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+        both()                                  # warm-up: attributes, tensor maps, the folded router weight
+    torch.cuda.current_stream().wait_stream(side)
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        both()
+    for b in bufs:
+        b.zero_()
+    counts = torch.zeros(64, device=DEV)
+    for rep, seed in enumerate((1, 2, 3)):
+        x_new = torch.randn(n, h, generator=torch.Generator().manual_seed(seed)).to(torch.bfloat16).to(DEV)
+        x_static.copy_(x_new)
+        graph.replay()
+        torch.cuda.synchronize()
+        eager, w1 = Fn.moe_forward(x_new, *args, ws=Fn.MoEWorkspace(geo, DEV))
+        fused, _ = Fn.ffn_forward(x_new, nw, 1e-6, *args, ws=Fn.MoEWorkspace(geo, DEV))
+        assert torch.equal(out_a, eager) and torch.equal(out_b, fused)
+        counts += w1.counts().float()
+        assert float(bufs[0][7]) == rep + 1 and float(bufs[0][2]) == (rep + 1) * n
+        assert torch.equal(bufs[1], counts)
