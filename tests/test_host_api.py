@@ -175,3 +175,25 @@ def test_router_trace_flush_matches_the_reference_flush(name):
     assert float(trace.acc.abs().sum()) == 0 and float(trace.counts.sum()) == 0
     trace.close()
     assert model["a"]._router_trace is None and model["b"]._router_trace is None
+
+
+def test_ffn_seam_host_logic_without_a_gpu():
+    """Which path the feed-forward seam takes is decided on the host: CPU tensors never qualify for the fused
+    chain and are refused by the kernels' entry check rather than served by a slower path."""
+    import torch
+    from bibo_b200 import BiBoMoELayer, MoEConfig
+    from bibo_b200.moe import ffn_forward, fused_ffn_applies
+
+    class Norm(torch.nn.Module):
+        def __init__(self, h):
+            super().__init__()
+            self.weight = torch.nn.Parameter(torch.ones(h, dtype=torch.bfloat16))
+            self.variance_epsilon = 1e-6
+
+    dl = torch.nn.Module()
+    dl.mlp = BiBoMoELayer(MoEConfig(hidden_size=128, moe_intermediate_size=64)).to(torch.bfloat16).eval()
+    dl.post_attention_layernorm = Norm(128)
+    h = torch.randn(1, 8, 128).to(torch.bfloat16)
+    assert not fused_ffn_applies(dl.mlp, h, dl.post_attention_layernorm)
+    with torch.no_grad(), pytest.raises(RuntimeError, match="no CPU implementation"):
+        ffn_forward(dl, h)
