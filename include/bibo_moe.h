@@ -122,11 +122,15 @@ int bibo_moe_route_from_indices(const int32_t* topk_idx, int64_t n_tokens, int n
 /* ---- plan: histogram -> offsets ---------------------------------------------------------------
  * Replaces the sort / bincount / cumsum / .tolist() of BiBoFusedExperts.forward
  * (src/modeling/ffn/moe.py:56-68) without a host synchronisation.
- * plan layout (int32 words): [0]=n_tiles [1]=rows used [2]=status [3]=reserved; the status word is
+ * plan layout (int32 words): [0]=n_tiles [1]=rows used [2]=status [3]=n_pairs; the status word is
  * STICKY: the caller zeroes it once, kernels only ever raise it (1 = histogram total != N*k,
- * 100/101/102 = a bounded wait in the down / gate-up / router kernel gave up),
+ * 4 = a receive buffer of the expert-parallel path would overflow, 5 = a cross-rank barrier timed
+ * out, 100..111 = a bounded wait inside a tensor-core kernel gave up: 100 down, 101 gate/up,
+ * 102 router, 104 the gate/up kernel's exchange between its two column-block clusters),
  * then counts[E], expert_off[E_glu+1], block_base[blocks*E] (exclusive prefix of block_counts over
- * blocks), tiles[tiles_cap*4].  Accessors below return the word offsets.                         */
+ * blocks), tiles[tiles_cap*4] (int4 {expert, first row, rows, 0}), pairs[tiles_cap*2] (int2: two
+ * consecutive tiles of one expert, or {tile, -1}) and the scratch of the gate/up kernel.
+ * bibo_moe_plan_words gives the total; the accessors below return the word offsets.                */
 int bibo_moe_plan(const int32_t* block_counts, int64_t n_tokens, int top_k, int n_experts,
                   int n_glu, int32_t* plan, void* stream);
 /* bibo_moe_plan that also reduces the router's diagnostic sums (trace NULL = off).                */
