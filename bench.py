@@ -211,6 +211,8 @@ def main():
                     help="N>1: do not pin each rank to the CPUs local to its GPU (pinned host buffers then land anywhere)")
     ap.add_argument("--e2e-chunks", type=int, default=4, help="token slices of the host-buffer (e2e) forward (N>1)")
     ap.add_argument("--comm-sms", type=int, default=20, help="SMs left to the exchange kernels (N>1)")
+    ap.add_argument("--gather-in-gemm", action="store_true",
+                    help="1 GPU: the gate/up kernel gathers its own rows instead of a separate permute kernel (A/B)")
     ap.add_argument("--mode", default="fwd", choices=["fwd", "fwdbwd", "ffn", "ffn_separate"],
                     help="fwd = the headline metric; fwdbwd = forward + backward of the block (1 GPU); ffn = the decoder "
                          "layer's feed-forward half (RMSNorm + block + residual) with the norm folded into the router's and "
@@ -255,7 +257,8 @@ def main():
         ws = Fn.MoEWorkspace(geo, dev, keep_gate_up=False)
         out = torch.empty_like(t["x"])
         step = lambda: Fn.moe_forward(t["x"], t["w_router"], t["bias"], t["gate_up_proj"], t["down_proj"],
-                                      t["radial_theta"], TOP_K, "sum", ws=ws, out=out)
+                                      t["radial_theta"], TOP_K, "sum", ws=ws, out=out,
+                                      gather_in_gemm=args.gather_in_gemm)
         if args.mode in ("ffn", "ffn_separate"):
             norm_w = (1.0 + 0.1 * torch.randn(h, generator=torch.Generator().manual_seed(99))).to(dtype).to(dev)
             if args.mode == "ffn":

@@ -97,6 +97,10 @@ SIGNATURES = {
     "bibo_moe_gemm1_radial_fwd": (_i32, [_vp, _vp, _vp, _vp, _i64, _i32, _i32, _i32, _i32, _i32,
                                          _i32, _vp, _vp, _vp, _vp]),
     "bibo_moe_gemm1_is_fused": (_i32, [_i32, _i32, _i32]),
+    "bibo_moe_rowmap_fwd": (_i32, [_vp, _vp, _vp, _i64, _i32, _i32, _i32, _vp, _vp, _vp]),
+    "bibo_moe_gemm1_gather_supported": (_i32, [_i32, _i32, _i32]),
+    "bibo_moe_gemm1_gather_fwd": (_i32, [_vp, _vp, _vp, _vp, _vp, _i64, _i32, _i32, _i32, _i32, _i32, _i32, _i32,
+                                         _vp, _vp, _vp, _vp, _vp]),
     "bibo_moe_gemm2_fwd": (_i32, [_vp, _vp, _vp, _i64, _i32, _i32, _i32, _i32, _i32, _i32, _vp, _vp]),
     "bibo_moe_combine_fwd": (_i32, [_vp, _vp, _vp, _vp, _vp, _i64, _i32, _i32, _i32, _i32, _i32,
                                     _vp, _vp]),
@@ -130,6 +134,7 @@ SIGNATURES = {
     "bibo_moe_ep_experts": (_i32, [_vp, _vp, _vp, _vp, _vp, _i32, _i32, _i32, _i32, _i64, _i32, _vp, _vp, _vp, _vp, _i32,
                                    _vp]),
     "bibo_moe_ep_barrier": (_i32, [_vp, _i32, _i32, _i32, _vp, _vp]),
+    "bibo_moe_ep_barrier_bounded": (_i32, [_vp, _i32, _i32, _i32, _i64, _vp, _vp]),
     "bibo_moe_ep_combine": (_i32, [_vp, _vp, _vp, _vp, _i64, _i32, _i32, _i32, _i64, _i32, _vp, _vp]),
     "bibo_moe_route_noalloc": (_i32, [_vp, _vp, _vp, _i64, _i32, _i32, _i32, _i32, _f32, _i32, _vp, _vp, _vp, _vp]),
     "bibo_moe_route_noalloc_max_tokens": (_i64, []),

@@ -13,8 +13,10 @@ int radial_rows_launch(const void* gate_up, const float* theta, const PlanView& 
                        float* rnorm_out, cudaStream_t st);
 // gemm_tc.cu
 int gemm1_tc_supported(int hidden, int inter, int dtype);
+int gemm1_gather_supported(int hidden, int inter, int dtype);
 int gemm1_tc_launch(const void* xp, const void* gate_up_proj, const float* theta, const PlanView& pv, int hidden,
-                    int inter, int n_weight_experts, void* h, void* gate_up_out, float* rnorm_out, cudaStream_t st);
+                    int inter, int n_weight_experts, void* h, void* gate_up_out, float* rnorm_out, cudaStream_t st,
+                    const void* gather_src = nullptr, const int32_t* row_src = nullptr, int zero_padding = 0);
 int gemm2_tc_supported(int hidden, int inter, int dtype);
 int gemm2_tc_launch(const void* h, const void* down_proj, const PlanView& pv, int hidden, int inter,
                     int n_weight_experts, void* y, cudaStream_t st);
@@ -56,6 +58,30 @@ extern "C" int bibo_moe_gemm1_radial_fwd(const void* xp, const void* gate_up_pro
   rc = gemm_simt_launch(xp, gate_up_proj, gate_up_out, pv, hidden, 2 * inter, dtype, st);
   if (rc) return rc;
   return radial_rows_launch(gate_up_out, theta, pv, inter, dtype, h, rnorm_out, st);
+}
+
+extern "C" int bibo_moe_gemm1_gather_supported(int hidden, int inter, int dtype) {
+  return gemm1_gather_supported(hidden, inter, dtype);
+}
+
+extern "C" int bibo_moe_gemm1_gather_fwd(const void* x, const int32_t* row_token, const void* gate_up_proj,
+                                         const float* theta, const int32_t* plan, int64_t n_tokens, int hidden,
+                                         int inter, int n_experts, int n_glu, int top_k, int dtype,
+                                         int zero_padding, void* xp, void* h, void* gate_up_out, float* rnorm_out,
+                                         void* stream) {
+  int rc = check_common("gemm1_gather_fwd", n_tokens, hidden, inter, n_experts, n_glu, top_k, dtype);
+  if (rc) return rc;
+  if (n_glu == 0) return BIBO_OK;
+  if (!x || !row_token || !xp || !gate_up_proj || !theta || !plan || !h)
+    return fail(BIBO_ERR_ARG, "gemm1_gather_fwd: null pointer");
+  if (!gemm1_gather_supported(hidden, inter, dtype))
+    return fail(BIBO_ERR_UNSUPPORTED, "gemm1_gather_fwd: bf16 with intermediate 256 or 512 only (hidden=%d inter=%d)",
+                hidden, inter);
+  if (!aligned16(x) || !aligned16(xp) || !aligned16(gate_up_proj) || !aligned16(h) || !aligned16(gate_up_out))
+    return fail(BIBO_ERR_ALIGN, "gemm1_gather_fwd: pointers not 16-byte aligned");
+  const PlanView pv = local_plan_view(plan, n_tokens, top_k, n_experts, n_glu);
+  return gemm1_tc_launch(xp, gate_up_proj, theta, pv, hidden, inter, n_glu, h, gate_up_out, rnorm_out,
+                         static_cast<cudaStream_t>(stream), x, row_token, zero_padding & 1);
 }
 
 extern "C" int bibo_moe_gemm1_is_fused(int hidden, int inter, int dtype) {
@@ -108,18 +134,30 @@ static int forward_chain(const bibo_moe_shape* s, const void* x, const void* w_r
   rc = bibo_moe_plan_trace(ws->block_counts, s->n_tokens, s->top_k, s->n_experts, s->n_glu, ws->plan, tr, stream);
   if (rc) return rc;
   BIBO_STAGE(2);
+  // bit 1 of zero_padding: the gate/up kernel copies its own rows (bf16, intermediate 256 / 512) and the
+  // permute pass shrinks to the row maps
+  const bool gather = !norm_w && (s->zero_padding & 2) && s->n_glu > 0 &&
+                      gemm1_gather_supported(s->hidden, s->inter, s->dtype) && aligned16(x) && aligned16(ws->xp) &&
+                      aligned16(gate_up_proj) && aligned16(ws->h) && aligned16(ws->gate_up);
   rc = norm_w
       ? bibo_moe_permute_norm_fwd(x, rstd, norm_w, ws->topk_idx, ws->slot_rank, ws->plan, s->n_tokens, s->hidden,
-                                  s->n_experts, s->n_glu, s->top_k, s->zero_padding, ws->xp, ws->slot_row,
+                                  s->n_experts, s->n_glu, s->top_k, s->zero_padding & 1, ws->xp, ws->slot_row,
                                   ws->row_token, xn, stream)
+      : gather
+      ? bibo_moe_rowmap_fwd(ws->topk_idx, ws->slot_rank, ws->plan, s->n_tokens, s->n_experts, s->n_glu, s->top_k,
+                            ws->slot_row, ws->row_token, stream)
       : bibo_moe_permute_fwd(x, ws->topk_idx, ws->slot_rank, ws->plan, s->n_tokens, s->hidden, s->n_experts,
-                             s->n_glu, s->top_k, s->dtype, s->zero_padding, ws->xp, ws->slot_row,
+                             s->n_glu, s->top_k, s->dtype, s->zero_padding & 1, ws->xp, ws->slot_row,
                              ws->row_token, stream);
   if (rc) return rc;
   BIBO_STAGE(3);
-  rc = bibo_moe_gemm1_radial_fwd(ws->xp, gate_up_proj, theta, ws->plan, s->n_tokens, s->hidden, s->inter,
-                                 s->n_experts, s->n_glu, s->top_k, s->dtype, ws->h, ws->gate_up, ws->rnorm,
-                                 stream);
+  rc = gather
+      ? bibo_moe_gemm1_gather_fwd(x, ws->row_token, gate_up_proj, theta, ws->plan, s->n_tokens, s->hidden, s->inter,
+                                  s->n_experts, s->n_glu, s->top_k, s->dtype, s->zero_padding, ws->xp, ws->h,
+                                  ws->gate_up, ws->rnorm, stream)
+      : bibo_moe_gemm1_radial_fwd(ws->xp, gate_up_proj, theta, ws->plan, s->n_tokens, s->hidden, s->inter,
+                                  s->n_experts, s->n_glu, s->top_k, s->dtype, ws->h, ws->gate_up, ws->rnorm,
+                                  stream);
   if (rc) return rc;
   BIBO_STAGE(4);
   rc = bibo_moe_gemm2_fwd(ws->h, down_proj, ws->plan, s->n_tokens, s->hidden, s->inter, s->n_experts,
@@ -207,6 +245,22 @@ int host_slices(int64_t n_tokens, int64_t* lens) {
 }
 }  // namespace
 
+// Waits for the stream and looks at the sticky status word the kernels leave in plan[2] (the read rides on
+// the synchronisation the call does anyway): a bounded wait that gave up, or a bad routing index, becomes
+// BIBO_ERR_DEVICE_STATUS instead of a silently wrong result.
+namespace bibo {
+int sync_and_check_status(const int32_t* plan, cudaStream_t st, const char* who) {
+  static thread_local int32_t hdr[4];
+  hdr[PLAN_STATUS] = 0;
+  if (plan) BIBO_CUDA(cudaMemcpyAsync(hdr, plan, sizeof(hdr), cudaMemcpyDeviceToHost, st));
+  BIBO_CUDA(cudaStreamSynchronize(st));
+  if (hdr[PLAN_STATUS] != 0)
+    return fail(BIBO_ERR_DEVICE_STATUS, "%s: the kernels left status %d in the plan (see bibo_moe.h, plan layout)", who,
+                hdr[PLAN_STATUS]);
+  return BIBO_OK;
+}
+}  // namespace bibo
+
 extern "C" int bibo_moe_forward_host(const bibo_moe_shape* s, const void* x_host, void* x_dev,
                                      const void* w_router, const float* bias, const void* gate_up_proj,
                                      const void* down_proj, const float* theta,
@@ -223,8 +277,7 @@ extern "C" int bibo_moe_forward_host(const bibo_moe_shape* s, const void* x_host
     int rc = bibo_moe_forward(s, x_dev, w_router, bias, gate_up_proj, down_proj, theta, ws, out_dev, stream);
     if (rc) return rc;
     BIBO_CUDA(cudaMemcpyAsync(out_host, out_dev, bytes, cudaMemcpyDeviceToHost, st));
-    BIBO_CUDA(cudaStreamSynchronize(st));
-    return BIBO_OK;
+    return sync_and_check_status(ws->plan, st, "forward_host");
   }
   HostPipe* hp = nullptr;
   int rc = host_pipe(&hp);
@@ -257,8 +310,7 @@ extern "C" int bibo_moe_forward_host(const bibo_moe_shape* s, const void* x_host
   }
   BIBO_CUDA(cudaEventRecord(hp->done, hp->out));
   BIBO_CUDA(cudaStreamWaitEvent(st, hp->done, 0));
-  BIBO_CUDA(cudaStreamSynchronize(st));
-  return BIBO_OK;
+  return sync_and_check_status(ws->plan, st, "forward_host");
 }
 
 extern "C" int bibo_moe_debug_plan_header(const int32_t* plan, int32_t* header4_host, void* stream) {

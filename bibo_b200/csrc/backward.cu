@@ -381,7 +381,7 @@ static int backward_t(const bibo_moe_shape* s, const T* x, const T* w_router, co
   T* gu = static_cast<T*>(ws->gate_up);   // becomes dGate|dUp in place
   T* dxp = static_cast<T*>(ws->y);        // y is dead after combine_bwd: reused for dXp
   // tensor-core path: bf16, tile-friendly shapes, and a forward that zeroed the padding rows
-  const bool use_tc = std::is_same<T, __nv_bfloat16>::value && s->zero_padding && G > 0 && (H * 2) % 16 == 0 &&
+  const bool use_tc = std::is_same<T, __nv_bfloat16>::value && (s->zero_padding & 1) && G > 0 && (H * 2) % 16 == 0 &&
                       gemm_dx_tc_supported(H, I) && gemm_dx_tc_supported(2 * I, H) && gemm_dw_tc_supported(H, I) &&
                       gemm_dw_tc_supported(2 * I, H) && aligned16(dy) && aligned16(dh) && aligned16(gu) &&
                       aligned16(dxp) && aligned16(ws->h) && aligned16(ws->xp) && aligned16(d_down_proj) &&

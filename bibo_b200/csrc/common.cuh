@@ -7,6 +7,7 @@
 #include <atomic>
 #include <cstdarg>
 #include <cstdio>
+#include <mutex>
 
 #include "../../include/bibo_moe.h"
 
@@ -44,6 +45,43 @@ inline std::atomic<long long>& launch_counter() {
 
 inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 
+// ---- one-time set-up per device ---------------------------------------------------------------------
+// Function attributes (dynamic shared memory size, carve-out) and occupancy figures belong to a device,
+// not to the process: a launcher keeps one DeviceOnce and runs its set-up the first time it is called
+// with a given device current, under a mutex (host threads may share the library).
+constexpr int BIBO_MAX_DEVICES = 64;
+struct DeviceOnce {
+  std::mutex mu;
+  bool done[BIBO_MAX_DEVICES] = {};
+  int value[BIBO_MAX_DEVICES] = {};
+  template <typename F> int get(F&& init, int* value_out = nullptr) {
+    int dev = 0;
+    BIBO_CUDA(cudaGetDevice(&dev));
+    if (dev < 0 || dev >= BIBO_MAX_DEVICES) return fail(BIBO_ERR_UNSUPPORTED, "device index %d", dev);
+    std::lock_guard<std::mutex> g(mu);
+    if (!done[dev]) {
+      const int rc = init(&value[dev]);
+      if (rc) return rc;
+      done[dev] = true;
+    }
+    if (value_out) *value_out = value[dev];
+    return BIBO_OK;
+  }
+};
+// SM count of the current device
+inline int sm_count() {
+  static DeviceOnce once;
+  int n = 0;
+  const int rc = once.get([](int* v) {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(v, cudaDevAttrMultiProcessorCount, dev);
+    if (*v <= 0) *v = 148;
+    return BIBO_OK;
+  }, &n);
+  return rc == BIBO_OK && n > 0 ? n : 148;
+}
+
 // ---- plan layout (int32 words) ------------------------------------------------------------------
 constexpr int PLAN_N_TILES = 0, PLAN_ROWS_USED = 1, PLAN_STATUS = 2, PLAN_N_PAIRS = 3, PLAN_HDR = 4;
 __host__ __device__ inline int64_t router_blocks(int64_t n_tokens) {
@@ -78,8 +116,9 @@ constexpr int64_t XG_WORDS = XG_PART_WORDS + XG_MAX_CTAS * 2;
 __host__ __device__ inline int64_t plan_off_scratch(int64_t n, int k, int E, int n_glu) {
   return plan_off_pairs(n, k, E, n_glu) + tiles_cap(n, k, n_glu) * 2;
 }
+// ... followed by one arrival counter per tile pair for the kernels that gather their own A rows
 __host__ __device__ inline int64_t plan_words(int64_t n, int k, int E, int n_glu) {
-  return plan_off_scratch(n, k, E, n_glu) + XG_WORDS;
+  return plan_off_scratch(n, k, E, n_glu) + XG_WORDS + tiles_cap(n, k, n_glu);
 }
 
 // What a grouped-GEMM launcher needs to know about a row plan: where the header / tile list live and

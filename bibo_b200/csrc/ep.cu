@@ -244,7 +244,8 @@ ep_share_counts_kernel(const int32_t* __restrict__ counts, PeerPtrs cnt_peers, i
   for (int p = 0; p < world; ++p) static_cast<int32_t*>(cnt_peers.p[p])[rank * n_experts + e] = c;
 }
 
-__global__ void ep_barrier_kernel(PeerPtrs flags, int rank, int world, int epoch, int32_t* status);
+__global__ void ep_barrier_kernel(PeerPtrs flags, int rank, int world, int epoch, uint32_t max_polls,
+                                  int32_t* status);
 
 int ep_share_counts_launch(const int32_t* counts, void* const* cnt_peers, int rank, int world, int n_experts,
                            cudaStream_t st) {
@@ -260,8 +261,10 @@ int ep_share_counts_launch(const int32_t* counts, void* const* cnt_peers, int ra
 
 // gemm_tc.cu
 int gemm1_tc_supported(int hidden, int inter, int dtype);
+int gemm1_gather_supported(int hidden, int inter, int dtype);
 int gemm1_tc_launch(const void* xp, const void* gate_up_proj, const float* theta, const PlanView& pv, int hidden,
-                    int inter, int n_weight_experts, void* h, void* gate_up_out, float* rnorm_out, cudaStream_t st);
+                    int inter, int n_weight_experts, void* h, void* gate_up_out, float* rnorm_out, cudaStream_t st,
+                    const void* gather_src = nullptr, const int32_t* row_src = nullptr, int zero_padding = 0);
 int gemm2_tc_supported(int hidden, int inter, int dtype);
 int gemm2_tc_launch(const void* h, const void* down_proj, const PlanView& pv, int hidden, int inter,
                     int n_weight_experts, void* y, cudaStream_t st);
@@ -279,8 +282,8 @@ static void prefer_max_smem(Kern kern) {
   cudaFuncSetAttribute(kern, cudaFuncAttributePreferredSharedMemoryCarveout, (int)cudaSharedmemCarveoutMaxShared);
 }
 static void ep_set_carveouts() {
-  static bool done = false;
-  if (done) return;
+  static DeviceOnce once;
+  once.get([](int*) {
   prefer_max_smem(ep_plan_kernel);
   prefer_max_smem(ep_dispatch_kernel);
   prefer_max_smem(ep_barrier_kernel);
@@ -288,7 +291,8 @@ static void ep_set_carveouts() {
   prefer_max_smem(ep_combine_kernel<1>); prefer_max_smem(ep_combine_kernel<2>); prefer_max_smem(ep_combine_kernel<3>);
   prefer_max_smem(ep_combine_kernel<4>); prefer_max_smem(ep_combine_kernel<5>); prefer_max_smem(ep_combine_kernel<6>);
   prefer_max_smem(ep_combine_kernel<7>); prefer_max_smem(ep_combine_kernel<8>);
-  done = true;
+    return (int)BIBO_OK;
+  });
 }
 
 static int ep_check(const char* who, int world, int rank, int n_experts, int64_t rows_cap_recv) {
@@ -421,14 +425,15 @@ extern "C" int bibo_moe_ep_combine(void* const* y_peers, const int32_t* slot_row
 // waits until slot [p] of its own array reaches `epoch`.  The wait is bounded: after about two
 // seconds the kernel gives up, raises the status word to 5 and returns.
 namespace bibo {
-__global__ void ep_barrier_kernel(PeerPtrs flags, int rank, int world, int epoch, int32_t* status) {
+__global__ void ep_barrier_kernel(PeerPtrs flags, int rank, int world, int epoch, uint32_t max_polls,
+                                  int32_t* status) {
   const int p = threadIdx.x;
   if (p >= world) return;
   int* remote = static_cast<int*>(flags.p[p]) + rank;
   int* mine = static_cast<int*>(flags.p[rank]) + p;
   __threadfence_system();
   asm volatile("st.release.sys.global.s32 [%0], %1;" ::"l"(remote), "r"(epoch) : "memory");
-  for (uint32_t i = 0; i < (1u << 22); ++i) {
+  for (uint32_t i = 0; i < max_polls; ++i) {
     int v;
     asm volatile("ld.acquire.sys.global.s32 %0, [%1];" : "=r"(v) : "l"(mine) : "memory");
     if (v >= epoch) return;
@@ -440,7 +445,13 @@ __global__ void ep_barrier_kernel(PeerPtrs flags, int rank, int world, int epoch
 
 extern "C" int bibo_moe_ep_barrier(void* const* flags_peers, int rank, int world, int epoch, int32_t* status,
                                    void* stream) {
+  return bibo_moe_ep_barrier_bounded(flags_peers, rank, world, epoch, 0, status, stream);
+}
+
+extern "C" int bibo_moe_ep_barrier_bounded(void* const* flags_peers, int rank, int world, int epoch,
+                                           int64_t max_polls, int32_t* status, void* stream) {
   if (!flags_peers) return fail(BIBO_ERR_ARG, "ep_barrier: null pointer");
+  if (max_polls <= 0 || max_polls > (1ll << 22)) max_polls = 1ll << 22;   // about two seconds
   if (world < 1 || world > EP_MAX_RANKS || rank < 0 || rank >= world)
     return fail(BIBO_ERR_ARG, "ep_barrier: rank %d of %d", rank, world);
   PeerPtrs pp = {};
@@ -448,7 +459,8 @@ extern "C" int bibo_moe_ep_barrier(void* const* flags_peers, int rank, int world
     if (!flags_peers[i]) return fail(BIBO_ERR_ARG, "ep_barrier: peer %d has no flag array", i);
     pp.p[i] = flags_peers[i];
   }
-  ep_barrier_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(pp, rank, world, epoch, status);
+  ep_barrier_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(pp, rank, world, epoch, (uint32_t)max_polls,
+                                                                     status);
   BIBO_CHECK_LAUNCH("ep_barrier_kernel");
   return BIBO_OK;
 }

@@ -25,7 +25,7 @@ __host__ __device__ inline int64_t ep_off_scratch(int E, int64_t rows_cap_recv) 
   return ep_off_pairs(E, rows_cap_recv) + rows_cap_recv / BIBO_TILE_M * 2;
 }
 __host__ __device__ inline int64_t ep_plan_words(int E, int64_t rows_cap_recv) {
-  return ep_off_scratch(E, rows_cap_recv) + XG_WORDS;
+  return ep_off_scratch(E, rows_cap_recv) + XG_WORDS + rows_cap_recv / BIBO_TILE_M;
 }
 inline PlanView ep_plan_view(const int32_t* ep_plan, int n_experts, int64_t rows_cap_recv, int max_ctas) {
   return PlanView{ep_plan, ep_off_tiles(n_experts), ep_off_pairs(n_experts, rows_cap_recv),

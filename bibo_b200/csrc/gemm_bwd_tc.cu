@@ -234,27 +234,18 @@ gemm_bwd_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
   if (threadIdx.x == 0 && *abort_flag) atomicExch(&plan[PLAN_STATUS], 110 + MODE);
 }
 
-static int bwd_sm_count() {
-  static int n = [] {
-    int dev = 0, v = 0;
-    cudaGetDevice(&dev);
-    cudaDeviceGetAttribute(&v, cudaDevAttrMultiProcessorCount, dev);
-    return v > 0 ? v : 148;
-  }();
-  return n;
-}
-
 template <int MODE>
 static int bwd_launch(const CUtensorMap& tmA, const CUtensorMap& tmB, const CUtensorMap& tmC, const int32_t* plan,
                       int64_t tiles_off, int64_t counts_off, int64_t expert_off_off, int n_experts, int n_chunks,
                       int m_tiles, int k_dim, int m_dim, int64_t work_cap, cudaStream_t st) {
   auto kern = gemm_bwd_tc_kernel<MODE>;
-  static bool attr_done = false;
-  if (!attr_done) {
+  static DeviceOnce once;
+  const int rc = once.get([&](int*) {
     BIBO_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, XLayout::BYTES));
-    attr_done = true;
-  }
-  const int grid = (int)std::max<int64_t>(1, std::min<int64_t>(bwd_sm_count(), work_cap));
+    return (int)BIBO_OK;
+  });
+  if (rc) return rc;
+  const int grid = (int)std::max<int64_t>(1, std::min<int64_t>(sm_count(), work_cap));
   kern<<<grid, NUM_THREADS, XLayout::BYTES, st>>>(tmA, tmB, tmC, const_cast<int32_t*>(plan), tiles_off, counts_off,
                                                   expert_off_off, n_experts, n_chunks, m_tiles, k_dim, m_dim);
   BIBO_CHECK_LAUNCH("gemm_bwd_tc_kernel");

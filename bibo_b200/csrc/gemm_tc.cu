@@ -423,13 +423,33 @@ struct G1PairLayout {
 // exchange their partial sums through global memory (flag + 128 floats per CTA and parity) instead of
 // distributed shared memory, so the cluster size stays 2 and every SM can host a CTA; the launcher
 // guarantees that all CTAs are resident (grid <= SM count, one CTA per SM).
-template <int CLN, int STAGES, bool XG>
-__global__ void __launch_bounds__(NUM_THREADS, 1)
+//
+// GATHER: the kernel also builds its own A operand.  Six extra warps per CTA copy token rows
+// src[row_src[r]] into the expert-contiguous buffer behind tmA, up to two row pairs ahead of the loads: the
+// GROUP CTAs that work on a pair split its rows, every gather warp adds one to the pair's arrival
+// counter (release, after a generic->async proxy fence) and each CTA's load thread waits for the
+// GROUP * GATHER_WARPS arrivals (acquire) before its first tile load of that pair.  The copied rows are
+// read back by the tile loads while they are still in L2.  Measured on 32768 tokens, hidden 2048,
+// intermediate 512: the copies cost this kernel about as much as the separate permute pass takes
+// (0.76 ms against 0.56 + 0.16 ms), because the kernel already moves ~14 TB/s through L2 and the copies
+// add to that; the variant is therefore opt-in.  All waits are bounded like every other wait of this kernel.
+constexpr int GATHER_WARPS = 6;
+struct GatherArgs {
+  const uint8_t* src;       // source rows, pitch row_bytes (token-major)
+  uint8_t* dst;             // expert-contiguous rows: the tensor tmA describes
+  const int32_t* row_src;   // [rows] source row of every valid expert-contiguous row
+  int* ready;               // [pairs] arrival counters, zero at launch
+  int row_bytes;
+  int zero_padding;         // write zeros into the rows of a tile beyond its valid rows
+};
+
+template <int CLN, int STAGES, bool XG, bool GATHER = false>
+__global__ void __launch_bounds__(NUM_THREADS + (GATHER ? GATHER_WARPS * 32 : 0), 1)
 gemm1_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                   const __grid_constant__ CUtensorMap tmH, const float* __restrict__ theta,
                   int32_t* __restrict__ plan, int64_t tiles_off, int64_t pairs_off, int k_blocks, int inter,
                   __nv_bfloat16* __restrict__ gate_up_out, float* __restrict__ rnorm_out, float* xg_part,
-                  int* xg_flags) {
+                  int* xg_flags, const GatherArgs ga = GatherArgs{}) {
   using L = G1PairLayout<STAGES>;
   constexpr int NC = L::NC;
   constexpr int CL = XG ? 2 : 2 * CLN;          // hardware cluster size
@@ -446,6 +466,7 @@ gemm1_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
   uint64_t* xbar = uempty + 1;        // [2] partial-sum exchange with CTA r^2
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(xbar + 2);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+  volatile int* load_iter = reinterpret_cast<volatile int*>(tmem_slot + 2);   // pair iteration the load thread is on
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const uint32_t cr = cluster_ctarank();
@@ -460,6 +481,7 @@ gemm1_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
     mbar_init(gempty, 8); mbar_init(uempty, 8);
     mbar_init(&xbar[0], EPI_THREADS); mbar_init(&xbar[1], EPI_THREADS);
     *abort_flag = 0;
+    *load_iter = 0;
     fence_barrier_init();
     prefetch_tmap(&tmA); prefetch_tmap(&tmB); prefetch_tmap(&tmH);
   }
@@ -477,9 +499,22 @@ gemm1_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
     if (elect_one()) {
       PipeState ps;
       bool ok = true;
-      for (int p = cluster_id; p < n_pairs && ok; p += n_clusters) {
+      int it = 0;
+      for (int p = cluster_id; p < n_pairs && ok; p += n_clusters, ++it) {
         const int2 pp = pairs[p];
         const int4 t = tiles[(pr == 1 && pp.y >= 0) ? pp.y : pp.x];
+        if (GATHER) {   // the rows of this pair have been copied by the gather warps of the whole group
+          *load_iter = it;
+          bool got = false;
+          for (uint32_t spin = 0; spin < (1u << 22); ++spin) {
+            int v;
+            asm volatile("ld.acquire.gpu.global.s32 %0, [%1];" : "=r"(v) : "l"(ga.ready + p) : "memory");
+            if (v >= GROUP * GATHER_WARPS) { got = true; break; }
+            if ((spin & 255u) == 255u && *abort_flag) break;
+          }
+          if (!got) { *abort_flag = 1; ok = false; break; }
+          asm volatile("fence.proxy.async.global;" ::: "memory");
+        }
         for (int pass = 0; pass < 2 && ok; ++pass) {
           const int brow = t.x * 2 * inter + pass * inter + (int)ch * NC + (int)pr * (NC / 2);
           for (int kb = 0; kb < k_blocks; ++kb) {
@@ -520,6 +555,62 @@ gemm1_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
           if (ok) umma_commit_cg2_mc(pass == 0 ? gfull : ufull, pair_mask);
         }
       }
+    }
+  } else if (GATHER && warp >= 6) {
+    // ---- gather warps: copy this CTA's share of the rows of pair `it`, at most two pairs ahead of the loads
+    const int gw = warp - 6;
+    const int gi = blockIdx.x % GROUP;               // pr = gi & 1 (which tile), gi >> 1 = which part of its rows
+    constexpr int SHARE = BM / CLN;
+    const int chunks = ga.row_bytes >> 4;
+    int it = 0;
+    for (int p = cluster_id; p < n_pairs; p += n_clusters, ++it) {
+      bool go = true;
+      if (it >= 3) {
+        go = false;
+        for (uint32_t spin = 0; spin < (1u << 22); ++spin) {
+          if (*load_iter >= it - 2) { go = true; break; }
+          if (*abort_flag) break;
+          __nanosleep(200);
+        }
+      }
+      if (!go) { *abort_flag = 1; break; }
+      const int2 pp = pairs[p];
+      const int ti = (gi & 1) ? pp.y : pp.x;
+      if (ti >= 0) {
+        const int4 t = tiles[ti];
+        const int r0 = (gi >> 1) * SHARE;
+        // this warp's rows are r0 + gw + i * GATHER_WARPS, taken two at a time: the sixteen 16-byte loads of a
+        // lane (eight per row) are all issued before the first store; loads bypass L1 (the carve-out leaves
+        // next to none), and the loop has no division: the warps next to this one issue the MMAs
+        for (int ra = r0 + gw; ra < r0 + SHARE; ra += 2 * GATHER_WARPS) {
+          const int rb = ra + GATHER_WARPS;
+          const bool la = ra < t.z, lb = rb < r0 + SHARE && rb < t.z;
+          const bool wa = la || (ga.zero_padding & 1), wb = rb < r0 + SHARE && (lb || (ga.zero_padding & 1));
+          const uint4* sa = reinterpret_cast<const uint4*>(ga.src + (int64_t)(la ? __ldg(ga.row_src + t.y + ra) : 0) * ga.row_bytes);
+          const uint4* sb = reinterpret_cast<const uint4*>(ga.src + (int64_t)(lb ? __ldg(ga.row_src + t.y + rb) : 0) * ga.row_bytes);
+          uint4* da = reinterpret_cast<uint4*>(ga.dst + (int64_t)(t.y + ra) * ga.row_bytes);
+          uint4* db = reinterpret_cast<uint4*>(ga.dst + (int64_t)(t.y + rb) * ga.row_bytes);
+          for (int c0 = lane; c0 < chunks; c0 += 256) {
+            uint4 va[8], vb[8];
+#pragma unroll
+            for (int u = 0; u < 8; ++u) {
+              const int c = c0 + u * 32;
+              va[u] = (la && c < chunks) ? __ldcg(sa + c) : make_uint4(0, 0, 0, 0);
+              vb[u] = (lb && c < chunks) ? __ldcg(sb + c) : make_uint4(0, 0, 0, 0);
+            }
+#pragma unroll
+            for (int u = 0; u < 8; ++u) {
+              const int c = c0 + u * 32;
+              if (wa && c < chunks) da[c] = va[u];
+              if (wb && c < chunks) db[c] = vb[u];
+            }
+          }
+        }
+      }
+      asm volatile("fence.proxy.async.global;" ::: "memory");
+      __threadfence();
+      __syncwarp();
+      if (lane == 0) asm volatile("red.release.gpu.global.add.s32 [%0], 1;" ::"l"(ga.ready + p) : "memory");
     }
   } else {
     const int q = warp & 3;
@@ -712,16 +803,6 @@ int make_tmap_bf16_2d(CUtensorMap* out, const void* base, uint64_t rows, uint64_
   return BIBO_OK;
 }
 
-static int sm_count() {
-  static int n = [] {
-    int dev = 0, v = 0;
-    cudaGetDevice(&dev);
-    cudaDeviceGetAttribute(&v, cudaDevAttrMultiProcessorCount, dev);
-    return v > 0 ? v : 148;
-  }();
-  return n;
-}
-
 template <typename Kern>
 static int set_smem(Kern kern, int bytes) {
   BIBO_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes));
@@ -746,8 +827,8 @@ static int gemm2_launch_t(const void* h, const void* down_proj, const PlanView& 
   if ((rc = make_tmap_bf16_2d(&tmB, down_proj, (uint64_t)n_weight_experts * hidden, inter, inter, BN))) return rc;
   if ((rc = make_tmap_bf16_2d(&tmC, y, pv.rows_alloc, hidden, hidden, BM))) return rc;
   auto kern = gemm2_tc_kernel<BN, STAGES, RES>;
-  static bool attr_done = false;
-  if (!attr_done) { if ((rc = set_smem(kern, L::BYTES))) return rc; attr_done = true; }
+  static DeviceOnce once;
+  if ((rc = once.get([&](int*) { return set_smem(kern, L::BYTES); }))) return rc;
   const int64_t work_cap = pv.tiles_cap * (hidden / BN);
   const int sms = pv.max_ctas > 0 ? std::min(pv.max_ctas, sm_count()) : sm_count();
   const int grid = (int)std::min<int64_t>(sms, work_cap);
@@ -778,9 +859,9 @@ static int gemm1_launch_t(const CUtensorMap& tmA, const CUtensorMap& tmB, const 
                           int inter, void* gate_up_out, float* rnorm_out, cudaStream_t st) {
   using L = G1Layout<NC, STAGES>;
   auto kern = gemm1_tc_kernel<NC, CL, STAGES>;
-  static bool attr_done = false;
+  static DeviceOnce once;
   int rc;
-  if (!attr_done) { if ((rc = set_smem(kern, L::BYTES))) return rc; attr_done = true; }
+  if ((rc = once.get([&](int*) { return set_smem(kern, L::BYTES); }))) return rc;
   const int sms = max_ctas > 0 ? std::min(max_ctas, sm_count()) : sm_count();
   int clusters = (int)std::min<int64_t>(sms / CL, tile_cap);
   cudaLaunchConfig_t cfg = {};
@@ -801,18 +882,18 @@ static int gemm1_launch_t(const CUtensorMap& tmA, const CUtensorMap& tmB, const 
   return BIBO_OK;
 }
 
-template <int CLN, int STAGES, bool XG>
+template <int CLN, int STAGES, bool XG, bool GATHER>
 static int gemm1_pair_launch_t(const CUtensorMap& tmA, const CUtensorMap& tmB, const CUtensorMap& tmH,
                                const float* theta, const PlanView& pv, int k_blocks, int inter, void* gate_up_out,
-                               float* rnorm_out, cudaStream_t st) {
+                               float* rnorm_out, cudaStream_t st, GatherArgs ga = GatherArgs{}) {
   using L = G1PairLayout<STAGES>;
   constexpr int CL = XG ? 2 : 2 * CLN;      // hardware cluster size
   constexpr int GROUP = 2 * CLN;            // CTAs per row pair
-  auto kern = gemm1_pair_kernel<CLN, STAGES, XG>;
-  static int max_clusters = 0;
+  constexpr int THREADS = NUM_THREADS + (GATHER ? GATHER_WARPS * 32 : 0);
+  auto kern = gemm1_pair_kernel<CLN, STAGES, XG, GATHER>;
   int rc;
   cudaLaunchConfig_t cfg = {};
-  cfg.blockDim = dim3(NUM_THREADS);
+  cfg.blockDim = dim3(THREADS);
   cfg.dynamicSmemBytes = L::BYTES;
   cfg.stream = st;
   cudaLaunchAttribute attr[1];
@@ -822,57 +903,76 @@ static int gemm1_pair_launch_t(const CUtensorMap& tmA, const CUtensorMap& tmB, c
   attr[0].val.clusterDim.z = 1;
   cfg.attrs = attr;
   cfg.numAttrs = 1;
-  if (max_clusters == 0) {
-    if ((rc = set_smem(kern, L::BYTES))) return rc;
+  static DeviceOnce once;
+  int max_clusters = 0;
+  rc = once.get([&](int* v) {
+    int r = set_smem(kern, L::BYTES);
+    if (r) return r;
     cfg.gridDim = dim3((sm_count() / CL) * CL);
     int n = 0;
     BIBO_CUDA(cudaOccupancyMaxActiveClusters(&n, kern, &cfg));   // clusters of CL CTAs that fit at once
-    max_clusters = n > 0 ? n : 1;
-  }
+    *v = n > 0 ? n : 1;
+    return (int)BIBO_OK;
+  }, &max_clusters);
+  if (rc) return rc;
   const int sms = pv.max_ctas > 0 ? std::min(pv.max_ctas, sm_count()) : sm_count();
-  // resident CTAs only: with XG the groups wait on one another through global memory
+  // resident CTAs only: the CTAs of a group wait on one another through global memory (XG, GATHER)
   const int ctas = std::min(std::min(max_clusters * CL, sms), XG_MAX_CTAS);
   const int groups = (int)std::max<int64_t>(1, std::min<int64_t>(ctas / GROUP, pv.tiles_cap));
   cfg.gridDim = dim3(groups * GROUP);
   int32_t* scratch = const_cast<int32_t*>(pv.plan) + pv.scratch_off;
   float* xg_part = reinterpret_cast<float*>(scratch);
   int* xg_flags = scratch + XG_PART_WORDS;
-  if (XG) BIBO_CUDA(cudaMemsetAsync(xg_flags, 0, sizeof(int) * XG_MAX_CTAS * 2, st));
+  // the exchange flags and, behind them, the gather arrival counters start every launch at zero
+  const size_t clear_words = (XG ? XG_MAX_CTAS * 2 : 0) + (GATHER ? (size_t)pv.tiles_cap : 0);
+  if (GATHER) ga.ready = scratch + XG_WORDS;
+  if (clear_words) {
+    int* from = XG ? xg_flags : scratch + XG_WORDS;
+    BIBO_CUDA(cudaMemsetAsync(from, 0, sizeof(int) * clear_words, st));
+  }
   BIBO_CUDA(cudaLaunchKernelEx(&cfg, kern, tmA, tmB, tmH, theta, const_cast<int32_t*>(pv.plan), pv.tiles_off,
                                pv.pairs_off, k_blocks, inter, reinterpret_cast<__nv_bfloat16*>(gate_up_out),
-                               rnorm_out, xg_part, xg_flags));
+                               rnorm_out, xg_part, xg_flags, ga));
   launch_counter().fetch_add(1, std::memory_order_relaxed);
   return BIBO_OK;
 }
 
+// rows of `src` (pitch = hidden bf16) are gathered by the kernel itself: intermediate sizes with a CTA-pair kernel
+int gemm1_gather_supported(int hidden, int inter, int dtype) {
+  return dtype == BIBO_BF16 && hidden % 64 == 0 && hidden >= 64 && (inter == 256 || inter == 512);
+}
+
+// gather != nullptr: `xp` is written by the kernel from gather_src rows (see GatherArgs), not read from a permute pass
 int gemm1_tc_launch(const void* xp, const void* gate_up_proj, const float* theta, const PlanView& pv, int hidden,
-                    int inter, int n_weight_experts, void* h, void* gate_up_out, float* rnorm_out, cudaStream_t st) {
+                    int inter, int n_weight_experts, void* h, void* gate_up_out, float* rnorm_out, cudaStream_t st,
+                    const void* gather_src, const int32_t* row_src, int zero_padding) {
   const int nc = inter >= 256 ? 256 : 128;
   CUtensorMap tmA, tmB, tmH;
   int rc;
-  // BIBO_G1_SINGLE=1 selects the one-CTA-per-tile kernel (kept for A/B measurements)
-  static const bool single = [] { const char* e = getenv("BIBO_G1_SINGLE"); return e && atoi(e) != 0; }();
-  if (!single && inter >= 256) {
+  if (gather_src != nullptr && (!gemm1_gather_supported(hidden, inter, BIBO_BF16) || row_src == nullptr))
+    return fail(BIBO_ERR_UNSUPPORTED, "gate/up kernel: no row-gathering variant for hidden=%d inter=%d", hidden, inter);
+  if (inter >= 256) {
     if ((rc = make_tmap_bf16_2d(&tmA, xp, pv.rows_alloc, hidden, hidden, BM))) return rc;
     if ((rc = make_tmap_bf16_2d(&tmB, gate_up_proj, (uint64_t)n_weight_experts * 2 * inter, hidden, hidden, 128))) return rc;
     if ((rc = make_tmap_bf16_2d(&tmH, h, pv.rows_alloc, inter, inter, BM))) return rc;
-    // BIBO_G1_DSMEM=1: 4-CTA clusters exchanging through distributed shared memory (A/B measurements)
-    static const bool dsmem = [] { const char* e = getenv("BIBO_G1_DSMEM"); return e && atoi(e) != 0; }();
-    if (inter == 512 && dsmem)
-      return gemm1_pair_launch_t<2, 5, false>(tmA, tmB, tmH, theta, pv, hidden / BK, inter, gate_up_out, rnorm_out, st);
+    if (gather_src != nullptr) {
+      GatherArgs ga{static_cast<const uint8_t*>(gather_src), static_cast<uint8_t*>(const_cast<void*>(xp)), row_src,
+                    nullptr, hidden * 2, zero_padding & 1};
+      if (inter == 512)
+        return gemm1_pair_launch_t<2, 5, true, true>(tmA, tmB, tmH, theta, pv, hidden / BK, inter, gate_up_out,
+                                                     rnorm_out, st, ga);
+      return gemm1_pair_launch_t<1, 5, false, true>(tmA, tmB, tmH, theta, pv, hidden / BK, inter, gate_up_out,
+                                                    rnorm_out, st, ga);
+    }
     if (inter == 512)
-      return gemm1_pair_launch_t<2, 5, true>(tmA, tmB, tmH, theta, pv, hidden / BK, inter, gate_up_out, rnorm_out, st);
-    return gemm1_pair_launch_t<1, 5, false>(tmA, tmB, tmH, theta, pv, hidden / BK, inter, gate_up_out, rnorm_out, st);
+      return gemm1_pair_launch_t<2, 5, true, false>(tmA, tmB, tmH, theta, pv, hidden / BK, inter, gate_up_out,
+                                                    rnorm_out, st);
+    return gemm1_pair_launch_t<1, 5, false, false>(tmA, tmB, tmH, theta, pv, hidden / BK, inter, gate_up_out,
+                                                   rnorm_out, st);
   }
   if ((rc = make_tmap_bf16_2d(&tmA, xp, pv.rows_alloc, hidden, hidden, BM))) return rc;
   if ((rc = make_tmap_bf16_2d(&tmB, gate_up_proj, (uint64_t)n_weight_experts * 2 * inter, hidden, hidden, nc))) return rc;
   if ((rc = make_tmap_bf16_2d(&tmH, h, pv.rows_alloc, inter, inter, BM))) return rc;
-  if (inter == 512)
-    return gemm1_launch_t<256, 2, 3>(tmA, tmB, tmH, theta, pv.plan, pv.tiles_off, pv.tiles_cap, pv.max_ctas,
-                                     hidden / BK, inter, gate_up_out, rnorm_out, st);
-  if (inter == 256)
-    return gemm1_launch_t<256, 1, 3>(tmA, tmB, tmH, theta, pv.plan, pv.tiles_off, pv.tiles_cap, pv.max_ctas,
-                                     hidden / BK, inter, gate_up_out, rnorm_out, st);
   return gemm1_launch_t<128, 1, 4>(tmA, tmB, tmH, theta, pv.plan, pv.tiles_off, pv.tiles_cap, pv.max_ctas,
                                    hidden / BK, inter, gate_up_out, rnorm_out, st);
 }

@@ -343,8 +343,9 @@ extern "C" int bibo_moe_mlp_forward_residual(const void* x, const void* gate_pro
   if ((rc = make_tmap_bf16_2d(&tmG, gate_proj, (uint64_t)inter, hidden, hidden, 128))) return rc;
   if ((rc = make_tmap_bf16_2d(&tmU, up_proj, (uint64_t)inter, hidden, hidden, 128))) return rc;
   if ((rc = make_tmap_bf16_2d(&tmH, h, (uint64_t)n_tokens, inter, inter, BM))) return rc;
-  static int max_clusters = 0;
-  static int sms = 0;
+  static DeviceOnce once;
+  int max_clusters = 0;
+  const int sms = sm_count();
   cudaLaunchConfig_t cfg = {};
   cfg.blockDim = dim3(M_THREADS);
   cfg.dynamicSmemBytes = M_SMEM;
@@ -356,16 +357,15 @@ extern "C" int bibo_moe_mlp_forward_residual(const void* x, const void* gate_pro
   attr[0].val.clusterDim.z = 1;
   cfg.attrs = attr;
   cfg.numAttrs = 1;
-  if (max_clusters == 0) {
-    int dev = 0;
-    BIBO_CUDA(cudaGetDevice(&dev));
-    BIBO_CUDA(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
+  rc = once.get([&](int* v) {
     BIBO_CUDA(cudaFuncSetAttribute(mlp_gemm1_pair_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, M_SMEM));
     cfg.gridDim = dim3((sms / 2) * 2);
     int n = 0;
     BIBO_CUDA(cudaOccupancyMaxActiveClusters(&n, mlp_gemm1_pair_kernel, &cfg));
-    max_clusters = n > 0 ? n : 1;
-  }
+    *v = n > 0 ? n : 1;
+    return (int)BIBO_OK;
+  }, &max_clusters);
+  if (rc) return rc;
   const int64_t n_work = (int64_t)((n_tiles + 1) / 2) * (inter / M_NC);
   const int clusters = (int)std::max<int64_t>(1, std::min<int64_t>(std::min(max_clusters, sms / 2), n_work));
   cfg.gridDim = dim3(clusters * 2);

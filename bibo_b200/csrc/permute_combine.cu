@@ -34,8 +34,8 @@ permute_kernel(const uint8_t* __restrict__ x, const int32_t* __restrict__ topk_i
     bool identity = false;       // a slot on a +/-Identity expert: the combine kernel reads the normalised row itself
     if (lane < top_k) {
       const int e = topk_idx[w * top_k + lane];
-      identity = e >= n_glu;
-      if (e < n_glu) {
+      identity = e >= n_glu && e < n_experts;
+      if (e >= 0 && e < n_glu) {   // a negative index is an empty slot, one beyond the experts is ignored: no row
         const int64_t b = w / BIBO_ROUTER_BLOCK_TOKENS;
         my_row = expert_off[e] + block_base[b * n_experts + e] + slot_rank[w * top_k + lane];
         row_token[my_row] = (int32_t)w;
@@ -81,6 +81,37 @@ permute_kernel(const uint8_t* __restrict__ x, const int32_t* __restrict__ topk_i
       uint4* dst = reinterpret_cast<uint4*>(xp + (int64_t)row * row_bytes);
       for (int c = lane; c < chunks; c += 32) dst[c] = make_uint4(0, 0, 0, 0);
     }
+  }
+}
+
+// ---- K2 without the copy ------------------------------------------------------------------------------
+// The row maps alone (slot_row, row_token), for the gate/up kernel that gathers its own rows: thread per
+// slot; threads beyond the slots mark one padding row each.  A slot whose expert index is negative is an
+// empty slot (no row); indices >= n_glu are +/-Identity experts (no row either).
+__global__ void __launch_bounds__(256)
+rowmap_kernel(const int32_t* __restrict__ topk_idx, const int32_t* __restrict__ slot_rank,
+              const int32_t* __restrict__ plan, int64_t n_tokens, int n_experts, int n_glu, int top_k,
+              int32_t* __restrict__ slot_row, int32_t* __restrict__ row_token) {
+  const int64_t i = (int64_t)blockIdx.x * 256 + threadIdx.x;
+  const int64_t slots = n_tokens * top_k;
+  const int32_t* counts = plan + plan_off_counts();
+  const int32_t* expert_off = plan + plan_off_expert_off(n_experts);
+  const int32_t* block_base = plan + plan_off_block_base(n_experts, n_glu);
+  if (i < slots) {
+    const int64_t t = i / top_k;
+    const int e = topk_idx[i];
+    int row = -1;
+    if (e >= 0 && e < n_glu) {
+      row = expert_off[e] + block_base[(t / BIBO_ROUTER_BLOCK_TOKENS) * n_experts + e] + slot_rank[i];
+      row_token[row] = (int32_t)t;
+    }
+    slot_row[i] = row;
+  } else {
+    const int64_t p = i - slots;
+    const int e = (int)(p / (BIBO_TILE_M - 1));
+    if (e >= n_glu) return;
+    const int row = expert_off[e] + counts[e] + (int)(p % (BIBO_TILE_M - 1));
+    if (row < expert_off[e + 1]) row_token[row] = -1;
   }
 }
 
@@ -172,9 +203,10 @@ combine_kernel(const T* __restrict__ y, const T* __restrict__ x, const int32_t* 
   if (lane < K) {
     my_row = slot_row[t * K + lane];
     my_w = topk_w[t * K + lane];
-    if (my_row < 0) {  // +Identity / -Identity expert: contributes +w*x or -w*x
+    if (my_row < 0) {  // +Identity / -Identity expert: contributes +w*x or -w*x; a negative index is an empty slot
       const int e = topk_idx[t * K + lane];
       if (e >= n_glu + n_pos) my_w = -my_w;
+      if (e < 0) my_w = 0.f;
     }
   }
   const uint4* src[K];
@@ -260,6 +292,21 @@ extern "C" int bibo_moe_permute_fwd(const void* x, const int32_t* topk_idx, cons
       (const uint8_t*)x, topk_idx, slot_rank, plan, n_tokens, row_bytes, n_experts, n_glu, top_k,
       zero_padding, (uint8_t*)xp, slot_row, row_token);
   BIBO_CHECK_LAUNCH("permute_kernel");
+  return BIBO_OK;
+}
+
+extern "C" int bibo_moe_rowmap_fwd(const int32_t* topk_idx, const int32_t* slot_rank, const int32_t* plan,
+                                   int64_t n_tokens, int n_experts, int n_glu, int top_k, int32_t* slot_row,
+                                   int32_t* row_token, void* stream) {
+  if (n_tokens <= 0) return BIBO_OK;
+  if (!topk_idx || !slot_rank || !plan || !slot_row || !row_token) return fail(BIBO_ERR_ARG, "rowmap_fwd: null pointer");
+  if (top_k < 1 || top_k > BIBO_MAX_TOP_K || n_experts < 1 || n_experts > BIBO_MAX_EXPERTS || n_glu < 0 ||
+      n_glu > n_experts)
+    return fail(BIBO_ERR_UNSUPPORTED, "rowmap_fwd: n_experts=%d n_glu=%d top_k=%d", n_experts, n_glu, top_k);
+  const int64_t threads = n_tokens * top_k + (int64_t)n_glu * (BIBO_TILE_M - 1);
+  rowmap_kernel<<<(unsigned)((threads + 255) / 256), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      topk_idx, slot_rank, plan, n_tokens, n_experts, n_glu, top_k, slot_row, row_token);
+  BIBO_CHECK_LAUNCH("rowmap_kernel");
   return BIBO_OK;
 }
 

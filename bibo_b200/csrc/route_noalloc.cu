@@ -31,7 +31,7 @@ constexpr size_t NA_BLOCKS_BYTES =
     align256((NA_TOKENS / BIBO_ROUTER_BLOCK_TOKENS) * BIBO_MAX_EXPERTS * sizeof(int32_t));
 constexpr size_t NA_PLAN_BYTES = align256(
     (PLAN_HDR + BIBO_MAX_EXPERTS + BIBO_MAX_EXPERTS + 1 + 3 + (NA_TOKENS / BIBO_ROUTER_BLOCK_TOKENS) * BIBO_MAX_EXPERTS +
-     ((NA_TOKENS * BIBO_MAX_TOP_K + (int64_t)BIBO_MAX_EXPERTS * (BIBO_TILE_M - 1)) / BIBO_TILE_M + 1) * 6 + XG_WORDS) *
+     ((NA_TOKENS * BIBO_MAX_TOP_K + (int64_t)BIBO_MAX_EXPERTS * (BIBO_TILE_M - 1)) / BIBO_TILE_M + 1) * 7 + XG_WORDS) *
     sizeof(int32_t));
 constexpr size_t NA_BYTES = NA_RANK_BYTES + NA_BLOCKS_BYTES + NA_PLAN_BYTES;
 

@@ -115,10 +115,12 @@ rank_kernel(const int32_t* __restrict__ topk_idx, int64_t n_tokens, int n_expert
     for (int j = 0; j < BIBO_MAX_TOP_K; ++j) {
       if (j < top_k) {
         int e = topk_idx[t * top_k + j];
-        if (e < 0 || e >= n_experts) { if (status) atomicExch(status, 2); e = 0; }
-        sel[j] = e;
-        uint32_t old = atomicOr(&rmask[e * WORDS + (tid >> 5)], 1u << (tid & 31));
-        if ((old & (1u << (tid & 31))) && status) atomicExch(status, 3);  // one expert twice in a token
+        if (e >= n_experts) { if (status) atomicExch(status, 2); e = -1; }   // out of range: reported, then ignored
+        sel[j] = e;                                                          // negative = empty slot
+        if (e >= 0) {
+          uint32_t old = atomicOr(&rmask[e * WORDS + (tid >> 5)], 1u << (tid & 31));
+          if ((old & (1u << (tid & 31))) && status) atomicExch(status, 3);  // one expert twice in a token
+        }
       }
     }
   }
@@ -129,9 +131,12 @@ rank_kernel(const int32_t* __restrict__ topk_idx, int64_t n_tokens, int n_expert
 #pragma unroll
     for (int j = 0; j < BIBO_MAX_TOP_K; ++j) {
       if (j < top_k) {
-        const uint32_t* m = rmask + sel[j] * WORDS;
-        int r = __popc(m[wq] & lt);
-        for (int q = 0; q < wq; ++q) r += __popc(m[q]);
+        int r = 0;
+        if (sel[j] >= 0) {
+          const uint32_t* m = rmask + sel[j] * WORDS;
+          r = __popc(m[wq] & lt);
+          for (int q = 0; q < wq; ++q) r += __popc(m[q]);
+        }
         slot_rank[t * top_k + j] = r;
       }
     }
@@ -202,7 +207,7 @@ plan_kernel(const int32_t* __restrict__ block_counts, int64_t n_tokens, int top_
     plan[PLAN_N_TILES] = acc / BIBO_TILE_M;
     plan[PLAN_ROWS_USED] = acc;
     plan[PLAN_N_PAIRS] = pacc;
-    if (total != (long long)n_tokens * top_k) atomicMax(&plan[PLAN_STATUS], 1);  // sticky
+    if (total > (long long)n_tokens * top_k) atomicMax(&plan[PLAN_STATUS], 1);  // sticky (fewer = empty slots)
   }
   if (e < n_experts) {
     int run = s_part[tid];
@@ -385,11 +390,13 @@ extern "C" int bibo_moe_plan_trace(const int32_t* block_counts, int64_t n_tokens
   if (n_experts < 1 || n_experts > BIBO_MAX_EXPERTS || n_glu < 0 || n_glu > n_experts)
     return fail(BIBO_ERR_UNSUPPORTED, "plan: n_experts=%d n_glu=%d", n_experts, n_glu);
   if (n_tokens <= 0) return fail(BIBO_ERR_ARG, "plan: n_tokens=%lld", (long long)n_tokens);
-  static bool carve = false;
-  if (!carve) {  // same carve-out as the grouped GEMMs, so this kernel can share SMs with them (see ep.cu)
-    cudaFuncSetAttribute(plan_kernel, cudaFuncAttributePreferredSharedMemoryCarveout, (int)cudaSharedmemCarveoutMaxShared);
-    carve = true;
-  }
+  static DeviceOnce carve;   // same carve-out as the grouped GEMMs, so this kernel can share SMs with them (see ep.cu)
+  int rc0 = carve.get([](int*) {
+    BIBO_CUDA(cudaFuncSetAttribute(plan_kernel, cudaFuncAttributePreferredSharedMemoryCarveout,
+                                   (int)cudaSharedmemCarveoutMaxShared));
+    return (int)BIBO_OK;
+  });
+  if (rc0) return rc0;
   int ep = 1;
   while (ep < n_experts) ep <<= 1;
   plan_kernel<<<1, PLAN_THREADS, 0, static_cast<cudaStream_t>(stream)>>>(block_counts, n_tokens, top_k, n_experts,

@@ -209,8 +209,8 @@ int router_tc_launch(const void* x, const void* w_router, const float* bias, int
   int rc;
   if ((rc = make_tmap_bf16_2d(&tmX, x, (uint64_t)n_tokens, hidden, hidden, R_BM))) return rc;
   if ((rc = make_tmap_bf16_2d(&tmW, w_router, (uint64_t)n_experts, hidden, hidden, R_BN))) return rc;
-  static bool attr_done = false;
-  if (!attr_done) {
+  static DeviceOnce once;
+  rc = once.get([](int*) {
     BIBO_CUDA(cudaFuncSetAttribute(router_tc_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, R_SMEM));
     BIBO_CUDA(cudaFuncSetAttribute(router_tc_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, R_SMEM_NORM));
     // same carve-out as the grouped GEMMs, so this kernel can share SMs with them (see ep.cu)
@@ -218,8 +218,9 @@ int router_tc_launch(const void* x, const void* w_router, const float* bias, int
                          (int)cudaSharedmemCarveoutMaxShared);
     cudaFuncSetAttribute(router_tc_kernel<true>, cudaFuncAttributePreferredSharedMemoryCarveout,
                          (int)cudaSharedmemCarveoutMaxShared);
-    attr_done = true;
-  }
+    return (int)BIBO_OK;
+  });
+  if (rc) return rc;
   if (norm)
     router_tc_kernel<true><<<(unsigned)router_blocks(n_tokens), 128, R_SMEM_NORM, st>>>(
         tmX, tmW, bias, n_tokens, hidden / R_BK, top_k, norm_mode, scale, logits_out, topk_idx, topk_w, slot_rank,

@@ -92,6 +92,9 @@ class MoEWorkspace:
         self.rnorm = torch.empty(rows, dtype=torch.float32, device=device) if keep_gate_up else None
         self.logits = torch.empty(n, e, dtype=torch.float32, device=device) if keep_logits else None
         self.status = torch.zeros(1, **i32)
+        # host copy of the plan header {n_tiles, rows, status, n_pairs}: refreshed by an asynchronous 16-byte
+        # copy behind every call, looked at (without waiting) before the next one -- see raise_if_failed
+        self.header_host = torch.zeros(4, dtype=torch.int32).pin_memory() if torch.device(device).type == "cuda" else None
         self.stage_events = None      # optional list of 7 torch.cuda.Event(enable_timing=True)
         self._stage_event_array = None
         self.trace_blocks = None      # [router_blocks, 8] fp32 scratch of the router diagnostics, on first use
@@ -120,6 +123,29 @@ class MoEWorkspace:
                               p(self.y), p(self.gate_up), p(self.rnorm), p(self.logits), ev,
                               p(getattr(self, "addend", None)), tr)
 
+    def post_status(self) -> None:
+        """Enqueue the copy of the plan header into pinned host memory behind the kernels just launched."""
+        if self.header_host is not None:
+            self.header_host.copy_(self.plan[:4], non_blocking=True)
+
+    def raise_if_failed(self, wait: bool = False) -> None:
+        """Raise RuntimeError if a kernel of an EARLIER call on this workspace left a non-zero status word
+        (a bounded wait that gave up, a routing index out of range, ...).  Without ``wait`` nothing is
+        synchronised: the check sees what has reached the host so far, so a failure is reported at the
+        latest by the call after the one in which it became visible (kernels skip their work while the word
+        is non-zero).  The word is cleared once it has been reported."""
+        if self.header_host is None:
+            return
+        if wait:
+            torch.cuda.current_stream(self.plan.device).synchronize()
+        code = int(self.header_host[2])
+        if code != 0:
+            self.header_host[2] = 0
+            self.plan[2:3].zero_()
+            raise RuntimeError(f"bibo_b200: a kernel of an earlier call reported device status {code} "
+                               f"({STATUS_TEXT.get(code, 'see the plan layout in bibo_moe.h')}); its results and those "
+                               "of the calls issued since are invalid")
+
     def enable_stage_timing(self) -> None:
         """Ask bibo_moe_forward to record an event around every stage (see stage_ms)."""
         self.stage_events = [torch.cuda.Event(enable_timing=True) for _ in range(7)]
@@ -147,6 +173,15 @@ class MoEWorkspace:
         return self.plan[o:o + 4 * n_rec].view(-1, 4)
 
 
+STATUS_TEXT = {
+    1: "per-expert histogram total exceeds tokens x top_k", 2: "an expert index is out of range",
+    3: "one expert appears twice in a token", 4: "an expert-parallel receive buffer would overflow",
+    5: "a cross-rank barrier timed out", 100: "down kernel: a bounded wait gave up",
+    101: "gate/up kernel: a bounded wait gave up", 102: "router kernel: a bounded wait gave up",
+    104: "gate/up CTA-pair kernel: a bounded wait gave up (exchange or row gather)",
+    110: "backward dX kernel: a bounded wait gave up", 111: "backward dW kernel: a bounded wait gave up",
+}
+
 _WS_CACHE: Dict[Tuple, MoEWorkspace] = {}
 
 
@@ -162,9 +197,11 @@ def get_workspace(geo: Geometry, device, keep_logits=False, keep_gate_up=True, f
     return ws
 
 
-def _shape(geo: Geometry, norm_mode, scale: float, zero_padding: bool) -> _lib.Shape:
+def _shape(geo: Geometry, norm_mode, scale: float, zero_padding: bool, gather: bool = False) -> _lib.Shape:
+    """zero_padding field: bit 0 = zero-fill padding rows, bit 1 = the gate/up kernel gathers its own rows."""
     return _lib.Shape(geo.n_tokens, geo.hidden, geo.inter, geo.n_experts, geo.n_glu, geo.n_pos, geo.top_k,
-                      norm_code(norm_mode), dtype_code(geo.dtype), float(scale), int(zero_padding))
+                      norm_code(norm_mode), dtype_code(geo.dtype), float(scale),
+                      int(bool(zero_padding)) | (2 if gather else 0))
 
 
 # ---------------------------------------------------------------------------------------------------
@@ -212,8 +249,10 @@ def moe_forward(x: torch.Tensor, w_router: torch.Tensor, bias: torch.Tensor, gat
                 zero_padding: bool = False, keep_logits: bool = False,
                 addend: Optional[torch.Tensor] = None,
                 trace: Optional[Tuple[Optional[torch.Tensor], Optional[torch.Tensor], Optional[torch.Tensor]]] = None,
-                ) -> Tuple[torch.Tensor, MoEWorkspace]:
+                gather_in_gemm: bool = False) -> Tuple[torch.Tensor, MoEWorkspace]:
     """The whole block on flat tokens x [N,H]: one call of bibo_moe_forward.  Returns (out, workspace).
+    ``gather_in_gemm`` lets the gate/up kernel gather its own rows where it can (bf16, intermediate 256 / 512)
+    instead of running the permute as a kernel of its own: same bits, measured slightly slower.
     ``addend`` [N,H] (the shared expert's output) is added in the combine kernel.
     ``trace`` = (acc [8], counts [E], gap [1]) fp32 device tensors, each optional: the router and plan
     kernels fold this call's routing diagnostics into them (see bibo_moe_router_trace in the header)."""
@@ -237,7 +276,7 @@ def moe_forward(x: torch.Tensor, w_router: torch.Tensor, bias: torch.Tensor, gat
         return out, ws
     bias32 = bias if bias.dtype == torch.float32 else bias.float()
     theta32 = theta if theta.dtype == torch.float32 else theta.float()
-    shape = _shape(geo, norm_mode, scale, zero_padding)
+    shape = _shape(geo, norm_mode, scale, zero_padding, gather_in_gemm)
     if addend is not None and (addend.shape != x.shape or addend.dtype != x.dtype or not addend.is_contiguous()):
         raise RuntimeError("addend must be a contiguous tensor of the activations' shape and dtype")
     if trace is not None:
@@ -245,6 +284,7 @@ def moe_forward(x: torch.Tensor, w_router: torch.Tensor, bias: torch.Tensor, gat
             if t is not None and (t.dtype != torch.float32 or t.numel() != words or t.device != x.device
                                   or not t.is_contiguous()):
                 raise RuntimeError("trace tensors must be contiguous fp32 device tensors of 8 / n_experts / 1 elements")
+    ws.raise_if_failed()
     ws.addend, ws.trace = addend, trace
     cws = ws.c_struct()
     ws.addend = ws.trace = None
@@ -252,6 +292,7 @@ def moe_forward(x: torch.Tensor, w_router: torch.Tensor, bias: torch.Tensor, gat
                               _lib.ptr(gate_up_proj), _lib.ptr(down_proj), _lib.ptr(theta32), C.byref(cws),
                               _lib.ptr(out), _stream(x.device))
     _lib.check(rc, "bibo_moe_forward")
+    ws.post_status()
     return out, ws
 
 
@@ -302,6 +343,7 @@ def ffn_forward(h: torch.Tensor, norm_weight: torch.Tensor, eps: float, w_router
     bias32 = bias if bias.dtype == torch.float32 else bias.float()
     theta32 = theta if theta.dtype == torch.float32 else theta.float()
     shape = _shape(geo, norm_mode, scale, False)
+    ws.raise_if_failed()
     ws.addend, ws.trace = None, trace
     cws = ws.c_struct()
     ws.trace = None
@@ -310,6 +352,7 @@ def ffn_forward(h: torch.Tensor, norm_weight: torch.Tensor, eps: float, w_router
                                   C.byref(cws), _lib.ptr(ws.rstd), _lib.ptr(ws.w_fold), refold, _lib.ptr(ws.xn),
                                   _lib.ptr(out), _stream(h.device))
     _lib.check(rc, "bibo_moe_ffn_forward")
+    ws.post_status()
     return out, ws
 
 
@@ -355,9 +398,10 @@ def experts_forward(x: torch.Tensor, topk_idx: torch.Tensor, topk_w: torch.Tenso
     w32 = topk_w.to(torch.float32).contiguous()
     theta32 = theta if theta.dtype == torch.float32 else theta.float()
     p = _lib.ptr
-    ws.status.zero_()
+    ws.raise_if_failed()
+    # bad indices (status 2 / 3) land in the plan's status word, which raise_if_failed reports
     _lib.check(lib.bibo_moe_route_from_indices(p(idx32), n, n_experts, k, p(ws.slot_rank), p(ws.block_counts),
-                                               p(ws.status), st), "bibo_moe_route_from_indices")
+                                               p(ws.plan[2:]), st), "bibo_moe_route_from_indices")
     _lib.check(lib.bibo_moe_plan(p(ws.block_counts), n, k, n_experts, n_glu, p(ws.plan), st), "bibo_moe_plan")
     _lib.check(lib.bibo_moe_permute_fwd(p(x), p(idx32), p(ws.slot_rank), p(ws.plan), n, hidden, n_experts, n_glu, k,
                                         dt, int(zero_padding), p(ws.xp), p(ws.slot_row), p(ws.row_token), st),
@@ -371,6 +415,7 @@ def experts_forward(x: torch.Tensor, topk_idx: torch.Tensor, topk_w: torch.Tenso
                                         dt, p(out), st), "bibo_moe_combine_fwd")
     ws.topk_idx_external = idx32  # keep alive until the stream has consumed it
     ws.topk_w_external = w32
+    ws.post_status()
     return out, ws
 
 
@@ -496,12 +541,14 @@ def moe_backward(dout: torch.Tensor, x: torch.Tensor, w_router: torch.Tensor, ga
     bws = _lib.BwdWorkspace(p(dy), p(dh), p(dw), p(dlogit), p(dlogit_row), p(dtheta_row))
     # zero_padded: the forward ran with zero_padding=True (lets the weight-gradient GEMMs use tensor cores)
     shape = _shape(geo, norm_mode, scale, zero_padded)
+    ws.raise_if_failed()
     cws = ws.c_struct()
     theta32 = theta if theta.dtype == torch.float32 else theta.float()
     rc = lib.bibo_moe_backward(C.byref(shape), p(x), p(w_router), p(gate_up_proj), p(down_proj), p(theta32),
                                C.byref(cws), p(dout), C.byref(bws), p(dx), p(d_wr), p(d_gu), p(d_dn), p(d_theta),
                                _stream(dev))
     _lib.check(rc, "bibo_moe_backward")
+    ws.post_status()
     return dx, d_wr, d_gu, d_dn, d_theta
 
 

@@ -123,7 +123,8 @@ int bibo_moe_route_from_indices(const int32_t* topk_idx, int64_t n_tokens, int n
  * Replaces the sort / bincount / cumsum / .tolist() of BiBoFusedExperts.forward
  * (src/modeling/ffn/moe.py:56-68) without a host synchronisation.
  * plan layout (int32 words): [0]=n_tiles [1]=rows used [2]=status [3]=n_pairs; the status word is
- * STICKY: the caller zeroes it once, kernels only ever raise it (1 = histogram total != N*k,
+ * STICKY: the caller zeroes it once, kernels only ever raise it (1 = histogram total > N*k,
+ * 2 = an expert index >= n_experts (the slot is ignored), 3 = one expert twice in a token,
  * 4 = a receive buffer of the expert-parallel path would overflow, 5 = a cross-rank barrier timed
  * out, 100..111 = a bounded wait inside a tensor-core kernel gave up: 100 down, 101 gate/up,
  * 102 router, 104 the gate/up kernel's exchange between its two column-block clusters),
@@ -165,6 +166,25 @@ int bibo_moe_gemm1_radial_fwd(const void* xp, const void* gate_up_proj, const fl
 
 /* 1 when the fused tensor-core kernel covers this shape (gate_up_out may then be NULL), else 0.   */
 int bibo_moe_gemm1_is_fused(int hidden, int inter, int dtype);
+
+/* ---- K2 + K3 in one kernel: the gate/up kernel gathers its own rows ------------------------------
+ * Same reference lines as K2 and K3 (src/modeling/ffn/moe.py:77,81,84-92).  bibo_moe_rowmap_fwd writes
+ * only the row maps of K2 (slot_row [N,k], row_token [rows_cap]; no row is copied; a negative expert
+ * index is an empty slot without a row).  bibo_moe_gemm1_gather_fwd then runs K3 with six extra warps
+ * per CTA that copy x[row_token[r]] into xp [rows_cap,H] up to two row-tile pairs ahead of the tile
+ * loads, so the copies are read back from L2; xp is left complete (what the backward pass re-reads).
+ * bf16, intermediate size 256 or 512 (bibo_moe_gemm1_gather_supported); zero_padding bit 0 as in K2.
+ * Results are bit-identical to K2 followed by K3.  Opt-in (bibo_moe_shape.zero_padding bit 1): on the
+ * benchmark shape it measured 0.77 ms against 0.73 ms for K2 + K3, the copies' L2 traffic costing the
+ * tensor-core kernel what the separate pass costs.                                                  */
+int bibo_moe_rowmap_fwd(const int32_t* topk_idx, const int32_t* slot_rank, const int32_t* plan,
+                        int64_t n_tokens, int n_experts, int n_glu, int top_k, int32_t* slot_row,
+                        int32_t* row_token, void* stream);
+int bibo_moe_gemm1_gather_supported(int hidden, int inter, int dtype);
+int bibo_moe_gemm1_gather_fwd(const void* x, const int32_t* row_token, const void* gate_up_proj,
+                              const float* theta, const int32_t* plan, int64_t n_tokens, int hidden,
+                              int inter, int n_experts, int n_glu, int top_k, int dtype, int zero_padding,
+                              void* xp, void* h, void* gate_up_out, float* rnorm_out, void* stream);
 
 /* ---- K4: grouped down GEMM ---------------------------------------------------------------------
  * Replaces F.linear(activated * up, down_proj[e]) (src/modeling/ffn/moe.py:92).
@@ -219,7 +239,9 @@ typedef struct {
   int64_t n_tokens;
   int hidden, inter, n_experts, n_glu, n_pos, top_k, norm_mode, dtype;
   float scale;            /* routed_scaling_factor */
-  int zero_padding;
+  int zero_padding;       /* bit 0: zero-fill the padding rows of xp (training); bit 1: let the gate/up kernel
+                             gather its own rows where it can (bibo_moe_gemm1_gather_fwd) instead of running K2
+                             as a pass of its own: same bits, measured slightly slower, see below            */
 } bibo_moe_shape;
 
 int bibo_moe_forward(const bibo_moe_shape* shape, const void* x, const void* w_router,
@@ -337,6 +359,12 @@ int bibo_moe_ep_experts(const void* xp_recv, const void* gate_up_proj, const voi
  * two seconds); on timeout *status is raised to 5 and the kernel returns.                          */
 int bibo_moe_ep_barrier(void* const* flags_peers, int rank, int world, int epoch, int32_t* status,
                         void* stream);
+/* The same with the number of polls (about 0.5 us each) chosen by the caller; max_polls <= 0 or beyond
+ * 2^22 means the default.  A caller that wants a short failure-detection timeout, or a test that makes
+ * the wait run out on purpose (a flag nobody writes), passes a small number: the kernel then raises
+ * *status to 5 and returns, the context stays usable.                                               */
+int bibo_moe_ep_barrier_bounded(void* const* flags_peers, int rank, int world, int epoch, int64_t max_polls,
+                                int32_t* status, void* stream);
 int bibo_moe_ep_combine(void* const* y_peers, const int32_t* slot_row, const float* topk_w,
                         const int32_t* ep_plan, int64_t n_tokens, int hidden, int world, int top_k,
                         int64_t rows_cap_recv, int comm_ctas, void* out, void* stream);
