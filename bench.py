@@ -128,6 +128,50 @@ class ClockSampler(threading.Thread):
                 "samples": len(s)}
 
 
+def reference_layer(wl, tensors, device, dtype):
+    """The UNMODIFIED reference BiBoMoELayer (from oracle/_ref, built by oracle/make_ref.py) carrying the
+    benchmark's weights, or None where oracle/_ref is absent.  Checker / baseline only."""
+    from oracle import make_ref
+    if not make_ref.available():
+        return None
+    make_ref.activate()
+    from src.configuration_bibo import BiBoConfig
+    from src.modeling.ffn.moe import BiBoMoELayer
+    cfg = BiBoConfig(hidden_size=wl["hidden"], num_attention_heads=wl["hidden"] // 256, num_key_value_heads=2,
+                     moe_intermediate_size=wl["inter"], num_routed_experts=N_EXPERTS, num_experts_per_tok=TOP_K,
+                     special_expert_pairs=0)
+    layer = BiBoMoELayer(cfg).to(dtype).to(device).eval()
+    with torch.no_grad():
+        layer.gate.gate_proj.weight.copy_(tensors["w_router"])
+        layer.gate.bias.copy_(tensors["bias"])
+        layer.experts.gate_up_proj.copy_(tensors["gate_up_proj"])
+        layer.experts.down_proj.copy_(tensors["down_proj"])
+        layer.experts.radial_theta.copy_(tensors["radial_theta"])
+    return layer
+
+
+def gpu_eager_reference(wl, t, dev, steps=5):
+    """tokens/s of the reference's own eager BiBoMoELayer.forward (per-expert Python loop, one host sync per
+    forward) in bf16 on this GPU, same tokens and weights: the only GPU implementation the reference ships."""
+    layer = reference_layer(wl, t, dev, torch.bfloat16)
+    if layer is None:
+        return None
+    x = t["x"][None]
+    with torch.no_grad():
+        for _ in range(2):
+            ref_out = layer(x)
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        torch.cuda.synchronize()
+        e0.record()
+        for _ in range(steps):
+            layer(x)
+        e1.record()
+        torch.cuda.synchronize()
+    ms = e0.elapsed_time(e1) / steps
+    return {"value": wl["n_tokens"] / (ms * 1e-3), "unit": UNIT, "ms_per_step": round(ms, 3), "steps": steps,
+            "kind": "the reference's BiBoMoELayer.forward, eager PyTorch, bf16, same GPU, same tokens and weights"}, ref_out[0]
+
+
 def cpu_oracle_rate(wl, seconds_cap=20.0, sample_tokens=2048, threads=None):
     """tokens/s of the CPU oracle (fp32, all host threads) on a bounded sample of the workload."""
     from oracle import moe_oracle as orc
@@ -138,6 +182,12 @@ def cpu_oracle_rate(wl, seconds_cap=20.0, sample_tokens=2048, threads=None):
                           theta_std=0.5, zipf_alpha=wl["zipf_alpha"] or 1.0)
     run = lambda: orc.moe_forward(inp["x"], inp["w_router"], inp["bias"], inp["gate_up_proj"], inp["down_proj"],
                                   inp["radial_theta"], TOP_K)
+    kind, what = "port", "CPU oracle = restatement of the reference's eager per-expert loop"
+    layer = reference_layer(wl, inp, "cpu", torch.float32)
+    if layer is not None:
+        x3 = inp["x"][None]
+        run = lambda: layer(x3)
+        kind, what = "reference", "the reference's own BiBoMoELayer.forward (unmodified, from oracle/_ref)"
     with torch.no_grad():
         run()
         t0, reps = time.perf_counter(), 0
@@ -147,9 +197,9 @@ def cpu_oracle_rate(wl, seconds_cap=20.0, sample_tokens=2048, threads=None):
             dt = time.perf_counter() - t0
             if dt > seconds_cap or (reps >= 3 and dt > 10.0):
                 break
-    return dict(value=sample_tokens * reps / dt, unit=UNIT, cores=torch.get_num_threads(), kind="port",
+    return dict(value=sample_tokens * reps / dt, unit=UNIT, cores=torch.get_num_threads(), kind=kind,
                 sample=f"{reps} passes of {sample_tokens} tokens (same hidden/intermediate/experts/top-k, fp32) "
-                       f"in {dt:.1f} s; CPU oracle = restatement of the reference's eager per-expert loop")
+                       f"in {dt:.1f} s; {what}")
 
 
 def run_reference(args, wl, rank, world):
@@ -164,6 +214,16 @@ def run_reference(args, wl, rank, world):
                           zipf_alpha=wl["zipf_alpha"] or 1.0)
     run = lambda: orc.moe_forward(inp["x"], inp["w_router"], inp["bias"], inp["gate_up_proj"], inp["down_proj"],
                                   inp["radial_theta"], TOP_K)
+    kind = "port"
+    desc = (f"each step = one fp32 forward of {sample} tokens of the workload through the CPU oracle "
+            f"(restatement of the reference's eager per-expert loop; oracle/_ref is not present on this machine)")
+    layer = reference_layer(wl, inp, "cpu", torch.float32)
+    if layer is not None:
+        kind = "reference"
+        x3 = inp["x"][None]
+        run = lambda: layer(x3)
+        desc = (f"each step = one fp32 forward of {sample} tokens of the workload through the reference's own "
+                f"BiBoMoELayer.forward (unmodified, byte-compiled into oracle/_ref) on the host cores")
     with torch.no_grad():
         for _ in range(args.warmup):
             run()
@@ -172,15 +232,12 @@ def run_reference(args, wl, rank, world):
             run()
         dt = time.perf_counter() - t0
     val = sample * args.steps / dt
-    desc = (f"each step = one fp32 forward of {sample} tokens of the workload through the CPU oracle "
-            f"(restatement of the reference's eager per-expert loop; the reference itself is Python and is "
-            f"not present on this machine)")
     print(json.dumps({
         "impl": "reference", "metric": METRIC, "value": val, "unit": UNIT, "n_gpus": args.gpus, "steps": args.steps,
         "warmup": args.warmup, "ms_per_step": dt / args.steps * 1e3, "higher_is_better": True, "scaling": "weak",
         "vs_baseline": None, "dtype": "f32", "data": "synthetic",
         "config": workload_config(args, wl, world),
-        "cpu_baseline": {"value": val, "unit": UNIT, "cores": torch.get_num_threads(), "kind": "port", "sample": desc},
+        "cpu_baseline": {"value": val, "unit": UNIT, "cores": torch.get_num_threads(), "kind": kind, "sample": desc},
         "e2e": {"value": val, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0}))
 
@@ -195,6 +252,117 @@ def workload_config(args, wl, world):
             "l2": "per-step working set (activations + expert weights + intermediates) exceeds the 126 MB L2"}
 
 
+BF16_MAX_REL, BF16_MEAN_REL = 2e-2, 1e-2      # the bf16 parity bars against the fp32 oracle
+PEER_COPY_GBS = 770.0                         # peer copy per direction measured on this pool's B200s (nominal 900)
+
+
+def _lane_topk_idx(lane):
+    return lane.buf.topk_idx if hasattr(lane, "buf") else lane.topk_idx
+
+
+def run_ep_check(args, wl, t, runner, rank, world, dev, fwdbwd_step):
+    """After the timed region: one more expert-parallel step, then the first 256 tokens of every rank are
+    gathered on rank 0 and compared with (i) the single-GPU kernel chain on those tokens with the full expert
+    set and (ii) the fp32 CPU oracle on them (tokens are independent, so a sample checks the same rows).
+    Forward + backward mode compares the sampled rows of dx with the single-GPU backward."""
+    import torch.distributed as dist
+    from bibo_b200 import functional as Fn
+    sample = min(256, wl["n_tokens"])
+    h, i = wl["hidden"], wl["inter"]
+    if fwdbwd_step is None:
+        out = runner.forward(t["x"])
+        dx = None
+    else:
+        lane = runner.lanes[0]
+        out = lane.forward(t["x"], training=True)
+        dout = torch.randn(t["x"].shape, generator=torch.Generator(device=dev).manual_seed(77 + rank), device=dev,
+                           dtype=torch.float32).to(torch.bfloat16)
+        dx = lane.backward(dout)[0]
+    torch.cuda.synchronize()
+    status = runner.status()
+    pieces = [t["x"][:sample], out[:sample]] + ([dout[:sample], dx[:sample]] if dx is not None else [])
+    mine = torch.cat([p_.contiguous().view(torch.int16).reshape(sample, -1) for p_ in pieces], dim=1).contiguous()
+    idx_mine = _lane_topk_idx(runner.lanes[0])[:sample].contiguous()
+    gathered = torch.empty(world * sample, mine.shape[1], dtype=torch.int16, device=dev)
+    idx_all = torch.empty(world * sample, TOP_K, dtype=torch.int32, device=dev)
+    st_all = torch.empty(world, dtype=torch.int32, device=dev)
+    dist.all_gather_into_tensor(gathered, mine)
+    dist.all_gather_into_tensor(idx_all, idx_mine)
+    dist.all_gather_into_tensor(st_all, torch.tensor([status], dtype=torch.int32, device=dev))
+    if rank != 0:
+        return None
+    cols = gathered.view(torch.bfloat16).split(h, dim=1)
+    xs, outs = cols[0].contiguous(), cols[1].contiguous()
+    geo = Fn.Geometry(xs.shape[0], h, i, N_EXPERTS, N_EXPERTS, 0, TOP_K, torch.bfloat16)
+    ws1 = Fn.MoEWorkspace(geo, dev, keep_logits=True, keep_gate_up=True)
+    ref1, _ = Fn.moe_forward(xs, t["w_router"], t["bias"], t["gate_up_proj"], t["down_proj"], t["radial_theta"], TOP_K,
+                             "sum", ws=ws1, zero_padding=dx is not None)
+    rel = lambda a, b: float((a.double() - b.double()).abs().max() / b.double().abs().max().clamp_min(1e-30))
+    mrel = lambda a, b: float((a.double() - b.double()).abs().mean() / b.double().abs().mean().clamp_min(1e-30))
+    res = {"sample_tokens_per_rank": sample, "status": int(st_all.max()),
+           "routing_identical": bool(torch.equal(idx_all, ws1.topk_idx)),
+           "vs_single_gpu_max_rel": rel(outs.float(), ref1.float()),
+           "vs_single_gpu_bit_identical": bool(torch.equal(outs.view(torch.int16), ref1.view(torch.int16)))}
+    from oracle import moe_oracle as orc
+    f32 = lambda k_: t[k_].float().cpu()
+    ref, _, idx_o, _, _ = orc.moe_forward(xs.float().cpu(), f32("w_router"), f32("bias"), f32("gate_up_proj"),
+                                          f32("down_proj"), f32("radial_theta"), TOP_K, return_routing=True)
+    same = (idx_all.cpu().long() == idx_o).all(-1)
+    res.update(oracle_same_routing_frac=float(same.float().mean()),
+               vs_oracle_max_rel=rel(outs.float().cpu()[same], ref[same]),
+               vs_oracle_mean_rel=mrel(outs.float().cpu()[same], ref[same]))
+    ok = (res["status"] == 0 and res["routing_identical"] and res["vs_oracle_max_rel"] < BF16_MAX_REL
+          and res["vs_oracle_mean_rel"] < BF16_MEAN_REL and res["oracle_same_routing_frac"] > 0.97)
+    if dx is not None:
+        douts, dxs = cols[2].contiguous(), cols[3].contiguous()
+        dx1 = Fn.moe_backward(douts, xs, t["w_router"], t["gate_up_proj"], t["down_proj"], t["radial_theta"], ws1, "sum")[0]
+        res["dx_vs_single_gpu_max_rel"] = rel(dxs.float(), dx1.float())
+        res["dx_vs_single_gpu_mean_rel"] = mrel(dxs.float(), dx1.float())
+        ok = ok and res["dx_vs_single_gpu_max_rel"] < BF16_MAX_REL and res["dx_vs_single_gpu_mean_rel"] < BF16_MEAN_REL
+    res["ok"] = bool(ok)
+    res["bars"] = {"max_rel": BF16_MAX_REL, "mean_rel": BF16_MEAN_REL}
+    return res
+
+
+def nvlink_roofline(args, wl, t, runner, world, rank, ep_phases):
+    """N > 1: the NVLink phase of the profiled step against the measured peer-copy rate.  Bytes = rows this
+    rank sends to OTHER ranks in the dispatch phase (counted from its routing) x row size; the return phase
+    moves the same number of rows the other way."""
+    el = N_EXPERTS // world
+    rows = 0
+    dedup = args.ep_exchange == "dedup"
+    for lane in runner.lanes:
+        n_lane = lane._n_cap if dedup else lane._n
+        idx = _lane_topk_idx(lane)[:n_lane].long()
+        owner = idx // el
+        remote = owner != rank
+        if dedup:     # distinct remote owners per token
+            onehot = torch.zeros(idx.shape[0], world, dtype=torch.bool, device=idx.device)
+            onehot.scatter_(1, owner, True)
+            onehot[:, rank] = False
+            rows += int(onehot.sum())
+        else:
+            rows += int(remote.sum())
+    nbytes = rows * wl["hidden"] * 2
+    if rank != 0:
+        return None
+    # time during which any slice was in its dispatch phase / its return phase
+    names = ("dispatch", "partial") if dedup else ("dispatch", "combine")
+    starts = {"dispatch": "route" if dedup else "gather_plan", "partial": "experts", "combine": "barrier2"}
+    out = {}
+    for nm in names:
+        t0 = min(ph[starts[nm]] for ph in ep_phases if starts[nm] in ph)
+        t1 = max(ph[nm] for ph in ep_phases if nm in ph)
+        out[nm] = max(t1 - t0, 1e-6)
+    top = max(out, key=out.get)
+    ach = nbytes / (out[top] * 1e-3) / 1e9
+    return {"kernel": "ep_" + top, "bound": "nvlink", "achieved": round(ach, 1), "peak": PEER_COPY_GBS, "unit": "GB/s",
+            "frac": round(ach / PEER_COPY_GBS, 4), "traffic": None, "bytes_per_direction_per_rank": nbytes,
+            "phase_ms": {k_: round(v, 4) for k_, v in out.items()},
+            "peak_source": "peer copy per direction measured on this pool (nominal 900 GB/s); the phase interval "
+                           "spans all token slices, whose phases overlap other slices' GEMMs"}
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -203,9 +371,18 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="c4", choices=sorted(WORKLOADS))
     ap.add_argument("--no-cpu-baseline", action="store_true")
-    ap.add_argument("--ep-chunks", type=int, default=1, help="token slices pipelined on separate streams (N>1)")
-    ap.add_argument("--ep-exchange", default="kernel", choices=["copy", "kernel"],
-                    help="N>1: rows travel by peer copies on the copy engines, or by the dispatch/combine kernels")
+    ap.add_argument("--no-gpu-reference", action="store_true",
+                    help="skip timing the reference's eager layer on this GPU (needs oracle/_ref)")
+    ap.add_argument("--ep-chunks", type=int, default=None,
+                    help="token slices pipelined on separate streams (N>1; default 2 for the dedup exchange, else 1)")
+    ap.add_argument("--ep-exchange", default="dedup", choices=["dedup", "copy", "kernel"],
+                    help="N>1: dedup = one row per (token, destination rank) each way (default); kernel = one row per "
+                         "slot through the dispatch/combine kernels; copy = per-slot rows by peer copies on the copy engines")
+    ap.add_argument("--gemm-ctas", type=int, default=None, help="N>1: cap of the grouped-GEMM grids (0 = none)")
+    ap.add_argument("--comm-ctas", type=int, default=None, help="N>1: cap of the exchange kernels' grids (0 = none)")
+    ap.add_argument("--repeats", type=int, default=9, help="extra timed regions of --steps steps (median / min / max)")
+    ap.add_argument("--sustained-s", type=float, default=2.0, help="seconds of back-to-back steps for the sustained figure (0 = skip)")
+    ap.add_argument("--no-ep-check", action="store_true", help="N>1: skip the parity check of sampled tokens")
     ap.add_argument("--copy-streams", type=int, default=0, help="copy exchange: 1 = one stream per peer, 0 = one stream")
     ap.add_argument("--no-numa-bind", action="store_true",
                     help="N>1: do not pin each rank to the CPUs local to its GPU (pinned host buffers then land anywhere)")
@@ -219,6 +396,10 @@ def main():
                          "the permute's loads; ffn_separate = the same with the norm as a kernel of its own (1 GPU)")
     args = ap.parse_args()
     wl = WORKLOADS[args.workload]
+    if args.mode == "fwdbwd" and args.ep_exchange == "dedup":
+        args.ep_exchange = "kernel"            # the de-duplicated exchange is forward-only
+    if args.ep_chunks is None:
+        args.ep_chunks = 2 if args.ep_exchange == "dedup" else 1
     rank, world = int(os.environ.get("RANK", 0)), int(os.environ.get("WORLD_SIZE", 1))
     local = int(os.environ.get("LOCAL_RANK", 0))
     if args.impl == "reference":
@@ -241,8 +422,12 @@ def main():
     if world > 1:
         from bibo_b200 import ep
         dma = args.ep_exchange == "copy" and args.mode == "fwd"
+        dedup = args.ep_exchange == "dedup"
+        ep_kw = dict(comm_sms=args.comm_sms, dedup=dedup, gemm_ctas=args.gemm_ctas, comm_ctas=args.comm_ctas)
+        if not dedup:
+            ep_kw.update(dma=dma, copy_streams=bool(args.copy_streams))
         runner = ep.PipelinedExpertParallelMoE(t, TOP_K, dist.group.WORLD, n_tokens=wl["n_tokens"], chunks=args.ep_chunks,
-                                               comm_sms=args.comm_sms, dma=dma, copy_streams=bool(args.copy_streams))
+                                               **ep_kw)
         step = lambda: runner.forward(t["x"])
         ws = None
         if args.mode == "fwdbwd":
@@ -315,6 +500,36 @@ def main():
     ms_step = float(ms_total) / args.steps
     value = n * world / (ms_step * 1e-3)
 
+    # ---- the same region repeated: spread of the per-step time, then seconds of back-to-back steps -------
+    if ws is not None:
+        ws.stage_events = None
+
+    def timed_region(k_steps):
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        barrier()
+        a.record()
+        for _ in range(k_steps):
+            step()
+        b.record()
+        barrier()
+        ms = torch.tensor([a.elapsed_time(b)], device=dev)
+        if world > 1:
+            dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+        return float(ms) / k_steps
+
+    rep = sorted(timed_region(args.steps) for _ in range(max(0, args.repeats)))
+    repeats = ({"regions": len(rep), "steps_each": args.steps, "ms_median": round(rep[len(rep) // 2], 4),
+                "ms_min": round(rep[0], 4), "ms_max": round(rep[-1], 4)} if rep else None)
+    sustained = None
+    if args.sustained_s > 0:
+        k_sus = max(args.steps, int(args.sustained_s * 1e3 / ms_step))
+        sus_sampler = ClockSampler(local)
+        sus_sampler.start()
+        ms_sus = timed_region(k_sus)
+        sus_clocks = sus_sampler.stop()
+        sustained = {"steps": k_sus, "seconds": round(ms_sus * k_sus * 1e-3, 2), "ms_per_step": round(ms_sus, 4),
+                     "clocks": sus_clocks}
+
     # ---- end-to-end: host buffers through the C-ABI host entry (N=1) / the public forward (N>1) ------
     x_host = t["x"].cpu().pin_memory()
     out_host = torch.empty_like(x_host).pin_memory()
@@ -322,7 +537,7 @@ def main():
     if world > 1:
         # token slices on separate streams: the copies of one slice run under the kernels of another
         e2e_runner = runner if args.e2e_chunks == args.ep_chunks else ep.PipelinedExpertParallelMoE(
-            t, TOP_K, dist.group.WORLD, n_tokens=wl["n_tokens"], chunks=args.e2e_chunks, comm_sms=args.comm_sms, dma=dma, copy_streams=bool(args.copy_streams))
+            t, TOP_K, dist.group.WORLD, n_tokens=wl["n_tokens"], chunks=args.e2e_chunks, **ep_kw)
         e2e_step = lambda: e2e_runner.forward_host(x_host, out_host, x_dev, out_dev)
     else:
         if ws is not None:
@@ -353,6 +568,12 @@ def main():
         ep_phases = [{n: round(t_start.elapsed_time(ev), 3) for n, ev in lane.marks} for lane in runner.lanes]
         for lane in runner.lanes:
             lane.profile = False
+    ep_check = None
+    if world > 1 and not args.no_ep_check:
+        ep_check = run_ep_check(args, wl, t, runner, rank, world, dev, step if args.mode == "fwdbwd" else None)
+    nvlink = None
+    if world > 1 and ep_phases:
+        nvlink = nvlink_roofline(args, wl, t, runner, world, rank, ep_phases)
     if rank != 0:
         if world > 1:
             dist.destroy_process_group()
@@ -395,12 +616,31 @@ def main():
         "data": "synthetic", "config": workload_config(args, wl, world),
         "layer_tflops": round(layer_flops * world / (ms_step * 1e-3) / 1e12, 2),
         "layer_frac_of_bf16_peak": round(layer_flops / (ms_step * 1e-3) / 1e12 / pk["tf"], 4),
-        "roofline": roof, "stages": stages, "ep_phases_ms": ep_phases, "clocks": clocks, "gpu_launches": launches,
+        "roofline": roof if roof is not None else nvlink, "stages": stages, "ep_phases_ms": ep_phases,
+        "ep_check": ep_check, "repeats": repeats, "sustained": sustained, "clocks": clocks, "gpu_launches": launches,
         "e2e": {"value": e2e_val, "unit": UNIT, "h2d_bytes_per_step": x_host.numel() * 2 * world,
                 "d2h_bytes_per_step": out_host.numel() * 2 * world},
     }
+    if sustained is not None:
+        sustained["layer_frac_of_sustained_bf16_peak"] = (
+            round(layer_flops / (sustained["ms_per_step"] * 1e-3) / 1e12 / pk["tf_sus"], 4) if pk["tf_sus"] else None)
+    if ep_check is not None and not ep_check["ok"]:
+        print(json.dumps(line))
+        sys.exit("expert-parallel parity check failed: " + json.dumps(ep_check))
     if args.mode != "fwd":      # the host-buffer call is the block's forward: it says nothing about the other modes
         line["e2e"]["note"] = "host-buffer forward of the block alone (mode fwd), not of mode " + args.mode
+    if world == 1 and args.mode == "fwd" and not args.no_gpu_reference:
+        res = gpu_eager_reference(wl, t, dev)
+        if res is not None:
+            line["gpu_eager_reference"], ref_out = res
+            ours, _ = Fn.moe_forward(t["x"], t["w_router"], t["bias"], t["gate_up_proj"], t["down_proj"],
+                                     t["radial_theta"], TOP_K, "sum")
+            torch.cuda.synchronize()
+            per_tok = (ours.float() - ref_out.float()).norm(dim=-1) / ref_out.float().norm(dim=-1).clamp_min(1e-30)
+            line["gpu_eager_reference"]["our_output_vs_it"] = {
+                "median_token_rel": float(per_tok.median()), "tokens_above_5e-2": int((per_tok > 5e-2).sum()),
+                "note": "both bf16; a token above the bar took another expert at a bf16 near-tie of the router"}
+            line["gpu_eager_reference"]["speedup_device_timed"] = round(value / line["gpu_eager_reference"]["value"], 1)
     if world == 1 and not args.no_cpu_baseline:
         line["cpu_baseline"] = cpu_oracle_rate(wl)
     print(json.dumps(line))

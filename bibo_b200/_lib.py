@@ -59,6 +59,20 @@ class EpBwdArgs(C.Structure):
                                     "d_gate_up_proj", "d_down_proj", "d_theta")] + [("epoch_base", _i32)])
 
 
+class EpDedupOwner(C.Structure):
+    _fields_ = ([("n_cap", _i64)] +
+                [(n, _i32) for n in ("hidden", "inter", "n_experts", "top_k", "rank", "world", "max_ctas", "comm_ctas")] +
+                [(n, _vp) for n in ("xu", "midx", "mw", "gate_up_proj", "down_proj", "theta", "slot_rank", "block_counts",
+                                    "plan", "slot_row", "row_token", "xp", "h", "y", "part_peers")])
+
+
+class EpDedup(C.Structure):
+    _fields_ = ([("owner", EpDedupOwner), ("n_tokens", _i64), ("norm_mode", _i32), ("epoch_base", _i32), ("scale", _f32)] +
+                [(n, _vp) for n in ("x", "w_router", "bias", "topk_idx", "topk_w", "slot_rank_home", "block_counts_home",
+                                    "xu_peers", "midx_peers", "mw_peers", "flags_peers", "part_local", "out", "marks",
+                                    "trace")])
+
+
 class Shape(C.Structure):
     _fields_ = [("n_tokens", _i64), ("hidden", _i32), ("inter", _i32), ("n_experts", _i32),
                 ("n_glu", _i32), ("n_pos", _i32), ("top_k", _i32), ("norm_mode", _i32),
@@ -136,6 +150,14 @@ SIGNATURES = {
     "bibo_moe_ep_barrier": (_i32, [_vp, _i32, _i32, _i32, _vp, _vp]),
     "bibo_moe_ep_barrier_bounded": (_i32, [_vp, _i32, _i32, _i32, _i64, _vp, _vp]),
     "bibo_moe_ep_combine": (_i32, [_vp, _vp, _vp, _vp, _i64, _i32, _i32, _i32, _i64, _i32, _vp, _vp]),
+    "bibo_moe_ep_dedup_rows_cap": (_i64, [_i32, _i64, _i32, _i32]),
+    "bibo_moe_ep_dedup_plan_words": (_i64, [_i32, _i64, _i32, _i32]),
+    "bibo_moe_ep_dedup_virtual_tokens": (_i64, [_i32, _i64]),
+    "bibo_moe_ep_dedup_dispatch": (_i32, [_vp, _vp, _vp, _vp, _vp, _vp, _i64, _i64, _i32, _i32, _i32, _i32, _i32, _i32,
+                                          _vp]),
+    "bibo_moe_ep_dedup_owner": (_i32, [C.POINTER(EpDedupOwner), _vp]),
+    "bibo_moe_ep_dedup_final": (_i32, [_vp, _vp, _vp, _i64, _i64, _i32, _i32, _i32, _i32, _i32, _vp, _vp]),
+    "bibo_moe_ep_dedup_forward": (_i32, [C.POINTER(EpDedup), _vp]),
     "bibo_moe_route_noalloc": (_i32, [_vp, _vp, _vp, _i64, _i32, _i32, _i32, _i32, _f32, _i32, _vp, _vp, _vp, _vp]),
     "bibo_moe_route_noalloc_max_tokens": (_i64, []),
     "bibo_moe_debug_plan_header": (_i32, [_vp, _vp, _vp]),

@@ -49,7 +49,10 @@ permute_kernel(const uint8_t* __restrict__ x, const int32_t* __restrict__ topk_i
     const float rs = rstd != nullptr ? rstd[w] : 0.f;
     uint4* keep = (xn != nullptr && __any_sync(0xffffffffu, identity)) ? reinterpret_cast<uint4*>(xn + w * row_bytes)
                                                                       : nullptr;
-    for (int c = lane; c < chunks; c += 32) {
+    // a token without any row (all its slots empty or on +/-Identity experts) is not even read, unless its
+    // normalised row has to be kept for the combine kernel
+    const bool copy = __any_sync(0xffffffffu, my_row >= 0) || keep != nullptr;
+    for (int c = lane; c < (copy ? chunks : 0); c += 32) {
       uint4 v = __ldg(src + c);
       if (rstd != nullptr) {
         const uint4 wv = __ldg(reinterpret_cast<const uint4*>(norm_w) + c);

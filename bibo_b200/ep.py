@@ -328,6 +328,166 @@ class ExpertParallelMoE:
         return max(int(self.ep_plan[2].item()), int(self.local_plan[2].item()))
 
 
+class DedupBuffers:
+    """The buffers one rank needs for the de-duplicated exchange (``include/bibo_moe.h``, "expert-parallel
+    forward with a de-duplicated exchange").  ``group`` given: the four exchange buffers and the barrier flags are
+    symmetric (peer-mapped) allocations; ``group=None``: plain local tensors, for playing several ranks on
+    one device (tests)."""
+
+    def __init__(self, world: int, n_cap: int, top_k: int, n_experts: int, hidden: int, inter: int, device, group=None):
+        lib = _lib.load()
+        self.world, self.n_cap, self.top_k = world, n_cap, top_k
+        nv = world * n_cap
+        el = n_experts // world
+        rows = int(lib.bibo_moe_ep_dedup_rows_cap(world, n_cap, top_k, n_experts))
+        i32 = dict(dtype=torch.int32, device=device)
+        bf = dict(dtype=torch.bfloat16, device=device)
+
+        def shared(shape, dtype):
+            if group is None:
+                return None, torch.empty(*shape, dtype=dtype, device=device)
+            sym = _Symmetric(shape, dtype, device, group)
+            return sym, sym.tensor
+
+        self.sym_xu, self.xu = shared((nv, hidden), torch.bfloat16)
+        self.sym_midx, self.midx = shared((nv, top_k), torch.int32)
+        self.sym_mw, self.mw = shared((nv, top_k), torch.float32)
+        self.sym_part, self.part = shared((nv, hidden), torch.bfloat16)
+        self.sym_flags, self.flags = shared((64,), torch.int32)
+        self.flags.zero_()
+        self.midx.fill_(-1)              # until a source rank has written its records, its tokens do not exist
+        self.slot_rank = torch.empty(nv, top_k, **i32)
+        self.block_counts = torch.empty(int(lib.bibo_moe_router_blocks(nv)), el, **i32)
+        self.plan = torch.zeros(int(lib.bibo_moe_ep_dedup_plan_words(world, n_cap, top_k, n_experts)), **i32)
+        self.slot_row = torch.empty(nv, top_k, **i32)
+        self.row_token = torch.empty(rows, **i32)
+        self.xp = torch.empty(rows, hidden, **bf)
+        self.h = torch.empty(rows, inter, **bf)
+        self.y = torch.empty(rows, hidden, **bf)
+        # home side: routing of this rank's own tokens
+        self.topk_idx = torch.empty(n_cap, top_k, **i32)
+        self.topk_w = torch.empty(n_cap, top_k, dtype=torch.float32, device=device)
+        self.slot_rank_home = torch.empty(n_cap, top_k, **i32)
+        self.block_counts_home = torch.empty(int(lib.bibo_moe_router_blocks(n_cap)), n_experts, **i32)
+
+    def owner_args(self, rank: int, hidden: int, inter: int, n_experts: int, gate_up, down, theta, part_ptr_array,
+                   max_ctas: int = 0, comm_ctas: int = 0) -> _lib.EpDedupOwner:
+        p = _lib.ptr
+        return _lib.EpDedupOwner(self.n_cap, hidden, inter, n_experts, self.top_k, rank, self.world, max_ctas, comm_ctas,
+                                 p(self.xu), p(self.midx), p(self.mw), p(gate_up), p(down), p(theta), p(self.slot_rank),
+                                 p(self.block_counts), p(self.plan), p(self.slot_row), p(self.row_token), p(self.xp),
+                                 p(self.h), p(self.y), C.cast(part_ptr_array, C.c_void_p))
+
+
+class DedupExpertParallelMoE:
+    """Inference forward of the MoE block with the experts sharded over ``group`` and a de-duplicated exchange:
+    one row per (token, destination rank) goes out, one partial result row per (token, rank) comes back
+    (``bibo_moe_ep_dedup_forward``).  Dropless: the owner's buffers hold the worst case.  Results are within
+    the bf16 parity bars of the fp32 oracle; they are not bit-identical to the single-GPU chain (every rank's
+    partial sum is rounded to bf16 once).  ``weights`` as for ``ExpertParallelMoE``."""
+
+    MARKS = ("start", "route", "dispatch", "received", "experts", "partial", "returned", "sum")
+
+    def __init__(self, weights, top_k: int, group=None, n_tokens: Optional[int] = None, norm_mode="sum",
+                 scale: float = 1.0, max_ctas: int = 0, comm_ctas: int = 0, **_unused):
+        os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")   # plain peer loads/stores only
+        self.group = group if group is not None else dist.group.WORLD
+        self.rank, self.world = dist.get_rank(self.group), dist.get_world_size(self.group)
+        self.top_k, self.norm_mode, self.scale = top_k, norm_mode, scale
+        self.max_ctas, self.comm_ctas = max_ctas, comm_ctas
+        w_r = weights["w_router"]
+        self.device = w_r.device
+        self.n_experts, self.hidden = w_r.shape
+        if self.n_experts % self.world:
+            raise RuntimeError(f"{self.n_experts} experts do not shard evenly over {self.world} ranks")
+        if w_r.dtype != torch.bfloat16:
+            raise RuntimeError("the expert-parallel path runs the bf16 tensor-core kernels only")
+        self.el = self.n_experts // self.world
+        lo, hi = self.rank * self.el, (self.rank + 1) * self.el
+        shard = lambda t: (t[lo:hi] if t.shape[0] == self.n_experts else t).contiguous()
+        self.w_router, self.bias = w_r.contiguous(), weights["bias"].float().contiguous()
+        self.gate_up, self.down = shard(weights["gate_up_proj"]), shard(weights["down_proj"])
+        self.theta = shard(weights["radial_theta"]).float().contiguous()
+        self.inter = self.gate_up.shape[1] // 2
+        self.dma = False
+        self._n_cap, self._epoch, self.buf, self.profile, self.trace = None, 0, None, False, None
+        if n_tokens is not None:
+            self._allocate(n_tokens)
+
+    def _allocate(self, n_tokens: int) -> None:
+        cap = torch.tensor([n_tokens], dtype=torch.int64, device=self.device)
+        dist.all_reduce(cap, op=dist.ReduceOp.MAX, group=self.group)      # ranks may hold different token counts
+        self._n_cap = int(cap)
+        self.buf = DedupBuffers(self.world, self._n_cap, self.top_k, self.n_experts, self.hidden, self.inter,
+                                self.device, self.group)
+        self.header_host = torch.zeros(4, dtype=torch.int32).pin_memory()
+        self._epoch = 0
+        torch.cuda.synchronize(self.device)
+        dist.barrier(self.group)            # every rank's flags and records are initialised before the first step
+
+    def forward(self, x: torch.Tensor, out: Optional[torch.Tensor] = None, training: bool = False,
+                phase: int = 0) -> torch.Tensor:
+        if training:
+            raise RuntimeError("the de-duplicated exchange is forward-only; train through ExpertParallelMoE")
+        n, hidden = x.shape
+        if self.buf is None or n > self._n_cap:
+            self._allocate(n)
+        self.raise_if_failed()
+        if out is None:
+            out = torch.empty_like(x)
+        b, p = self.buf, _lib.ptr
+        cast = lambda sym: C.cast(sym.ptr_array, C.c_void_p)
+        marks = None
+        if self.profile:
+            evs = [torch.cuda.Event(enable_timing=True) for _ in self.MARKS]
+            for e in evs:
+                e.record()
+            self.marks = list(zip(self.MARKS, evs))
+            self._mark_ptrs = (C.c_void_p * len(evs))(*[e.cuda_event for e in evs])
+            marks = C.cast(self._mark_ptrs, C.c_void_p)
+        owner = b.owner_args(self.rank, hidden, self.inter, self.n_experts, self.gate_up, self.down, self.theta,
+                             b.sym_part.ptr_array, self.max_ctas, self.comm_ctas)
+        a = _lib.EpDedup(owner, n, Fn.norm_code(self.norm_mode), self._epoch, float(self.scale), p(x), p(self.w_router),
+                         p(self.bias), p(b.topk_idx), p(b.topk_w), p(b.slot_rank_home), p(b.block_counts_home),
+                         cast(b.sym_xu), cast(b.sym_midx), cast(b.sym_mw), cast(b.sym_flags), p(b.part), p(out), marks,
+                         self._trace_struct(n))
+        self._epoch += 2
+        st = torch.cuda.current_stream(self.device).cuda_stream
+        _lib.check(_lib.load().bibo_moe_ep_dedup_forward(C.byref(a), st), "bibo_moe_ep_dedup_forward")
+        self.header_host.copy_(b.plan[:4], non_blocking=True)
+        return out
+
+    def _trace_struct(self, n: int):
+        if self.trace is None:
+            return None
+        blocks = _lib.load().bibo_moe_router_blocks(n)
+        if getattr(self, "_trace_blocks", None) is None or self._trace_blocks.shape[0] != blocks:
+            self._trace_blocks = torch.empty(blocks, _lib.TRACE_WORDS, dtype=torch.float32, device=self.device)
+        self._trace_c = _lib.RouterTrace(_lib.ptr(self._trace_blocks), *[_lib.ptr(t) for t in self.trace])
+        return C.cast(C.pointer(self._trace_c), C.c_void_p)
+
+    def raise_if_failed(self, wait: bool = False) -> None:
+        """RuntimeError if a kernel of an earlier forward left a status word (5 = a cross-rank barrier timed
+        out, 100.. = a bounded wait in a kernel gave up); see ``functional.MoEWorkspace.raise_if_failed``."""
+        if self.buf is None:
+            return
+        if wait:
+            torch.cuda.current_stream(self.device).synchronize()
+        code = int(self.header_host[2])
+        if code != 0:
+            self.header_host[2] = 0
+            self.buf.plan[2:3].zero_()
+            raise RuntimeError(f"bibo_b200: an expert-parallel forward reported device status {code} "
+                               f"({Fn.STATUS_TEXT.get(code, 'see the plan layout in bibo_moe.h')}); its results and "
+                               "those of the calls issued since are invalid")
+
+    def phase_ms(self):
+        return {n: self.marks[i - 1][1].elapsed_time(ev) for i, (n, ev) in enumerate(self.marks) if i > 0}
+
+    def status(self) -> int:
+        return int(self.buf.plan[2].item()) if self.buf is not None else 0
+
+
 class PipelinedExpertParallelMoE:
     """The expert-parallel forward on ``chunks`` token slices, each on its own CUDA stream.
 
@@ -340,14 +500,22 @@ class PipelinedExpertParallelMoE:
     """
 
     def __init__(self, weights, top_k: int, group=None, n_tokens: Optional[int] = None, chunks: int = 2,
-                 comm_sms: int = 20, **kw):
+                 comm_sms: int = 20, dedup: bool = False, gemm_ctas: Optional[int] = None,
+                 comm_ctas: Optional[int] = None, **kw):
+        """``dedup``: lanes use the de-duplicated exchange (``DedupExpertParallelMoE``, forward only).
+        ``gemm_ctas`` / ``comm_ctas`` override the grid caps derived from ``comm_sms`` (0 = no cap)."""
         self.chunks = max(1, int(chunks))
         dev = weights["w_router"].device
         sms = torch.cuda.get_device_properties(dev).multi_processor_count
         sm_exchange = self.chunks > 1 and not kw.get("dma", False)   # copy-engine exchange needs no SMs
         max_ctas = max(8, sms - comm_sms) if sm_exchange else 0
-        comm_ctas = comm_sms * 4 if sm_exchange else 0          # 4 resident 8-warp blocks per exchange SM
-        self.lanes = [ExpertParallelMoE(weights, top_k, group, max_ctas=max_ctas, comm_ctas=comm_ctas, **kw)
+        c_ctas = comm_sms * 4 if sm_exchange else 0             # 4 resident 8-warp blocks per exchange SM
+        if gemm_ctas is not None:
+            max_ctas = int(gemm_ctas)
+        if comm_ctas is not None:
+            c_ctas = int(comm_ctas)
+        cls = DedupExpertParallelMoE if dedup else ExpertParallelMoE
+        self.lanes = [cls(weights, top_k, group, max_ctas=max_ctas, comm_ctas=c_ctas, **kw)
                       for _ in range(self.chunks)]
         self.streams = [torch.cuda.Stream(device=dev) for _ in range(self.chunks)]
         self.device = dev

@@ -441,6 +441,69 @@ typedef struct {
 } bibo_moe_ep_bwd_args;
 int bibo_moe_ep_backward(const bibo_moe_ep_args* fwd, const bibo_moe_ep_bwd_args* bwd, void* stream);
 
+/* ---- expert-parallel forward with a de-duplicated exchange ---------------------------------------------
+ * No counterpart in the reference (the reference states the need for expert parallelism with a replicated
+ * router, AGENTS.md:174,199,703, and has none).  Same sharding as above, but a token row crosses NVLink once
+ * per DESTINATION RANK instead of once per selected expert, and one partial result row per (token, rank)
+ * comes back: with 64 experts and top-6, 0.99 / 2.50 / 3.96 rows per token and direction at 2 / 4 / 8 ranks
+ * instead of 2.98 / 4.49 / 5.25.  Every rank provides four peer-mapped buffers:
+ *   xu   [world*n_cap, H] bf16   received rows, slot v = source*n_cap + token (no compaction, so a sender
+ *                                needs nothing from anybody before it stores)
+ *   midx [world*n_cap, k] int32  local expert index of every slot (-1: slot of another rank / no such token)
+ *   mw   [world*n_cap, k] fp32   routing weights
+ *   part [world*n_cap, H] bf16   on the home rank: part[d*n_cap + t] = owner d's contribution to token t
+ * n_cap = the largest token count of any rank.  The owner runs the caller-routed single-GPU chain (rank with
+ * empty slots, plan, permute, gate/up, down) over the world*n_cap virtual tokens of its receive buffer with
+ * its E/world experts and then sums each virtual token's local slots (fp32, ascending expert) into ONE bf16
+ * row stored into the home rank's `part`; the home rank adds the partial rows of the owners a token went to
+ * in ascending owner order.  Same summation order as one GPU, one extra bf16 rounding per owner: inside the
+ * bf16 parity bars of the fp32 oracle, not bit-identical to the single-GPU chain.
+ * Buffers of the owner chain are sized for the worst case (every slot of every token on this rank):
+ * bibo_moe_ep_dedup_rows_cap rows for xp / h / y / row_token, bibo_moe_ep_dedup_plan_words for plan,
+ * [world*n_cap, k] for slot_rank / slot_row, [router_blocks(world*n_cap), E/world] for block_counts.
+ * The stage entry points take explicit pointers, so several ranks can also be played one after another on
+ * ONE device (no kernel waits on another kernel): that is how the single-GPU tests cover this path.      */
+int64_t bibo_moe_ep_dedup_rows_cap(int world, int64_t n_cap, int top_k, int n_experts);
+int64_t bibo_moe_ep_dedup_plan_words(int world, int64_t n_cap, int top_k, int n_experts);
+int64_t bibo_moe_ep_dedup_virtual_tokens(int world, int64_t n_cap);
+/* home rank: rows to the distinct owners of each token, routing records to every rank                     */
+int bibo_moe_ep_dedup_dispatch(const void* x, const int32_t* topk_idx, const float* topk_w,
+                               void* const* xu_peers, void* const* midx_peers, void* const* mw_peers,
+                               int64_t n_tokens, int64_t n_cap, int hidden, int n_experts, int rank,
+                               int world, int top_k, int comm_ctas, void* stream);
+typedef struct {
+  int64_t n_cap;
+  int hidden, inter, n_experts, top_k, rank, world, max_ctas, comm_ctas;
+  const void* xu; const int32_t* midx; const float* mw;                  /* this rank's receive buffers  */
+  const void* gate_up_proj; const void* down_proj; const float* theta;   /* this rank's E/world experts  */
+  int32_t* slot_rank; int32_t* block_counts; int32_t* plan; int32_t* slot_row; int32_t* row_token;
+  void* xp; void* h; void* y;
+  void* const* part_peers;        /* part_peers[s] = rank s's `part` buffer as mapped into this process   */
+} bibo_moe_ep_dedup_owner_args;
+/* owner rank: experts over the received rows, one partial row per (token, this rank) to the home ranks    */
+int bibo_moe_ep_dedup_owner(const bibo_moe_ep_dedup_owner_args* args, void* stream);
+/* home rank: out[t] = sum of the partial rows of token t's owners; `status` = a device word, the kernel
+ * does nothing when it is non-zero (pass the owner plan's status word)                                    */
+int bibo_moe_ep_dedup_final(const void* part, const int32_t* topk_idx, const int32_t* status, int64_t n_tokens,
+                            int64_t n_cap, int hidden, int n_experts, int world, int top_k, int comm_ctas,
+                            void* out, void* stream);
+/* router + the three stages with the two stream barriers in between (epochs epoch_base+1, +2; the caller
+ * advances epoch_base by 2 per call).  marks: NULL or 8 cudaEvent_t recorded on the stream: start, routed,
+ * dispatched, all rows received, experts done, partials stored, all partials received, summed.          */
+typedef struct {
+  bibo_moe_ep_dedup_owner_args owner;
+  int64_t n_tokens;
+  int norm_mode, epoch_base;
+  float scale;
+  const void* x; const void* w_router; const float* bias;
+  int32_t* topk_idx; float* topk_w; int32_t* slot_rank_home; int32_t* block_counts_home;
+  void* const* xu_peers; void* const* midx_peers; void* const* mw_peers; void* const* flags_peers;
+  const void* part_local; void* out;
+  void* const* marks;
+  const bibo_moe_router_trace* trace;
+} bibo_moe_ep_dedup_args;
+int bibo_moe_ep_dedup_forward(const bibo_moe_ep_dedup_args* args, void* stream);
+
 /* ---- RMSNorm in front of the block -------------------------------------------------------------------
  * Replaces BiBoRMSNorm.forward (src/modeling/norm.py:19-24) where BiBoDecoderLayer._ffn_forward
  * applies post_attention_layernorm before the feed-forward block (src/modeling/layers.py:57-67):

@@ -42,3 +42,13 @@ def test_expert_parallel_module_trains_like_the_single_gpu_layer():
     r = _run(world, (1200, 512, 256, 64, 6), port=29553, worker="ep_module_worker.py")
     assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]
     assert "forward identical True" in r.stdout
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs at least 2 GPUs")
+@pytest.mark.parametrize("args", [(1000, 512, 256, 64, 6, "uniform"), (3000, 1024, 512, 64, 6, "zipf")])
+def test_deduplicated_exchange_matches_single_gpu_and_oracle(args):
+    world = 2 if torch.cuda.device_count() < 4 else 4
+    r = _run(world, args, port=29559, worker="ep_dedup_worker.py")
+    assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]
+    assert "routing identical to single GPU: True" in r.stdout
+    print(r.stdout[-400:])

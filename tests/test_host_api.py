@@ -9,7 +9,7 @@ import pytest
 import torch
 
 ROOT = pathlib.Path(__file__).resolve().parents[1]
-REF = pathlib.Path("/root/reference")
+REF = pathlib.Path(os.environ.get("BIBO_REFERENCE", "/root/reference"))   # a checkout of the reference, where present
 
 
 def test_library_exports_every_declared_symbol():
