@@ -38,6 +38,8 @@ WORKLOADS = {
     "c3a": dict(n_tokens=65536, hidden=2048, inter=512, bias="zipf", zipf_alpha=0.07),
     # one MoE layer of benchmark configuration 5 (batch 8 x 4096 tokens, hidden 1024, intermediate 256)
     "c5layer": dict(n_tokens=32768, hidden=1024, inter=256, bias="uniform", zipf_alpha=0.0),
+    # benchmark configuration 5 itself: the reference's 10-layer model with its feed-forward blocks swapped (run_c5)
+    "c5": dict(n_tokens=32768, hidden=1024, inter=256, bias="uniform", zipf_alpha=0.0, model=True),
 }
 N_EXPERTS, TOP_K = 64, 6
 METRIC, UNIT = "moe_layer_fwd_tokens_per_s", "tokens/s"
@@ -281,9 +283,9 @@ def run_ep_check(args, wl, t, runner, rank, world, dev, fwdbwd_step):
     torch.cuda.synchronize()
     status = runner.status()
     pieces = [t["x"][:sample], out[:sample]] + ([dout[:sample], dx[:sample]] if dx is not None else [])
-    mine = torch.cat([p_.contiguous().view(torch.int16).reshape(sample, -1) for p_ in pieces], dim=1).contiguous()
+    mine = torch.cat([p_.contiguous().reshape(sample, -1) for p_ in pieces], dim=1).contiguous()
     idx_mine = _lane_topk_idx(runner.lanes[0])[:sample].contiguous()
-    gathered = torch.empty(world * sample, mine.shape[1], dtype=torch.int16, device=dev)
+    gathered = torch.empty(world * sample, mine.shape[1], dtype=torch.bfloat16, device=dev)
     idx_all = torch.empty(world * sample, TOP_K, dtype=torch.int32, device=dev)
     st_all = torch.empty(world, dtype=torch.int32, device=dev)
     dist.all_gather_into_tensor(gathered, mine)
@@ -291,7 +293,7 @@ def run_ep_check(args, wl, t, runner, rank, world, dev, fwdbwd_step):
     dist.all_gather_into_tensor(st_all, torch.tensor([status], dtype=torch.int32, device=dev))
     if rank != 0:
         return None
-    cols = gathered.view(torch.bfloat16).split(h, dim=1)
+    cols = gathered.split(h, dim=1)
     xs, outs = cols[0].contiguous(), cols[1].contiguous()
     geo = Fn.Geometry(xs.shape[0], h, i, N_EXPERTS, N_EXPERTS, 0, TOP_K, torch.bfloat16)
     ws1 = Fn.MoEWorkspace(geo, dev, keep_logits=True, keep_gate_up=True)
@@ -330,8 +332,11 @@ def nvlink_roofline(args, wl, t, runner, world, rank, ep_phases):
     moves the same number of rows the other way."""
     el = N_EXPERTS // world
     rows = 0
-    dedup = args.ep_exchange == "dedup"
+    dedup = args.ep_exchange in ("dedup", "allgather")
     for lane in runner.lanes:
+        if args.ep_exchange == "allgather":       # every row to every peer
+            rows += lane._n_cap * (world - 1)
+            continue
         n_lane = lane._n_cap if dedup else lane._n
         idx = _lane_topk_idx(lane)[:n_lane].long()
         owner = idx // el
@@ -349,6 +354,8 @@ def nvlink_roofline(args, wl, t, runner, world, rank, ep_phases):
     # time during which any slice was in its dispatch phase / its return phase
     names = ("dispatch", "partial") if dedup else ("dispatch", "combine")
     starts = {"dispatch": "route" if dedup else "gather_plan", "partial": "experts", "combine": "barrier2"}
+    if args.ep_exchange == "allgather":          # rows leave at "start"; all of a slice's rows and records are in at "received"
+        names, starts = ("received", "returned"), {"received": "start", "returned": "experts"}
     out = {}
     for nm in names:
         t0 = min(ph[starts[nm]] for ph in ep_phases if starts[nm] in ph)
@@ -363,6 +370,89 @@ def nvlink_roofline(args, wl, t, runner, world, rank, ep_phases):
                            "spans all token slices, whose phases overlap other slices' GEMMs"}
 
 
+def run_c5(args):
+    """Benchmark configuration 5 on one GPU: the reference's own 10-layer BiBoModel (from oracle/_ref), bf16, a
+    prefill of 8 x 4096 token ids, first unmodified (eager PyTorch everywhere), then with ONLY the feed-forward
+    blocks swapped for the kernels (bibo_b200.install() + install(seam="mlp")).  Prints one JSON line: prefill
+    tokens/s with the kernels, the unmodified model's figure, the share of the prefill spent inside the
+    feed-forward blocks in both runs (CUDA events around every .mlp module), and how far the two last hidden
+    states are apart."""
+    from oracle import make_ref
+    line = {"metric": "c5_prefill_tokens_per_s", "unit": UNIT, "n_gpus": 1, "higher_is_better": True, "dtype": "bf16",
+            "data": "synthetic", "config": {"workload": "c5: 10-layer BiBo prefill, batch 8 x sequence 4096, hidden 1024, "
+                                            "layers 0/9 dense MLP (4096), layers 1-8 MoE (64 experts, top-6, 256)"}}
+    if not make_ref.available():
+        line["unavailable"] = "oracle/_ref is absent on this machine (python oracle/make_ref.py needs a checkout of the reference)"
+        print(json.dumps(line))
+        return
+    make_ref.activate()
+    import bibo_b200
+    from src.configuration_bibo import BiBoConfig
+    from src.modeling.models import BiBoModel
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(0)
+    cfg = BiBoConfig(vocab_size=32000, hidden_size=1024, intermediate_size=4096, num_hidden_layers=10,
+                     num_attention_heads=4, num_key_value_heads=2, moe_intermediate_size=256, num_routed_experts=N_EXPERTS,
+                     num_experts_per_tok=TOP_K, special_expert_pairs=0, hybrid_layer_pattern=[0, 1, 1, 0, 1, 1, 0, 1, 1, 0],
+                     sliding_window=128, tie_word_embeddings=True, mlp_only_layers=[0, 9], use_cache=False)
+    torch.manual_seed(0)
+    model = BiBoModel(cfg).to(torch.bfloat16).to(dev).eval()
+    batch, seq = 8, 4096
+    ids = torch.randint(0, 32000, (batch, seq), generator=torch.Generator().manual_seed(1)).to(dev)
+
+    def timed(steps):
+        spans = []
+        hooks = []
+        for layer in model.layers:
+            def pre(m, a, spans=spans):
+                e = torch.cuda.Event(enable_timing=True); e.record(); spans.append([e, None])
+            def post(m, a, o, spans=spans):
+                e = torch.cuda.Event(enable_timing=True); e.record(); spans[-1][1] = e
+            hooks += [layer.mlp.register_forward_pre_hook(pre), layer.mlp.register_forward_hook(post)]
+        with torch.no_grad():
+            out = model(input_ids=ids, use_cache=False).last_hidden_state      # warm-up (and the compared output)
+            spans.clear()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            torch.cuda.synchronize()
+            e0.record()
+            for _ in range(steps):
+                model(input_ids=ids, use_cache=False)
+            e1.record()
+            torch.cuda.synchronize()
+        for h in hooks:
+            h.remove()
+        total = e0.elapsed_time(e1) / steps
+        ffn = sum(a.elapsed_time(b) for a, b in spans) / steps
+        return total, ffn, out
+
+    steps = max(1, min(args.steps, 5))
+    ref_ms, ref_ffn, ref_out = timed(steps)
+    launches0 = 0
+    from bibo_b200 import functional as Fn
+    bibo_b200.install()
+    bibo_b200.install(seam="mlp")
+    try:
+        launches0 = Fn.launch_count()
+        ms, ffn, out = timed(steps)
+        launches = (Fn.launch_count() - launches0) // (steps + 1)
+    finally:
+        bibo_b200.uninstall()
+    g, r = out.reshape(-1, 1024).float(), ref_out.reshape(-1, 1024).float()
+    per_tok = (g - r).norm(dim=-1) / r.norm(dim=-1).clamp_min(1e-30)
+    line.update({
+        "value": batch * seq / (ms * 1e-3), "steps": steps, "warmup": 1, "ms_per_step": round(ms, 3),
+        "feed_forward_ms": round(ffn, 3), "feed_forward_share": round(ffn / ms, 4),
+        "unmodified_reference": {"ms_per_step": round(ref_ms, 3), "feed_forward_ms": round(ref_ffn, 3),
+                                 "feed_forward_share": round(ref_ffn / ref_ms, 4),
+                                 "value": batch * seq / (ref_ms * 1e-3)},
+        "prefill_speedup": round(ref_ms / ms, 3), "feed_forward_speedup": round(ref_ffn / ffn, 2),
+        "gpu_launches": int(launches),
+        "last_hidden_state_vs_unmodified": {"median_token_rel": float(per_tok.median()),
+                                            "tokens_above_1e-1": int((per_tok > 1e-1).sum()), "tokens": int(per_tok.numel())},
+        "note": "attention, norms and embedding stay the reference's eager PyTorch in both runs; eval mode"})
+    print(json.dumps(line))
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -374,10 +464,15 @@ def main():
     ap.add_argument("--no-gpu-reference", action="store_true",
                     help="skip timing the reference's eager layer on this GPU (needs oracle/_ref)")
     ap.add_argument("--ep-chunks", type=int, default=None,
-                    help="token slices pipelined on separate streams (N>1; default 2 for the dedup exchange, else 1)")
-    ap.add_argument("--ep-exchange", default="dedup", choices=["dedup", "copy", "kernel"],
-                    help="N>1: dedup = one row per (token, destination rank) each way (default); kernel = one row per "
-                         "slot through the dispatch/combine kernels; copy = per-slot rows by peer copies on the copy engines")
+                    help="token slices pipelined on separate streams (N>1; default 4 for the dedup exchange, else 1)")
+    ap.add_argument("--ep-exchange", default="auto", choices=["auto", "allgather", "dedup", "copy", "kernel"],
+                    help="N>1: allgather = every rank's rows to every peer and partial rows back on the copy engines, "
+                         "token slices pipelined (default at 2 and 4 GPUs); dedup = one row per (token, destination rank) "
+                         "each way through exchange kernels (default at 8 GPUs); kernel = one row per slot through the "
+                         "dispatch/combine kernels; copy = per-slot rows by peer copies")
+    ap.add_argument("--ep-lockstep", action="store_true",
+                    help="N>1, dedup: one stream per token slice (all slices in the same phase at once) instead of "
+                         "one stream per resource (NVLink work / tensor-core work)")
     ap.add_argument("--gemm-ctas", type=int, default=None, help="N>1: cap of the grouped-GEMM grids (0 = none)")
     ap.add_argument("--comm-ctas", type=int, default=None, help="N>1: cap of the exchange kernels' grids (0 = none)")
     ap.add_argument("--repeats", type=int, default=9, help="extra timed regions of --steps steps (median / min / max)")
@@ -387,7 +482,7 @@ def main():
     ap.add_argument("--no-numa-bind", action="store_true",
                     help="N>1: do not pin each rank to the CPUs local to its GPU (pinned host buffers then land anywhere)")
     ap.add_argument("--e2e-chunks", type=int, default=4, help="token slices of the host-buffer (e2e) forward (N>1)")
-    ap.add_argument("--comm-sms", type=int, default=20, help="SMs left to the exchange kernels (N>1)")
+    ap.add_argument("--comm-sms", type=int, default=16, help="SMs set aside for the exchange kernels (N>1, several slices)")
     ap.add_argument("--gather-in-gemm", action="store_true",
                     help="1 GPU: the gate/up kernel gathers its own rows instead of a separate permute kernel (A/B)")
     ap.add_argument("--mode", default="fwd", choices=["fwd", "fwdbwd", "ffn", "ffn_separate"],
@@ -396,14 +491,20 @@ def main():
                          "the permute's loads; ffn_separate = the same with the norm as a kernel of its own (1 GPU)")
     args = ap.parse_args()
     wl = WORKLOADS[args.workload]
-    if args.mode == "fwdbwd" and args.ep_exchange == "dedup":
-        args.ep_exchange = "kernel"            # the de-duplicated exchange is forward-only
-    if args.ep_chunks is None:
-        args.ep_chunks = 2 if args.ep_exchange == "dedup" else 1
     rank, world = int(os.environ.get("RANK", 0)), int(os.environ.get("WORLD_SIZE", 1))
+    if args.ep_exchange == "auto":
+        args.ep_exchange = "allgather" if world <= 4 else "dedup"
+    if args.mode == "fwdbwd" and args.ep_exchange in ("dedup", "allgather"):
+        args.ep_exchange = "kernel"            # the de-duplicated exchanges are forward-only
+    if args.ep_chunks is None:
+        args.ep_chunks = 4 if args.ep_exchange == "allgather" else 1
     local = int(os.environ.get("LOCAL_RANK", 0))
     if args.impl == "reference":
         return run_reference(args, wl, rank, world)
+    if wl.get("model"):
+        if rank == 0:
+            run_c5(args)
+        return
     if args.warmup < 3:
         args.warmup = 3
 
@@ -426,8 +527,14 @@ def main():
         ep_kw = dict(comm_sms=args.comm_sms, dedup=dedup, gemm_ctas=args.gemm_ctas, comm_ctas=args.comm_ctas)
         if not dedup:
             ep_kw.update(dma=dma, copy_streams=bool(args.copy_streams))
-        runner = ep.PipelinedExpertParallelMoE(t, TOP_K, dist.group.WORLD, n_tokens=wl["n_tokens"], chunks=args.ep_chunks,
-                                               **ep_kw)
+        make_runner = lambda chunks: (
+            ep.PipelinedAllGatherMoE(t, TOP_K, dist.group.WORLD, n_tokens=wl["n_tokens"], chunks=chunks)
+            if args.ep_exchange == "allgather" else
+            ep.PipelinedDedupMoE(t, TOP_K, dist.group.WORLD, n_tokens=wl["n_tokens"], chunks=chunks,
+                                 comm_sms=args.comm_sms, gemm_ctas=args.gemm_ctas, comm_ctas=args.comm_ctas)
+            if dedup and not args.ep_lockstep else
+            ep.PipelinedExpertParallelMoE(t, TOP_K, dist.group.WORLD, n_tokens=wl["n_tokens"], chunks=chunks, **ep_kw))
+        runner = make_runner(args.ep_chunks)
         step = lambda: runner.forward(t["x"])
         ws = None
         if args.mode == "fwdbwd":
@@ -536,8 +643,7 @@ def main():
     x_dev, out_dev = torch.empty_like(t["x"]), torch.empty_like(t["x"])
     if world > 1:
         # token slices on separate streams: the copies of one slice run under the kernels of another
-        e2e_runner = runner if args.e2e_chunks == args.ep_chunks else ep.PipelinedExpertParallelMoE(
-            t, TOP_K, dist.group.WORLD, n_tokens=wl["n_tokens"], chunks=args.e2e_chunks, **ep_kw)
+        e2e_runner = runner if args.e2e_chunks == args.ep_chunks else make_runner(args.e2e_chunks)
         e2e_step = lambda: e2e_runner.forward_host(x_host, out_host, x_dev, out_dev)
     else:
         if ws is not None:

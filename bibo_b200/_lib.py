@@ -156,10 +156,15 @@ SIGNATURES = {
     "bibo_moe_ep_dedup_dispatch": (_i32, [_vp, _vp, _vp, _vp, _vp, _vp, _i64, _i64, _i32, _i32, _i32, _i32, _i32, _i32,
                                           _vp]),
     "bibo_moe_ep_dedup_owner": (_i32, [C.POINTER(EpDedupOwner), _vp]),
+    "bibo_moe_ep_dedup_experts": (_i32, [C.POINTER(EpDedupOwner), _vp]),
+    "bibo_moe_ep_dedup_partial": (_i32, [C.POINTER(EpDedupOwner), _vp]),
     "bibo_moe_ep_dedup_final": (_i32, [_vp, _vp, _vp, _i64, _i64, _i32, _i32, _i32, _i32, _i32, _vp, _vp]),
+    "bibo_moe_ep_localize": (_i32, [_vp, _i64, _i32, _i32, _i32, _i32, _vp, _vp]),
+    "bibo_moe_ep_copy_to_peers": (_i32, [_vp, _i64, _vp, _i64, _i64, _i32, _i32, _i32, _vp]),
     "bibo_moe_ep_dedup_forward": (_i32, [C.POINTER(EpDedup), _vp]),
     "bibo_moe_route_noalloc": (_i32, [_vp, _vp, _vp, _i64, _i32, _i32, _i32, _i32, _f32, _i32, _vp, _vp, _vp, _vp]),
     "bibo_moe_route_noalloc_max_tokens": (_i64, []),
+    "bibo_moe_route_noalloc_status": (_i32, [_vp, _vp]),
     "bibo_moe_debug_plan_header": (_i32, [_vp, _vp, _vp]),
     "bibo_moe_launch_count": (_i64, []),
 }

@@ -34,7 +34,16 @@
 
 namespace bibo {
 
-constexpr int DW = 8;   // warps per block of the exchange kernels
+constexpr int DW = 8;        // warps per block of the exchange kernels when they have the GPU to themselves
+constexpr int DW_TAGGED = 16; // warps per block of a capped grid
+// A capped exchange grid (comm_ctas > 0: token slices pipelined against another slice's grouped GEMMs) runs
+// blocks of 16 warps that ask for this much dynamic shared memory and never touch it.  Two such blocks do
+// not fit on one SM and none fits beside a GEMM CTA (which takes all but 1 KB of the shared memory), so the
+// hardware places every exchange block on an SM of its own, whichever kernel arrives first: comm_ctas IS the
+// number of SMs the exchange uses, and the grouped GEMMs (capped by the caller to the rest) keep theirs.
+// Without the tag the block scheduler spreads small blocks over as many SMs as it can, each of which then
+// lacks the shared memory for a GEMM CTA: the GEMMs ran 1.5-1.75x slower while an exchange kernel was active.
+constexpr int COMM_TAG_BYTES = 120 * 1024;
 
 __device__ __forceinline__ void fma_bf16x8_d(const uint4& v, float w, float* acc) {
   const uint32_t u[4] = {v.x, v.y, v.z, v.w};
@@ -53,14 +62,14 @@ __device__ __forceinline__ uint4 pack_bf16x8(const float* a) {
 }
 
 // Warp per token slot t in [0, n_cap).  t >= n_tokens: only "no such token" records are written.
-__global__ void __launch_bounds__(DW * 32)
+__global__ void __launch_bounds__(DW_TAGGED * 32, 1)
 ep_dedup_dispatch_kernel(const uint8_t* __restrict__ x, const int32_t* __restrict__ topk_idx,
                          const float* __restrict__ topk_w, PeerPtrs xu, PeerPtrs midx, PeerPtrs mw,
                          int64_t n_tokens, int64_t n_cap, int row_bytes, int n_experts, int rank, int world,
                          int top_k) {
   const int lane = threadIdx.x & 31;
   const int el = n_experts / world;
-  for (int64_t t = (int64_t)blockIdx.x * DW + (threadIdx.x >> 5); t < n_cap; t += (int64_t)gridDim.x * DW) {
+  for (int64_t t = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5); t < n_cap; t += (int64_t)gridDim.x * (blockDim.x >> 5)) {
     const int64_t v = (int64_t)rank * n_cap + t;
     int e = -1;
     float w = 0.f;
@@ -101,16 +110,32 @@ ep_dedup_dispatch_kernel(const uint8_t* __restrict__ x, const int32_t* __restric
   }
 }
 
+// Routing records that arrived as plain copies of every rank's top-k table (GLOBAL expert indices, -1 for
+// "no such token"): keep the slots of this rank's experts, as local indices; everything else becomes -1.
+__global__ void __launch_bounds__(256)
+ep_localize_kernel(const int32_t* __restrict__ raw, int64_t n_slots, int lo, int el, int32_t* __restrict__ midx) {
+  const int64_t i = (int64_t)blockIdx.x * 256 + threadIdx.x;
+  if (i >= n_slots) return;
+  const int e = raw[i] - lo;
+  midx[i] = (e >= 0 && e < el) ? e : -1;
+}
+
 // Warp per virtual token v = s*n_cap + t of this owner.  Its local slots form one run of consecutive j
 // (the k experts of a token are ascending and this owner's experts are contiguous).
 template <int K>
-__global__ void __launch_bounds__(DW * 32, 3)
+__global__ void __launch_bounds__(DW_TAGGED * 32, 1)
 ep_dedup_partial_kernel(const __nv_bfloat16* __restrict__ y, const int32_t* __restrict__ slot_row,
                         const float* __restrict__ mw, PeerPtrs part, const int32_t* __restrict__ plan,
                         int64_t n_virtual, int64_t n_cap, int hidden, int rank) {
   const int lane = threadIdx.x & 31;
   if (plan[PLAN_STATUS] != 0) return;
-  for (int64_t v = (int64_t)blockIdx.x * DW + (threadIdx.x >> 5); v < n_virtual; v += (int64_t)gridDim.x * DW) {
+  const int world = (int)(n_virtual / n_cap);
+  for (int64_t i = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5); i < n_virtual; i += (int64_t)gridDim.x * (blockDim.x >> 5)) {
+    // home ranks are visited in the order rank+1, rank+2, ..., rank: at any moment every owner stores to a
+    // DIFFERENT home rank (all owners walking the blocks in the same order would aim at one receiver at a time)
+    const int64_t blk = i / n_cap, t = i - blk * n_cap;
+    const int64_t s = (rank + 1 + blk) % world;
+    const int64_t v = s * n_cap + t;
     int row = -1;
     float w = 0.f;
     if (lane < K) { row = slot_row[v * K + lane]; w = mw[v * K + lane]; }
@@ -125,9 +150,32 @@ ep_dedup_partial_kernel(const __nv_bfloat16* __restrict__ y, const int32_t* __re
       ws[i] = __shfl_sync(0xffffffffu, w, min(j0 + i, 31));
       src[i] = reinterpret_cast<const uint4*>(y + (int64_t)(i < cnt ? r : 0) * hidden);
     }
-    const int64_t s = v / n_cap, t = v - s * n_cap;
     uint4* dst = reinterpret_cast<uint4*>(static_cast<__nv_bfloat16*>(part.p[s]) + ((int64_t)rank * n_cap + t) * hidden);
     const int chunks = hidden >> 3;
+    if (cnt <= 2) {
+      // the common case (a token rarely has more than two experts on one rank): four chunks per lane in flight
+      for (int c0 = lane; c0 < chunks; c0 += 128) {
+        uint4 va[4], vb[4];
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+          if (c0 + u * 32 < chunks) {
+            va[u] = __ldcs(src[0] + c0 + u * 32);
+            if (cnt == 2) vb[u] = __ldcs(src[1] + c0 + u * 32);
+          }
+        }
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+          if (c0 + u * 32 >= chunks) continue;
+          float a[8];
+#pragma unroll
+          for (int q = 0; q < 8; ++q) a[q] = 0.f;
+          fma_bf16x8_d(va[u], ws[0], a);
+          if (cnt == 2) fma_bf16x8_d(vb[u], ws[1], a);
+          dst[c0 + u * 32] = pack_bf16x8(a);
+        }
+      }
+      continue;
+    }
     for (int c0 = lane; c0 < chunks; c0 += 64) {       // two chunks per lane in flight, times the local slots
       uint4 val[2][K];
 #pragma unroll
@@ -151,14 +199,14 @@ ep_dedup_partial_kernel(const __nv_bfloat16* __restrict__ y, const int32_t* __re
 }
 
 // Warp per home token: adds the partial rows of the owners the token was sent to, ascending owner.
-__global__ void __launch_bounds__(DW * 32, 2)
+__global__ void __launch_bounds__(DW_TAGGED * 32, 1)
 ep_dedup_final_kernel(const __nv_bfloat16* __restrict__ part, const int32_t* __restrict__ topk_idx,
                       const int32_t* __restrict__ status, int64_t n_tokens, int64_t n_cap, int hidden, int n_experts,
                       int world, int top_k, __nv_bfloat16* __restrict__ out) {
   const int lane = threadIdx.x & 31;
   if (status[0] != 0) return;
   const int el = n_experts / world;
-  for (int64_t t = (int64_t)blockIdx.x * DW + (threadIdx.x >> 5); t < n_tokens; t += (int64_t)gridDim.x * DW) {
+  for (int64_t t = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5); t < n_tokens; t += (int64_t)gridDim.x * (blockDim.x >> 5)) {
     int owner = -1;
     if (lane < top_k) {
       const int e = topk_idx[t * top_k + lane];
@@ -172,25 +220,19 @@ ep_dedup_final_kernel(const __nv_bfloat16* __restrict__ part, const int32_t* __r
     }
     uint4* dst = reinterpret_cast<uint4*>(out + t * hidden);
     const int chunks = hidden >> 3;
-    for (int c0 = lane; c0 < chunks; c0 += 64) {
-      uint4 val[2][EP_MAX_RANKS];
+    for (int c = lane; c < chunks; c += 32) {
+      uint4 val[EP_MAX_RANKS];
 #pragma unroll
-      for (int u = 0; u < 2; ++u)
+      for (int d = 0; d < EP_MAX_RANKS; ++d)
+        if ((hit >> d) & 1u)
+          val[d] = __ldcs(reinterpret_cast<const uint4*>(part + ((int64_t)d * n_cap + t) * hidden) + c);
+      float a[8];
 #pragma unroll
-        for (int d = 0; d < EP_MAX_RANKS; ++d)
-          if (((hit >> d) & 1u) && c0 + u * 32 < chunks)
-            val[u][d] = __ldcs(reinterpret_cast<const uint4*>(part + ((int64_t)d * n_cap + t) * hidden) + c0 + u * 32);
+      for (int q = 0; q < 8; ++q) a[q] = 0.f;
 #pragma unroll
-      for (int u = 0; u < 2; ++u) {
-        if (c0 + u * 32 >= chunks) continue;
-        float a[8];
-#pragma unroll
-        for (int q = 0; q < 8; ++q) a[q] = 0.f;
-#pragma unroll
-        for (int d = 0; d < EP_MAX_RANKS; ++d)
-          if ((hit >> d) & 1u) fma_bf16x8_d(val[u][d], 1.0f, a);
-        dst[c0 + u * 32] = pack_bf16x8(a);
-      }
+      for (int d = 0; d < EP_MAX_RANKS; ++d)
+        if ((hit >> d) & 1u) fma_bf16x8_d(val[d], 1.0f, a);
+      dst[c] = pack_bf16x8(a);
     }
   }
 }
@@ -213,9 +255,19 @@ static void prefer_max_smem_d(Kern kern) {
   cudaFuncSetAttribute(kern, cudaFuncAttributePreferredSharedMemoryCarveout, (int)cudaSharedmemCarveoutMaxShared);
 }
 // same carve-out as the grouped GEMMs, so these kernels can share SMs with another token slice's GEMMs
+template <typename Kern>
+static void allow_tag_smem(Kern kern) {
+  cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, COMM_TAG_BYTES);
+}
 static void dedup_set_carveouts() {
   static DeviceOnce once;
   once.get([](int*) {
+    allow_tag_smem(ep_dedup_dispatch_kernel);
+    allow_tag_smem(ep_dedup_final_kernel);
+    allow_tag_smem(ep_dedup_partial_kernel<1>); allow_tag_smem(ep_dedup_partial_kernel<2>);
+    allow_tag_smem(ep_dedup_partial_kernel<3>); allow_tag_smem(ep_dedup_partial_kernel<4>);
+    allow_tag_smem(ep_dedup_partial_kernel<5>); allow_tag_smem(ep_dedup_partial_kernel<6>);
+    allow_tag_smem(ep_dedup_partial_kernel<7>); allow_tag_smem(ep_dedup_partial_kernel<8>);
     prefer_max_smem_d(ep_dedup_dispatch_kernel);
     prefer_max_smem_d(ep_dedup_final_kernel);
     prefer_max_smem_d(ep_dedup_partial_kernel<1>); prefer_max_smem_d(ep_dedup_partial_kernel<2>);
@@ -248,10 +300,11 @@ static int fill_peers(const char* who, void* const* in, int world, PeerPtrs* out
 }
 
 static unsigned exchange_grid(int64_t warps, int comm_ctas) {
-  int64_t blocks = (warps + DW - 1) / DW;
-  if (comm_ctas > 0) blocks = std::min<int64_t>(blocks, comm_ctas);
-  return (unsigned)std::max<int64_t>(1, blocks);
+  if (comm_ctas > 0) return (unsigned)std::max<int64_t>(1, std::min<int64_t>((warps + DW_TAGGED - 1) / DW_TAGGED, comm_ctas));
+  return (unsigned)std::max<int64_t>(1, (warps + DW - 1) / DW);
 }
+static unsigned exchange_block(int comm_ctas) { return (comm_ctas > 0 ? DW_TAGGED : DW) * 32; }
+static size_t exchange_smem(int comm_ctas) { return comm_ctas > 0 ? COMM_TAG_BYTES : 0; }
 
 extern "C" int64_t bibo_moe_ep_dedup_virtual_tokens(int world, int64_t n_cap) { return (int64_t)world * n_cap; }
 
@@ -270,7 +323,8 @@ extern "C" int bibo_moe_ep_dedup_dispatch(const void* x, const int32_t* topk_idx
   if ((rc = fill_peers("ep_dedup_dispatch", midx_peers, world, &mi))) return rc;
   if ((rc = fill_peers("ep_dedup_dispatch", mw_peers, world, &mw))) return rc;
   dedup_set_carveouts();
-  ep_dedup_dispatch_kernel<<<exchange_grid(n_cap, comm_ctas), DW * 32, 0, static_cast<cudaStream_t>(stream)>>>(
+  ep_dedup_dispatch_kernel<<<exchange_grid(n_cap, comm_ctas), exchange_block(comm_ctas), exchange_smem(comm_ctas),
+                             static_cast<cudaStream_t>(stream)>>>(
       static_cast<const uint8_t*>(x), topk_idx, topk_w, xu, mi, mw, n_tokens, n_cap, hidden * 2, n_experts, rank, world,
       top_k);
   BIBO_CHECK_LAUNCH("ep_dedup_dispatch_kernel");
@@ -322,8 +376,8 @@ static int dedup_owner_partial(const bibo_moe_ep_dedup_owner_args* a, void* stre
   const unsigned grid = exchange_grid(nv, a->comm_ctas);
 #define BIBO_DPART(KK)                                                                                             \
   case KK:                                                                                                         \
-    ep_dedup_partial_kernel<KK><<<grid, DW * 32, 0, st>>>(static_cast<const __nv_bfloat16*>(a->y), a->slot_row,    \
-                                                          a->mw, part, a->plan, nv, a->n_cap, a->hidden, a->rank); \
+    ep_dedup_partial_kernel<KK><<<grid, exchange_block(a->comm_ctas), exchange_smem(a->comm_ctas), st>>>(                              \
+        static_cast<const __nv_bfloat16*>(a->y), a->slot_row, a->mw, part, a->plan, nv, a->n_cap, a->hidden, a->rank); \
     break;
   switch (a->top_k) {
     BIBO_DPART(1) BIBO_DPART(2) BIBO_DPART(3) BIBO_DPART(4) BIBO_DPART(5) BIBO_DPART(6) BIBO_DPART(7) BIBO_DPART(8)
@@ -339,6 +393,20 @@ extern "C" int bibo_moe_ep_dedup_owner(const bibo_moe_ep_dedup_owner_args* a, vo
   const int rc = dedup_owner_experts(a, stream);
   return rc ? rc : dedup_owner_partial(a, stream);
 }
+// the two halves on their own, for a caller that keeps the tensor-core work of one token slice and the
+// NVLink work of another on different streams
+extern "C" int bibo_moe_ep_dedup_experts(const bibo_moe_ep_dedup_owner_args* a, void* stream) {
+  if (!a) return fail(BIBO_ERR_ARG, "ep_dedup_experts: null args");
+  return dedup_owner_experts(a, stream);
+}
+extern "C" int bibo_moe_ep_dedup_partial(const bibo_moe_ep_dedup_owner_args* a, void* stream) {
+  if (!a) return fail(BIBO_ERR_ARG, "ep_dedup_partial: null args");
+  const int rc = dedup_check("ep_dedup_partial", a->world, a->rank, a->n_experts, a->top_k, a->hidden, a->n_cap);
+  if (rc) return rc;
+  if (!a->y || !a->slot_row || !a->mw || !a->plan) return fail(BIBO_ERR_ARG, "ep_dedup_partial: null pointer");
+  dedup_set_carveouts();
+  return dedup_owner_partial(a, stream);
+}
 
 extern "C" int bibo_moe_ep_dedup_final(const void* part, const int32_t* topk_idx, const int32_t* status,
                                        int64_t n_tokens, int64_t n_cap, int hidden, int n_experts, int world,
@@ -349,10 +417,49 @@ extern "C" int bibo_moe_ep_dedup_final(const void* part, const int32_t* topk_idx
   if (!part || !topk_idx || !status || !out || !aligned16(part) || !aligned16(out))
     return fail(BIBO_ERR_ARG, "ep_dedup_final: null or unaligned pointer");
   dedup_set_carveouts();
-  ep_dedup_final_kernel<<<exchange_grid(n_tokens, comm_ctas), DW * 32, 0, static_cast<cudaStream_t>(stream)>>>(
+  ep_dedup_final_kernel<<<exchange_grid(n_tokens, comm_ctas), exchange_block(comm_ctas), exchange_smem(comm_ctas),
+                          static_cast<cudaStream_t>(stream)>>>(
       static_cast<const __nv_bfloat16*>(part), topk_idx, status, n_tokens, n_cap, hidden, n_experts, world, top_k,
       static_cast<__nv_bfloat16*>(out));
   BIBO_CHECK_LAUNCH("ep_dedup_final_kernel");
+  return BIBO_OK;
+}
+
+extern "C" int bibo_moe_ep_localize(const int32_t* raw_idx, int64_t n_virtual, int top_k, int n_experts, int rank,
+                                    int world, int32_t* midx, void* stream) {
+  if (n_virtual <= 0) return BIBO_OK;
+  if (!raw_idx || !midx) return fail(BIBO_ERR_ARG, "ep_localize: null pointer");
+  if (world < 1 || rank < 0 || rank >= world || n_experts % world != 0 || top_k < 1 || top_k > BIBO_MAX_TOP_K)
+    return fail(BIBO_ERR_ARG, "ep_localize: rank %d of %d, %d experts, top_k %d", rank, world, n_experts, top_k);
+  const int el = n_experts / world;
+  const int64_t slots = n_virtual * top_k;
+  ep_localize_kernel<<<(unsigned)((slots + 255) / 256), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      raw_idx, slots, rank * el, el, midx);
+  BIBO_CHECK_LAUNCH("ep_localize_kernel");
+  return BIBO_OK;
+}
+
+// One block of bytes from this rank to the same place in every rank's buffer (an all-gather leg), or from a
+// per-destination place of a local buffer to this rank's place in every rank's buffer (an all-to-all leg), as
+// asynchronous copies on the copy engines: dst_peers[d] + dst_offset  <-  src + d * src_stride, `bytes` each,
+// for d = rank+1, rank+2, ... (every rank starts with another peer), the own rank last and only with
+// include_self.  No kernel, no SM: the copies run beside whatever the SMs are doing.
+extern "C" int bibo_moe_ep_copy_to_peers(void* const* dst_peers, int64_t dst_offset, const void* src,
+                                         int64_t src_stride, int64_t bytes, int rank, int world, int include_self,
+                                         void* stream) {
+  if (!dst_peers || !src) return fail(BIBO_ERR_ARG, "ep_copy_to_peers: null pointer");
+  if (world < 1 || world > EP_MAX_RANKS || rank < 0 || rank >= world || bytes < 0 || dst_offset < 0)
+    return fail(BIBO_ERR_ARG, "ep_copy_to_peers: rank %d of %d, %lld bytes", rank, world, (long long)bytes);
+  if (bytes == 0) return BIBO_OK;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  for (int i = 1; i <= world; ++i) {
+    const int d = (rank + i) % world;
+    if (d == rank && !include_self) continue;
+    if (!dst_peers[d]) return fail(BIBO_ERR_ARG, "ep_copy_to_peers: peer %d has no buffer", d);
+    BIBO_CUDA(cudaMemcpyAsync(static_cast<char*>(dst_peers[d]) + dst_offset,
+                              static_cast<const char*>(src) + (int64_t)d * src_stride, (size_t)bytes,
+                              cudaMemcpyDefault, st));
+  }
   return BIBO_OK;
 }
 

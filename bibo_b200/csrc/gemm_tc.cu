@@ -964,6 +964,12 @@ int gemm1_tc_launch(const void* xp, const void* gate_up_proj, const float* theta
       return gemm1_pair_launch_t<1, 5, false, true>(tmA, tmB, tmH, theta, pv, hidden / BK, inter, gate_up_out,
                                                     rnorm_out, st, ga);
     }
+    // A capped grid shares the GPU with another stream's kernels, and nothing guarantees that every CTA of it
+    // is resident at once: the variant whose column-block pairs exchange through distributed shared memory
+    // inside ONE 4-CTA cluster (co-scheduled by the hardware) waits on nobody outside its cluster.
+    if (inter == 512 && pv.max_ctas > 0)
+      return gemm1_pair_launch_t<2, 5, false, false>(tmA, tmB, tmH, theta, pv, hidden / BK, inter, gate_up_out,
+                                                     rnorm_out, st);
     if (inter == 512)
       return gemm1_pair_launch_t<2, 5, true, false>(tmA, tmB, tmH, theta, pv, hidden / BK, inter, gate_up_out,
                                                     rnorm_out, st);

@@ -68,7 +68,11 @@ using namespace bibo;
 extern "C" int bibo_moe_route_noalloc(const void* x, const void* w_router, const float* bias, int64_t n_tokens,
                                       int hidden, int n_experts, int top_k, int norm_mode, float scale, int dtype,
                                       int32_t* topk_idx, float* topk_w, int32_t* counts, void* stream) {
-  if (n_tokens <= 0) return BIBO_OK;
+  if (n_tokens <= 0) {   // nothing to route: the histogram is all zeros (no scratch, no kernel)
+    if (counts && n_experts > 0 && n_experts <= BIBO_MAX_EXPERTS)
+      BIBO_CUDA(cudaMemsetAsync(counts, 0, (size_t)n_experts * sizeof(int32_t), static_cast<cudaStream_t>(stream)));
+    return BIBO_OK;
+  }
   if (!x || !w_router || !bias || !topk_idx || !topk_w || !counts)
     return fail(BIBO_ERR_ARG, "route_noalloc: null pointer");
   if (n_tokens > NA_TOKENS)
@@ -102,3 +106,17 @@ extern "C" int bibo_moe_route_noalloc(const void* x, const void* w_router, const
 }
 
 extern "C" int64_t bibo_moe_route_noalloc_max_tokens(void) { return NA_TOKENS; }
+
+// The status word of the last bibo_moe_route_noalloc call on the current device lives inside the shared
+// array; this copies it into a caller-owned device word (stream-ordered, no allocation, no synchronisation).
+// 0 = fine; 1 = histogram total too large; 102 = a bounded wait of the router kernel gave up.
+extern "C" int bibo_moe_route_noalloc_status(int32_t* status_out, void* stream) {
+  if (!status_out) return fail(BIBO_ERR_ARG, "route_noalloc_status: null pointer");
+  unsigned char* base = nullptr;
+  int rc = scratch_for_current_device(&base);
+  if (rc) return rc;
+  const int32_t* plan = reinterpret_cast<const int32_t*>(base + NA_RANK_BYTES + NA_BLOCKS_BYTES);
+  BIBO_CUDA(cudaMemcpyAsync(status_out, plan + PLAN_STATUS, sizeof(int32_t), cudaMemcpyDeviceToDevice,
+                            static_cast<cudaStream_t>(stream)));
+  return BIBO_OK;
+}

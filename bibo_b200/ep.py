@@ -58,13 +58,13 @@ def ep_layout(cnt_all: torch.Tensor, rank: int, world: int, source_major: bool =
     return dict(send_base=send_base, recv_off=recv_off, recv_cnt=recv_cnt, rows=rows)
 
 
-def recv_rows_cap(n_tokens: int, top_k: int, n_experts: int, world: int, capacity_factor: float) -> int:
+def recv_rows_cap(n_tokens: int, top_k: int, n_experts: int, world: int, capacity_factor: Optional[float]) -> int:
     """Rows provisioned per rank for received tokens: capacity_factor x the balanced share, plus the
     worst-case padding of the E groups, rounded to the tile size (never more than every row of every
-    rank)."""
+    rank).  ``None`` = the worst case (every slot of every rank lands here): dropless, like the reference."""
     balanced = n_tokens * top_k                      # world * N * k / world
     worst = world * n_tokens * top_k
-    rows = min(int(balanced * capacity_factor), worst) + n_experts * (TILE_M - 1)
+    rows = (worst if capacity_factor is None else min(int(balanced * capacity_factor), worst)) + n_experts * (TILE_M - 1)
     return (rows + TILE_M - 1) // TILE_M * TILE_M
 
 
@@ -88,8 +88,12 @@ class ExpertParallelMoE:
     """
 
     def __init__(self, weights, top_k: int, group=None, n_tokens: Optional[int] = None, norm_mode="sum",
-                 scale: float = 1.0, capacity_factor: float = 2.0, max_ctas: int = 0, comm_ctas: int = 0,
+                 scale: float = 1.0, capacity_factor: Optional[float] = None, max_ctas: int = 0, comm_ctas: int = 0,
                  dma: bool = False, copy_streams: bool = False):
+        """``capacity_factor``: receive buffers hold this multiple of the balanced load; ``None`` (default)
+        provisions the worst case, so no routing can overflow them (the reference is dropless).  With a cap, an
+        overflow is detected on the device by every rank (status 4), nothing is written, and the next call on
+        this object raises."""
         os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")   # plain peer loads/stores only
         self.group = group if group is not None else dist.group.WORLD
         self.rank, self.world = dist.get_rank(self.group), dist.get_world_size(self.group)
@@ -155,6 +159,7 @@ class ExpertParallelMoE:
             self._aux_event_ptrs = (C.c_void_p * 18)(*[ev.cuda_event for ev in self._aux_events])
         self.flags = _Symmetric((64,), torch.int32, dev, self.group)
         self.flags.tensor.zero_()
+        self.header_host = torch.zeros(8, dtype=torch.int32).pin_memory()   # both plans' headers, see raise_if_failed
         torch.cuda.synchronize(dev)
         dist.barrier(self.group)            # every rank's flags are zero before the first device barrier
         o = int(lib.bibo_moe_plan_off_counts())
@@ -179,8 +184,13 @@ class ExpertParallelMoE:
         if out is None:
             out = torch.empty_like(x)
         k, e, st = self.top_k, self.n_experts, torch.cuda.current_stream(self.device).cuda_stream
+        if phase != 2:
+            self.raise_if_failed()
         if training or self.dma or not getattr(self, "profile", False):
-            return self._forward_one_call(x, out, st, training, phase if self.dma and not training else 0)
+            out = self._forward_one_call(x, out, st, training, phase if self.dma and not training else 0)
+            if phase != 1:
+                self._post_status()
+            return out
         ev = self._mark
         ev("start")
         _lib.check(lib.bibo_moe_router_fwd(p(x), p(self.w_router), p(self.bias), None, n, hidden, e, k,
@@ -210,7 +220,31 @@ class ExpertParallelMoE:
                                            hidden, self.world, k, self.cap, self.comm_ctas, p(out), st),
                    "bibo_moe_ep_combine")
         ev("combine")
+        self._post_status()
         return out
+
+    def _post_status(self) -> None:
+        self.header_host[:4].copy_(self.ep_plan[:4], non_blocking=True)
+        self.header_host[4:].copy_(self.local_plan[:4], non_blocking=True)
+
+    def raise_if_failed(self, wait: bool = False) -> None:
+        """RuntimeError if a kernel of an earlier call on this object left a status word (4 = a receive buffer
+        would have overflowed: nothing was exchanged; 5 = a cross-rank barrier timed out; 100.. = a bounded
+        wait in a kernel gave up).  Looks at what an asynchronous copy behind that call brought to the host, so
+        without ``wait`` nothing is synchronised; the words are cleared once reported."""
+        if self._n is None:
+            return
+        if wait:
+            torch.cuda.current_stream(self.device).synchronize()
+        code = max(int(self.header_host[2]), int(self.header_host[6]))
+        if code != 0:
+            self.header_host.zero_()
+            self.ep_plan[2:3].zero_()
+            self.local_plan[2:3].zero_()
+            hint = " (raise capacity_factor, or leave it at None for the dropless worst case)" if code == 4 else ""
+            raise RuntimeError(f"bibo_b200: an expert-parallel call reported device status {code} "
+                               f"({Fn.STATUS_TEXT.get(code, 'see the plan layout in bibo_moe.h')}){hint}; its results "
+                               "and those of the calls issued since are invalid")
 
     def _allocate_training(self) -> None:
         """Extra buffers the backward pass needs (allocated on the first training forward)."""
@@ -245,6 +279,7 @@ class ExpertParallelMoE:
         st = torch.cuda.current_stream(dev).cuda_stream
         _lib.check(_lib.load().bibo_moe_ep_backward(C.byref(self._last_args), C.byref(b), st), "bibo_moe_ep_backward")
         self._last_args = None
+        self._post_status()
         return dx, d_wr, d_gu, d_dn, d_th
 
     DMA_MARKS = ("start", "histograms", "sorted", "sent", "received", "experts", "returned", "all_returned", "combine")
@@ -264,6 +299,7 @@ class ExpertParallelMoE:
         """Second half of a ``forward(..., phase=1)`` of the copy-engine path (same stream)."""
         a, d, st = self._dma_call
         _lib.check(_lib.load().bibo_moe_ep_forward_dma(C.byref(a), C.byref(d), 2, st), "bibo_moe_ep_forward_dma")
+        self._post_status()
 
     def _forward_one_call(self, x: torch.Tensor, out: torch.Tensor, st: int, training: bool = False,
                           phase: int = 0) -> torch.Tensor:
@@ -457,6 +493,71 @@ class DedupExpertParallelMoE:
         self.header_host.copy_(b.plan[:4], non_blocking=True)
         return out
 
+    # ---- the forward in three stream-ordered stages (used by PipelinedDedupMoE) -------------------------
+    def _mark(self, name: str) -> None:
+        if self.profile:
+            if name == "start":
+                self.marks = []
+            e = torch.cuda.Event(enable_timing=True)
+            e.record()
+            self.marks.append((name, e))
+
+    def _barrier(self, st: int) -> None:
+        self._epoch += 1
+        b = self.buf
+        _lib.check(_lib.load().bibo_moe_ep_barrier(b.sym_flags.ptr_array, self.rank, self.world, self._epoch,
+                                                   _lib.ptr(b.plan[2:]), st), "bibo_moe_ep_barrier")
+
+    def stage_home(self, x: torch.Tensor) -> None:
+        """Router and dispatch of this rank's tokens, then the barrier after which every rank's rows have
+        landed (current stream)."""
+        lib, p, b = _lib.load(), _lib.ptr, self.buf
+        n, hidden = x.shape
+        if b is None or n > self._n_cap:
+            raise RuntimeError("allocate the lane before staging it")
+        self.raise_if_failed()
+        st = torch.cuda.current_stream(self.device).cuda_stream
+        self._mark("start")
+        if n:
+            _lib.check(lib.bibo_moe_router_fwd(p(x), p(self.w_router), p(self.bias), None, n, hidden, self.n_experts,
+                                               self.top_k, Fn.norm_code(self.norm_mode), float(self.scale), _lib.BF16, None,
+                                               p(b.topk_idx), p(b.topk_w), p(b.slot_rank_home), p(b.block_counts_home),
+                                               p(b.plan[2:]), st), "bibo_moe_router_fwd")
+        self._mark("route")
+        _lib.check(lib.bibo_moe_ep_dedup_dispatch(p(x) if n else None, p(b.topk_idx), p(b.topk_w), b.sym_xu.ptr_array,
+                                                  b.sym_midx.ptr_array, b.sym_mw.ptr_array, n, self._n_cap, hidden,
+                                                  self.n_experts, self.rank, self.world, self.top_k, self.comm_ctas, st),
+                   "bibo_moe_ep_dedup_dispatch")
+        self._mark("dispatch")
+        self._barrier(st)
+        self._mark("received")
+        self._n_last = n
+
+    def _owner(self) -> _lib.EpDedupOwner:
+        b = self.buf
+        return b.owner_args(self.rank, self.hidden, self.inter, self.n_experts, self.gate_up, self.down, self.theta,
+                            b.sym_part.ptr_array, self.max_ctas, self.comm_ctas)
+
+    def stage_experts(self) -> None:
+        """The tensor-core part of the owner's work on the received rows (current stream)."""
+        st = torch.cuda.current_stream(self.device).cuda_stream
+        _lib.check(_lib.load().bibo_moe_ep_dedup_experts(C.byref(self._owner()), st), "bibo_moe_ep_dedup_experts")
+
+    def stage_back(self, out: torch.Tensor) -> None:
+        """Partial rows to the home ranks, the barrier, and the final sum into ``out`` (current stream)."""
+        lib, p, b = _lib.load(), _lib.ptr, self.buf
+        st = torch.cuda.current_stream(self.device).cuda_stream
+        self._mark("experts")
+        _lib.check(lib.bibo_moe_ep_dedup_partial(C.byref(self._owner()), st), "bibo_moe_ep_dedup_partial")
+        self._mark("partial")
+        self._barrier(st)
+        self._mark("returned")
+        _lib.check(lib.bibo_moe_ep_dedup_final(p(b.part), p(b.topk_idx), p(b.plan[2:]), self._n_last, self._n_cap,
+                                               self.hidden, self.n_experts, self.world, self.top_k, self.comm_ctas,
+                                               p(out), st), "bibo_moe_ep_dedup_final")
+        self._mark("sum")
+        self.header_host.copy_(b.plan[:4], non_blocking=True)
+
     def _trace_struct(self, n: int):
         if self.trace is None:
             return None
@@ -486,6 +587,298 @@ class DedupExpertParallelMoE:
 
     def status(self) -> int:
         return int(self.buf.plan[2].item()) if self.buf is not None else 0
+
+
+class PipelinedDedupMoE:
+    """The de-duplicated forward on ``chunks`` token slices, pipelined over TWO streams by resource: one stream
+    carries everything that uses NVLink (router + dispatch + barrier of every slice, later partial rows +
+    barrier + final sum of every slice), the other the tensor-core work (rank, plan, permute, grouped GEMMs) of
+    every slice.  Work on one resource runs in slice order and never competes with itself; slice i's GEMMs run
+    while slice i+1's rows travel and slice i-1's partial rows return.  Every rank issues the same sequence
+    per stream, so the per-slice barriers pair up across ranks.  Results equal the one-slice forward bit for
+    bit (tokens are independent)."""
+
+    def __init__(self, weights, top_k: int, group=None, n_tokens: Optional[int] = None, chunks: int = 4,
+                 comm_sms: int = 16, gemm_ctas: Optional[int] = None, comm_ctas: Optional[int] = None, **kw):
+        """``comm_sms`` SMs are set aside for the exchange kernels (one block of 16 warps each, tagged with shared
+        memory so that it never shares an SM with a GEMM CTA); the grouped GEMMs get the rest minus one SM per
+        GPC (their 4-CTA clusters need four free SMs in one GPC), rounded down to whole clusters.
+        ``gemm_ctas`` / ``comm_ctas`` override the two caps (0 = no cap, no tag)."""
+        self.chunks = max(1, int(chunks))
+        dev = weights["w_router"].device
+        self.device = dev
+        sms = torch.cuda.get_device_properties(dev).multi_processor_count
+        if self.chunks == 1:
+            comm_sms = 0                                        # nothing to overlap with: every kernel gets the whole GPU
+        if gemm_ctas is None:
+            gemm_ctas = (sms - comm_sms - 8) // 4 * 4 if comm_sms > 0 else 0
+        if comm_ctas is None:
+            comm_ctas = comm_sms
+        self.lanes = [DedupExpertParallelMoE(weights, top_k, group, max_ctas=gemm_ctas, comm_ctas=comm_ctas, **kw)
+                      for _ in range(self.chunks)]
+        self.link = torch.cuda.Stream(device=dev, priority=-1)     # exchange kernels are scheduled first
+        self.tensor = torch.cuda.Stream(device=dev)
+        self.copy_in, self.copy_out = torch.cuda.Stream(device=dev), torch.cuda.Stream(device=dev)
+        ev = lambda: [torch.cuda.Event() for _ in range(self.chunks)]
+        self._received, self._computed, self._copied, self._done = ev(), ev(), ev(), ev()
+        if n_tokens is not None:
+            for lane, (lo, hi) in zip(self.lanes, self._bounds(n_tokens)):
+                lane._allocate(hi - lo)
+
+    def _bounds(self, n: int):
+        per = (n + self.chunks - 1) // self.chunks
+        return [(min(c * per, n), min((c + 1) * per, n)) for c in range(self.chunks)]
+
+    def forward(self, x: torch.Tensor, out: Optional[torch.Tensor] = None, x_host=None, out_host=None) -> torch.Tensor:
+        if out is None:
+            out = torch.empty_like(x)
+        n = x.shape[0]
+        bounds = self._bounds(n)
+        for lane, (lo, hi) in zip(self.lanes, bounds):
+            if lane.buf is None or hi - lo > lane._n_cap:
+                lane._allocate(hi - lo)
+        cur = torch.cuda.current_stream(self.device)
+        start = torch.cuda.Event()
+        start.record(cur)
+        for st in (self.link, self.tensor, self.copy_in, self.copy_out):
+            st.wait_event(start)
+        if x_host is not None:
+            with torch.cuda.stream(self.copy_in):
+                for i, (lo, hi) in enumerate(bounds):
+                    x[lo:hi].copy_(x_host[lo:hi], non_blocking=True)
+                    self._copied[i].record()
+        with torch.cuda.stream(self.link):
+            for i, (lane, (lo, hi)) in enumerate(zip(self.lanes, bounds)):
+                if x_host is not None:
+                    self.link.wait_event(self._copied[i])
+                lane.stage_home(x[lo:hi])
+                self._received[i].record()
+        with torch.cuda.stream(self.tensor):
+            for i, lane in enumerate(self.lanes):
+                self.tensor.wait_event(self._received[i])
+                lane.stage_experts()
+                self._computed[i].record()
+        with torch.cuda.stream(self.link):
+            for i, (lane, (lo, hi)) in enumerate(zip(self.lanes, bounds)):
+                self.link.wait_event(self._computed[i])
+                lane.stage_back(out[lo:hi])
+                self._done[i].record()
+        if out_host is not None:
+            with torch.cuda.stream(self.copy_out):
+                for i, (lo, hi) in enumerate(bounds):
+                    self.copy_out.wait_event(self._done[i])
+                    out_host[lo:hi].copy_(out[lo:hi], non_blocking=True)
+            cur.wait_stream(self.copy_out)
+        cur.wait_stream(self.link)
+        cur.wait_stream(self.tensor)
+        return out
+
+    def forward_host(self, x_host: torch.Tensor, out_host: torch.Tensor, x_dev: torch.Tensor,
+                     out_dev: torch.Tensor) -> torch.Tensor:
+        """Host-buffer forward (pinned tensors): the copies of the slices run on two more streams under the
+        kernels of other slices; waits for the result."""
+        self.forward(x_dev, out_dev, x_host=x_host, out_host=out_host)
+        torch.cuda.current_stream(self.device).synchronize()
+        return out_host
+
+    def status(self) -> int:
+        return max(lane.status() for lane in self.lanes)
+
+
+class PipelinedAllGatherMoE:
+    """The forward on ``chunks`` token slices with the exchange on the COPY ENGINES (dense all-gather out, one
+    block per peer back; see ``bibo_moe_ep_copy_to_peers`` in the header).  Two streams by resource: the copy
+    stream carries the peer copies and the cross-rank barriers of every slice, the tensor stream every kernel
+    (router, the owner chain over the gathered rows, the partial sums, the final sum).  No SM moves a row over
+    NVLink, so the grouped GEMMs keep the whole GPU while other slices' rows travel.  More bytes than the
+    de-duplicated kernels send: ``world - 1`` rows per token each way."""
+
+    def __init__(self, weights, top_k: int, group=None, n_tokens: Optional[int] = None, chunks: int = 4, **kw):
+        self.chunks = max(1, int(chunks))
+        dev = weights["w_router"].device
+        self.device = dev
+        self.lanes = [DedupExpertParallelMoE(weights, top_k, group, **kw) for _ in range(self.chunks)]
+        self.copy = torch.cuda.Stream(device=dev, priority=-1)
+        self.tensor = torch.cuda.Stream(device=dev)
+        self.copy_in, self.copy_out = torch.cuda.Stream(device=dev), torch.cuda.Stream(device=dev)
+        ev = lambda: [torch.cuda.Event() for _ in range(self.chunks)]
+        self._routed, self._received, self._computed, self._returned, self._copied, self._done = (ev() for _ in range(6))
+        if n_tokens is not None:
+            for lane, (lo, hi) in zip(self.lanes, self._bounds(n_tokens)):
+                self._prepare(lane, hi - lo)
+
+    def _bounds(self, n: int):
+        per = (n + self.chunks - 1) // self.chunks
+        return [(min(c * per, n), min((c + 1) * per, n)) for c in range(self.chunks)]
+
+    @staticmethod
+    def _prepare(lane, n: int) -> None:
+        """Buffers of the de-duplicated path plus the gathered raw top-k table (peer-mapped) and the local staging
+        buffer of the partial rows; the partial kernel's destination table points into the staging buffer for
+        every other home rank and into this rank's own ``part`` for its own tokens."""
+        lane._allocate(n)
+        b, dev = lane.buf, lane.device
+        nv = lane.world * lane._n_cap
+        b.sym_raw = _Symmetric((nv, lane.top_k), torch.int32, dev, lane.group)
+        b.sym_raw.tensor.fill_(-1)
+        b.topk_idx.fill_(-1)
+        b.pstage = torch.empty(nv, lane.hidden, dtype=torch.bfloat16, device=dev)
+        row = lane._n_cap * lane.hidden * 2
+        table = [b.pstage.data_ptr() + (s_ - lane.rank) * row for s_ in range(lane.world)]
+        table[lane.rank] = b.part.data_ptr()
+        b.stage_table = (C.c_void_p * lane.world)(*table)
+        b.n_routed = lane._n_cap
+        torch.cuda.synchronize(dev)
+        dist.barrier(lane.group)
+
+    # ---- per-slice stages ---------------------------------------------------------------------------------
+    @staticmethod
+    def _send_rows(lane, x) -> None:
+        b, st = lane.buf, torch.cuda.current_stream(lane.device).cuda_stream
+        row = lane.hidden * 2
+        _lib.check(_lib.load().bibo_moe_ep_copy_to_peers(b.sym_xu.ptr_array, lane.rank * lane._n_cap * row, _lib.ptr(x), 0,
+                                                         x.shape[0] * row, lane.rank, lane.world, 1, st),
+                   "bibo_moe_ep_copy_to_peers")
+
+    @staticmethod
+    def _route(lane, x) -> None:
+        lib, p, b = _lib.load(), _lib.ptr, lane.buf
+        n, st = x.shape[0], torch.cuda.current_stream(lane.device).cuda_stream
+        lane.raise_if_failed()
+        if n < b.n_routed:
+            b.topk_idx[n:].fill_(-1)              # slots past this call's tokens: "no such token"
+        b.n_routed = n
+        if n:
+            _lib.check(lib.bibo_moe_router_fwd(p(x), p(lane.w_router), p(lane.bias), None, n, lane.hidden, lane.n_experts,
+                                               lane.top_k, Fn.norm_code(lane.norm_mode), float(lane.scale), _lib.BF16, None,
+                                               p(b.topk_idx), p(b.topk_w), p(b.slot_rank_home), p(b.block_counts_home),
+                                               p(b.plan[2:]), st), "bibo_moe_router_fwd")
+        lane._n_last = n
+
+    @staticmethod
+    def _send_records(lane) -> None:
+        lib, p, b = _lib.load(), _lib.ptr, lane.buf
+        st = torch.cuda.current_stream(lane.device).cuda_stream
+        block = lane._n_cap * lane.top_k * 4
+        for sym, src in ((b.sym_raw, b.topk_idx), (b.sym_mw, b.topk_w)):
+            _lib.check(lib.bibo_moe_ep_copy_to_peers(sym.ptr_array, lane.rank * block, p(src), 0, block, lane.rank,
+                                                     lane.world, 1, st), "bibo_moe_ep_copy_to_peers")
+        lane._barrier(st)
+
+    @staticmethod
+    def _experts(lane) -> None:
+        lib, p, b = _lib.load(), _lib.ptr, lane.buf
+        st = torch.cuda.current_stream(lane.device).cuda_stream
+        nv = lane.world * lane._n_cap
+        _lib.check(lib.bibo_moe_ep_localize(p(b.sym_raw.tensor), nv, lane.top_k, lane.n_experts, lane.rank, lane.world,
+                                            p(b.midx), st), "bibo_moe_ep_localize")
+        owner = b.owner_args(lane.rank, lane.hidden, lane.inter, lane.n_experts, lane.gate_up, lane.down, lane.theta,
+                             b.stage_table, lane.max_ctas, 0)
+        _lib.check(lib.bibo_moe_ep_dedup_owner(C.byref(owner), st), "bibo_moe_ep_dedup_owner")
+
+    @staticmethod
+    def _return(lane) -> None:
+        b, st = lane.buf, torch.cuda.current_stream(lane.device).cuda_stream
+        block = lane._n_cap * lane.hidden * 2
+        _lib.check(_lib.load().bibo_moe_ep_copy_to_peers(b.sym_part.ptr_array, lane.rank * block, _lib.ptr(b.pstage), block,
+                                                         block, lane.rank, lane.world, 0, st), "bibo_moe_ep_copy_to_peers")
+        lane._barrier(st)
+
+    @staticmethod
+    def _final(lane, out) -> None:
+        lib, p, b = _lib.load(), _lib.ptr, lane.buf
+        st = torch.cuda.current_stream(lane.device).cuda_stream
+        _lib.check(lib.bibo_moe_ep_dedup_final(p(b.part), p(b.topk_idx), p(b.plan[2:]), lane._n_last, lane._n_cap,
+                                               lane.hidden, lane.n_experts, lane.world, lane.top_k, 0, p(out), st),
+                   "bibo_moe_ep_dedup_final")
+        lane.header_host.copy_(b.plan[:4], non_blocking=True)
+
+    @staticmethod
+    def _mark(lane, name: str, stream) -> None:
+        if lane.profile:
+            if name == "start":
+                lane.marks = []
+            e = torch.cuda.Event(enable_timing=True)
+            e.record(stream)
+            lane.marks.append((name, e))
+
+    def forward(self, x: torch.Tensor, out: Optional[torch.Tensor] = None, x_host=None, out_host=None) -> torch.Tensor:
+        if out is None:
+            out = torch.empty_like(x)
+        bounds = self._bounds(x.shape[0])
+        for lane, (lo, hi) in zip(self.lanes, bounds):
+            if lane.buf is None or hi - lo > lane._n_cap or not hasattr(lane.buf, "pstage"):
+                self._prepare(lane, hi - lo)
+        cur = torch.cuda.current_stream(self.device)
+        start = torch.cuda.Event()
+        start.record(cur)
+        for st in (self.copy, self.tensor, self.copy_in, self.copy_out):
+            st.wait_event(start)
+        work = list(enumerate(zip(self.lanes, bounds)))
+        if x_host is not None:
+            with torch.cuda.stream(self.copy_in):
+                for i, (lane, (lo, hi)) in work:
+                    x[lo:hi].copy_(x_host[lo:hi], non_blocking=True)
+                    self._copied[i].record()
+        for i, (lane, (lo, hi)) in work:
+            with torch.cuda.stream(self.copy):                   # the rows need no routing: they leave at once
+                if x_host is not None:
+                    self.copy.wait_event(self._copied[i])
+                self._mark(lane, "start", self.copy)
+                self._send_rows(lane, x[lo:hi])
+            with torch.cuda.stream(self.tensor):
+                if x_host is not None:
+                    self.tensor.wait_event(self._copied[i])
+                self._route(lane, x[lo:hi])
+                self._routed[i].record()
+                self._mark(lane, "route", self.tensor)
+            with torch.cuda.stream(self.copy):
+                self.copy.wait_event(self._routed[i])
+                self._mark(lane, "dispatch", self.copy)
+                self._send_records(lane)
+                self._received[i].record()
+                self._mark(lane, "received", self.copy)
+        for i, (lane, (lo, hi)) in work:                         # E0 R0 | E1 R1 F0 | E2 R2 F1 | ... | F(last)
+            with torch.cuda.stream(self.tensor):
+                self.tensor.wait_event(self._received[i])
+                self._experts(lane)
+                self._computed[i].record()
+                self._mark(lane, "experts", self.tensor)
+            with torch.cuda.stream(self.copy):
+                self.copy.wait_event(self._computed[i])
+                self._return(lane)
+                self._returned[i].record()
+                self._mark(lane, "partial", self.copy)
+                self._mark(lane, "returned", self.copy)
+            if i >= 1:
+                self._finish(i - 1, bounds[i - 1], out, out_host)
+        self._finish(len(work) - 1, bounds[-1], out, out_host)
+        if out_host is not None:
+            cur.wait_stream(self.copy_out)
+        cur.wait_stream(self.copy)
+        cur.wait_stream(self.tensor)
+        return out
+
+    def _finish(self, i, bound, out, out_host) -> None:
+        lane, (lo, hi) = self.lanes[i], bound
+        with torch.cuda.stream(self.tensor):
+            self.tensor.wait_event(self._returned[i])
+            self._final(lane, out[lo:hi])
+            self._done[i].record()
+            self._mark(lane, "sum", self.tensor)
+        if out_host is not None:
+            with torch.cuda.stream(self.copy_out):
+                self.copy_out.wait_event(self._done[i])
+                out_host[lo:hi].copy_(out[lo:hi], non_blocking=True)
+
+    def forward_host(self, x_host: torch.Tensor, out_host: torch.Tensor, x_dev: torch.Tensor,
+                     out_dev: torch.Tensor) -> torch.Tensor:
+        self.forward(x_dev, out_dev, x_host=x_host, out_host=out_host)
+        torch.cuda.current_stream(self.device).synchronize()
+        return out_host
+
+    def status(self) -> int:
+        return max(lane.status() for lane in self.lanes)
 
 
 class PipelinedExpertParallelMoE:
@@ -626,7 +1019,7 @@ class ExpertParallelMoELayer(torch.nn.Module):
     experts, no shared expert.
     """
 
-    def __init__(self, config, group=None, capacity_factor: float = 2.0, reduce_router_grad: bool = True):
+    def __init__(self, config, group=None, capacity_factor: Optional[float] = None, reduce_router_grad: bool = True):
         super().__init__()
         from .moe import BiBoMoERouter, _cfg
         self.group = group if group is not None else dist.group.WORLD

@@ -482,11 +482,28 @@ typedef struct {
 } bibo_moe_ep_dedup_owner_args;
 /* owner rank: experts over the received rows, one partial row per (token, this rank) to the home ranks    */
 int bibo_moe_ep_dedup_owner(const bibo_moe_ep_dedup_owner_args* args, void* stream);
+/* its two halves: the tensor-core part (rank, plan, permute, gate/up, down) and the NVLink part (partial rows
+ * to the home ranks), for callers that run them on different streams (pipelined token slices)             */
+int bibo_moe_ep_dedup_experts(const bibo_moe_ep_dedup_owner_args* args, void* stream);
+int bibo_moe_ep_dedup_partial(const bibo_moe_ep_dedup_owner_args* args, void* stream);
 /* home rank: out[t] = sum of the partial rows of token t's owners; `status` = a device word, the kernel
  * does nothing when it is non-zero (pass the owner plan's status word)                                    */
 int bibo_moe_ep_dedup_final(const void* part, const int32_t* topk_idx, const int32_t* status, int64_t n_tokens,
                             int64_t n_cap, int hidden, int n_experts, int world, int top_k, int comm_ctas,
                             void* out, void* stream);
+/* The same exchange on the COPY ENGINES, dense: every rank copies ALL its token rows and its whole top-k table
+ * to every peer (an all-gather: the slot layout makes each rank's rows one contiguous block of the receiver's
+ * xu), the owner keeps the slots of its own experts (bibo_moe_ep_localize turns the gathered GLOBAL indices
+ * into local ones, -1 elsewhere) and stores its partial rows into a local staging buffer laid out by home rank,
+ * whose blocks go back as one copy per peer.  More bytes than the kernels above send (world-1 rows per token
+ * instead of the distinct owners), but no SM and next to no interference with the grouped GEMMs of another token
+ * slice: the better trade while (world-1) is close to the distinct-owner count (2 and 4 ranks).
+ * bibo_moe_ep_copy_to_peers: dst_peers[d] + dst_offset <- src + d*src_stride, `bytes` each, as asynchronous
+ * copies on `stream`, peers in the order rank+1, rank+2, ...; the own rank only with include_self.          */
+int bibo_moe_ep_localize(const int32_t* raw_idx, int64_t n_virtual, int top_k, int n_experts, int rank,
+                         int world, int32_t* midx, void* stream);
+int bibo_moe_ep_copy_to_peers(void* const* dst_peers, int64_t dst_offset, const void* src, int64_t src_stride,
+                              int64_t bytes, int rank, int world, int include_self, void* stream);
 /* router + the three stages with the two stream barriers in between (epochs epoch_base+1, +2; the caller
  * advances epoch_base by 2 per call).  marks: NULL or 8 cudaEvent_t recorded on the stream: start, routed,
  * dispatched, all rows received, experts done, partials stored, all partials received, summed.          */
@@ -561,6 +578,10 @@ int bibo_moe_route_noalloc(const void* x, const void* w_router, const float* bia
                            int hidden, int n_experts, int top_k, int norm_mode, float scale, int dtype,
                            int32_t* topk_idx, float* topk_w, int32_t* counts, void* stream);
 int64_t bibo_moe_route_noalloc_max_tokens(void);
+/* The router / plan kernels' status word of the last call on the current device sits inside the shared array
+ * and is otherwise unobservable: this copies it into a caller-owned DEVICE word on `stream` (no allocation,
+ * no synchronisation; no counterpart in the reference).  n_tokens <= 0 only zeroes `counts`.              */
+int bibo_moe_route_noalloc_status(int32_t* status_out, void* stream);
 
 /* Debug: copies plan[0..3] to the host (synchronises `stream`) and returns plan[2] (status).     */
 int bibo_moe_debug_plan_header(const int32_t* plan, int32_t* header4_host, void* stream);

@@ -41,7 +41,7 @@ def main():
     torch.cuda.synchronize()
     moe.raise_if_failed(wait=True)
     assert torch.equal(outs[0], outs[1]) and torch.equal(outs[0], outs[2]), "forward is not deterministic"
-    piped = ep.PipelinedExpertParallelMoE(weights, k, dist.group.WORLD, chunks=3, dedup=True, gemm_ctas=0, comm_ctas=32)
+    piped = ep.PipelinedExpertParallelMoE(weights, k, dist.group.WORLD, chunks=3, dedup=True, gemm_ctas=96, comm_ctas=16)
     o3 = piped.forward(x_local)
     torch.cuda.synchronize()
     assert piped.status() == 0, f"rank {rank}: sliced status {piped.status()}"
@@ -49,6 +49,28 @@ def main():
     x_host, out_host = x_local.cpu().pin_memory(), torch.empty_like(x_local, device="cpu").pin_memory()
     piped.forward_host(x_host, out_host, torch.empty_like(x_local), torch.empty_like(x_local))
     assert torch.equal(out_host, outs[0].cpu()), "sliced host-buffer forward differs from the device forward"
+    # slices pipelined by resource (one stream for the NVLink work, one for the tensor-core work)
+    staged = ep.PipelinedDedupMoE(weights, k, dist.group.WORLD, chunks=3, comm_sms=16)
+    for _ in range(2):
+        o4 = staged.forward(x_local)
+        torch.cuda.synchronize()
+        assert staged.status() == 0, f"rank {rank}: staged status {staged.status()}"
+        assert torch.equal(o4, outs[0]), "resource-pipelined slices differ from one slice"
+    out_host.zero_()
+    staged.forward_host(x_host, out_host, torch.empty_like(x_local), torch.empty_like(x_local))
+    assert torch.equal(out_host, outs[0].cpu()), "resource-pipelined host-buffer forward differs"
+
+    # the same exchange on the copy engines (dense all-gather, blocks back), three slices and one
+    for chunks in (3, 1):
+        ag = ep.PipelinedAllGatherMoE(weights, k, dist.group.WORLD, chunks=chunks)
+        for _ in range(2):
+            o5 = ag.forward(x_local)
+            torch.cuda.synchronize()
+            assert ag.status() == 0, f"rank {rank}: copy-engine status {ag.status()}"
+            assert torch.equal(o5, outs[0]), f"copy-engine exchange ({chunks} slices) differs from the kernel exchange"
+        out_host.zero_()
+        ag.forward_host(x_host, out_host, torch.empty_like(x_local), torch.empty_like(x_local))
+        assert torch.equal(out_host, outs[0].cpu()), "copy-engine host-buffer forward differs"
 
     pad = torch.zeros(n, hidden, dtype=torch.bfloat16, device=dev)
     pad[:counts[rank]] = outs[0]

@@ -62,6 +62,18 @@ def main():
     out_host.zero_()
     dma3.forward_host(x_host, out_host, torch.empty_like(x_local), torch.empty_like(x_local))
     assert torch.equal(out_host, outs[0].cpu()), "sliced copy-engine host-buffer forward differs"
+    # a receive buffer that is too small: every rank sees the overflow on the device (status 4), no row is
+    # exchanged, the barriers still pass, and the host layer raises instead of handing out an unwritten result
+    small = ep.ExpertParallelMoE(weights, k, dist.group.WORLD, capacity_factor=0.25)
+    sentinel = torch.full_like(x_local, 3.0)
+    small.forward(x_local, out=sentinel)
+    try:
+        small.raise_if_failed(wait=True)
+        raise AssertionError("an overflowing receive buffer went unnoticed")
+    except RuntimeError as err:
+        assert "device status 4" in str(err), str(err)
+    assert bool((sentinel == 3.0).all()), "the combine must not write anything after an overflow"
+    assert small.status() == 0, "the status word is cleared once it has been reported"
     gathered = [torch.empty_like(outs[0]) for _ in range(world)] if rank == 0 else None
     dist.gather(outs[0], gathered, dst=0)
     ok = True

@@ -62,3 +62,37 @@ def test_route_noalloc_refuses_oversized_batches():
     rc = lib.bibo_moe_route_noalloc(x.data_ptr(), wr.data_ptr(), bias.data_ptr(), n, 64, 64, 6, _lib.NORM_SUM, 1.0,
                                     _lib.BF16, idx.data_ptr(), w.data_ptr(), counts.data_ptr(), None)
     assert rc == -4 and b"exceed the fixed scratch" in lib.bibo_moe_last_error_string()
+
+
+def test_route_noalloc_against_the_cpu_oracle_at_the_largest_layout():
+    """The largest call the fixed array must hold (max tokens, 256 experts, top-8; CUDA-core router) against the
+    CPU oracle's selection on the kernel's own fp32 logits path: histogram = bincount of the oracle's indices,
+    except tokens at a last-bit near-tie; then the status word through its accessor, and an empty call."""
+    from bibo_b200 import _lib
+    from oracle import moe_oracle as orc
+    lib = _lib.load()
+    n, h, e, k = int(lib.bibo_moe_route_noalloc_max_tokens()), 64, 256, 8
+    g = torch.Generator().manual_seed(9)
+    x = torch.randn(n, h, generator=g)
+    wr = torch.randn(e, h, generator=g) * 0.02
+    bias = (torch.rand(e, generator=g) * 2 - 1) * 0.01
+    idx, w, counts = _call(lib, _lib, x.to(DEV), wr.to(DEV), bias.to(DEV), k, _lib.NORM_SUM, 1.0)
+    status = torch.full((1,), -1, dtype=torch.int32, device=DEV)
+    _lib.check(lib.bibo_moe_route_noalloc_status(status.data_ptr(), torch.cuda.current_stream().cuda_stream), "status")
+    torch.cuda.synchronize()
+    assert int(status) == 0
+    logits = orc.router_logits(x, wr)
+    ref_idx, ref_w, ref_counts = orc.router_select(logits, bias, k)
+    same = (idx.cpu().long() == ref_idx).all(-1)
+    gap = orc.boundary_gap(logits, bias, k)
+    assert bool((gap[~same] < 1e-5).all()), "a token may differ from the oracle only at a near-tie of the k-th score"
+    assert float(same.float().mean()) > 0.999
+    assert int((counts.cpu().long() - ref_counts).abs().sum()) <= 2 * int((~same).sum())
+    assert float((w.cpu()[same] - ref_w[same]).abs().max()) < 1e-6
+    # an empty call writes an all-zero histogram and touches nothing else
+    counts.fill_(7)
+    rc = lib.bibo_moe_route_noalloc(None, None, None, 0, h, e, k, _lib.NORM_SUM, 1.0, _lib.F32, None, None,
+                                    counts.data_ptr(), torch.cuda.current_stream().cuda_stream)
+    assert rc == 0
+    torch.cuda.synchronize()
+    assert int(counts.abs().sum()) == 0
