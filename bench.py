@@ -4,18 +4,26 @@
     python bench.py [--gpus N] [--steps K] [--warmup W] [--workload c4|c2|c3|c3a] [--impl reference]
 
 One "step" is one forward pass of the MoE layer over one batch of synthetic tokens.  Prints ONE JSON
-line (rank 0).  `value` is tokens/s of the whole job with the batch already resident in HBM;
-`e2e` is the same metric through the host-buffer C-ABI call (pinned host input copied to the
-device and the result copied back inside the timed region); `roofline` describes the dominant
-kernel, timed with CUDA events recorded around each kernel of the chain inside the timed steps;
-`cpu_baseline` is the CPU oracle (a restatement of the reference's eager per-expert loop) timed on
-this machine's host cores on a bounded sample of the same workload.
+line (rank 0).  `value` is tokens/s of the whole job with the batch already resident in HBM, from ONE
+timed region of --steps steps; `repeats` gives median / min / max of further regions and `sustained`
+seconds of back-to-back steps with the clocks seen; `e2e` is the same metric through the host-buffer
+call (pinned host input copied to the device and the result copied back inside the timed region);
+`roofline` describes the dominant kernel, timed with CUDA events recorded around each kernel of the
+chain inside the timed steps (at N > 1: the NVLink phase against the measured peer-copy rate);
+`cpu_baseline` is the reference's own eager layer (from oracle/_ref when it has been built, else the
+CPU oracle, a restatement of its per-expert loop) timed on this machine's host cores on a bounded
+sample of the same workload; `gpu_eager_reference` is that layer in bf16 on this GPU; at N > 1
+`ep_check` compares sampled tokens of every rank with the single-GPU chain and the CPU oracle and the
+run exits non-zero outside the bf16 bars.
 
 Workloads (synthetic, seeded; shapes and distributions of the benchmark configurations):
   c4  32768 tokens per GPU, hidden 2048, 64 experts, top-6, intermediate 512, bias 0   (default)
   c2  16384 tokens, hidden 1024, intermediate 256, bias ~ U(-0.01, 0.01)
   c3  65536 tokens, hidden 2048, intermediate 512, bias = log Zipf(1.1) profile (literal)
   c3a same with the bias scaled by 0.07 (per-expert counts span about 20x)
+  c5layer  one MoE layer of benchmark configuration 5 (32768 tokens, hidden 1024, intermediate 256)
+  c5  the reference's 10-layer model (from oracle/_ref), prefill of 8 x 4096 tokens, with and without its
+      feed-forward blocks swapped for the kernels (one GPU; a line of its own)
 """
 import argparse
 import json

@@ -158,6 +158,7 @@ SIGNATURES = {
     "bibo_moe_ep_dedup_owner": (_i32, [C.POINTER(EpDedupOwner), _vp]),
     "bibo_moe_ep_dedup_experts": (_i32, [C.POINTER(EpDedupOwner), _vp]),
     "bibo_moe_ep_dedup_partial": (_i32, [C.POINTER(EpDedupOwner), _vp]),
+    "bibo_moe_ep_dedup_push": (_i32, [_vp, _vp, _vp, _vp, _i64, _i32, _i32, _i32, _i32, _i32, _vp]),
     "bibo_moe_ep_dedup_final": (_i32, [_vp, _vp, _vp, _i64, _i64, _i32, _i32, _i32, _i32, _i32, _vp, _vp]),
     "bibo_moe_ep_localize": (_i32, [_vp, _i64, _i32, _i32, _i32, _i32, _vp, _vp]),
     "bibo_moe_ep_copy_to_peers": (_i32, [_vp, _i64, _vp, _i64, _i64, _i32, _i32, _i32, _vp]),

@@ -198,6 +198,39 @@ ep_dedup_partial_kernel(const __nv_bfloat16* __restrict__ y, const int32_t* __re
   }
 }
 
+// Partial rows that were summed into a LOCAL staging buffer (laid out like `part`: row s*n_cap + t for home
+// rank s) travel to the home ranks: warp per virtual token with local slots, a plain 16-byte copy loop with
+// eight loads in flight per lane.  Nothing but streaming, so a handful of SMs keeps NVLink busy while the
+// rest of the GPU runs another token slice's grouped GEMMs.  Home ranks in the rotated order rank+1, ...
+__global__ void __launch_bounds__(DW_TAGGED * 32, 1)
+ep_dedup_push_kernel(const uint8_t* __restrict__ stage, const int32_t* __restrict__ midx, PeerPtrs part,
+                     const int32_t* __restrict__ plan, int64_t n_virtual, int64_t n_cap, int row_bytes, int top_k,
+                     int rank) {
+  const int lane = threadIdx.x & 31;
+  if (plan[PLAN_STATUS] != 0) return;
+  const int world = (int)(n_virtual / n_cap);
+  const int chunks = row_bytes >> 4;
+  for (int64_t i = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5); i < n_virtual - n_cap;
+       i += (int64_t)gridDim.x * (blockDim.x >> 5)) {
+    const int64_t blk = i / n_cap, t = i - blk * n_cap;
+    const int64_t s = (rank + 1 + blk) % world;          // never the own rank: its rows are summed in place
+    const int64_t v = s * n_cap + t;
+    const bool any = __any_sync(0xffffffffu, lane < top_k && midx[v * top_k + lane] >= 0);
+    if (!any) continue;
+    const uint4* src = reinterpret_cast<const uint4*>(stage + v * row_bytes);
+    uint4* dst = reinterpret_cast<uint4*>(static_cast<uint8_t*>(part.p[s]) + ((int64_t)rank * n_cap + t) * row_bytes);
+    for (int c0 = lane; c0 < chunks; c0 += 256) {
+      uint4 val[8];
+#pragma unroll
+      for (int u = 0; u < 8; ++u)
+        if (c0 + u * 32 < chunks) val[u] = __ldcs(src + c0 + u * 32);
+#pragma unroll
+      for (int u = 0; u < 8; ++u)
+        if (c0 + u * 32 < chunks) dst[c0 + u * 32] = val[u];
+    }
+  }
+}
+
 // Warp per home token: adds the partial rows of the owners the token was sent to, ascending owner.
 __global__ void __launch_bounds__(DW_TAGGED * 32, 1)
 ep_dedup_final_kernel(const __nv_bfloat16* __restrict__ part, const int32_t* __restrict__ topk_idx,
@@ -264,6 +297,8 @@ static void dedup_set_carveouts() {
   once.get([](int*) {
     allow_tag_smem(ep_dedup_dispatch_kernel);
     allow_tag_smem(ep_dedup_final_kernel);
+    allow_tag_smem(ep_dedup_push_kernel);
+    prefer_max_smem_d(ep_dedup_push_kernel);
     allow_tag_smem(ep_dedup_partial_kernel<1>); allow_tag_smem(ep_dedup_partial_kernel<2>);
     allow_tag_smem(ep_dedup_partial_kernel<3>); allow_tag_smem(ep_dedup_partial_kernel<4>);
     allow_tag_smem(ep_dedup_partial_kernel<5>); allow_tag_smem(ep_dedup_partial_kernel<6>);
@@ -406,6 +441,26 @@ extern "C" int bibo_moe_ep_dedup_partial(const bibo_moe_ep_dedup_owner_args* a, 
   if (!a->y || !a->slot_row || !a->mw || !a->plan) return fail(BIBO_ERR_ARG, "ep_dedup_partial: null pointer");
   dedup_set_carveouts();
   return dedup_owner_partial(a, stream);
+}
+
+// Rows of a local staging buffer [world*n_cap, H] (what bibo_moe_ep_dedup_partial wrote when it was given a
+// table that points every other home rank into that buffer) to the home ranks' `part` buffers.
+extern "C" int bibo_moe_ep_dedup_push(const void* stage, const int32_t* midx, void* const* part_peers,
+                                      const int32_t* plan, int64_t n_cap, int hidden, int top_k, int rank, int world,
+                                      int comm_ctas, void* stream) {
+  int rc = dedup_check("ep_dedup_push", world, rank, world, top_k, hidden, n_cap);
+  if (rc) return rc;
+  if (world == 1) return BIBO_OK;
+  if (!stage || !midx || !plan || !aligned16(stage)) return fail(BIBO_ERR_ARG, "ep_dedup_push: null or unaligned pointer");
+  PeerPtrs part = {};
+  if ((rc = fill_peers("ep_dedup_push", part_peers, world, &part))) return rc;
+  dedup_set_carveouts();
+  const int64_t nv = (int64_t)world * n_cap;
+  ep_dedup_push_kernel<<<exchange_grid(nv - n_cap, comm_ctas), exchange_block(comm_ctas), exchange_smem(comm_ctas),
+                         static_cast<cudaStream_t>(stream)>>>(static_cast<const uint8_t*>(stage), midx, part, plan, nv,
+                                                              n_cap, hidden * 2, top_k, rank);
+  BIBO_CHECK_LAUNCH("ep_dedup_push_kernel");
+  return BIBO_OK;
 }
 
 extern "C" int bibo_moe_ep_dedup_final(const void* part, const int32_t* topk_idx, const int32_t* status,

@@ -539,9 +539,48 @@ class DedupExpertParallelMoE:
                             b.sym_part.ptr_array, self.max_ctas, self.comm_ctas)
 
     def stage_experts(self) -> None:
-        """The tensor-core part of the owner's work on the received rows (current stream)."""
+        """The tensor-core part of the owner's work on the received rows (current stream).  With a staging
+        buffer (``add_staging``) the partial rows are summed here too, at full HBM speed, into that buffer."""
         st = torch.cuda.current_stream(self.device).cuda_stream
-        _lib.check(_lib.load().bibo_moe_ep_dedup_experts(C.byref(self._owner()), st), "bibo_moe_ep_dedup_experts")
+        lib, b = _lib.load(), self.buf
+        if getattr(b, "pstage", None) is None:
+            _lib.check(lib.bibo_moe_ep_dedup_experts(C.byref(self._owner()), st), "bibo_moe_ep_dedup_experts")
+            return
+        owner = b.owner_args(self.rank, self.hidden, self.inter, self.n_experts, self.gate_up, self.down, self.theta,
+                             b.stage_table, self.max_ctas, 0)
+        _lib.check(lib.bibo_moe_ep_dedup_owner(C.byref(owner), st), "bibo_moe_ep_dedup_owner")
+
+    def add_staging(self) -> None:
+        """A local buffer for the partial rows of other ranks' tokens (the own rank's go straight into ``part``)."""
+        b = self.buf
+        nv = self.world * self._n_cap
+        b.pstage = torch.empty(nv, self.hidden, dtype=torch.bfloat16, device=self.device)
+        row = self._n_cap * self.hidden * 2
+        table = [b.pstage.data_ptr() + (s_ - self.rank) * row for s_ in range(self.world)]
+        table[self.rank] = b.part.data_ptr()
+        b.stage_table = (C.c_void_p * self.world)(*table)
+
+    def stage_push(self) -> None:
+        """Staged partial rows to the home ranks (a streaming kernel on the exchange SMs), then the barrier."""
+        lib, p, b = _lib.load(), _lib.ptr, self.buf
+        st = torch.cuda.current_stream(self.device).cuda_stream
+        self._mark("experts")
+        _lib.check(lib.bibo_moe_ep_dedup_push(p(b.pstage), p(b.midx), b.sym_part.ptr_array, p(b.plan), self._n_cap,
+                                              self.hidden, self.top_k, self.rank, self.world, self.comm_ctas, st),
+                   "bibo_moe_ep_dedup_push")
+        self._mark("partial")
+        self._barrier(st)
+        self._mark("returned")
+
+    def stage_final(self, out: torch.Tensor) -> None:
+        """The final sum of the partial rows into ``out`` (current stream; full GPU, HBM-bound)."""
+        lib, p, b = _lib.load(), _lib.ptr, self.buf
+        st = torch.cuda.current_stream(self.device).cuda_stream
+        _lib.check(lib.bibo_moe_ep_dedup_final(p(b.part), p(b.topk_idx), p(b.plan[2:]), self._n_last, self._n_cap,
+                                               self.hidden, self.n_experts, self.world, self.top_k, 0, p(out), st),
+                   "bibo_moe_ep_dedup_final")
+        self._mark("sum")
+        self.header_host.copy_(b.plan[:4], non_blocking=True)
 
     def stage_back(self, out: torch.Tensor) -> None:
         """Partial rows to the home ranks, the barrier, and the final sum into ``out`` (current stream)."""
@@ -591,9 +630,9 @@ class DedupExpertParallelMoE:
 
 class PipelinedDedupMoE:
     """The de-duplicated forward on ``chunks`` token slices, pipelined over TWO streams by resource: one stream
-    carries everything that uses NVLink (router + dispatch + barrier of every slice, later partial rows +
-    barrier + final sum of every slice), the other the tensor-core work (rank, plan, permute, grouped GEMMs) of
-    every slice.  Work on one resource runs in slice order and never competes with itself; slice i's GEMMs run
+    carries everything that uses NVLink (router + dispatch + barrier of every slice, later the push of the
+    staged partial rows + barrier), the other the work that wants the whole GPU (rank, plan, permute, grouped
+    GEMMs, the partial sums into a local staging buffer, the final sum) of every slice.  Work on one resource runs in slice order and never competes with itself; slice i's GEMMs run
     while slice i+1's rows travel and slice i-1's partial rows return.  Every rank issues the same sequence
     per stream, so the per-slice barriers pair up across ranks.  Results equal the one-slice forward bit for
     bit (tokens are independent)."""
@@ -620,10 +659,11 @@ class PipelinedDedupMoE:
         self.tensor = torch.cuda.Stream(device=dev)
         self.copy_in, self.copy_out = torch.cuda.Stream(device=dev), torch.cuda.Stream(device=dev)
         ev = lambda: [torch.cuda.Event() for _ in range(self.chunks)]
-        self._received, self._computed, self._copied, self._done = ev(), ev(), ev(), ev()
+        self._received, self._computed, self._returned, self._copied, self._done = ev(), ev(), ev(), ev(), ev()
         if n_tokens is not None:
             for lane, (lo, hi) in zip(self.lanes, self._bounds(n_tokens)):
                 lane._allocate(hi - lo)
+                lane.add_staging()
 
     def _bounds(self, n: int):
         per = (n + self.chunks - 1) // self.chunks
@@ -633,10 +673,18 @@ class PipelinedDedupMoE:
         if out is None:
             out = torch.empty_like(x)
         n = x.shape[0]
+        if self.chunks == 1:                 # nothing to pipeline: the one-call forward (partial rows stored directly)
+            if x_host is not None:
+                x.copy_(x_host, non_blocking=True)
+            self.lanes[0].forward(x, out)
+            if out_host is not None:
+                out_host.copy_(out, non_blocking=True)
+            return out
         bounds = self._bounds(n)
         for lane, (lo, hi) in zip(self.lanes, bounds):
             if lane.buf is None or hi - lo > lane._n_cap:
                 lane._allocate(hi - lo)
+                lane.add_staging()
         cur = torch.cuda.current_stream(self.device)
         start = torch.cuda.Event()
         start.record(cur)
@@ -647,27 +695,38 @@ class PipelinedDedupMoE:
                 for i, (lo, hi) in enumerate(bounds):
                     x[lo:hi].copy_(x_host[lo:hi], non_blocking=True)
                     self._copied[i].record()
+        work = list(enumerate(zip(self.lanes, bounds)))
         with torch.cuda.stream(self.link):
-            for i, (lane, (lo, hi)) in enumerate(zip(self.lanes, bounds)):
+            for i, (lane, (lo, hi)) in work:
                 if x_host is not None:
                     self.link.wait_event(self._copied[i])
                 lane.stage_home(x[lo:hi])
                 self._received[i].record()
-        with torch.cuda.stream(self.tensor):
-            for i, lane in enumerate(self.lanes):
+
+        def finish(i):
+            lane, (lo, hi) = self.lanes[i], bounds[i]
+            with torch.cuda.stream(self.tensor):
+                self.tensor.wait_event(self._returned[i])
+                lane.stage_final(out[lo:hi])
+                self._done[i].record()
+            if out_host is not None:
+                with torch.cuda.stream(self.copy_out):
+                    self.copy_out.wait_event(self._done[i])
+                    out_host[lo:hi].copy_(out[lo:hi], non_blocking=True)
+
+        for i, (lane, _) in work:                                # tensor stream: E0 E1 F0 E2 F1 ... F(last)
+            with torch.cuda.stream(self.tensor):
                 self.tensor.wait_event(self._received[i])
                 lane.stage_experts()
                 self._computed[i].record()
-        with torch.cuda.stream(self.link):
-            for i, (lane, (lo, hi)) in enumerate(zip(self.lanes, bounds)):
+            with torch.cuda.stream(self.link):
                 self.link.wait_event(self._computed[i])
-                lane.stage_back(out[lo:hi])
-                self._done[i].record()
+                lane.stage_push()
+                self._returned[i].record()
+            if i >= 1:
+                finish(i - 1)
+        finish(len(work) - 1)
         if out_host is not None:
-            with torch.cuda.stream(self.copy_out):
-                for i, (lo, hi) in enumerate(bounds):
-                    self.copy_out.wait_event(self._done[i])
-                    out_host[lo:hi].copy_(out[lo:hi], non_blocking=True)
             cur.wait_stream(self.copy_out)
         cur.wait_stream(self.link)
         cur.wait_stream(self.tensor)

@@ -486,6 +486,12 @@ int bibo_moe_ep_dedup_owner(const bibo_moe_ep_dedup_owner_args* args, void* stre
  * to the home ranks), for callers that run them on different streams (pipelined token slices)             */
 int bibo_moe_ep_dedup_experts(const bibo_moe_ep_dedup_owner_args* args, void* stream);
 int bibo_moe_ep_dedup_partial(const bibo_moe_ep_dedup_owner_args* args, void* stream);
+/* A partial call whose part_peers table points every OTHER home rank s into a local staging buffer
+ * (entry s = stage + (s - rank) * n_cap * H * 2 bytes, so that the row lands at stage[s*n_cap + t]) sums at
+ * full HBM speed without touching NVLink; bibo_moe_ep_dedup_push then streams the staged rows of the virtual
+ * tokens with local slots to the home ranks (a pure copy: a few SMs saturate the links).                    */
+int bibo_moe_ep_dedup_push(const void* stage, const int32_t* midx, void* const* part_peers, const int32_t* plan,
+                           int64_t n_cap, int hidden, int top_k, int rank, int world, int comm_ctas, void* stream);
 /* home rank: out[t] = sum of the partial rows of token t's owners; `status` = a device word, the kernel
  * does nothing when it is non-zero (pass the owner plan's status word)                                    */
 int bibo_moe_ep_dedup_final(const void* part, const int32_t* topk_idx, const int32_t* status, int64_t n_tokens,

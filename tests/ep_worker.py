@@ -64,7 +64,7 @@ def main():
     assert torch.equal(out_host, outs[0].cpu()), "sliced copy-engine host-buffer forward differs"
     # a receive buffer that is too small: every rank sees the overflow on the device (status 4), no row is
     # exchanged, the barriers still pass, and the host layer raises instead of handing out an unwritten result
-    small = ep.ExpertParallelMoE(weights, k, dist.group.WORLD, capacity_factor=0.25)
+    small = ep.ExpertParallelMoE(weights, k, dist.group.WORLD, capacity_factor=0.01)   # the padding allowance alone
     sentinel = torch.full_like(x_local, 3.0)
     small.forward(x_local, out=sentinel)
     try:
