@@ -128,3 +128,60 @@ def _module_worker(rank, world, path):
 def test_expert_parallel_module_shards_and_balances_on_cpu_ranks():
     with tempfile.TemporaryDirectory() as d:
         mp.spawn(_module_worker, args=(2, os.path.join(d, "store")), nprocs=2, join=True)
+
+
+def _dedup_worker(rank, world, path):
+    """The de-duplicated exchange restated on CPU ranks (fp32, gloo collectives in place of peer stores): fixed
+    slots v = source*n_cap + token, local expert indices with empty slots, one partial sum per (token, owner) in
+    ascending expert order, partial rows added on the home rank in ascending owner order.  Must reproduce the
+    single-process oracle on the concatenated batch to fp32 rounding, with ragged token counts per rank."""
+    from oracle import moe_oracle as orc
+    dist.init_process_group("gloo", init_method=f"file://{path}", rank=rank, world_size=world)
+    n_exp, k, hidden, inter = 16, 4, 32, 24
+    counts = [37 - 9 * r for r in range(world)]
+    offs = [sum(counts[:r]) for r in range(world + 1)]
+    full = orc.make_inputs(offs[-1], hidden, inter, n_exp, seed=3, bias_mode="uniform", theta_std=0.5)
+    x = full["x"][offs[rank]:offs[rank + 1]]
+    n = x.shape[0]
+    cap = torch.tensor([n])
+    dist.all_reduce(cap, op=dist.ReduceOp.MAX)
+    n_cap = int(cap)
+    assert n_cap == max(counts)
+    idx, w, _ = orc.router_select(orc.router_logits(x, full["w_router"]), full["bias"], k)
+    # "dispatch": every rank's rows and records into the slot layout of every rank (dense here; the kernels
+    # send a row only to the ranks that own one of the token's experts)
+    pad = lambda t, fill: torch.cat([t, torch.full((n_cap - n,) + t.shape[1:], fill, dtype=t.dtype)])
+    xu = torch.empty(world * n_cap, hidden)
+    gidx = torch.empty(world * n_cap, k, dtype=torch.int64)
+    gw = torch.empty(world * n_cap, k)
+    dist.all_gather_into_tensor(xu, pad(x, 0.0))
+    dist.all_gather_into_tensor(gidx, pad(idx, -1))
+    dist.all_gather_into_tensor(gw, pad(w, 0.0))
+    el = n_exp // world
+    lo = rank * el
+    local = (gidx >= lo) & (gidx < lo + el)
+    midx = torch.where(local, gidx - lo, torch.full_like(gidx, -1))
+    # owner: its experts over the virtual tokens; an empty slot contributes nothing (index 0 with weight 0)
+    part = orc.experts_forward(xu, midx.clamp_min(0), torch.where(local, gw, torch.zeros_like(gw)),
+                               full["gate_up_proj"][lo:lo + el], full["down_proj"][lo:lo + el],
+                               full["radial_theta"][lo:lo + el])
+    # "return": block s of every owner's partial rows to home rank s, summed in ascending owner order
+    blocks = [torch.empty(world * n_cap, hidden) for _ in range(world)]
+    dist.all_gather(blocks, part)
+    out = torch.zeros(n, hidden)
+    for d in range(world):
+        hit = ((idx >= d * el) & (idx < (d + 1) * el)).any(-1)
+        out[hit] += blocks[d][rank * n_cap:rank * n_cap + n][hit]
+    ref = orc.moe_forward(full["x"], full["w_router"], full["bias"], full["gate_up_proj"], full["down_proj"],
+                          full["radial_theta"], k)[offs[rank]:offs[rank + 1]]
+    assert float((out - ref).abs().max() / ref.abs().max()) < 1e-6
+    # distinct owners per token = rows the kernels send: never more than the slots, never more than the ranks
+    owners = torch.zeros(n, world, dtype=torch.bool).scatter_(1, idx // el, True)
+    assert int(owners.sum(-1).max()) <= min(k, world) and int(owners.sum()) <= n * k
+    dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("world", [2, 4])
+def test_deduplicated_exchange_semantics_on_cpu_ranks(world):
+    with tempfile.TemporaryDirectory() as d:
+        mp.spawn(_dedup_worker, args=(world, os.path.join(d, "store")), nprocs=world, join=True)

@@ -29,8 +29,9 @@ def _weights(hidden, inter, seed):
     return inp, t
 
 
-def _play(world, counts, t, hidden, inter, xs, bufs=None, comm_ctas=0):
-    """One forward of `world` ranks on this device; returns (outs per rank, buffers)."""
+def _play(world, counts, t, hidden, inter, xs, bufs=None, comm_ctas=0, staged=False):
+    """One forward of `world` ranks on this device; returns (outs per rank, buffers).  ``staged``: the owners sum
+    their partial rows into a local staging buffer and a separate streaming kernel moves them to the home ranks."""
     from bibo_b200 import _lib, ep, functional as Fn
     lib, p = _lib.load(), _lib.ptr
     n_cap = max(max(counts), 1)
@@ -53,6 +54,16 @@ def _play(world, counts, t, hidden, inter, xs, bufs=None, comm_ctas=0):
         gu, dn = t["gate_up_proj"][r * el:(r + 1) * el].contiguous(), t["down_proj"][r * el:(r + 1) * el].contiguous()
         th = t["radial_theta"][r * el:(r + 1) * el].contiguous()
         b._keep = (gu, dn, th)
+        if staged:
+            b.pstage = torch.full((world * n_cap, hidden), float("nan"), dtype=torch.bfloat16, device=DEV)
+            row = n_cap * hidden * 2
+            table = [b.pstage.data_ptr() + (s_ - r) * row for s_ in range(world)]
+            table[r] = b.part.data_ptr()
+            a = b.owner_args(r, hidden, inter, E, gu, dn, th, (C.c_void_p * world)(*table), 0, 0)
+            _lib.check(lib.bibo_moe_ep_dedup_owner(C.byref(a), st), "owner")
+            _lib.check(lib.bibo_moe_ep_dedup_push(p(b.pstage), p(b.midx), part, p(b.plan), n_cap, hidden, K, r, world,
+                                                  comm_ctas, st), "push")
+            continue
         a = b.owner_args(r, hidden, inter, E, gu, dn, th, part, 0, comm_ctas)
         _lib.check(lib.bibo_moe_ep_dedup_owner(C.byref(a), st), "owner")
     outs = []
@@ -68,13 +79,13 @@ def _play(world, counts, t, hidden, inter, xs, bufs=None, comm_ctas=0):
     return outs, bufs
 
 
-def _check(world, counts, hidden, inter, seed, bufs=None, comm_ctas=0):
+def _check(world, counts, hidden, inter, seed, bufs=None, comm_ctas=0, staged=False):
     from bibo_b200 import functional as Fn
     inp, t = _weights(hidden, inter, seed=3)
     g = torch.Generator().manual_seed(seed)
     xs_cpu = [torch.randn(n, hidden, generator=g).to(torch.bfloat16) for n in counts]
     xs = [x.to(DEV) for x in xs_cpu]
-    outs, bufs = _play(world, counts, t, hidden, inter, xs, bufs, comm_ctas)
+    outs, bufs = _play(world, counts, t, hidden, inter, xs, bufs, comm_ctas, staged)
     x_all = torch.cat(xs)
     ref_gpu, ws = Fn.moe_forward(x_all, t["w_router"], t["bias"], t["gate_up_proj"], t["down_proj"], t["radial_theta"], K)
     torch.cuda.synchronize()
@@ -114,6 +125,13 @@ def test_rank_without_tokens_and_reuse_of_buffers():
 
 def test_capped_exchange_grids_and_intermediate_512():
     _check(2, [2048, 1500], hidden=1024, inter=512, seed=5, comm_ctas=16)
+
+
+@pytest.mark.parametrize("world,comm_ctas", [(4, 0), (8, 12)])
+def test_partial_rows_through_a_staging_buffer(world, comm_ctas):
+    """Same result when the owners sum into a local staging buffer and a streaming kernel carries the rows home."""
+    counts = [600, 333, 128, 900, 1, 512, 64, 257][:world]
+    _check(world, counts, hidden=512, inter=256, seed=30 + world, comm_ctas=comm_ctas, staged=True)
 
 
 def test_argument_checks():
