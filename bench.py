@@ -472,12 +472,12 @@ def main():
     ap.add_argument("--no-gpu-reference", action="store_true",
                     help="skip timing the reference's eager layer on this GPU (needs oracle/_ref)")
     ap.add_argument("--ep-chunks", type=int, default=None,
-                    help="token slices pipelined on separate streams (N>1; default 4 for the dedup exchange, else 1)")
+                    help="token slices pipelined on separate streams (N>1; default 1)")
     ap.add_argument("--ep-exchange", default="auto", choices=["auto", "allgather", "dedup", "copy", "kernel"],
-                    help="N>1: allgather = every rank's rows to every peer and partial rows back on the copy engines, "
-                         "token slices pipelined (default at 2 and 4 GPUs); dedup = one row per (token, destination rank) "
-                         "each way through exchange kernels (default at 8 GPUs); kernel = one row per slot through the "
-                         "dispatch/combine kernels; copy = per-slot rows by peer copies")
+                    help="N>1: dedup = one row per (token, destination rank) each way through exchange kernels (auto); "
+                         "allgather = every rank's rows to every peer and partial rows back on the copy engines, token "
+                         "slices pipelined; kernel = one row per slot through the dispatch/combine kernels (training "
+                         "path); copy = per-slot rows by peer copies")
     ap.add_argument("--ep-lockstep", action="store_true",
                     help="N>1, dedup: one stream per token slice (all slices in the same phase at once) instead of "
                          "one stream per resource (NVLink work / tensor-core work)")
@@ -501,11 +501,11 @@ def main():
     wl = WORKLOADS[args.workload]
     rank, world = int(os.environ.get("RANK", 0)), int(os.environ.get("WORLD_SIZE", 1))
     if args.ep_exchange == "auto":
-        args.ep_exchange = "allgather" if world <= 4 else "dedup"
+        args.ep_exchange = "dedup"
     if args.mode == "fwdbwd" and args.ep_exchange in ("dedup", "allgather"):
         args.ep_exchange = "kernel"            # the de-duplicated exchanges are forward-only
     if args.ep_chunks is None:
-        args.ep_chunks = 4 if args.ep_exchange == "allgather" else 1
+        args.ep_chunks = 1          # every pipelined form measured slower than one slice at 2 GPUs, equal at 4
     local = int(os.environ.get("LOCAL_RANK", 0))
     if args.impl == "reference":
         return run_reference(args, wl, rank, world)
@@ -651,7 +651,11 @@ def main():
     x_dev, out_dev = torch.empty_like(t["x"]), torch.empty_like(t["x"])
     if world > 1:
         # token slices on separate streams: the copies of one slice run under the kernels of another
-        e2e_runner = runner if args.e2e_chunks == args.ep_chunks else make_runner(args.e2e_chunks)
+        if dedup:     # host buffers: one stream per slice (copy-in, forward, copy-out), every kernel with the whole GPU
+            e2e_runner = ep.PipelinedExpertParallelMoE(t, TOP_K, dist.group.WORLD, n_tokens=wl["n_tokens"],
+                                                       chunks=args.e2e_chunks, dedup=True, gemm_ctas=0, comm_ctas=0)
+        else:
+            e2e_runner = runner if args.e2e_chunks == args.ep_chunks else make_runner(args.e2e_chunks)
         e2e_step = lambda: e2e_runner.forward_host(x_host, out_host, x_dev, out_dev)
     else:
         if ws is not None:

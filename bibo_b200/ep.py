@@ -655,8 +655,10 @@ class PipelinedDedupMoE:
             comm_ctas = comm_sms
         self.lanes = [DedupExpertParallelMoE(weights, top_k, group, max_ctas=gemm_ctas, comm_ctas=comm_ctas, **kw)
                       for _ in range(self.chunks)]
-        self.link = torch.cuda.Stream(device=dev, priority=-1)     # exchange kernels are scheduled first
-        self.tensor = torch.cuda.Stream(device=dev)
+        # the grouped GEMMs' CTAs are placed first whenever SMs come free; exchange blocks take what is left
+        prio = int(os.environ.get("BIBO_EP_LINK_PRIORITY", "0"))
+        self.link = torch.cuda.Stream(device=dev, priority=prio)
+        self.tensor = torch.cuda.Stream(device=dev, priority=-1 if prio == 0 else 0)
         self.copy_in, self.copy_out = torch.cuda.Stream(device=dev), torch.cuda.Stream(device=dev)
         ev = lambda: [torch.cuda.Event() for _ in range(self.chunks)]
         self._received, self._computed, self._returned, self._copied, self._done = ev(), ev(), ev(), ev(), ev()
