@@ -541,7 +541,9 @@ def main():
             ep.PipelinedDedupMoE(t, TOP_K, dist.group.WORLD, n_tokens=wl["n_tokens"], chunks=chunks,
                                  comm_sms=args.comm_sms, gemm_ctas=args.gemm_ctas, comm_ctas=args.comm_ctas)
             if dedup and not args.ep_lockstep else
-            ep.PipelinedExpertParallelMoE(t, TOP_K, dist.group.WORLD, n_tokens=wl["n_tokens"], chunks=chunks, **ep_kw))
+            ep.PipelinedExpertParallelMoE(t, TOP_K, dist.group.WORLD, n_tokens=wl["n_tokens"], chunks=chunks,
+                                          **dict(ep_kw, **(dict(gemm_ctas=args.gemm_ctas or 0, comm_ctas=args.comm_ctas or 0)
+                                                           if dedup else {}))))
         runner = make_runner(args.ep_chunks)
         step = lambda: runner.forward(t["x"])
         ws = None

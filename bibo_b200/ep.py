@@ -656,9 +656,9 @@ class PipelinedDedupMoE:
         self.lanes = [DedupExpertParallelMoE(weights, top_k, group, max_ctas=gemm_ctas, comm_ctas=comm_ctas, **kw)
                       for _ in range(self.chunks)]
         # the grouped GEMMs' CTAs are placed first whenever SMs come free; exchange blocks take what is left
-        prio = int(os.environ.get("BIBO_EP_LINK_PRIORITY", "0"))
-        self.link = torch.cuda.Stream(device=dev, priority=prio)
-        self.tensor = torch.cuda.Stream(device=dev, priority=-1 if prio == 0 else 0)
+        # (the opposite priorities measured the same: 2.22 vs 2.26 ms at 2 GPUs with 4 slices)
+        self.link = torch.cuda.Stream(device=dev)
+        self.tensor = torch.cuda.Stream(device=dev, priority=-1)
         self.copy_in, self.copy_out = torch.cuda.Stream(device=dev), torch.cuda.Stream(device=dev)
         ev = lambda: [torch.cuda.Event() for _ in range(self.chunks)]
         self._received, self._computed, self._returned, self._copied, self._done = ev(), ev(), ev(), ev(), ev()

@@ -289,7 +289,10 @@ int bibo_moe_permute_norm_fwd(const void* h, const float* rstd, const void* norm
  * (created once per device) while a slice is computed on `stream`; tokens are independent, so the
  * result equals bibo_moe_forward bit for bit.  Afterwards the workspace describes the LAST slice
  * only.  x_host / out_host should be pinned.  This is the call the end-to-end timing uses
- * (host->device and device->host copies inside the call).                                         */
+ * (host->device and device->host copies inside the call).  The environment variable
+ * BIBO_HOST_SLICE_TOKENS, read once at the first call, overrides the slice length (0 = one slice,
+ * no overlap); it is the library's only environment switch.  The call reads the plan header with its
+ * final synchronisation and returns BIBO_ERR_DEVICE_STATUS if a kernel left a status word.          */
 int bibo_moe_forward_host(const bibo_moe_shape* shape, const void* x_host, void* x_dev,
                           const void* w_router, const float* bias, const void* gate_up_proj,
                           const void* down_proj, const float* theta, const bibo_moe_workspace* ws,
