@@ -66,7 +66,7 @@ __global__ void __launch_bounds__(DW_TAGGED * 32, 1)
 ep_dedup_dispatch_kernel(const uint8_t* __restrict__ x, const int32_t* __restrict__ topk_idx,
                          const float* __restrict__ topk_w, PeerPtrs xu, PeerPtrs midx, PeerPtrs mw,
                          int64_t n_tokens, int64_t n_cap, int row_bytes, int n_experts, int rank, int world,
-                         int top_k) {
+                         int top_k, int records) {
   const int lane = threadIdx.x & 31;
   const int el = n_experts / world;
   for (int64_t t = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5); t < n_cap; t += (int64_t)gridDim.x * (blockDim.x >> 5)) {
@@ -85,7 +85,7 @@ ep_dedup_dispatch_kernel(const uint8_t* __restrict__ x, const int32_t* __restric
       const int o = __shfl_sync(0xffffffffu, owner, j);
       if (j < top_k && o >= 0) hit |= 1u << o;
     }
-    if (lane < top_k) {
+    if (records && lane < top_k) {
       for (int d = 0; d < world; ++d) {
         static_cast<int32_t*>(midx.p[d])[v * top_k + lane] = owner == d ? e - d * el : -1;
         static_cast<float*>(mw.p[d])[v * top_k + lane] = w;
@@ -355,13 +355,18 @@ extern "C" int bibo_moe_ep_dedup_dispatch(const void* x, const int32_t* topk_idx
     return fail(BIBO_ERR_ARG, "ep_dedup_dispatch: null or unaligned input");
   PeerPtrs xu = {}, mi = {}, mw = {};
   if ((rc = fill_peers("ep_dedup_dispatch", xu_peers, world, &xu))) return rc;
-  if ((rc = fill_peers("ep_dedup_dispatch", midx_peers, world, &mi))) return rc;
-  if ((rc = fill_peers("ep_dedup_dispatch", mw_peers, world, &mw))) return rc;
+  // without record tables only the rows travel: the caller sends the routing records as two block copies per
+  // peer (bibo_moe_ep_copy_to_peers + bibo_moe_ep_localize) instead of 2 * world small remote stores per token
+  const int records = midx_peers != nullptr && mw_peers != nullptr;
+  if (records) {
+    if ((rc = fill_peers("ep_dedup_dispatch", midx_peers, world, &mi))) return rc;
+    if ((rc = fill_peers("ep_dedup_dispatch", mw_peers, world, &mw))) return rc;
+  }
   dedup_set_carveouts();
   ep_dedup_dispatch_kernel<<<exchange_grid(n_cap, comm_ctas), exchange_block(comm_ctas), exchange_smem(comm_ctas),
                              static_cast<cudaStream_t>(stream)>>>(
       static_cast<const uint8_t*>(x), topk_idx, topk_w, xu, mi, mw, n_tokens, n_cap, hidden * 2, n_experts, rank, world,
-      top_k);
+      top_k, records);
   BIBO_CHECK_LAUNCH("ep_dedup_dispatch_kernel");
   return BIBO_OK;
 }

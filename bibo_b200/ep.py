@@ -524,10 +524,25 @@ class DedupExpertParallelMoE:
                                                p(b.topk_idx), p(b.topk_w), p(b.slot_rank_home), p(b.block_counts_home),
                                                p(b.plan[2:]), st), "bibo_moe_router_fwd")
         self._mark("route")
-        _lib.check(lib.bibo_moe_ep_dedup_dispatch(p(x) if n else None, p(b.topk_idx), p(b.topk_w), b.sym_xu.ptr_array,
-                                                  b.sym_midx.ptr_array, b.sym_mw.ptr_array, n, self._n_cap, hidden,
-                                                  self.n_experts, self.rank, self.world, self.top_k, self.comm_ctas, st),
-                   "bibo_moe_ep_dedup_dispatch")
+        raw = getattr(b, "sym_raw", None)
+        if raw is None:
+            _lib.check(lib.bibo_moe_ep_dedup_dispatch(p(x) if n else None, p(b.topk_idx), p(b.topk_w), b.sym_xu.ptr_array,
+                                                      b.sym_midx.ptr_array, b.sym_mw.ptr_array, n, self._n_cap, hidden,
+                                                      self.n_experts, self.rank, self.world, self.top_k, self.comm_ctas,
+                                                      st), "bibo_moe_ep_dedup_dispatch")
+        else:
+            # pipelined form: the records travel as two block copies per peer (copy engines), the kernel stores rows only
+            if n < b.n_routed:
+                b.topk_idx[n:].fill_(-1)
+            b.n_routed = n
+            block = self._n_cap * self.top_k * 4
+            for sym, src in ((raw, b.topk_idx), (b.sym_mw, b.topk_w)):
+                _lib.check(lib.bibo_moe_ep_copy_to_peers(sym.ptr_array, self.rank * block, p(src), 0, block, self.rank,
+                                                         self.world, 1, st), "bibo_moe_ep_copy_to_peers")
+            _lib.check(lib.bibo_moe_ep_dedup_dispatch(p(x) if n else None, p(b.topk_idx), p(b.topk_w), b.sym_xu.ptr_array,
+                                                      None, None, n, self._n_cap, hidden, self.n_experts, self.rank,
+                                                      self.world, self.top_k, self.comm_ctas, st),
+                       "bibo_moe_ep_dedup_dispatch")
         self._mark("dispatch")
         self._barrier(st)
         self._mark("received")
@@ -543,6 +558,10 @@ class DedupExpertParallelMoE:
         buffer (``add_staging``) the partial rows are summed here too, at full HBM speed, into that buffer."""
         st = torch.cuda.current_stream(self.device).cuda_stream
         lib, b = _lib.load(), self.buf
+        if getattr(b, "sym_raw", None) is not None:      # records arrived as raw top-k tables: keep this rank's slots
+            _lib.check(lib.bibo_moe_ep_localize(_lib.ptr(b.sym_raw.tensor), self.world * self._n_cap, self.top_k,
+                                                self.n_experts, self.rank, self.world, _lib.ptr(b.midx), st),
+                       "bibo_moe_ep_localize")
         if getattr(b, "pstage", None) is None:
             _lib.check(lib.bibo_moe_ep_dedup_experts(C.byref(self._owner()), st), "bibo_moe_ep_dedup_experts")
             return
@@ -551,9 +570,16 @@ class DedupExpertParallelMoE:
         _lib.check(lib.bibo_moe_ep_dedup_owner(C.byref(owner), st), "bibo_moe_ep_dedup_owner")
 
     def add_staging(self) -> None:
-        """A local buffer for the partial rows of other ranks' tokens (the own rank's go straight into ``part``)."""
+        """A local buffer for the partial rows of other ranks' tokens (the own rank's go straight into ``part``),
+        and a peer-mapped table for the raw top-k records of every rank (sent as block copies)."""
         b = self.buf
         nv = self.world * self._n_cap
+        b.sym_raw = _Symmetric((nv, self.top_k), torch.int32, self.device, self.group)
+        b.sym_raw.tensor.fill_(-1)
+        b.topk_idx.fill_(-1)
+        b.n_routed = self._n_cap
+        torch.cuda.synchronize(self.device)
+        dist.barrier(self.group)
         b.pstage = torch.empty(nv, self.hidden, dtype=torch.bfloat16, device=self.device)
         row = self._n_cap * self.hidden * 2
         table = [b.pstage.data_ptr() + (s_ - self.rank) * row for s_ in range(self.world)]

@@ -469,7 +469,9 @@ int bibo_moe_ep_backward(const bibo_moe_ep_args* fwd, const bibo_moe_ep_bwd_args
 int64_t bibo_moe_ep_dedup_rows_cap(int world, int64_t n_cap, int top_k, int n_experts);
 int64_t bibo_moe_ep_dedup_plan_words(int world, int64_t n_cap, int top_k, int n_experts);
 int64_t bibo_moe_ep_dedup_virtual_tokens(int world, int64_t n_cap);
-/* home rank: rows to the distinct owners of each token, routing records to every rank                     */
+/* home rank: rows to the distinct owners of each token, routing records to every rank.  midx_peers / mw_peers
+ * may be NULL: then only rows are stored and the caller ships the records as block copies of its top-k table
+ * (bibo_moe_ep_copy_to_peers into a raw table, bibo_moe_ep_localize on the owner).                         */
 int bibo_moe_ep_dedup_dispatch(const void* x, const int32_t* topk_idx, const float* topk_w,
                                void* const* xu_peers, void* const* midx_peers, void* const* mw_peers,
                                int64_t n_tokens, int64_t n_cap, int hidden, int n_experts, int rank,
