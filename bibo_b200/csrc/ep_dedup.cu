@@ -232,10 +232,13 @@ ep_dedup_push_kernel(const uint8_t* __restrict__ stage, const int32_t* __restric
 }
 
 // Warp per home token: adds the partial rows of the owners the token was sent to, ascending owner.
+// W = ranks the kernel is compiled for (2, 4 or 8): 8 / W chunks of every owner's row are in flight per lane.
+template <int W>
 __global__ void __launch_bounds__(DW_TAGGED * 32, 1)
 ep_dedup_final_kernel(const __nv_bfloat16* __restrict__ part, const int32_t* __restrict__ topk_idx,
                       const int32_t* __restrict__ status, int64_t n_tokens, int64_t n_cap, int hidden, int n_experts,
                       int world, int top_k, __nv_bfloat16* __restrict__ out) {
+  constexpr int U = 8 / W;
   const int lane = threadIdx.x & 31;
   if (status[0] != 0) return;
   const int el = n_experts / world;
@@ -253,19 +256,25 @@ ep_dedup_final_kernel(const __nv_bfloat16* __restrict__ part, const int32_t* __r
     }
     uint4* dst = reinterpret_cast<uint4*>(out + t * hidden);
     const int chunks = hidden >> 3;
-    for (int c = lane; c < chunks; c += 32) {
-      uint4 val[EP_MAX_RANKS];
+    for (int c0 = lane; c0 < chunks; c0 += 32 * U) {
+      uint4 val[U][W];
 #pragma unroll
-      for (int d = 0; d < EP_MAX_RANKS; ++d)
-        if ((hit >> d) & 1u)
-          val[d] = __ldcs(reinterpret_cast<const uint4*>(part + ((int64_t)d * n_cap + t) * hidden) + c);
-      float a[8];
+      for (int u = 0; u < U; ++u)
 #pragma unroll
-      for (int q = 0; q < 8; ++q) a[q] = 0.f;
+        for (int d = 0; d < W; ++d)
+          if (((hit >> d) & 1u) && c0 + u * 32 < chunks)
+            val[u][d] = __ldcs(reinterpret_cast<const uint4*>(part + ((int64_t)d * n_cap + t) * hidden) + c0 + u * 32);
 #pragma unroll
-      for (int d = 0; d < EP_MAX_RANKS; ++d)
-        if ((hit >> d) & 1u) fma_bf16x8_d(val[d], 1.0f, a);
-      dst[c] = pack_bf16x8(a);
+      for (int u = 0; u < U; ++u) {
+        if (c0 + u * 32 >= chunks) continue;
+        float a[8];
+#pragma unroll
+        for (int q = 0; q < 8; ++q) a[q] = 0.f;
+#pragma unroll
+        for (int d = 0; d < W; ++d)
+          if ((hit >> d) & 1u) fma_bf16x8_d(val[u][d], 1.0f, a);
+        dst[c0 + u * 32] = pack_bf16x8(a);
+      }
     }
   }
 }
@@ -296,7 +305,8 @@ static void dedup_set_carveouts() {
   static DeviceOnce once;
   once.get([](int*) {
     allow_tag_smem(ep_dedup_dispatch_kernel);
-    allow_tag_smem(ep_dedup_final_kernel);
+    allow_tag_smem(ep_dedup_final_kernel<2>); allow_tag_smem(ep_dedup_final_kernel<4>);
+    allow_tag_smem(ep_dedup_final_kernel<8>);
     allow_tag_smem(ep_dedup_push_kernel);
     prefer_max_smem_d(ep_dedup_push_kernel);
     allow_tag_smem(ep_dedup_partial_kernel<1>); allow_tag_smem(ep_dedup_partial_kernel<2>);
@@ -304,7 +314,8 @@ static void dedup_set_carveouts() {
     allow_tag_smem(ep_dedup_partial_kernel<5>); allow_tag_smem(ep_dedup_partial_kernel<6>);
     allow_tag_smem(ep_dedup_partial_kernel<7>); allow_tag_smem(ep_dedup_partial_kernel<8>);
     prefer_max_smem_d(ep_dedup_dispatch_kernel);
-    prefer_max_smem_d(ep_dedup_final_kernel);
+    prefer_max_smem_d(ep_dedup_final_kernel<2>); prefer_max_smem_d(ep_dedup_final_kernel<4>);
+    prefer_max_smem_d(ep_dedup_final_kernel<8>);
     prefer_max_smem_d(ep_dedup_partial_kernel<1>); prefer_max_smem_d(ep_dedup_partial_kernel<2>);
     prefer_max_smem_d(ep_dedup_partial_kernel<3>); prefer_max_smem_d(ep_dedup_partial_kernel<4>);
     prefer_max_smem_d(ep_dedup_partial_kernel<5>); prefer_max_smem_d(ep_dedup_partial_kernel<6>);
@@ -477,10 +488,17 @@ extern "C" int bibo_moe_ep_dedup_final(const void* part, const int32_t* topk_idx
   if (!part || !topk_idx || !status || !out || !aligned16(part) || !aligned16(out))
     return fail(BIBO_ERR_ARG, "ep_dedup_final: null or unaligned pointer");
   dedup_set_carveouts();
-  ep_dedup_final_kernel<<<exchange_grid(n_tokens, comm_ctas), exchange_block(comm_ctas), exchange_smem(comm_ctas),
-                          static_cast<cudaStream_t>(stream)>>>(
-      static_cast<const __nv_bfloat16*>(part), topk_idx, status, n_tokens, n_cap, hidden, n_experts, world, top_k,
-      static_cast<__nv_bfloat16*>(out));
+  const dim3 grid(exchange_grid(n_tokens, comm_ctas)), block(exchange_block(comm_ctas));
+  const size_t smem = exchange_smem(comm_ctas);
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const __nv_bfloat16* pp = static_cast<const __nv_bfloat16*>(part);
+  __nv_bfloat16* oo = static_cast<__nv_bfloat16*>(out);
+  if (world <= 2)
+    ep_dedup_final_kernel<2><<<grid, block, smem, st>>>(pp, topk_idx, status, n_tokens, n_cap, hidden, n_experts, world, top_k, oo);
+  else if (world <= 4)
+    ep_dedup_final_kernel<4><<<grid, block, smem, st>>>(pp, topk_idx, status, n_tokens, n_cap, hidden, n_experts, world, top_k, oo);
+  else
+    ep_dedup_final_kernel<8><<<grid, block, smem, st>>>(pp, topk_idx, status, n_tokens, n_cap, hidden, n_experts, world, top_k, oo);
   BIBO_CHECK_LAUNCH("ep_dedup_final_kernel");
   return BIBO_OK;
 }

@@ -24,6 +24,29 @@ def test_library_exports_every_declared_symbol():
     assert lib.bibo_moe_version() >= 100
 
 
+def test_argument_errors_of_the_newer_entry_points_without_a_gpu():
+    """Every check below fails before the first CUDA call."""
+    from bibo_b200 import _lib
+    lib = _lib.load()
+    one = ctypes.c_int(0)
+    p = ctypes.addressof(one) & ~15 | 16          # a non-null, 16-byte aligned dummy that is never dereferenced
+    assert lib.bibo_moe_rowmap_fwd(None, None, None, 10, 64, 64, 6, None, None, None) == -1
+    assert lib.bibo_moe_gemm1_gather_supported(1024, 128, _lib.BF16) == 0 and lib.bibo_moe_gemm1_gather_supported(2048, 512, _lib.BF16) == 1
+    rc = lib.bibo_moe_gemm1_gather_fwd(p, p, p, p, p, 10, 1024, 128, 64, 64, 6, _lib.BF16, 0, p, p, None, None, None)
+    assert rc == -4 and b"intermediate 256 or 512" in lib.bibo_moe_last_error_string()
+    assert lib.bibo_moe_ep_copy_to_peers(None, 0, None, 0, 16, 0, 2, 1, None) == -1
+    assert lib.bibo_moe_ep_copy_to_peers((ctypes.c_void_p * 2)(p, p), 0, p, 0, 16, 3, 2, 1, None) == -1      # rank >= world
+    assert lib.bibo_moe_ep_localize(None, 10, 6, 64, 0, 2, None, None) == -1
+    assert lib.bibo_moe_ep_localize(p, 10, 6, 63, 0, 2, p, None) == -1                                        # 63 experts over 2 ranks
+    assert lib.bibo_moe_ep_dedup_push(None, None, None, None, 128, 512, 6, 0, 2, 0, None) == -1
+    assert lib.bibo_moe_ep_dedup_experts(None, None) == -1 and lib.bibo_moe_ep_dedup_partial(None, None) == -1
+    assert lib.bibo_moe_ep_dedup_forward(None, None) == -1
+    assert lib.bibo_moe_ep_barrier_bounded(None, 0, 2, 1, 100, None, None) == -1
+    assert lib.bibo_moe_route_noalloc_status(None, None) == -1
+    assert lib.bibo_moe_ep_dedup_virtual_tokens(8, 1000) == 8000
+    assert lib.bibo_moe_ep_dedup_plan_words(4, 1024, 6, 64) == lib.bibo_moe_plan_words(4096, 6, 16, 16)
+
+
 def test_size_helpers_and_argument_errors_without_a_gpu():
     from bibo_b200 import _lib
     lib = _lib.load()
