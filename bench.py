@@ -378,35 +378,50 @@ def nvlink_roofline(args, wl, t, runner, world, rank, ep_phases):
                            "spans all token slices, whose phases overlap other slices' GEMMs"}
 
 
-def run_c5(args):
-    """Benchmark configuration 5 on one GPU: the reference's own 10-layer BiBoModel (from oracle/_ref), bf16, a
-    prefill of 8 x 4096 token ids, first unmodified (eager PyTorch everywhere), then with ONLY the feed-forward
-    blocks swapped for the kernels (bibo_b200.install() + install(seam="mlp")).  Prints one JSON line: prefill
+def run_c5(args, rank=0, world=1, local=0):
+    """Benchmark configuration 5: the reference's own 10-layer BiBoModel (from oracle/_ref), bf16, a prefill of
+    8 x 4096 token ids on one GPU (on N GPUs: data-parallel replicas, one sequence of 4096 ids per GPU, every
+    replica with all 64 experts; times are the maximum over the ranks), first unmodified (eager PyTorch
+    everywhere), then with ONLY the feed-forward blocks swapped for the kernels (bibo_b200.install() +
+    install(seam="mlp")).  Prints one JSON line: prefill
     tokens/s with the kernels, the unmodified model's figure, the share of the prefill spent inside the
     feed-forward blocks in both runs (CUDA events around every .mlp module), and how far the two last hidden
     states are apart."""
     from oracle import make_ref
-    line = {"metric": "c5_prefill_tokens_per_s", "unit": UNIT, "n_gpus": 1, "higher_is_better": True, "dtype": "bf16",
-            "data": "synthetic", "config": {"workload": "c5: 10-layer BiBo prefill, batch 8 x sequence 4096, hidden 1024, "
-                                            "layers 0/9 dense MLP (4096), layers 1-8 MoE (64 experts, top-6, 256)"}}
+    batch = 8 if world == 1 else 1
+    line = {"metric": "c5_prefill_tokens_per_s", "unit": UNIT, "n_gpus": world, "higher_is_better": True, "dtype": "bf16",
+            "scaling": "weak" if world == 1 else "replicas only (one sequence per GPU, no exchange)",
+            "data": "synthetic", "config": {"workload": f"c5: 10-layer BiBo prefill, batch {batch} x sequence 4096 per GPU, "
+                                            "hidden 1024, layers 0/9 dense MLP (4096), layers 1-8 MoE (64 experts, top-6, 256)"}}
     if not make_ref.available():
         line["unavailable"] = "oracle/_ref is absent on this machine (python oracle/make_ref.py needs a checkout of the reference)"
-        print(json.dumps(line))
+        if rank == 0:
+            print(json.dumps(line))
         return
     make_ref.activate()
     import bibo_b200
     from src.configuration_bibo import BiBoConfig
     from src.modeling.models import BiBoModel
-    dev = torch.device("cuda", 0)
-    torch.cuda.set_device(0)
+    dev = torch.device("cuda", local)
+    torch.cuda.set_device(local)
+    if world > 1:
+        import torch.distributed as dist
+        dist.init_process_group("nccl", device_id=dev)
     cfg = BiBoConfig(vocab_size=32000, hidden_size=1024, intermediate_size=4096, num_hidden_layers=10,
                      num_attention_heads=4, num_key_value_heads=2, moe_intermediate_size=256, num_routed_experts=N_EXPERTS,
                      num_experts_per_tok=TOP_K, special_expert_pairs=0, hybrid_layer_pattern=[0, 1, 1, 0, 1, 1, 0, 1, 1, 0],
                      sliding_window=128, tie_word_embeddings=True, mlp_only_layers=[0, 9], use_cache=False)
     torch.manual_seed(0)
     model = BiBoModel(cfg).to(torch.bfloat16).to(dev).eval()
-    batch, seq = 8, 4096
-    ids = torch.randint(0, 32000, (batch, seq), generator=torch.Generator().manual_seed(1)).to(dev)
+    seq = 4096
+    ids = torch.randint(0, 32000, (batch, seq), generator=torch.Generator().manual_seed(1 + rank)).to(dev)
+
+    def over_ranks(ms):
+        if world == 1:
+            return ms
+        v = torch.tensor([ms], device=dev)
+        dist.all_reduce(v, op=dist.ReduceOp.MAX)
+        return float(v)
 
     def timed(steps):
         spans = []
@@ -422,6 +437,8 @@ def run_c5(args):
             spans.clear()
             e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
             torch.cuda.synchronize()
+            if world > 1:
+                dist.barrier()
             e0.record()
             for _ in range(steps):
                 model(input_ids=ids, use_cache=False)
@@ -429,8 +446,8 @@ def run_c5(args):
             torch.cuda.synchronize()
         for h in hooks:
             h.remove()
-        total = e0.elapsed_time(e1) / steps
-        ffn = sum(a.elapsed_time(b) for a, b in spans) / steps
+        total = over_ranks(e0.elapsed_time(e1) / steps)
+        ffn = over_ranks(sum(a.elapsed_time(b) for a, b in spans) / steps)
         return total, ffn, out
 
     steps = max(1, min(args.steps, 5))
@@ -447,12 +464,16 @@ def run_c5(args):
         bibo_b200.uninstall()
     g, r = out.reshape(-1, 1024).float(), ref_out.reshape(-1, 1024).float()
     per_tok = (g - r).norm(dim=-1) / r.norm(dim=-1).clamp_min(1e-30)
+    if world > 1:
+        dist.destroy_process_group()
+    if rank != 0:
+        return
     line.update({
-        "value": batch * seq / (ms * 1e-3), "steps": steps, "warmup": 1, "ms_per_step": round(ms, 3),
+        "value": world * batch * seq / (ms * 1e-3), "steps": steps, "warmup": 1, "ms_per_step": round(ms, 3),
         "feed_forward_ms": round(ffn, 3), "feed_forward_share": round(ffn / ms, 4),
         "unmodified_reference": {"ms_per_step": round(ref_ms, 3), "feed_forward_ms": round(ref_ffn, 3),
                                  "feed_forward_share": round(ref_ffn / ref_ms, 4),
-                                 "value": batch * seq / (ref_ms * 1e-3)},
+                                 "value": world * batch * seq / (ref_ms * 1e-3)},
         "prefill_speedup": round(ref_ms / ms, 3), "feed_forward_speedup": round(ref_ffn / ffn, 2),
         "gpu_launches": int(launches),
         "last_hidden_state_vs_unmodified": {"median_token_rel": float(per_tok.median()),
@@ -510,9 +531,7 @@ def main():
     if args.impl == "reference":
         return run_reference(args, wl, rank, world)
     if wl.get("model"):
-        if rank == 0:
-            run_c5(args)
-        return
+        return run_c5(args, rank, world, local)
     if args.warmup < 3:
         args.warmup = 3
 
