@@ -131,9 +131,12 @@ ep_dedup_partial_kernel(const __nv_bfloat16* __restrict__ y, const int32_t* __re
   if (plan[PLAN_STATUS] != 0) return;
   const int world = (int)(n_virtual / n_cap);
   for (int64_t i = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5); i < n_virtual; i += (int64_t)gridDim.x * (blockDim.x >> 5)) {
-    // home ranks are visited in the order rank+1, rank+2, ..., rank: at any moment every owner stores to a
-    // DIFFERENT home rank (all owners walking the blocks in the same order would aim at one receiver at a time)
-    const int64_t blk = i / n_cap, t = i - blk * n_cap;
+    // consecutive warps take the same token slot of consecutive home ranks, starting at rank+1: at any moment
+    // every owner stores to ALL home ranks at once, its own included (walking the blocks of home ranks one after
+    // the other in the same order on every owner aimed all owners at one receiver at a time: 0.4 ms of waiting
+    // for the slowest rank at 4 GPUs; walking them in a rotated order left the local, HBM-only part for the end
+    // instead of under the NVLink stores)
+    const int64_t t = i / world, blk = i - t * world;
     const int64_t s = (rank + 1 + blk) % world;
     const int64_t v = s * n_cap + t;
     int row = -1;
