@@ -127,7 +127,7 @@ class ClockSampler(threading.Thread):
                 self.reasons |= {n for b, n in self.BITS.items() if r & b}
             except Exception:
                 pass
-            time.sleep(0.02)
+            time.sleep(0.004)
 
     def stop(self):
         self._stop_evt.set()
