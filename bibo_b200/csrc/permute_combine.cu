@@ -52,26 +52,35 @@ permute_kernel(const uint8_t* __restrict__ x, const int32_t* __restrict__ topk_i
     // a token without any row (all its slots empty or on +/-Identity experts) is not even read, unless its
     // normalised row has to be kept for the combine kernel
     const bool copy = __any_sync(0xffffffffu, my_row >= 0) || keep != nullptr;
-    for (int c = lane; c < (copy ? chunks : 0); c += 32) {
-      uint4 v = __ldg(src + c);
-      if (rstd != nullptr) {
-        const uint4 wv = __ldg(reinterpret_cast<const uint4*>(norm_w) + c);
-        uint32_t* hv = reinterpret_cast<uint32_t*>(&v);
-        const uint32_t* ww = reinterpret_cast<const uint32_t*>(&wv);
+    // eight 16-byte loads of the row are in flight per lane before the first of the (up to k x 8) stores
+    for (int c0 = lane; c0 < (copy ? chunks : 0); c0 += 256) {
+      uint4 v[8];
 #pragma unroll
-        for (int i = 0; i < 4; ++i) {
-          const float a = __uint_as_float(hv[i] << 16), b = __uint_as_float(hv[i] & 0xffff0000u);
-          const float na = __bfloat162float(__float2bfloat16_rn(a * rs)), nb = __bfloat162float(__float2bfloat16_rn(b * rs));
-          const __nv_bfloat162 o = __floats2bfloat162_rn(na * __uint_as_float(ww[i] << 16),
-                                                         nb * __uint_as_float(ww[i] & 0xffff0000u));
-          hv[i] = *reinterpret_cast<const uint32_t*>(&o);
+      for (int u = 0; u < 8; ++u)
+        if (c0 + u * 32 < chunks) v[u] = __ldg(src + c0 + u * 32);
+#pragma unroll
+      for (int u = 0; u < 8; ++u) {
+        const int c = c0 + u * 32;
+        if (c >= chunks) continue;
+        if (rstd != nullptr) {
+          const uint4 wv = __ldg(reinterpret_cast<const uint4*>(norm_w) + c);
+          uint32_t* hv = reinterpret_cast<uint32_t*>(&v[u]);
+          const uint32_t* ww = reinterpret_cast<const uint32_t*>(&wv);
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            const float a = __uint_as_float(hv[i] << 16), b = __uint_as_float(hv[i] & 0xffff0000u);
+            const float na = __bfloat162float(__float2bfloat16_rn(a * rs)), nb = __bfloat162float(__float2bfloat16_rn(b * rs));
+            const __nv_bfloat162 o = __floats2bfloat162_rn(na * __uint_as_float(ww[i] << 16),
+                                                           nb * __uint_as_float(ww[i] & 0xffff0000u));
+            hv[i] = *reinterpret_cast<const uint32_t*>(&o);
+          }
+          if (keep != nullptr) keep[c] = v[u];
         }
-        if (keep != nullptr) keep[c] = v;
-      }
 #pragma unroll
-      for (int j = 0; j < BIBO_MAX_TOP_K; ++j)
-        if (j < top_k && rows[j] >= 0)
-          reinterpret_cast<uint4*>(xp + (int64_t)rows[j] * row_bytes)[c] = v;
+        for (int j = 0; j < BIBO_MAX_TOP_K; ++j)
+          if (j < top_k && rows[j] >= 0)
+            reinterpret_cast<uint4*>(xp + (int64_t)rows[j] * row_bytes)[c] = v[u];
+      }
     }
   } else {
     const int64_t p = w - n_tokens;
