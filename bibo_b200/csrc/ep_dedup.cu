@@ -120,8 +120,9 @@ ep_localize_kernel(const int32_t* __restrict__ raw, int64_t n_slots, int lo, int
   midx[i] = (e >= 0 && e < el) ? e : -1;
 }
 
-// Warp per virtual token v = s*n_cap + t of this owner.  Its local slots form one run of consecutive j
-// (the k experts of a token are ascending and this owner's experts are contiguous).
+// Warp per virtual token v = s*n_cap + t of this owner.  Its local slots are summed in ascending slot order:
+// with the router's ascending expert lists that is ascending expert order (the order of the single-GPU
+// combine); a caller-routed list in another order changes only the order of the fp32 additions.
 template <int K>
 __global__ void __launch_bounds__(DW_TAGGED * 32, 1)
 ep_dedup_partial_kernel(const __nv_bfloat16* __restrict__ y, const int32_t* __restrict__ slot_row,
@@ -144,13 +145,16 @@ ep_dedup_partial_kernel(const __nv_bfloat16* __restrict__ y, const int32_t* __re
     if (lane < K) { row = slot_row[v * K + lane]; w = mw[v * K + lane]; }
     const unsigned valid = __ballot_sync(0xffffffffu, row >= 0);
     if (valid == 0) continue;
-    const int j0 = __ffs(valid) - 1, cnt = __popc(valid);
+    const int cnt = __popc(valid);
     const uint4* src[K];
     float ws[K];
+    unsigned rest = valid;                             // the local slots in ascending slot order, wherever they sit
 #pragma unroll
     for (int i = 0; i < K; ++i) {
-      const int r = __shfl_sync(0xffffffffu, row, min(j0 + i, 31));
-      ws[i] = __shfl_sync(0xffffffffu, w, min(j0 + i, 31));
+      const int j = rest ? __ffs(rest) - 1 : 0;
+      rest &= rest - 1;
+      const int r = __shfl_sync(0xffffffffu, row, j);
+      ws[i] = __shfl_sync(0xffffffffu, w, j);
       src[i] = reinterpret_cast<const uint4*>(y + (int64_t)(i < cnt ? r : 0) * hidden);
     }
     uint4* dst = reinterpret_cast<uint4*>(static_cast<__nv_bfloat16*>(part.p[s]) + ((int64_t)rank * n_cap + t) * hidden);

@@ -457,7 +457,8 @@ int bibo_moe_ep_backward(const bibo_moe_ep_args* fwd, const bibo_moe_ep_bwd_args
  *   part [world*n_cap, H] bf16   on the home rank: part[d*n_cap + t] = owner d's contribution to token t
  * n_cap = the largest token count of any rank.  The owner runs the caller-routed single-GPU chain (rank with
  * empty slots, plan, permute, gate/up, down) over the world*n_cap virtual tokens of its receive buffer with
- * its E/world experts and then sums each virtual token's local slots (fp32, ascending expert) into ONE bf16
+ * its E/world experts and then sums each virtual token's local slots (fp32, in slot order: ascending expert
+ * for the router's lists; a caller's list may be in any order and may hold -1 for unused slots) into ONE bf16
  * row stored into the home rank's `part`; the home rank adds the partial rows of the owners a token went to
  * in ascending owner order.  Same summation order as one GPU, one extra bf16 rounding per owner: inside the
  * bf16 parity bars of the fp32 oracle, not bit-identical to the single-GPU chain.

@@ -29,9 +29,11 @@ def _weights(hidden, inter, seed):
     return inp, t
 
 
-def _play(world, counts, t, hidden, inter, xs, bufs=None, comm_ctas=0, staged=False):
+def _play(world, counts, t, hidden, inter, xs, bufs=None, comm_ctas=0, staged=False, shuffle=None):
     """One forward of `world` ranks on this device; returns (outs per rank, buffers).  ``staged``: the owners sum
-    their partial rows into a local staging buffer and a separate streaming kernel moves them to the home ranks."""
+    their partial rows into a local staging buffer and a separate streaming kernel moves them to the home ranks.
+    ``shuffle``: a generator; every token's k slots are put into a random order before the dispatch (a caller
+    that routes by itself, as ``torch.topk(sorted=False)`` gives no order) and one slot in eight is emptied."""
     from bibo_b200 import _lib, ep, functional as Fn
     lib, p = _lib.load(), _lib.ptr
     n_cap = max(max(counts), 1)
@@ -47,6 +49,11 @@ def _play(world, counts, t, hidden, inter, xs, bufs=None, comm_ctas=0, staged=Fa
             _lib.check(lib.bibo_moe_router_fwd(p(xs[r]), p(t["w_router"]), p(t["bias"]), None, n, hidden, E, K,
                                                _lib.NORM_SUM, 1.0, _lib.BF16, None, p(b.topk_idx), p(b.topk_w),
                                                p(b.slot_rank_home), p(b.block_counts_home), p(b.plan[2:]), st), "router")
+            if shuffle is not None:
+                perm = torch.argsort(torch.rand(n, K, generator=shuffle), dim=1).to(DEV)
+                drop = (torch.rand(n, K, generator=shuffle) < 0.125).to(DEV)
+                b.topk_idx[:n] = torch.where(drop, -1, b.topk_idx[:n].gather(1, perm))
+                b.topk_w[:n] = b.topk_w[:n].gather(1, perm)
         _lib.check(lib.bibo_moe_ep_dedup_dispatch(p(xs[r]) if n else None, p(b.topk_idx), p(b.topk_w), xu, midx, mw, n,
                                                   n_cap, hidden, E, r, world, K, comm_ctas, st), "dispatch")
     for r in range(world):                                    # owner: experts + partial sums
@@ -132,6 +139,28 @@ def test_partial_rows_through_a_staging_buffer(world, comm_ctas):
     """Same result when the owners sum into a local staging buffer and a streaming kernel carries the rows home."""
     counts = [600, 333, 128, 900, 1, 512, 64, 257][:world]
     _check(world, counts, hidden=512, inter=256, seed=30 + world, comm_ctas=comm_ctas, staged=True)
+
+
+def test_caller_routed_lists_in_any_order_with_empty_slots():
+    """Slots of a token in random order and some of them empty (-1): against the caller-routed single-GPU chain
+    on the same lists (the order changes only the order of the fp32 additions)."""
+    from bibo_b200 import functional as Fn
+    world, counts, hidden, inter = 4, [800, 257, 1, 600], 512, 256
+    _, t = _weights(hidden, inter, seed=3)
+    g = torch.Generator().manual_seed(77)
+    xs = [torch.randn(n, hidden, generator=g).to(torch.bfloat16).to(DEV) for n in counts]
+    outs, bufs = _play(world, counts, t, hidden, inter, xs, shuffle=g)
+    idx = torch.cat([bufs[r].topk_idx[:n] for r, n in enumerate(counts)])
+    w = torch.cat([bufs[r].topk_w[:n] for r, n in enumerate(counts)])
+    assert bool((idx < 0).any()) and not bool((idx[:, 1:] >= idx[:, :-1]).all())
+    ref, _ = Fn.experts_forward(torch.cat(xs), idx, w, t["gate_up_proj"], t["down_proj"], t["radial_theta"], E)
+    torch.cuda.synchronize()
+    got = torch.cat(outs)
+    assert not bool(torch.isnan(got.float()).any())
+    assert rel_err(got.float(), ref.float()) < 1.2e-2
+    assert mean_rel_err(got.float(), ref.float()) < 4e-3
+    empty = (idx < 0).all(-1)
+    assert not bool(got[empty].float().abs().any())
 
 
 def test_argument_checks():
