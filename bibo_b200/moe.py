@@ -231,7 +231,11 @@ class BiBoMoELayer(nn.Module):
 
 
 def _balance_from_counts(layer, counts: torch.Tensor, num_tokens: int):
-    """`_balance_step` of the reference (moe.py:139-155) fed with the kernel's histogram."""
+    """`_balance_step` of the reference (moe.py:139-155) fed with the kernel's histogram.
+
+    As in the reference, the histogram is accumulated in the dtype of the ``accumulated_tpe`` buffer: a module
+    cast with ``.to(torch.bfloat16)`` carries a bf16 buffer, which rounds counts above 256.  Callers that want
+    exact counts keep that buffer fp32 (``layer.accumulated_tpe = layer.accumulated_tpe.float()``)."""
     with torch.no_grad():
         layer.accumulated_tpe += counts.float()
         if layer._update_every is None:

@@ -51,6 +51,10 @@ def main():
     shard.gate.bias.data = full.gate.bias.data.clone()
     lo, hi = rank * shard.el, (rank + 1) * shard.el
     shard.radial_theta.data = inp["radial_theta"][lo:hi].to(dev)
+    # the cast above also took the balancer's histogram buffer to bf16 (8 bits of mantissa: counts above 256 would be
+    # rounded, differently in the two layers, which sum them in a different order); keep it fp32 like bias and theta
+    full.accumulated_tpe = full.accumulated_tpe.float()
+    shard.accumulated_tpe = shard.accumulated_tpe.float()
 
     x_all = inp["x"].to(torch.bfloat16).to(dev)
     xs = x_all[rank * n:(rank + 1) * n].clone().requires_grad_(True)
@@ -95,7 +99,9 @@ def main():
     ok &= trace_same
     bias_same = torch.allclose(shard.gate.bias.data, full.gate.bias.data, rtol=0, atol=1e-7)
     moved = float((full.gate.bias.data - inp["bias"].to(dev)).abs().max()) > 0
-    msgs.append(f"bias update identical {bias_same} (moved {moved})")
+    bias_diff = float((shard.gate.bias.data - full.gate.bias.data).abs().max())
+    msgs.append(f"bias update identical {bias_same} (moved {moved}, max diff {bias_diff:.2e}, update every "
+                f"{shard._update_every} / {full._update_every} forwards, forwards {shard._fwd_step} / {full._fwd_step})")
     ok &= bias_same and moved
     print(f"rank {rank}: " + "; ".join(msgs), flush=True)
     flag = torch.tensor([1 if ok else 0], device=dev)
