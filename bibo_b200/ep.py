@@ -420,7 +420,13 @@ class DedupExpertParallelMoE:
     one row per (token, destination rank) goes out, one partial result row per (token, rank) comes back
     (``bibo_moe_ep_dedup_forward``).  Dropless: the owner's buffers hold the worst case.  Results are within
     the bf16 parity bars of the fp32 oracle; they are not bit-identical to the single-GPU chain (every rank's
-    partial sum is rounded to bf16 once).  ``weights`` as for ``ExpertParallelMoE``."""
+    partial sum is rounded to bf16 once).  ``weights`` as for ``ExpertParallelMoE``.
+
+    Every rank calls ``forward`` the same number of times (each call holds two device barriers); token counts may
+    differ between ranks and between calls up to the capacity the group agreed on at the first call (the largest
+    count of any rank then, or ``n_tokens``).  A call above that capacity re-allocates the peer buffers with a
+    collective, so it has to happen on every rank in the same call: pass ``n_tokens`` = the largest count that
+    will ever occur when the ranks' counts grow independently."""
 
     MARKS = ("start", "route", "dispatch", "received", "experts", "partial", "returned", "sum")
 
